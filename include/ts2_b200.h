@@ -1,0 +1,259 @@
+/*
+ * ts2_b200.h — C ABI of the B200 (sm_100a) training-backward engine.
+ *
+ * The library behind this header replaces the compute backend that the
+ * TScale2 trainer reaches through IModel / IModelInstance
+ * (src/gpt/compute/model.h:22-56) and the factory CreateLocalTransformer
+ * (src/gpt/compute/model.h:141).  Everything is plain pointers and sizes; all
+ * host arrays are caller-owned and are copied before the call returns.
+ *
+ * Conventions
+ *  - every matrix is row-major fp32 [y_size = out][x_size = in], the shapes
+ *    and the order are those of TModelDescr::EnumLayerMatrices
+ *    (src/gpt/model_params/model_dim.h:219-258): index 0 = embedding
+ *    [label_count][dim], 1 = final layer [output_token_count][dim], then for
+ *    each layer in order its matrices (ATT: Q,K,V,Gate,Combiner; FFN:
+ *    Expand,Gate,Contract; MOE: Expand,Gate,Contract,Select).
+ *  - "gradient" is the ascent direction the reference back-propagates
+ *    (onehot - p, src/gpt/compute/cpu_transformer.cpp:146-156); the optimizer
+ *    adds rate * normalized gradient.
+ *  - every function returns TS2_OK or a negative error code; nothing aborts
+ *    (the reference aborts through Y_VERIFY; return codes are the one
+ *    deliberate difference).  ts2_last_error() gives the message.
+ *  - there is no CPU fallback: without a CUDA device ts2_create fails with
+ *    TS2_ERR_NO_DEVICE.
+ */
+#ifndef TS2_B200_H
+#define TS2_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TS2_OK 0
+#define TS2_ERR_INVALID_ARG (-1)
+#define TS2_ERR_NO_DEVICE (-2)
+#define TS2_ERR_CUDA (-3)
+#define TS2_ERR_UNSUPPORTED (-4)
+#define TS2_ERR_TOO_LARGE (-5)
+#define TS2_ERR_TIMEOUT (-6)
+#define TS2_ERR_COMM (-7)
+#define TS2_ERR_DEVICE_STATUS (-8)
+
+/* ELayerType, src/gpt/model_params/model_dim.h:56-61 */
+#define TS2_LAYER_ATT 0
+#define TS2_LAYER_ATT_3LIN 1 /* RNN variant: rejected with TS2_ERR_UNSUPPORTED */
+#define TS2_LAYER_FFN 2
+#define TS2_LAYER_MOE 3
+
+/* subset of the MPF_* model flags that changes the backward pass,
+ * src/gpt/model_params/model_dim.h:35-53 */
+#define TS2_MPF_DISABLE_TUNE_EMBED 0x8ull
+#define TS2_MPF_DISABLE_TUNE_FINAL_LAYER 0x4000ull
+#define TS2_MPF_DISABLE_TUNE_LAYERS 0x8000ull
+
+/* arithmetic of the contractions; the reference selects this at compile time
+ * in src/gpt/compute/cfg_precision.h:18-46 */
+#define TS2_PREC_FP8 0  /* e4m3 operands, fp32 accumulate (reference "fp8 matmul" block) */
+#define TS2_PREC_F16 1  /* fp16 operands, fp32 accumulate (reference "fp16 matmul" block) */
+#define TS2_PREC_INT8 2 /* int8 operands, int32 accumulate (op-level GEMM only) */
+
+/* ts2_backprop add_to_model; EAddToModel, src/gpt/matrix/base_host.h:20-23 */
+#define TS2_GRADIENT_ACCUMULATE 0
+#define TS2_GRADIENT_APPLY 1
+
+#define TS2_LABEL_NEGATIVE 0x80000000u /* src/gpt/att/nodes_batch.h:6 */
+#define TS2_LABEL_MASK 0x7fffffffu
+
+/* TModelDescr::TLayerParams, src/gpt/model_params/model_dim.h:159-168 */
+typedef struct ts2_layer_params {
+    int32_t layer_type;
+    float alibi_slope;
+    int32_t attention_type_id;
+} ts2_layer_params;
+
+/* TModelDims + TModelDescr, src/gpt/model_params/model_dim.h:118-180.
+ * q_dim and tt_dim must be 128 (cfg_precision.h:79-80), dim a multiple of 128. */
+typedef struct ts2_model_descr {
+    int32_t dim;
+    int32_t q_dim;
+    int32_t tt_dim;
+    int32_t head_count;
+    int32_t ffn_tiles; /* FFN width = 128 * ffn_tiles */
+    int32_t expert_dim;
+    int32_t moe_expert_count;
+    int32_t moe_selected;
+    int32_t label_count;        /* embedding rows */
+    int32_t output_token_count; /* final layer rows (vocabulary) */
+    int32_t attention_type_count;
+    int32_t layer_count;
+    const ts2_layer_params *layers;
+    uint64_t flags;
+    int32_t precision; /* TS2_PREC_FP8 or TS2_PREC_F16 */
+    int32_t reserved;
+} ts2_model_descr;
+
+typedef struct ts2_matrix_view {
+    float *data;    /* row-major, row stride = x_size */
+    int64_t x_size; /* input width */
+    int64_t y_size; /* output width */
+} ts2_matrix_view;
+
+/* TAttentionInfo, src/gpt/att/att.h:22-49: CSR list of inclusive [start,finish]
+ * spans per node.  The engine accepts at most one span per node, which is what
+ * the trainer generates (src/gpt/att/sliding_window.cpp:113-118,213-224). */
+typedef struct ts2_attention_info {
+    const int32_t *span_start;
+    const int32_t *span_finish;
+    const int32_t *span_ptr; /* node_count + 1 */
+} ts2_attention_info;
+
+/* TBatchNodes, src/gpt/att/nodes_batch.h:36-49 */
+typedef struct ts2_batch_nodes {
+    int32_t node_count;
+    const uint32_t *label_arr; /* top bit = negative sign */
+    const uint32_t *label_ptr; /* node_count + 1 */
+    int32_t target_count;
+    const int32_t *target_node;
+    const int32_t *target_id;
+    int32_t attention_type_count;
+    const ts2_attention_info *att;
+} ts2_batch_nodes;
+
+/* TTrainingStep, src/gpt/train_config/train_step.h:4-26 */
+typedef struct ts2_training_step {
+    float rate;
+    float l2reg;
+    float beta1;
+    float weight0;
+    float weight1;
+    float disp_decay;
+} ts2_training_step;
+
+typedef struct ts2_model ts2_model;
+
+/* ------------------------------------------------------------------------- */
+/* model life cycle: CreateLocalTransformer, src/gpt/compute/model.cu:257-264 */
+
+/* Number of matrices (2 + per-layer) and their shapes for a description. */
+int ts2_matrix_count(const ts2_model_descr *descr);
+int ts2_matrix_shape(const ts2_model_descr *descr, int index, int64_t *x_size, int64_t *y_size);
+
+/* mats: fp32 master weights in the order above; bias: output_token_count floats
+ * (may be NULL = zeros).  device: CUDA ordinal this process drives (one process
+ * per GPU).  max_nodes: capacity in nodes (tokens) per step. */
+int ts2_create(const ts2_model_descr *descr, const ts2_matrix_view *mats, int n_mats, const float *bias,
+               int device, int max_nodes, ts2_model **out);
+void ts2_destroy(ts2_model *m);
+const char *ts2_last_error(const ts2_model *m); /* m may be NULL: last create error */
+
+/* IModelInstance::GetNodes + Init(INIT_BACKPROP), src/gpt/compute/model.h:32-35;
+ * TSinlgeComputeContext::Init, src/gpt/compute/gpu_transformer.cu:526-566 */
+int ts2_set_batch(ts2_model *m, const ts2_batch_nodes *nodes);
+/* same, with the batch already in pinned host memory prepared by the caller
+ * for repeated steps (no semantic difference) */
+
+/* IModel::Backprop, src/gpt/compute/model.h:53 — asynchronous: enqueues the
+ * forward pass, the backward pass and (TS2_GRADIENT_APPLY) the gradient
+ * reduction + optimizer + requantization. */
+int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model);
+/* IModel::WaitAllCompute, src/gpt/compute/model.h:54 — bounded wait */
+int ts2_wait(ts2_model *m);
+/* IModelInstance::ComputeScore, src/gpt/compute/model.h:39: mean log p(target) (natural log) */
+int ts2_forward_score(ts2_model *m, float *out_score);
+/* IModel::GetAvrgTrainErr, src/gpt/compute/model.h:55: mean -log p(target) of the last backprop */
+int ts2_avg_train_err(ts2_model *m, float *out_err);
+
+/* IModel::GetParams / SetParams, src/gpt/compute/model.h:48-49.  what selects
+ * the per-matrix tensor: master weights, momentum (Grad1), or the raw fp32
+ * weight gradient of the last ts2_backprop (the tap the parity tests read:
+ * the tensor the reference hands to HostApplyDelta,
+ * src/gpt/compute/cpu_util.h:86-95). */
+#define TS2_PARAM_WEIGHTS 0
+#define TS2_PARAM_MOMENTUM 1
+#define TS2_PARAM_GRADIENT 2
+int ts2_get_params(ts2_model *m, int what, ts2_matrix_view *mats_out, int n_mats);
+int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_mats);
+/* RowDisp / SumWeight of a matrix (TModelMatrix, src/gpt/model_params/model_matrix.h:61-70) */
+int ts2_get_row_disp(ts2_model *m, int index, float *row_disp, int64_t n, float *sum_weight);
+/* quantized weights as the contractions see them: bytes (e4m3) or halves,
+ * [y][x], and the per-matrix scale sko (src/gpt/matrix/agpu_cuda.cuh:63-101) */
+int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, float *matrix_scale);
+
+/* debugging / parity taps: fp32 residual state entering layer `layer`
+ * (layer == layer_count: after the last layer) and the state gradient at the
+ * same boundary captured during the last ts2_backprop (enabled by
+ * ts2_set_debug_taps before the call; costs one copy per layer). */
+int ts2_set_debug_taps(ts2_model *m, int enable);
+int ts2_get_state_tap(ts2_model *m, int layer, int gradient, float *dst, int64_t n_floats);
+
+/* ------------------------------------------------------------------------- */
+/* data-parallel gradient reduction; replaces TMultiDeviceReducer::AllReduce,
+ * src/lib/cuda/multi_device_buf.cu:193-265, called from
+ * TAgpuCudaModelMatrix::ApplyGradientImpl, src/gpt/matrix/agpu_cuda.cuh:484-500.
+ * One process per GPU; rank 0 creates the 128-byte id and the host shares it. */
+#define TS2_COMM_ID_BYTES 128
+int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES]);
+int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_COMM_ID_BYTES]);
+
+/* counters for the bench: kernels of this library launched since the last reset */
+int64_t ts2_launch_count(ts2_model *m, int reset);
+/* device time of the last ts2_backprop in ms (CUDA events on the engine's stream) */
+int ts2_last_step_ms(ts2_model *m, float *ms);
+/* average duration (ms) and launch count of the contraction kernel over the
+ * steps since the last reset, measured with CUDA events on the engine's stream
+ * when profiling is enabled (adds a pair of events per launch) */
+int ts2_set_kernel_timing(ts2_model *m, int enable);
+int ts2_get_kernel_timing(ts2_model *m, int reset, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total);
+
+/* ------------------------------------------------------------------------- */
+/* operator-level entry points (device pointers unless named host_*); these
+ * are the pieces ts2_backprop is built from, exported for the parity tests
+ * and micro-benchmarks.  stream is a cudaStream_t passed as void*. */
+
+int ts2_device_count(void);
+int ts2_dev_alloc(int device, size_t bytes, void **ptr);
+int ts2_dev_free(int device, void *ptr);
+int ts2_dev_upload(int device, void *dst, const void *host_src, size_t bytes);
+int ts2_dev_download(int device, void *host_dst, const void *src, size_t bytes);
+int ts2_dev_memset(int device, void *dst, int value, size_t bytes);
+int ts2_dev_sync(int device);
+
+/* C[M][N] (+)= alpha * A[M][K] · B[N][K]^T — both operands K-contiguous.
+ * Replaces Fp8MatMul / Int8MatMul / Fp16MatMul (src/lib/cuda/cuda_fp8.cuh:123-228,
+ * cuda_i8.cuh:157-260, cuda_fp16.cuh:49-164).  prec: TS2_PREC_*; out_kind:
+ * TS2_OUT_*; row_scale[M] / col_scale[N] optional fp32 factors applied in the
+ * epilogue (TStoreScaled, Int8MatMulKernelRowScale).  M, N, K multiples of 128
+ * (MM_TILE, src/lib/cuda/cuda_matmul.cuh:10). */
+#define TS2_OUT_F32 0
+#define TS2_OUT_F32_ADD 1 /* C += result */
+#define TS2_OUT_F16 2
+#define TS2_OUT_BF16 3
+int ts2_gemm_tn(int device, void *stream, int prec, int out_kind, int64_t M, int64_t N, int64_t K, const void *A,
+                int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc, float alpha, const float *row_scale,
+                const float *col_scale);
+
+/* dX = dY[T][out] · W[out][in]  (MulBackwardWithAccum without the accumulate,
+ * src/gpt/compute/cpu_util.cpp:30-47; TMatMulBuffers::Backprop,
+ * src/gpt/compute/layer_cuda_base.cuh:238-250).  Wt is W stored transposed
+ * [in][out] as the requantizer keeps it. */
+int ts2_gemm_dx(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                const void *dY, const void *Wt, void *dX, float alpha, const float *row_scale,
+                const float *col_scale);
+
+/* dW[out][in] (+)= alpha * dY[T][out]^T · X[T][in]  (SumRankOne,
+ * src/gpt/compute/cpu_util.cpp:50-67; TMatMulBuffers::BackpropDelta,
+ * src/gpt/compute/matmul_fwdbwd.cuh:149-162).  Both operands are token-major;
+ * the contraction dimension T is split over the SMs and the partial tiles are
+ * reduced through `workspace` (ts2_gemm_dw_workspace_bytes). */
+size_t ts2_gemm_dw_workspace_bytes(int64_t T, int64_t in_dim, int64_t out_dim);
+int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                const void *dY, const void *X, void *dW, float alpha, void *workspace, size_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
