@@ -119,8 +119,14 @@ def _declare(lib):
         "ts2_gemm_dw_workspace_bytes": (C.c_size_t, [i64, i64, i64]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),
     }
+    missing = []
     for name, (res, args) in sig.items():
-        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            missing.append(name)
+            continue
         fn.restype = res
         fn.argtypes = args
     lib._ts2_signatures = sig
+    lib._ts2_missing = missing  # tests assert this is empty

@@ -1,0 +1,69 @@
+// Library-wide state: last error, launch counter, per-device status word.
+#include "common.cuh"
+#include <cstdarg>
+#include <mutex>
+
+namespace ts2 {
+
+thread_local std::string g_last_error;
+std::atomic<long long> g_launch_count{0};
+static std::string g_global_error; // last error of any thread, for ts2_last_error(NULL)
+static std::mutex g_err_mu;
+
+int fail(int code, const char *fmt, ...)
+{
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    {
+        std::lock_guard<std::mutex> lk(g_err_mu);
+        g_global_error = buf;
+    }
+    return code;
+}
+
+const char *global_error()
+{
+    std::lock_guard<std::mutex> lk(g_err_mu);
+    static thread_local std::string copy;
+    copy = g_global_error;
+    return copy.c_str();
+}
+
+int sm_count(int device)
+{
+    static int cached[16] = {};
+    int &c = cached[device & 15];
+    if (c == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0)
+            v = 148;
+        c = v;
+    }
+    return c;
+}
+
+int32_t *device_status_word(int device)
+{
+    static int32_t *words[16] = {};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    int32_t *&w = words[device & 15];
+    if (!w) {
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(device);
+        if (cudaMalloc(&w, 256) != cudaSuccess) {
+            w = nullptr;
+        } else {
+            cudaMemset(w, 0, 256);
+        }
+        cudaSetDevice(prev);
+    }
+    return w;
+}
+
+} // namespace ts2

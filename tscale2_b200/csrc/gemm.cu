@@ -1,0 +1,682 @@
+// Persistent warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   warp 0      : TMA producer — cp.async.bulk.tensor (no multicast) into a ring of
+//                 128B-swizzled shared-memory stages, completion on mbarriers
+//   warp 1      : allocates TMEM, issues tcgen05.mma (one elected thread), releases
+//                 stages and publishes accumulators with tcgen05.commit
+//   warps 2..5  : epilogue — tcgen05.ld the fp32/int32 accumulator (128 lanes x BN
+//                 columns) out of TMEM, apply scales, convert, store
+// Two TMEM accumulators (2 x BN columns) let the epilogue of one tile overlap the
+// main loop of the next.  Work units are (tile, K-split); partial tiles of split
+// units go to an fp32 workspace and are combined by reduce_splitk_kernel in a fixed
+// order (deterministic, no atomics).
+//
+// It replaces the mma.sync kernels of the reference: Fp8MatMul
+// (src/lib/cuda/cuda_fp8.cuh:123-228), Int8MatMulKernel* (src/lib/cuda/cuda_i8.cuh:157-320),
+// Fp16MatMul (src/lib/cuda/cuda_fp16.cuh:49-164), and, because the dW operands are read
+// token-major through MN-major shared-memory descriptors, also the per-step transposes
+// (src/gpt/compute/matmul_fwdbwd.cuh:149-162,169-280).
+#include "gemm.cuh"
+#include <cuda.h>
+#include <vector>
+#include <mutex>
+
+namespace ts2 {
+
+static constexpr int BM = 128;
+static constexpr int STAGE_ROW_BYTES = 128; // one swizzle row
+static constexpr int NUM_THREADS = 192;
+
+struct GemmParams {
+    int M, N;
+    int m_tiles, n_tiles, splits;
+    int k_blocks;      // total K blocks (one block = one pipeline stage)
+    int kb_per_split;
+    uint32_t idesc;
+    void *C;
+    long long ldc;
+    float alpha;
+    const float *dyn_scale, *dyn_scale2, *row_scale, *col_scale;
+    int out_kind;
+    float *workspace;
+    int32_t *status;
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46; // descriptor version of sm_100
+    d |= 2ull << 61; // 128-byte swizzle
+    return d;
+}
+
+template <int MMA>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (MMA == 0) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                     : "memory");
+    } else if constexpr (MMA == 1) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                     : "memory");
+    } else {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                     : "memory");
+    }
+}
+
+template <int BN>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * STAGE_ROW_BYTES;
+    static constexpr int B_BYTES = BN * STAGE_ROW_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // barriers + alignment slack
+};
+
+// ES: element size in bytes; MMA: 0 = f8f6f4, 1 = f16 (fp16/bf16), 2 = i8; MN: operand layout
+template <int BN, int ES, int MMA, bool MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+{
+    using L = SmemLayout<BN>;
+    constexpr int STAGES = L::STAGES;
+    constexpr int ELEMS_PER_ROW = STAGE_ROW_BYTES / ES; // elements in one 128-byte swizzle row
+    constexpr int UMMA_K = 32 / ES;                     // elements per MMA along K
+    constexpr int K_STEPS = 4;                          // MMAs per stage
+    constexpr int BK = MN ? (UMMA_K * K_STEPS) : ELEMS_PER_ROW; // K elements per stage (equal in both layouts)
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = (uint64_t *)(smem + L::BAR_OFFSET);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull0 = smem_u32(bars + 2 * STAGES),
+                   tempty0 = smem_u32(bars + 2 * STAGES + 2), drain = smem_u32(bars + 2 * STAGES + 4);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 5);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull0 + 8 * a, 1);
+            mbar_init(tempty0 + 8 * a, 4);
+        }
+        mbar_init(drain, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int units = tiles * p.splits;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const int tile = u / p.splits, split = u - tile * p.splits;
+                const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = full0 + 8 * stage;
+                    mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES), sb = sa + L::A_BYTES;
+                    const int k0 = kb * BK;
+                    if constexpr (!MN) {
+                        tma_load_2d(sa, &tmA, fb, k0, m0);
+                        tma_load_2d(sb, &tmB, fb, k0, n0);
+                    } else {
+                        // one box per 128-byte atom along M / N, each BK rows of the token-major operand
+#pragma unroll
+                        for (int j = 0; j < BM / ELEMS_PER_ROW; ++j)
+                            tma_load_2d(sa + j * BK * STAGE_ROW_BYTES, &tmA, fb, m0 + j * ELEMS_PER_ROW, k0);
+#pragma unroll
+                        for (int j = 0; j < BN / ELEMS_PER_ROW; ++j)
+                            tma_load_2d(sb + j * BK * STAGE_ROW_BYTES, &tmB, fb, n0 + j * ELEMS_PER_ROW, k0);
+                    }
+                    ++issued;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                // abort path: wait (bounded) for the copies still in flight before the CTA gives its
+                // shared memory back.  The last min(issued, STAGES) stages may have pending copies.
+                int s = stage;
+                uint32_t ph = phase;
+                for (int i = 0; i < min(issued, STAGES); ++i) {
+                    if (--s < 0) {
+                        s = STAGES - 1;
+                        ph ^= 1;
+                    }
+                    long long t0 = clock64();
+                    while (!mbar_try_wait(full0 + 8 * s, ph) && clock64() - t0 < 200000000ll) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const int tile = u / p.splits, split = u - tile * p.splits;
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag))
+                    break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES), sb = sa + L::A_BYTES;
+                    uint64_t adesc, bdesc;
+                    uint32_t step;
+                    if constexpr (!MN) {
+                        adesc = make_smem_desc(sa, 16, 1024);
+                        bdesc = make_smem_desc(sb, 16, 1024);
+                        step = (UMMA_K * ES) >> 4; // 32 bytes along the swizzle row
+                    } else {
+                        adesc = make_smem_desc(sa, BK * STAGE_ROW_BYTES, 1024);
+                        bdesc = make_smem_desc(sb, BK * STAGE_ROW_BYTES, 1024);
+                        step = (UMMA_K * STAGE_ROW_BYTES) >> 4; // UMMA_K token rows
+                    }
+#pragma unroll
+                    for (int k = 0; k < K_STEPS; ++k)
+                        umma<MMA>(tmem_d, adesc + (uint64_t)(k * step), bdesc + (uint64_t)(k * step), p.idesc,
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * stage);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok)
+                    tc_commit(tfull0 + 8 * acc);
+                acc ^= 1;
+                if (acc == 0)
+                    acc_phase ^= 1;
+            }
+            // every MMA issued so far has completed once this commit arrives
+            tc_commit(drain);
+            long long t0 = clock64();
+            while (!mbar_try_wait(drain, 0) && clock64() - t0 < 1500000000ll) {
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quarter = warp & 3; // TMEM lanes this warp may read: [32*quarter, +32)
+        float alpha = p.alpha;
+        if (p.dyn_scale)
+            alpha *= __ldg(p.dyn_scale);
+        if (p.dyn_scale2)
+            alpha *= __ldg(p.dyn_scale2);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const int tile = u / p.splits;
+            const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag))
+                break;
+            tc_fence_after();
+            const int row_in_tile = quarter * 32 + lane;
+            const long long row = m0 + row_in_tile;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            float rs = 1.f;
+            if (p.splits == 1 && p.row_scale && row < p.M)
+                rs = __ldg(p.row_scale + row);
+            rs *= alpha;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int col = n0 + c * 32;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    v[i] = (MMA == 2) ? (float)(int)r[i] : __uint_as_float(r[i]);
+                if (p.splits > 1) {
+                    float4 *dst = (float4 *)(p.workspace + ((size_t)u * BM + row_in_tile) * BN + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    continue;
+                }
+                if (row >= p.M || col >= p.N)
+                    continue;
+                if (p.col_scale) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float4 cs = __ldg((const float4 *)(p.col_scale + col) + i);
+                        v[4 * i] *= cs.x * rs;
+                        v[4 * i + 1] *= cs.y * rs;
+                        v[4 * i + 2] *= cs.z * rs;
+                        v[4 * i + 3] *= cs.w * rs;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] *= rs;
+                }
+                if (p.out_kind == TS2_OUT_F32 || p.out_kind == TS2_OUT_F32_ADD) {
+                    float4 *dst = (float4 *)((float *)p.C + row * p.ldc + col);
+                    if (p.out_kind == TS2_OUT_F32_ADD) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float4 o = dst[i];
+                            dst[i] = make_float4(o.x + v[4 * i], o.y + v[4 * i + 1], o.z + v[4 * i + 2], o.w + v[4 * i + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                } else if (p.out_kind == TS2_OUT_F16) {
+                    uint4 *dst = (uint4 *)((__half *)p.C + row * p.ldc + col);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
+                                h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                        dst[i] = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                    }
+                } else {
+                    uint4 *dst = (uint4 *)((__nv_bfloat16 *)p.C + row * p.ldc + col);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]),
+                                       h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]),
+                                       h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]),
+                                       h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                        dst[i] = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tempty0 + 8 * acc);
+            acc ^= 1;
+            if (acc == 0)
+                acc_phase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicOr(p.status, TS2_STATUS_WAIT_TIMEOUT);
+}
+
+// Sums the K-split partial tiles in split order and applies the epilogue.
+template <int BN>
+__global__ void reduce_splitk_kernel(const GemmParams p)
+{
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int vec_per_tile = BM * BN / 4;
+    const long long total = (long long)tiles * vec_per_tile;
+    float alpha = p.alpha;
+    if (p.dyn_scale)
+        alpha *= __ldg(p.dyn_scale);
+    if (p.dyn_scale2)
+        alpha *= __ldg(p.dyn_scale2);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int tile = (int)(i / vec_per_tile), e = (int)(i % vec_per_tile);
+        const int r = e / (BN / 4), c = (e % (BN / 4)) * 4;
+        const long long row = (long long)(tile % p.m_tiles) * BM + r;
+        const int col = (tile / p.m_tiles) * BN + c;
+        if (row >= p.M || col >= p.N)
+            continue;
+        float4 s = make_float4(0, 0, 0, 0);
+        for (int sp = 0; sp < p.splits; ++sp) {
+            float4 v = *(const float4 *)(p.workspace + ((size_t)(tile * p.splits + sp) * BM + r) * BN + c);
+            s.x += v.x;
+            s.y += v.y;
+            s.z += v.z;
+            s.w += v.w;
+        }
+        float rs = alpha * (p.row_scale ? __ldg(p.row_scale + row) : 1.f);
+        float4 cs = p.col_scale ? __ldg((const float4 *)(p.col_scale + col)) : make_float4(1, 1, 1, 1);
+        s.x *= rs * cs.x;
+        s.y *= rs * cs.y;
+        s.z *= rs * cs.z;
+        s.w *= rs * cs.w;
+        if (p.out_kind == TS2_OUT_F32) {
+            *(float4 *)((float *)p.C + row * p.ldc + col) = s;
+        } else if (p.out_kind == TS2_OUT_F32_ADD) {
+            float4 *d = (float4 *)((float *)p.C + row * p.ldc + col);
+            float4 o = *d;
+            *d = make_float4(o.x + s.x, o.y + s.y, o.z + s.z, o.w + s.w);
+        } else if (p.out_kind == TS2_OUT_F16) {
+            __half2 a = __floats2half2_rn(s.x, s.y), b = __floats2half2_rn(s.z, s.w);
+            *(uint2 *)((__half *)p.C + row * p.ldc + col) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(s.x, s.y), b = __floats2bfloat162_rn(s.z, s.w);
+            *(uint2 *)((__nv_bfloat16 *)p.C + row * p.ldc + col) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 2-D map over a row-major [rows][ld] array of es-byte elements; box = 128 bytes x box_rows
+static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn)
+        return fail(TS2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    if (((uintptr_t)base & 15) || ((ld * es) & 15))
+        return fail(TS2_ERR_INVALID_ARG, "operand base and row pitch must be multiples of 16 bytes");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld * es)};
+    cuuint32_t box[2] = {(cuuint32_t)(STAGE_ROW_BYTES / es), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = (es == 1) ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    CUresult r = fn(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TS2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TS2_OK;
+}
+
+static int elem_size(int kind) { return (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1; }
+
+static uint32_t instr_desc(int kind, bool mn, int bn)
+{
+    uint32_t c_fmt, ab_fmt;
+    switch (kind) {
+    case KIND_E4M3: c_fmt = 1; ab_fmt = 0; break; // f32 accumulate, e4m3
+    case KIND_F16: c_fmt = 1; ab_fmt = 0; break;  // f16
+    case KIND_BF16: c_fmt = 1; ab_fmt = 1; break; // bf16
+    default: c_fmt = 2; ab_fmt = 1; break;        // s32 accumulate, s8
+    }
+    uint32_t d = 0;
+    d |= c_fmt << 4;
+    d |= ab_fmt << 7;
+    d |= ab_fmt << 10;
+    d |= (mn ? 1u : 0u) << 15; // A is MN-major
+    d |= (mn ? 1u : 0u) << 16; // B is MN-major
+    d |= (uint32_t)(bn >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+static int pick_bn(int64_t N) { return (N % 256 == 0 || N > 1024) ? 256 : 128; }
+
+struct Plan {
+    int bn, m_tiles, n_tiles, k_blocks, splits, kb_per_split, grid;
+};
+
+static Plan make_plan(int device, int kind, bool mn, int64_t M, int64_t N, int64_t K)
+{
+    Plan pl;
+    const int es = elem_size(kind);
+    const int bk = STAGE_ROW_BYTES / es;
+    pl.bn = pick_bn(N);
+    pl.m_tiles = (int)ceil_div(M, BM);
+    pl.n_tiles = (int)ceil_div(N, pl.bn);
+    pl.k_blocks = (int)ceil_div(K, bk);
+    const int sms = sm_count(device);
+    const int tiles = pl.m_tiles * pl.n_tiles;
+    int splits = 1;
+    if (tiles * 2 <= sms) { // fewer than half the SMs would have work: split K
+        splits = sms / tiles;
+        splits = std::min(splits, std::max(1, pl.k_blocks / 8)); // keep at least 8 K blocks per unit
+    }
+    pl.kb_per_split = (int)ceil_div(pl.k_blocks, splits);
+    pl.splits = (int)ceil_div(pl.k_blocks, pl.kb_per_split);
+    pl.grid = std::min(sms, tiles * pl.splits);
+    return pl;
+}
+
+int gemm_splits(int device, int kind, bool mn, int64_t M, int64_t N, int64_t K) { return make_plan(device, kind, mn, M, N, K).splits; }
+
+size_t gemm_workspace_bytes(int device, int kind, bool mn, int64_t M, int64_t N, int64_t K)
+{
+    Plan pl = make_plan(device, kind, mn, M, N, K);
+    if (pl.splits == 1)
+        return 0;
+    return (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float);
+}
+
+// ---- timing ----------------------------------------------------------------------
+static std::mutex g_time_mu;
+static bool g_time_on = false;
+struct TimedLaunch {
+    cudaEvent_t a, b;
+    double flops;
+};
+static std::vector<TimedLaunch> g_timed;
+static std::vector<cudaEvent_t> g_event_pool;
+static double g_ms_total = 0, g_flops_total = 0;
+static long long g_timed_launches = 0;
+
+void gemm_timing_enable(bool on)
+{
+    std::lock_guard<std::mutex> lk(g_time_mu);
+    g_time_on = on;
+}
+
+static void timing_collect_locked()
+{
+    for (auto &t : g_timed) {
+        if (cudaEventSynchronize(t.b) == cudaSuccess) {
+            float ms = 0;
+            if (cudaEventElapsedTime(&ms, t.a, t.b) == cudaSuccess) {
+                g_ms_total += ms;
+                g_flops_total += t.flops;
+                ++g_timed_launches;
+            }
+        }
+        g_event_pool.push_back(t.a);
+        g_event_pool.push_back(t.b);
+    }
+    g_timed.clear();
+}
+
+void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total)
+{
+    std::lock_guard<std::mutex> lk(g_time_mu);
+    timing_collect_locked();
+    if (ms_total)
+        *ms_total = g_ms_total;
+    if (launches)
+        *launches = g_timed_launches;
+    if (flops_total)
+        *flops_total = g_flops_total;
+    if (reset) {
+        g_ms_total = g_flops_total = 0;
+        g_timed_launches = 0;
+    }
+}
+
+static cudaEvent_t pooled_event()
+{
+    if (!g_event_pool.empty()) {
+        cudaEvent_t e = g_event_pool.back();
+        g_event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+template <int BN, int ES, int MMA, bool MN>
+static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p)
+{
+    auto kern = gemm_kernel<BN, ES, MMA, MN>;
+    static bool configured[16] = {};
+    if (!configured[a.device & 15]) {
+        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL));
+        configured[a.device & 15] = true;
+    }
+    kern<<<pl.grid, NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, p);
+    TS2_CHECK_LAUNCH();
+    if (pl.splits > 1) {
+        const long long total = (long long)pl.m_tiles * pl.n_tiles * BM * BN / 4;
+        int blocks = (int)std::min<long long>(ceil_div(total, 256), 4 * sm_count(a.device));
+        reduce_splitk_kernel<BN><<<blocks, 256, 0, a.stream>>>(p);
+        TS2_CHECK_LAUNCH();
+    }
+    return TS2_OK;
+}
+
+int gemm(const GemmArgs &a)
+{
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "gemm: empty problem (M=%lld N=%lld K=%lld)", (long long)a.M, (long long)a.N, (long long)a.K);
+    if (a.N % 32)
+        return fail(TS2_ERR_INVALID_ARG, "gemm: N must be a multiple of 32 (N=%lld)", (long long)a.N);
+    if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31))
+        return fail(TS2_ERR_TOO_LARGE, "gemm: dimension exceeds 2^31");
+    const int es = elem_size(a.kind);
+    const int out_es = (a.epi.out_kind == TS2_OUT_F32 || a.epi.out_kind == TS2_OUT_F32_ADD) ? 4 : 2;
+    if (((uintptr_t)a.C & 15) || ((a.ldc * out_es) & 15))
+        return fail(TS2_ERR_INVALID_ARG, "gemm: output base and pitch must be multiples of 16 bytes");
+    if (a.epi.col_scale && ((uintptr_t)a.epi.col_scale & 15))
+        return fail(TS2_ERR_INVALID_ARG, "gemm: col_scale must be 16-byte aligned");
+    TS2_CUDA(cudaSetDevice(a.device));
+    Plan pl = make_plan(a.device, a.kind, a.mn_major, a.M, a.N, a.K);
+    if (pl.splits > 1) {
+        size_t need = (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float);
+        if (!a.workspace || a.workspace_bytes < need)
+            return fail(TS2_ERR_INVALID_ARG, "gemm: split-K needs %zu workspace bytes, got %zu", need, a.workspace_bytes);
+    }
+    CUtensorMap tmA, tmB;
+    const int bk = STAGE_ROW_BYTES / es;
+    int rc;
+    if (!a.mn_major) {
+        if ((rc = make_tmap(&tmA, a.A, es, a.K, a.M, a.lda, BM)) != TS2_OK)
+            return rc;
+        if ((rc = make_tmap(&tmB, a.B, es, a.K, a.N, a.ldb, pl.bn)) != TS2_OK)
+            return rc;
+    } else {
+        if ((rc = make_tmap(&tmA, a.A, es, a.M, a.K, a.lda, bk)) != TS2_OK)
+            return rc;
+        if ((rc = make_tmap(&tmB, a.B, es, a.N, a.K, a.ldb, bk)) != TS2_OK)
+            return rc;
+    }
+    GemmParams p;
+    p.M = (int)a.M;
+    p.N = (int)a.N;
+    p.m_tiles = pl.m_tiles;
+    p.n_tiles = pl.n_tiles;
+    p.splits = pl.splits;
+    p.k_blocks = pl.k_blocks;
+    p.kb_per_split = pl.kb_per_split;
+    p.idesc = instr_desc(a.kind, a.mn_major, pl.bn);
+    p.C = a.C;
+    p.ldc = a.ldc;
+    p.alpha = a.epi.alpha;
+    p.dyn_scale = a.epi.dyn_scale;
+    p.dyn_scale2 = a.epi.dyn_scale2;
+    p.row_scale = a.epi.row_scale;
+    p.col_scale = a.epi.col_scale;
+    p.out_kind = a.epi.out_kind;
+    p.workspace = (float *)a.workspace;
+    p.status = device_status_word(a.device);
+    if (!p.status)
+        return fail(TS2_ERR_CUDA, "gemm: no device status word");
+
+    cudaEvent_t ea = nullptr, eb = nullptr;
+    bool timed;
+    {
+        std::lock_guard<std::mutex> lk(g_time_mu);
+        timed = g_time_on;
+        if (timed) {
+            ea = pooled_event();
+            eb = pooled_event();
+        }
+    }
+    if (timed)
+        cudaEventRecord(ea, a.stream);
+
+    const int mma = (a.kind == KIND_E4M3) ? 0 : (a.kind == KIND_I8 ? 2 : 1);
+#define TS2_GEMM_CASE(BN_, ES_, MMA_, MN_)                                   \
+    if (pl.bn == BN_ && es == ES_ && mma == MMA_ && a.mn_major == MN_)       \
+        rc = launch<BN_, ES_, MMA_, MN_>(a, pl, tmA, tmB, p);
+    rc = TS2_ERR_UNSUPPORTED;
+    TS2_GEMM_CASE(256, 1, 0, false)
+    TS2_GEMM_CASE(128, 1, 0, false)
+    TS2_GEMM_CASE(256, 1, 0, true)
+    TS2_GEMM_CASE(128, 1, 0, true)
+    TS2_GEMM_CASE(256, 2, 1, false)
+    TS2_GEMM_CASE(128, 2, 1, false)
+    TS2_GEMM_CASE(256, 2, 1, true)
+    TS2_GEMM_CASE(128, 2, 1, true)
+    TS2_GEMM_CASE(256, 1, 2, false)
+    TS2_GEMM_CASE(128, 1, 2, false)
+    TS2_GEMM_CASE(256, 1, 2, true)
+    TS2_GEMM_CASE(128, 1, 2, true)
+#undef TS2_GEMM_CASE
+    if (rc == TS2_ERR_UNSUPPORTED)
+        return fail(rc, "gemm: unsupported configuration");
+    if (timed) {
+        cudaEventRecord(eb, a.stream);
+        std::lock_guard<std::mutex> lk(g_time_mu);
+        g_timed.push_back({ea, eb, 2.0 * (double)a.M * (double)a.N * (double)a.K});
+    }
+    return rc;
+}
+
+} // namespace ts2

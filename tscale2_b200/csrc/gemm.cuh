@@ -1,0 +1,48 @@
+// Tensor-core contraction for sm_100a: C[M][N] = epilogue(sum_k A(m,k) * B(n,k)).
+// One persistent, warp-specialised kernel (gemm.cu) serves the forward, dX and dW
+// contractions of the training step.
+#pragma once
+#include "common.cuh"
+
+namespace ts2 {
+
+enum GemmKind { KIND_E4M3 = 0, KIND_F16 = 1, KIND_I8 = 2, KIND_BF16 = 3 };
+
+struct Epilogue {
+    float alpha = 1.f;
+    const float *dyn_scale = nullptr;  // device scalar multiplied in (loss-scale bookkeeping)
+    const float *dyn_scale2 = nullptr; // second device scalar
+    const float *row_scale = nullptr;  // [M] device
+    const float *col_scale = nullptr;  // [N] device
+    int out_kind = TS2_OUT_F32;
+};
+
+struct GemmArgs {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int kind = KIND_E4M3;
+    // false: A is [M][lda], B is [N][ldb], K contiguous (forward and dX)
+    // true : A is [K][lda] with M contiguous, B is [K][ldb] with N contiguous (dW: both operands token-major)
+    bool mn_major = false;
+    int64_t M = 0, N = 0, K = 0;
+    const void *A = nullptr;
+    int64_t lda = 0;
+    const void *B = nullptr;
+    int64_t ldb = 0;
+    void *C = nullptr;
+    int64_t ldc = 0;
+    Epilogue epi;
+    void *workspace = nullptr; // split-K partial tiles (fp32); needed when gemm_splits() > 1
+    size_t workspace_bytes = 0;
+};
+
+// number of K splits the scheduler will use for this shape (1 = no workspace needed)
+int gemm_splits(int device, int kind, bool mn_major, int64_t M, int64_t N, int64_t K);
+size_t gemm_workspace_bytes(int device, int kind, bool mn_major, int64_t M, int64_t N, int64_t K);
+int gemm(const GemmArgs &a);
+
+// accumulated device time of the contraction kernel (enabled by gemm_timing_enable)
+void gemm_timing_enable(bool on);
+void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total);
+
+} // namespace ts2
