@@ -203,6 +203,11 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
 int64_t ts2_launch_count(ts2_model *m, int reset);
 /* device time of the last ts2_backprop in ms (CUDA events on the engine's stream) */
 int ts2_last_step_ms(ts2_model *m, float *ms);
+/* a CUDA-event bracket on the engine's stream around any number of calls: ts2_timer_begin
+ * records the first event, ts2_timer_end records the second, waits for it and returns the
+ * elapsed device time in ms */
+int ts2_timer_begin(ts2_model *m);
+int ts2_timer_end(ts2_model *m, float *ms);
 /* average duration (ms) and launch count of the contraction kernel over the
  * steps since the last reset, measured with CUDA events on the engine's stream
  * when profiling is enabled (adds a pair of events per launch) */

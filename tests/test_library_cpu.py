@@ -1,0 +1,81 @@
+"""What can be checked of the CUDA library without a GPU: it loads, exports every symbol
+that include/ts2_b200.h declares, and refuses to run without a device (no CPU fallback)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from tscale2_b200 import capi, host
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(capi.LIB_PATH):
+        from tscale2_b200 import build
+        build.build()
+    return capi.load_library()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ts2_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ts2_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/ts2_b200.h but not exported"
+    assert not lib._ts2_missing
+    # and the ctypes table covers the header
+    assert set(names) == set(lib._ts2_signatures), set(names) ^ set(lib._ts2_signatures)
+
+
+def test_no_cpu_fallback(lib):
+    if lib.ts2_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    spec = host.ModelSpec(dim=128, head_count=1, ffn_tiles=1, vocab=128).add_blocks(1)
+    mats = host.init_weights(spec, 1)
+    descr, keep = spec.to_c()
+    h = C.c_void_p()
+    rc = lib.ts2_create(C.byref(descr), host.matrix_views(mats), len(mats), None, 0, 128, C.byref(h))
+    assert rc == capi.TS2_ERR_NO_DEVICE
+    assert b"no CPU fallback" in lib.ts2_last_error(None)
+
+
+def test_description_is_validated_without_a_device(lib):
+    spec = host.ModelSpec(dim=256, head_count=2, ffn_tiles=4, vocab=512).add_blocks(2)
+    descr, keep = spec.to_c()
+    assert lib.ts2_matrix_count(C.byref(descr)) == 2 + 2 * 8
+    x, y = C.c_int64(), C.c_int64()
+    for i, (yy, xx) in enumerate(spec.matrix_shapes()):
+        assert lib.ts2_matrix_shape(C.byref(descr), i, C.byref(x), C.byref(y)) == 0
+        assert (x.value, y.value) == (xx, yy)
+    bad = host.ModelSpec(dim=200, head_count=2, ffn_tiles=4, vocab=512).add_blocks(1)
+    d2, k2 = bad.to_c()
+    assert lib.ts2_matrix_count(C.byref(d2)) == capi.TS2_ERR_INVALID_ARG
+    d3, k3 = spec.to_c()
+    d3.q_dim = 64  # head dim 64 is not what the reference computes with (Q_DIM = 128)
+    assert lib.ts2_matrix_count(C.byref(d3)) == capi.TS2_ERR_UNSUPPORTED
+
+
+def test_host_batch_matches_reference_span_rule():
+    """[max(fragment start, t - width), t - 1] per node, none for the first node of a fragment."""
+    spec = host.ModelSpec(dim=128, head_count=1, ffn_tiles=1, vocab=64, attention_widths=[4, 1000])
+    b = host.synthetic_batch(spec, 2, 10, 3)
+    assert b.node_count == 20
+    s, f, p = b.att[0]
+    assert p[1] == 0 and p[2] == 1 and p[11] - p[10] == 0  # nodes 0 and 10 start fragments
+    assert (s[0], f[0]) == (0, 0)  # node 1 sees node 0
+    k = p[7]
+    assert (s[k], f[k]) == (3, 6)  # node 7, width 4
+    s, f, p = b.att[1]
+    k = p[15]
+    assert (s[k], f[k]) == (10, 14)
+    assert np.array_equal(b.label_arr[:3], b.target_id[:0].astype(np.uint32).tolist() + list(b.label_arr[:3]))
+    assert b.label_arr.max() <= spec.vocab and b.label_arr.min() >= 1

@@ -105,6 +105,8 @@ def _declare(lib):
         "ts2_comm_init": (i32, [vp, i32, i32, P(C.c_uint8)]),
         "ts2_launch_count": (i64, [vp, i32]),
         "ts2_last_step_ms": (i32, [vp, P(f32)]),
+        "ts2_timer_begin": (i32, [vp]),
+        "ts2_timer_end": (i32, [vp, P(f32)]),
         "ts2_set_kernel_timing": (i32, [vp, i32]),
         "ts2_get_kernel_timing": (i32, [vp, i32, P(C.c_double), P(i64), P(C.c_double)]),
         "ts2_device_count": (i32, []),

@@ -1,0 +1,105 @@
+// Device helpers shared by the bandwidth-bound kernels: 4-element vector access
+// for the operand formats of the contractions and the reference's scalar math.
+#pragma once
+#include "common.cuh"
+
+namespace ts2 {
+
+template <int FT>
+struct Fast;
+
+// e4m3 bytes, saturating round-to-nearest-even (activations and gradients)
+template <>
+struct Fast<0> {
+    static constexpr int SIZE = 1;
+    static __device__ __forceinline__ void store4(void *base, size_t idx, float4 v)
+    {
+        __nv_fp8x4_e4m3 p(v);
+        *(uint32_t *)((uint8_t *)base + idx) = p.__x;
+    }
+    static __device__ __forceinline__ float4 load4(const void *base, size_t idx)
+    {
+        uint32_t raw = *(const uint32_t *)((const uint8_t *)base + idx);
+        __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(raw & 0xffff), __NV_E4M3);
+        __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(raw >> 16), __NV_E4M3);
+        float2 a = __half22float2(*(__half2 *)&lo), b = __half22float2(*(__half2 *)&hi);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+template <>
+struct Fast<1> {
+    static constexpr int SIZE = 2;
+    static __device__ __forceinline__ void store4(void *base, size_t idx, float4 v)
+    {
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        *(uint2 *)((__half *)base + idx) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+    }
+    static __device__ __forceinline__ float4 load4(const void *base, size_t idx)
+    {
+        uint2 raw = *(const uint2 *)((const __half *)base + idx);
+        float2 a = __half22float2(*(__half2 *)&raw.x), b = __half22float2(*(__half2 *)&raw.y);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+__device__ __forceinline__ float4 load_half4(const __half *p)
+{
+    uint2 raw = *(const uint2 *)p;
+    float2 a = __half22float2(*(__half2 *)&raw.x), b = __half22float2(*(__half2 *)&raw.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store_half4(__half *p, float4 v)
+{
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *(uint2 *)p = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+}
+
+__device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+__device__ __forceinline__ float4 scale4(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float4 axpy4(float a, float4 x, float4 y)
+{
+    return make_float4(a * x.x + y.x, a * x.y + y.y, a * x.z + y.z, a * x.w + y.w);
+}
+
+// CpuComputeLolu, src/gpt/compute/cpu_util.cpp:139-151 (LOLU_SCALE = 2)
+__device__ __forceinline__ float lolu_mult(float gate)
+{
+    float arg = gate * 2.f;
+    if (arg < -20.f)
+        return 0.f;
+    if (arg > 20.f)
+        return 1.f;
+    float w = expf(arg);
+    return w / (1.f + w);
+}
+
+// scale of one 128-wide tile: sqrt(128 / sum of squares), 0 for an all-zero tile
+__device__ __forceinline__ float tile_scale(float sum2) { return sum2 == 0.f ? 0.f : sqrtf(128.f / sum2); }
+
+// Weight encoder of the reference's CPU path for e4m3 (ConvertToFp8e4m3,
+// src/gpt/model_params/sse_utils.h:161-204): round half away from zero on the 4th
+// mantissa bit, values below 2^-7 become 0, saturate to +-448.  Bit-exact with it.
+__device__ __forceinline__ uint8_t encode_e4m3_weight(float v)
+{
+    uint32_t bits = __float_as_uint(v);
+    float f0 = __uint_as_float(bits & 0xFF800000u), f1 = __uint_as_float(bits & 0xFF880000u);
+    v = __fadd_rn(v, __fsub_rn(f1, f0));
+    bits = __float_as_uint(v);
+    int sign = bits >> 31;
+    int exponent = (int)((bits & 0x7F800000u) >> 23) - 120;
+    int mantissa = (bits & 0x007FFFFFu) >> 20;
+    int fp8 = (sign << 7) | (exponent << 3) | mantissa;
+    if (exponent > 15)
+        fp8 = (sign << 7) | 0x7f;
+    if (exponent < 0)
+        fp8 = 0;
+    fp8 &= 0xff;
+    if (fp8 == 0xff)
+        fp8 = 0xfe;
+    if (fp8 == 0x7f)
+        fp8 = 0x7e;
+    return (uint8_t)fp8;
+}
+
+} // namespace ts2

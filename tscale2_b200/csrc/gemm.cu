@@ -36,7 +36,7 @@ struct GemmParams {
     void *C;
     long long ldc;
     float alpha;
-    const float *dyn_scale, *dyn_scale2, *row_scale, *col_scale;
+    const float *dyn_scale, *dyn_scale2, *row_scale, *col_scale, *c_in;
     int out_kind;
     float *workspace;
     int32_t *status;
@@ -300,9 +300,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (p.out_kind == TS2_OUT_F32 || p.out_kind == TS2_OUT_F32_ADD) {
                     float4 *dst = (float4 *)((float *)p.C + row * p.ldc + col);
                     if (p.out_kind == TS2_OUT_F32_ADD) {
+                        const float4 *src = (const float4 *)(p.c_in + row * p.ldc + col);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            float4 o = dst[i];
+                            float4 o = src[i];
                             dst[i] = make_float4(o.x + v[4 * i], o.y + v[4 * i + 1], o.z + v[4 * i + 2], o.w + v[4 * i + 3]);
                         }
                     } else {
@@ -385,7 +386,7 @@ __global__ void reduce_splitk_kernel(const GemmParams p)
             *(float4 *)((float *)p.C + row * p.ldc + col) = s;
         } else if (p.out_kind == TS2_OUT_F32_ADD) {
             float4 *d = (float4 *)((float *)p.C + row * p.ldc + col);
-            float4 o = *d;
+            float4 o = *(const float4 *)(p.c_in + row * p.ldc + col);
             *d = make_float4(o.x + s.x, o.y + s.y, o.z + s.z, o.w + s.w);
         } else if (p.out_kind == TS2_OUT_F16) {
             __half2 a = __floats2half2_rn(s.x, s.y), b = __floats2half2_rn(s.z, s.w);
@@ -476,14 +477,14 @@ static Plan make_plan(int device, int kind, bool mn, int64_t M, int64_t N, int64
     pl.n_tiles = (int)ceil_div(N, pl.bn);
     pl.k_blocks = (int)ceil_div(K, bk);
     const int sms = sm_count(device);
-    const int tiles = pl.m_tiles * pl.n_tiles;
+    const int tiles = std::max(1, pl.m_tiles * pl.n_tiles); // an empty problem is rejected by gemm(); keep the arithmetic defined
     int splits = 1;
     if (tiles * 2 <= sms) { // fewer than half the SMs would have work: split K
         splits = sms / tiles;
         splits = std::min(splits, std::max(1, pl.k_blocks / 8)); // keep at least 8 K blocks per unit
     }
-    pl.kb_per_split = (int)ceil_div(pl.k_blocks, splits);
-    pl.splits = (int)ceil_div(pl.k_blocks, pl.kb_per_split);
+    pl.kb_per_split = std::max(1, (int)ceil_div(pl.k_blocks, splits));
+    pl.splits = std::max(1, (int)ceil_div(pl.k_blocks, pl.kb_per_split));
     pl.grid = std::min(sms, tiles * pl.splits);
     return pl;
 }
@@ -632,6 +633,7 @@ int gemm(const GemmArgs &a)
     p.dyn_scale2 = a.epi.dyn_scale2;
     p.row_scale = a.epi.row_scale;
     p.col_scale = a.epi.col_scale;
+    p.c_in = a.epi.c_in ? a.epi.c_in : (const float *)a.C;
     p.out_kind = a.epi.out_kind;
     p.workspace = (float *)a.workspace;
     p.status = device_status_word(a.device);

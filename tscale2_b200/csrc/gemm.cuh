@@ -14,6 +14,7 @@ struct Epilogue {
     const float *dyn_scale2 = nullptr; // second device scalar
     const float *row_scale = nullptr;  // [M] device
     const float *col_scale = nullptr;  // [N] device
+    const float *c_in = nullptr;       // TS2_OUT_F32_ADD: C = c_in + result (same pitch as C); null: in place
     int out_kind = TS2_OUT_F32;
 };
 

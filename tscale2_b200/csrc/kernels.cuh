@@ -1,0 +1,96 @@
+// Launchers of the bandwidth-bound kernels of the training step (kernels_*.cu).
+// All pointers are device pointers; every launcher returns TS2_OK or an error code.
+// FT (fast type) selects the operand format of the contractions: 0 = e4m3 bytes,
+// 1 = fp16.
+#pragma once
+#include "common.cuh"
+
+namespace ts2 {
+
+constexpr int TILE = 128; // STATE_NORM_TILE / MM_TILE / head dim of the reference
+
+struct Ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int ft = 0;         // 0 e4m3, 1 fp16
+    float s_act = 16.f; // quantization scale of normalized activations (1 for fp16)
+};
+
+// ---- kernels_elem.cu ---------------------------------------------------------------
+// state0[t] = sum over the node's labels of +-E[label] * (sko/32)   (ComputeEmbedding, cpu_transformer.cpp:66-90)
+int embed_forward(const Ctx &c, const __half *embed, const float *sko, const uint32_t *label_arr, const uint32_t *label_ptr, int T,
+                  int D, float *state);
+// dE[label] += +-g[t]   (embedding delta, cpu_transformer.cpp:176-196)
+int embed_backward(const Ctx &c, const float *g, const uint32_t *label_arr, const uint32_t *label_ptr, int T, int D, float *dE);
+
+// n = tilenorm(x) quantized (NormalizeState with 128-wide tiles, cpu_util.cpp:72-99); n16 optional fp16 copy
+int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, __half *n16);
+
+// g_out = (add ? g_in : 0) + tilenorm_bwd(x, dn * (*dyn))   (NormalizeStateBackward, cpu_util.cpp:102-134;
+// BackpropLayerNormalize, gpu_layer_norm.cuh:89-115).  absmax: running max |g_out| as float bits.
+int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float *dyn, float dn_alpha, int T, int D, float *g, bool add,
+                      unsigned *absmax);
+
+// g_fast = g * mult, mult = largest power of two with max|g| * mult <= target; ginv = 1/mult;
+// fscale = f_static * (*sko) * ginv   (ScaleGrad / ComputeGradMult, gpu_grad_scale.cuh:33-62)
+int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, void *g_fast, float *ginv, float f_static, const float *sko,
+              float *fscale);
+
+// FFN activation (LoLU + tile-norm of the wide vector), TFFLayer::ComputeForward layer_ffn.cu:190-211.
+// wg: [T][2F] fp16 = [wide | gate]; what: normalized wide fp16 [T][F]; wscale [T][F/128]; rg fast [T][F]
+int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, float *wscale, void *rg);
+// BackpropLoLU + NormalizeStateBackward of the wide vector (layer_ffn.cu:232-236): d2 fast [T][2F] = [dwide | dgate]
+int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, const float *wscale, int T, int F, void *d2);
+
+// attention gate: rg = sigmoid(2 gate) * o  (LoLU, cpu_util.cpp:139-168); gate inside qkvg [T][4Q] at column 3Q
+int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg);
+// dgate -> d4[:, 3Q:4Q] (fast), do (fp16) and dScale[t][h] = sum do*o  (BackpropLoLU + ComputeDScale)
+int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const __half *o, int T, int Q, void *d4, __half *dout,
+                      float *dscale);
+
+// softmax cross-entropy over base-2 logits (SoftMax, cpu_transformer.cpp:12-37; gradient :146-159):
+// logits fp16 [rows][V] are replaced by (onehot - p) * gscale; logp_sum += log p(target) (natural log).
+int softmax_ce(const Ctx &c, __half *logits, int rows, int V, const float *bias, const int *target, float gscale, float *logp_sum,
+               bool write_grad);
+
+// ---- kernels_att.cu ----------------------------------------------------------------
+// qkvg [T][4Q] fp16 -> q = rope(tilenorm_h(Q)), k = rope(K), v = tilenorm_h(V), each [T][Q] fp16;
+// qscale, vscale [T][H]   (TAttLayer::ComputeForward, layer_att.cu:384-394)
+int att_post_forward(const Ctx &c, const __half *qkvg, const float *rope, int T, int H, __half *q, __half *k, __half *v, float *qscale,
+                     float *vscale);
+// inverse of the above for gradients (layer_att.cu:464-470): writes d4[:, 0:3Q] (fast)
+int att_post_backward(const Ctx &c, const float *dq, const float *dk, const float *dv, const __half *q, const __half *v,
+                      const float *qscale, const float *vscale, const float *rope, const float *sko_k, int T, int H, void *d4);
+int fill_rope(const Ctx &c, float *rope, int T);
+
+// attention over one span per node (ComputeValLookup / GradQ / GradK, layer_att_reference.h:41-212)
+// o [T][Q] fp16, lse [T][H] = maxDP + log2(sumWeight)
+int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
+                      int T, int H, float slope, __half *o, float *lse);
+int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                       const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
+                       int T, int H, float slope, float *dq, float *dk, float *dv);
+
+// ---- kernels_opt.cu ----------------------------------------------------------------
+// MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel (agpu_cuda.cu:32-134), one matrix.
+struct OptMatrix {
+    float *w, *avg_grad;
+    const float *grad;
+    int64_t x, y;
+    float *row_disp;
+    int row_disp_size;
+    float *sum_weight;
+    float sparsity;
+    float *row_sum2;  // scratch [y]
+    float *row_scale; // scratch [y]
+    float *w_sum2;    // scratch [y] (sum of squares of the new weights per row)
+};
+int apply_gradient(const Ctx &c, const OptMatrix &m, const ts2_training_step &step);
+// ConvertMatrixKernel (agpu_cuda.cuh:63-101) with the reference's CPU encoders
+// (sse_utils.h:56-78,161-204): q = enc(w * 32 / sko) into dst[y][ld] and, if dstT, the transposed copy
+// dstT[x][ldT] (optionally widened to fp16); sko written to *sko_out; scratch holds y doubles.
+int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant /*0 e4m3, 1 fp16*/, void *dst, int64_t ld, void *dstT,
+               int64_t ldT, float *sko_out, float *scratch_y_doubles, bool transposed_as_half);
+int fill_vector(const Ctx &c, float *dst, int n, float value, const float *dyn, bool reciprocal_dyn);
+
+} // namespace ts2

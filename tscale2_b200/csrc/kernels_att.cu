@@ -1,0 +1,244 @@
+// Attention part of the training step: per-head normalisation + RoPE of Q/K/V and
+// their backward, and the attention core over one inclusive key span per node
+// (ComputeValLookup / GradQ / GradK, src/gpt/compute/layer_att_reference.h:41-212):
+//   dp(from,to) = q_from . k_to * sqrt(1/128) * 0.5/ln2 - slope * (from - to)
+//   weights 2^(dp - maxDP) with maxDP >= 0 and an extra zero vector of weight 2^-maxDP.
+// This file holds the warp-per-row formulation (fp32 math, coalesced 8-byte loads).
+#include "kernels.cuh"
+#include "fast_types.cuh"
+
+namespace ts2 {
+
+static constexpr int WARPS = 8;
+static constexpr int THREADS = WARPS * 32;
+
+static int grid_for(const Ctx &c, long long warp_items)
+{
+    long long blocks = ceil_div(warp_items, WARPS);
+    long long cap = (long long)sm_count(c.device) * 8;
+    return (int)std::max<long long>(1, std::min(blocks, cap));
+}
+
+#define WARP_ITEM_LOOP(total)                                                                 \
+    const int lane = threadIdx.x & 31;                                                        \
+    for (long long item = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5); item < (total); \
+         item += (long long)gridDim.x * WARPS)
+
+// AttDotScale = CalcDotScale(128) * ATT_DOTPRODUCT_SCALE / LOG2 (layer_att_reference.h:30-33)
+__host__ __device__ inline float att_dot_scale() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
+
+// rope[t][2i] = cos(t * theta^(-2i/128)), rope[t][2i+1] = sin(...)   (TRopeComputer, src/gpt/att/rope.cpp:4-24)
+__global__ void fill_rope_kernel(float *__restrict__ rope, int T)
+{
+    const long long total = (long long)T * 64;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / 64), k = (int)(i % 64);
+        const float freq = (float)exp(-log(500000.0) * (k * 2. / 128));
+        const float angle = (float)t * freq;
+        rope[(size_t)t * 128 + 2 * k] = (float)cos((double)angle);
+        rope[(size_t)t * 128 + 2 * k + 1] = (float)sin((double)angle);
+    }
+}
+
+int fill_rope(const Ctx &c, float *rope, int T)
+{
+    fill_rope_kernel<<<std::max(1, std::min(T, 1024)), 64, 0, c.stream>>>(rope, T);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+__device__ __forceinline__ float4 rope_apply(float4 v, float4 cs, float dir)
+{
+    // pairs (0,1) and (2,3) of the lane's four elements; cs = (cos0, sin0, cos1, sin1)
+    const float s0 = cs.y * dir, s1 = cs.w * dir;
+    return make_float4(v.x * cs.x - v.y * s0, v.x * s0 + v.y * cs.x, v.z * cs.z - v.w * s1, v.z * s1 + v.w * cs.z);
+}
+
+__global__ void att_post_forward_kernel(const __half *__restrict__ qkvg, const float *__restrict__ rope, int T, int H,
+                                        __half *__restrict__ q, __half *__restrict__ k, __half *__restrict__ v,
+                                        float *__restrict__ qscale, float *__restrict__ vscale)
+{
+    const int Q = H * TILE;
+    WARP_ITEM_LOOP((long long)T * H)
+    {
+        const size_t t = item / H;
+        const int h = (int)(item % H), off = h * TILE + lane * 4;
+        const __half *src = qkvg + t * 4 * Q;
+        const float4 qs = load_half4(src + off), ks = load_half4(src + Q + off), vs = load_half4(src + 2 * Q + off);
+        const float4 cs = *(const float4 *)(rope + t * 128 + lane * 4);
+        const float sq = tile_scale(warp_sum(dot4(qs, qs))), sv = tile_scale(warp_sum(dot4(vs, vs)));
+        store_half4(q + t * Q + off, rope_apply(scale4(qs, sq), cs, 1.f));
+        store_half4(k + t * Q + off, rope_apply(ks, cs, 1.f));
+        store_half4(v + t * Q + off, scale4(vs, sv));
+        if (lane == 0) {
+            qscale[t * H + h] = sq;
+            vscale[t * H + h] = sv;
+        }
+    }
+}
+
+int att_post_forward(const Ctx &c, const __half *qkvg, const float *rope, int T, int H, __half *q, __half *k, __half *v, float *qscale,
+                     float *vscale)
+{
+    att_post_forward_kernel<<<grid_for(c, (long long)T * H), THREADS, 0, c.stream>>>(qkvg, rope, T, H, q, k, v, qscale, vscale);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+template <int FT>
+__global__ void att_post_backward_kernel(const float *__restrict__ dq, const float *__restrict__ dk, const float *__restrict__ dv,
+                                         const __half *__restrict__ q, const __half *__restrict__ v, const float *__restrict__ qscale,
+                                         const float *__restrict__ vscale, const float *__restrict__ rope,
+                                         const float *__restrict__ sko_k, int T, int H, void *__restrict__ d4)
+{
+    const int Q = H * TILE;
+    const float kfold = __ldg(sko_k);
+    WARP_ITEM_LOOP((long long)T * H)
+    {
+        const size_t t = item / H;
+        const int h = (int)(item % H), off = h * TILE + lane * 4;
+        const float4 cs = *(const float4 *)(rope + t * 128 + lane * 4);
+        // q: tile-norm backward in the rotated frame (the rotation is orthogonal), then rotate back
+        const float4 qv = load_half4(q + t * Q + off);
+        const float4 gq = *(const float4 *)(dq + t * Q + off);
+        const float pq = warp_sum(dot4(qv, gq)) * (1.f / 128);
+        const float sq = qscale[t * H + h];
+        float4 r = rope_apply(make_float4(gq.x - qv.x * pq, gq.y - qv.y * pq, gq.z - qv.z * pq, gq.w - qv.w * pq), cs, -1.f);
+        Fast<FT>::store4(d4, t * 4 * Q + off, scale4(r, sq));
+        // k: rotate back; the matrix scale of K is folded in here so that the 4-way dX contraction
+        // can use scale-free weights for every block
+        const float4 gk = rope_apply(*(const float4 *)(dk + t * Q + off), cs, -1.f);
+        Fast<FT>::store4(d4, t * 4 * Q + Q + off, scale4(gk, kfold));
+        // v: tile-norm backward
+        const float4 vv = load_half4(v + t * Q + off);
+        const float4 gv = *(const float4 *)(dv + t * Q + off);
+        const float pv = warp_sum(dot4(vv, gv)) * (1.f / 128);
+        const float sv = vscale[t * H + h];
+        Fast<FT>::store4(d4, t * 4 * Q + 2 * Q + off,
+                         make_float4(sv * (gv.x - vv.x * pv), sv * (gv.y - vv.y * pv), sv * (gv.z - vv.z * pv), sv * (gv.w - vv.w * pv)));
+    }
+}
+
+int att_post_backward(const Ctx &c, const float *dq, const float *dk, const float *dv, const __half *q, const __half *v,
+                      const float *qscale, const float *vscale, const float *rope, const float *sko_k, int T, int H, void *d4)
+{
+    const int grid = grid_for(c, (long long)T * H);
+    if (c.ft == 0)
+        att_post_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(dq, dk, dv, q, v, qscale, vscale, rope, sko_k, T, H, d4);
+    else
+        att_post_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(dq, dk, dv, q, v, qscale, vscale, rope, sko_k, T, H, d4);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// attention core, one warp per (node, head)
+
+__global__ void attention_forward_kernel(const __half *__restrict__ q, const __half *__restrict__ k, const __half *__restrict__ v,
+                                         const int *__restrict__ span_start, const int *__restrict__ span_finish, int T, int H,
+                                         float slope, __half *__restrict__ o, float *__restrict__ lse)
+{
+    const int Q = H * TILE;
+    const float ds = att_dot_scale();
+    WARP_ITEM_LOOP((long long)T * H)
+    {
+        const int t = (int)(item / H), h = (int)(item % H), off = h * TILE + lane * 4;
+        const float4 qv = load_half4(q + (size_t)t * Q + off);
+        float m = 0.f, S = 1.f; // running maximum (never below 0) and sum, including the zero vector of weight 2^-m
+        float4 acc = make_float4(0, 0, 0, 0);
+        const int s0 = span_start[t], s1 = span_finish[t];
+        for (int to = s0; to <= s1; ++to) {
+            const float4 kv = load_half4(k + (size_t)to * Q + off);
+            const float dp = warp_sum(dot4(qv, kv)) * ds - slope * (float)(t - to);
+            if (dp > m) {
+                const float r = exp2f(m - dp);
+                S *= r;
+                acc = scale4(acc, r);
+                m = dp;
+            }
+            const float w = exp2f(dp - m);
+            S += w;
+            acc = axpy4(w, load_half4(v + (size_t)to * Q + off), acc);
+        }
+        store_half4(o + (size_t)t * Q + off, scale4(acc, 1.f / S));
+        if (lane == 0)
+            lse[(size_t)t * H + h] = m + log2f(S);
+    }
+}
+
+int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
+                      int T, int H, float slope, __half *o, float *lse)
+{
+    attention_forward_kernel<<<grid_for(c, (long long)T * H), THREADS, 0, c.stream>>>(q, k, v, span_start, span_finish, T, H, slope, o, lse);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+__global__ void attention_dq_kernel(const __half *__restrict__ q, const __half *__restrict__ k, const __half *__restrict__ v,
+                                    const __half *__restrict__ dout, const float *__restrict__ lse, const float *__restrict__ dscale,
+                                    const int *__restrict__ span_start, const int *__restrict__ span_finish, int T, int H, float slope,
+                                    float *__restrict__ dq)
+{
+    const int Q = H * TILE;
+    const float ds = att_dot_scale(), c2 = ds * 0.693147f;
+    WARP_ITEM_LOOP((long long)T * H)
+    {
+        const int t = (int)(item / H), h = (int)(item % H), off = h * TILE + lane * 4;
+        const float4 qv = load_half4(q + (size_t)t * Q + off), dov = load_half4(dout + (size_t)t * Q + off);
+        const float l = lse[(size_t)t * H + h], dsc = dscale[(size_t)t * H + h];
+        float4 acc = make_float4(0, 0, 0, 0);
+        const int s0 = span_start[t], s1 = span_finish[t];
+        for (int to = s0; to <= s1; ++to) {
+            const float4 kv = load_half4(k + (size_t)to * Q + off), vv = load_half4(v + (size_t)to * Q + off);
+            const float dp = warp_sum(dot4(qv, kv)) * ds - slope * (float)(t - to);
+            const float w = exp2f(dp - l);
+            const float dW = warp_sum(dot4(dov, vv));
+            acc = axpy4(w * (dW - dsc) * c2, kv, acc);
+        }
+        *(float4 *)(dq + (size_t)t * Q + off) = acc;
+    }
+}
+
+__global__ void attention_dkv_kernel(const __half *__restrict__ q, const __half *__restrict__ k, const __half *__restrict__ v,
+                                     const __half *__restrict__ dout, const float *__restrict__ lse, const float *__restrict__ dscale,
+                                     const int *__restrict__ span_start, const int *__restrict__ span_finish,
+                                     const int *__restrict__ rev_first, const int *__restrict__ rev_last, int T, int H, float slope,
+                                     float *__restrict__ dk, float *__restrict__ dv)
+{
+    const int Q = H * TILE;
+    const float ds = att_dot_scale(), c2 = ds * 0.693147f;
+    WARP_ITEM_LOOP((long long)T * H)
+    {
+        const int to = (int)(item / H), h = (int)(item % H), off = h * TILE + lane * 4;
+        const float4 kv = load_half4(k + (size_t)to * Q + off), vv = load_half4(v + (size_t)to * Q + off);
+        float4 ak = make_float4(0, 0, 0, 0), av = make_float4(0, 0, 0, 0);
+        const int f0 = rev_first[to], f1 = rev_last[to];
+        for (int t = f0; t <= f1; ++t) {
+            if (span_start[t] > to || span_finish[t] < to)
+                continue;
+            const float4 qv = load_half4(q + (size_t)t * Q + off), dov = load_half4(dout + (size_t)t * Q + off);
+            const float dp = warp_sum(dot4(qv, kv)) * ds - slope * (float)(t - to);
+            const float w = exp2f(dp - lse[(size_t)t * H + h]);
+            const float dW = warp_sum(dot4(dov, vv));
+            ak = axpy4(w * (dW - dscale[(size_t)t * H + h]) * c2, qv, ak);
+            av = axpy4(w, dov, av);
+        }
+        *(float4 *)(dk + (size_t)to * Q + off) = ak;
+        *(float4 *)(dv + (size_t)to * Q + off) = av;
+    }
+}
+
+int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                       const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
+                       int T, int H, float slope, float *dq, float *dk, float *dv)
+{
+    const int grid = grid_for(c, (long long)T * H);
+    attention_dq_kernel<<<grid, THREADS, 0, c.stream>>>(q, k, v, dout, lse, dscale, span_start, span_finish, T, H, slope, dq);
+    TS2_CHECK_LAUNCH();
+    attention_dkv_kernel<<<grid, THREADS, 0, c.stream>>>(q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H,
+                                                         slope, dk, dv);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+} // namespace ts2

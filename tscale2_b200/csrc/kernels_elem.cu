@@ -1,0 +1,423 @@
+// Bandwidth-bound kernels of the training step: embedding, tile normalisation and
+// its backward, gradient cast/scale, LoLU activations and their backward, softmax
+// cross-entropy.  One warp owns one 128-wide tile of one row (a lane holds four
+// consecutive elements: 16-byte accesses for fp32, 8 for fp16, 4 for e4m3) and
+// strides over (row, tile) pairs; reductions are warp shuffles.
+#include "kernels.cuh"
+#include "fast_types.cuh"
+
+namespace ts2 {
+
+static constexpr int WARPS = 8;
+static constexpr int THREADS = WARPS * 32;
+
+static int grid_for(const Ctx &c, long long warp_items)
+{
+    long long blocks = ceil_div(warp_items, WARPS);
+    long long cap = (long long)sm_count(c.device) * 8;
+    return (int)std::max<long long>(1, std::min(blocks, cap));
+}
+
+#define WARP_ITEM_LOOP(total)                                                                              \
+    const int lane = threadIdx.x & 31;                                                                     \
+    for (long long item = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5); item < (total);              \
+         item += (long long)gridDim.x * WARPS)
+
+// ---------------------------------------------------------------------------------
+__global__ void embed_forward_kernel(const __half *__restrict__ embed, const float *__restrict__ sko,
+                                     const uint32_t *__restrict__ label_arr, const uint32_t *__restrict__ label_ptr, int T, int D,
+                                     float *__restrict__ state)
+{
+    const int tiles = D / TILE;
+    const float scale = __ldg(sko) * (1.f / 32);
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const int t = (int)(item / tiles), off = (int)(item % tiles) * TILE + lane * 4;
+        float4 acc = make_float4(0, 0, 0, 0);
+        for (uint32_t k = label_ptr[t]; k < label_ptr[t + 1]; ++k) {
+            uint32_t label = label_arr[k];
+            float w = (label & TS2_LABEL_NEGATIVE) ? -1.f : 1.f;
+            label &= TS2_LABEL_MASK;
+            float4 e = load_half4(embed + (size_t)label * D + off);
+            // the CPU path adds (q * scale) * w label by label
+            acc.x += (e.x * scale) * w;
+            acc.y += (e.y * scale) * w;
+            acc.z += (e.z * scale) * w;
+            acc.w += (e.w * scale) * w;
+        }
+        *(float4 *)(state + (size_t)t * D + off) = acc;
+    }
+}
+
+int embed_forward(const Ctx &c, const __half *embed, const float *sko, const uint32_t *label_arr, const uint32_t *label_ptr, int T,
+                  int D, float *state)
+{
+    embed_forward_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(embed, sko, label_arr, label_ptr, T, D, state);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+__global__ void embed_backward_kernel(const float *__restrict__ g, const uint32_t *__restrict__ label_arr,
+                                      const uint32_t *__restrict__ label_ptr, int T, int D, float *__restrict__ dE)
+{
+    const int tiles = D / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const int t = (int)(item / tiles), off = (int)(item % tiles) * TILE + lane * 4;
+        const float4 gv = *(const float4 *)(g + (size_t)t * D + off);
+        for (uint32_t k = label_ptr[t]; k < label_ptr[t + 1]; ++k) {
+            uint32_t label = label_arr[k];
+            float w = (label & TS2_LABEL_NEGATIVE) ? -1.f : 1.f;
+            label &= TS2_LABEL_MASK;
+            atomicAdd((float4 *)(dE + (size_t)label * D + off), make_float4(gv.x * w, gv.y * w, gv.z * w, gv.w * w));
+        }
+    }
+}
+
+int embed_backward(const Ctx &c, const float *g, const uint32_t *label_arr, const uint32_t *label_ptr, int T, int D, float *dE)
+{
+    embed_backward_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(g, label_arr, label_ptr, T, D, dE);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+template <int FT>
+__global__ void tilenorm_forward_kernel(const float *__restrict__ x, int T, int D, float s_act, void *__restrict__ n_fast,
+                                        __half *__restrict__ n16)
+{
+    const int tiles = D / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t idx = (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4;
+        const float4 v = *(const float4 *)(x + idx);
+        const float scale = tile_scale(warp_sum(dot4(v, v)));
+        const float4 nv = scale4(v, scale);
+        Fast<FT>::store4(n_fast, idx, scale4(nv, s_act));
+        if (n16)
+            store_half4(n16 + idx, nv);
+    }
+}
+
+int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, __half *n16)
+{
+    const int grid = grid_for(c, (long long)T * (D / TILE));
+    if (c.ft == 0)
+        tilenorm_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
+    else
+        tilenorm_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+__global__ void tilenorm_backward_kernel(const float *__restrict__ x, const float *__restrict__ dn, const float *__restrict__ dyn,
+                                         float dn_alpha, int T, int D, float *__restrict__ g, int add, unsigned *__restrict__ absmax)
+{
+    const int tiles = D / TILE;
+    const float a = dn_alpha * (dyn ? __ldg(dyn) : 1.f);
+    float local_max = 0.f;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t idx = (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4;
+        const float4 xv = *(const float4 *)(x + idx);
+        const float4 dv = scale4(*(const float4 *)(dn + idx), a);
+        const float sum2 = warp_sum(dot4(xv, xv));
+        const float dp = warp_sum(dot4(xv, dv));
+        float4 r = make_float4(0, 0, 0, 0);
+        if (sum2 != 0.f) {
+            const float sigma = dp / sum2, scale = sqrtf(128.f / sum2);
+            r = make_float4(scale * (dv.x - xv.x * sigma), scale * (dv.y - xv.y * sigma), scale * (dv.z - xv.z * sigma),
+                            scale * (dv.w - xv.w * sigma));
+        }
+        if (add) {
+            const float4 o = *(const float4 *)(g + idx);
+            r = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
+        }
+        *(float4 *)(g + idx) = r;
+        local_max = fmaxf(local_max, fmaxf(fmaxf(fabsf(r.x), fabsf(r.y)), fmaxf(fabsf(r.z), fabsf(r.w))));
+    }
+    if (absmax) {
+        __shared__ float block_max[WARPS];
+        local_max = warp_max(local_max);
+        if ((threadIdx.x & 31) == 0)
+            block_max[threadIdx.x >> 5] = local_max;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = 0.f;
+            for (int i = 0; i < WARPS; ++i)
+                m = fmaxf(m, block_max[i]);
+            if (m == m && m < 3.0e38f) // NaN / inf never become the scale reference
+                atomicMax(absmax, __float_as_uint(m));
+        }
+    }
+}
+
+int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float *dyn, float dn_alpha, int T, int D, float *g, bool add,
+                      unsigned *absmax)
+{
+    tilenorm_backward_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(x, dn, dyn, dn_alpha, T, D, g, add ? 1 : 0,
+                                                                                          absmax);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// power-of-two multiplier that brings max|g| just below `target`
+__device__ __forceinline__ float grad_mult(unsigned absmax_bits, float target)
+{
+    const float m = __uint_as_float(absmax_bits);
+    if (!(m > 0.f))
+        return 1.f;
+    float e = floorf(log2f(target / m));
+    e = fminf(fmaxf(e, -100.f), 100.f);
+    return exp2f(e);
+}
+
+template <int FT>
+__global__ void cast_grad_kernel(const float *__restrict__ g, size_t n4, const unsigned *__restrict__ absmax, void *__restrict__ out,
+                                 float *__restrict__ ginv, float f_static, const float *__restrict__ sko, float *__restrict__ fscale)
+{
+    const float mult = grad_mult(*absmax, 128.f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        *ginv = 1.f / mult;
+        if (fscale)
+            *fscale = f_static * (sko ? *sko : 1.f) / mult;
+    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = *(const float4 *)(g + i * 4);
+        Fast<FT>::store4(out, i * 4, scale4(v, mult));
+    }
+}
+
+int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, void *g_fast, float *ginv, float f_static, const float *sko,
+              float *fscale)
+{
+    const size_t n4 = n / 4;
+    const int grid = (int)std::min<size_t>(ceil_div(n4, THREADS), (size_t)sm_count(c.device) * 8);
+    if (c.ft == 0)
+        cast_grad_kernel<0><<<grid, THREADS, 0, c.stream>>>(g, n4, absmax, g_fast, ginv, f_static, sko, fscale);
+    else
+        cast_grad_kernel<1><<<grid, THREADS, 0, c.stream>>>(g, n4, absmax, g_fast, ginv, f_static, sko, fscale);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+template <int FT>
+__global__ void ffn_act_forward_kernel(const __half *__restrict__ wg, int T, int F, float s_act, __half *__restrict__ what,
+                                       float *__restrict__ wscale, void *__restrict__ rg)
+{
+    const int tiles = F / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t t = item / tiles;
+        const int tile = (int)(item % tiles), off = tile * TILE + lane * 4;
+        const float4 wide = load_half4(wg + t * 2 * F + off);
+        const float4 gate = load_half4(wg + t * 2 * F + F + off);
+        const float scale = tile_scale(warp_sum(dot4(wide, wide)));
+        const float4 wn = scale4(wide, scale);
+        store_half4(what + t * F + off, wn);
+        if (lane == 0)
+            wscale[t * tiles + tile] = scale;
+        const float4 r = make_float4(lolu_mult(gate.x) * wn.x, lolu_mult(gate.y) * wn.y, lolu_mult(gate.z) * wn.z, lolu_mult(gate.w) * wn.w);
+        Fast<FT>::store4(rg, t * F + off, scale4(r, s_act));
+    }
+}
+
+int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, float *wscale, void *rg)
+{
+    const int grid = grid_for(c, (long long)T * (F / TILE));
+    if (c.ft == 0)
+        ffn_act_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(wg, T, F, c.s_act, what, wscale, rg);
+    else
+        ffn_act_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(wg, T, F, c.s_act, what, wscale, rg);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+template <int FT>
+__global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __half *__restrict__ wg, const __half *__restrict__ what,
+                                        const float *__restrict__ wscale, int T, int F, void *__restrict__ d2)
+{
+    const int tiles = F / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t t = item / tiles;
+        const int tile = (int)(item % tiles), off = tile * TILE + lane * 4;
+        const float4 g = load_half4(drg + t * F + off);
+        const float4 gate = load_half4(wg + t * 2 * F + F + off);
+        const float4 wn = load_half4(what + t * F + off);
+        const float scale = wscale[t * tiles + tile];
+        const float4 m = make_float4(lolu_mult(gate.x), lolu_mult(gate.y), lolu_mult(gate.z), lolu_mult(gate.w));
+        const float4 dgate = make_float4(g.x * wn.x * m.x * (1 - m.x) * 2.f, g.y * wn.y * m.y * (1 - m.y) * 2.f,
+                                         g.z * wn.z * m.z * (1 - m.z) * 2.f, g.w * wn.w * m.w * (1 - m.w) * 2.f);
+        const float4 dwn = make_float4(g.x * m.x, g.y * m.y, g.z * m.z, g.w * m.w);
+        // tile-norm backward expressed with the normalized vector: scale * (d - wn * (wn . d) / 128)
+        const float proj = warp_sum(dot4(wn, dwn)) * (1.f / 128);
+        const float4 dwide = make_float4(scale * (dwn.x - wn.x * proj), scale * (dwn.y - wn.y * proj), scale * (dwn.z - wn.z * proj),
+                                         scale * (dwn.w - wn.w * proj));
+        Fast<FT>::store4(d2, t * 2 * F + off, dwide);
+        Fast<FT>::store4(d2, t * 2 * F + F + off, dgate);
+    }
+}
+
+int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, const float *wscale, int T, int F, void *d2)
+{
+    const int grid = grid_for(c, (long long)T * (F / TILE));
+    if (c.ft == 0)
+        ffn_act_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, wscale, T, F, d2);
+    else
+        ffn_act_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, wscale, T, F, d2);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+template <int FT>
+__global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const __half *__restrict__ o, int T, int Q, float s_act,
+                                        void *__restrict__ rg)
+{
+    const int tiles = Q / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t t = item / tiles;
+        const int off = (int)(item % tiles) * TILE + lane * 4;
+        const float4 gate = load_half4(qkvg + t * 4 * Q + 3 * Q + off);
+        const float4 ov = load_half4(o + t * Q + off);
+        const float4 r = make_float4(lolu_mult(gate.x) * ov.x, lolu_mult(gate.y) * ov.y, lolu_mult(gate.z) * ov.z, lolu_mult(gate.w) * ov.w);
+        Fast<FT>::store4(rg, t * Q + off, scale4(r, s_act));
+    }
+}
+
+int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg)
+{
+    const int grid = grid_for(c, (long long)T * (Q / TILE));
+    if (c.ft == 0)
+        att_gate_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
+    else
+        att_gate_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+template <int FT>
+__global__ void att_gate_backward_kernel(const __half *__restrict__ drg, const __half *__restrict__ qkvg, const __half *__restrict__ o,
+                                         int T, int Q, void *__restrict__ d4, __half *__restrict__ dout, float *__restrict__ dscale)
+{
+    const int tiles = Q / TILE; // = heads
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t t = item / tiles;
+        const int h = (int)(item % tiles), off = h * TILE + lane * 4;
+        const float4 g = load_half4(drg + t * Q + off);
+        const float4 gate = load_half4(qkvg + t * 4 * Q + 3 * Q + off);
+        const float4 ov = load_half4(o + t * Q + off);
+        const float4 m = make_float4(lolu_mult(gate.x), lolu_mult(gate.y), lolu_mult(gate.z), lolu_mult(gate.w));
+        const float4 dgate = make_float4(g.x * ov.x * m.x * (1 - m.x) * 2.f, g.y * ov.y * m.y * (1 - m.y) * 2.f,
+                                         g.z * ov.z * m.z * (1 - m.z) * 2.f, g.w * ov.w * m.w * (1 - m.w) * 2.f);
+        const float4 dov = make_float4(g.x * m.x, g.y * m.y, g.z * m.z, g.w * m.w);
+        Fast<FT>::store4(d4, t * 4 * Q + 3 * Q + off, dgate);
+        store_half4(dout + t * Q + off, dov);
+        const float ds = warp_sum(dot4(dov, ov));
+        if (lane == 0)
+            dscale[t * tiles + h] = ds;
+    }
+}
+
+int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const __half *o, int T, int Q, void *d4, __half *dout,
+                      float *dscale)
+{
+    const int grid = grid_for(c, (long long)T * (Q / TILE));
+    if (c.ft == 0)
+        att_gate_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, qkvg, o, T, Q, d4, dout, dscale);
+    else
+        att_gate_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(drg, qkvg, o, T, Q, d4, dout, dscale);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// One block per row; the row of fp16 logits is staged in shared memory, read once
+// from HBM and overwritten once with the gradient.
+__global__ void softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, const float *__restrict__ bias,
+                                  const int *__restrict__ target, float gscale, float *__restrict__ logp_sum, int write_grad)
+{
+    extern __shared__ __half row_s[];
+    __shared__ float red[32];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        __half *src = logits + (size_t)row * V;
+        const int tgt = target[row];
+        if (tgt < 0) {
+            if (write_grad)
+                for (int i = tid; i < V / 8; i += nthr)
+                    ((uint4 *)src)[i] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        float mx = 0.f; // the reference starts the maximum at 0 and takes it over the logits without bias
+        for (int i = tid; i < V / 8; i += nthr) {
+            uint4 raw = ((const uint4 *)src)[i];
+            ((uint4 *)row_s)[i] = raw;
+            const __half2 *h = (const __half2 *)&raw;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __half22float2(h[j]);
+                mx = fmaxf(mx, fmaxf(f.x, f.y));
+            }
+        }
+        mx = warp_max(mx);
+        if ((tid & 31) == 0)
+            red[tid >> 5] = mx;
+        __syncthreads();
+        mx = 0.f;
+        for (int i = 0; i < nthr / 32; ++i)
+            mx = fmaxf(mx, red[i]);
+        __syncthreads();
+        float sum = 0.f;
+        for (int i = tid; i < V; i += nthr)
+            sum += exp2f(__half2float(row_s[i]) + (bias ? bias[i] : 0.f) - mx);
+        sum = warp_sum(sum);
+        if ((tid & 31) == 0)
+            red[tid >> 5] = sum;
+        __syncthreads();
+        sum = 0.f;
+        for (int i = 0; i < nthr / 32; ++i)
+            sum += red[i];
+        const float inv = 1.f / sum;
+        if (tid == 0) {
+            const float lt = __half2float(row_s[tgt]) + (bias ? bias[tgt] : 0.f) - mx;
+            atomicAdd(logp_sum, lt * 0.69314718f - logf(sum));
+        }
+        if (write_grad) {
+            for (int i = tid; i < V / 2; i += nthr) {
+                const float2 f = __half22float2(((const __half2 *)row_s)[i]);
+                float p0 = exp2f(f.x + (bias ? bias[2 * i] : 0.f) - mx) * inv;
+                float p1 = exp2f(f.y + (bias ? bias[2 * i + 1] : 0.f) - mx) * inv;
+                float g0 = ((2 * i == tgt) ? 1.f : 0.f) - p0, g1 = ((2 * i + 1 == tgt) ? 1.f : 0.f) - p1;
+                ((__half2 *)src)[i] = __floats2half2_rn(g0 * gscale, g1 * gscale);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+int softmax_ce(const Ctx &c, __half *logits, int rows, int V, const float *bias, const int *target, float gscale, float *logp_sum,
+               bool write_grad)
+{
+    if (V % 8)
+        return fail(TS2_ERR_INVALID_ARG, "softmax_ce: vocabulary must be a multiple of 8");
+    const size_t smem = (size_t)V * sizeof(__half);
+    static bool configured[16] = {};
+    if (smem > 48 * 1024 && !configured[c.device & 15]) {
+        TS2_CUDA(cudaFuncSetAttribute(softmax_ce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured[c.device & 15] = true;
+    }
+    if (smem > 200 * 1024)
+        return fail(TS2_ERR_TOO_LARGE, "softmax_ce: vocabulary %d does not fit the shared-memory row buffer", V);
+    const int grid = std::min(rows, sm_count(c.device) * 2);
+    softmax_ce_kernel<<<grid, 512, smem, c.stream>>>(logits, rows, V, bias, target, gscale, logp_sum, write_grad ? 1 : 0);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+} // namespace ts2

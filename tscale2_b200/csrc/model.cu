@@ -1,0 +1,1157 @@
+// The training-step engine behind the model-level C ABI: what the reference builds in
+// TSinlgeComputeContext (src/gpt/compute/gpu_transformer.cu:94-502) — forward pass, final
+// layer, per-layer backward, gradient hand-off, optimizer, requantisation — laid out
+// for one B200:
+//   * every activation the backward pass needs is kept (the reference keeps only the
+//     normalized state and re-runs each layer's forward inside backward,
+//     layer_ffn.cu:53-67,83-113; 180 GB of HBM makes that trade unnecessary);
+//   * the Q/K/V/Gate matrices (and Expand/Gate of an FFN) are stored concatenated, with a
+//     transposed copy written by the requantiser, so a layer is 6 contractions
+//     (2 forward, 2 dX, 2 dW) and no transposes;
+//   * weight gradients accumulate in one flat fp32 buffer (matrix order of the C ABI), which
+//     is also the message of the data-parallel all-reduce.
+// Scale bookkeeping follows the CPU formulas of the reference (cpu_util.cpp, layer_att.cu:368-482,
+// layer_ffn.cu:190-248); see the comments at each contraction.
+#include "gemm.cuh"
+#include "kernels.cuh"
+#include <nccl.h>
+#include <vector>
+#include <cmath>
+#include <cstring>
+#include <algorithm>
+#include <chrono>
+#include <thread>
+
+namespace ts2 {
+const char *global_error();
+
+static const float LOG2F = 0.693147f; // LOG2, model_dim.h:16
+
+struct Matrix {
+    int64_t x = 0, y = 0;
+    int row_disp_size = 1;
+    float sparsity = 1.f;
+    float *w = nullptr, *avg = nullptr, *grad = nullptr; // grad points into the flat buffer
+    float *row_disp = nullptr, *sum_weight = nullptr, *sko = nullptr;
+    size_t offset = 0; // element offset in the flat buffers
+};
+
+struct Layer {
+    int type = 0;
+    float slope = 0;
+    int att_type = 0;
+    int mat0 = 0;   // index of the first matrix
+    int wide = 0;   // Q (attention) or F (ffn)
+    int ncat = 0;   // 4 (attention) or 2 (ffn)
+    // quantized weights
+    void *Wcat = nullptr, *WcatT = nullptr; // [ncat*wide][D], [D][ncat*wide]
+    void *Wc = nullptr, *WcT = nullptr;     // [D][wide], [wide][D]
+    float *fwd_col = nullptr;               // [ncat*wide] forward column scales
+    float *bwd_row = nullptr;               // [ncat*wide] dW row scales
+    // saved activations
+    void *n_fast = nullptr;                 // [T][D]
+    __half *cat16 = nullptr;                // [T][ncat*wide]: Q|K|V|Gate or wide|gate
+    __half *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr; // attention
+    float *qscale = nullptr, *vscale = nullptr, *lse = nullptr;
+    __half *what = nullptr;                 // ffn: normalized wide
+    float *wscale = nullptr;
+    void *rg = nullptr;                     // [T][wide]
+};
+
+struct BatchDev {
+    uint32_t *label_arr = nullptr, *label_ptr = nullptr;
+    int *target = nullptr;
+    std::vector<int *> span_start, span_finish, rev_first, rev_last;
+    size_t label_cap = 0;
+    int node_count = 0, target_count = 0;
+};
+
+} // namespace ts2
+
+using namespace ts2;
+
+struct ts2_model {
+    ts2_model_descr descr;
+    std::vector<ts2_layer_params> layer_params;
+    int device = 0, max_nodes = 0;
+    int D = 0, H = 0, Q = 0, F = 0, V = 0, L = 0;
+    int ft = 0;
+    int kind = KIND_E4M3;
+    float s_act = 16.f;
+    cudaStream_t stream = nullptr, comm_stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr, ev_grads = nullptr, ev_reduced = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
+    std::string error;
+    std::vector<void *> allocs;
+    std::vector<Matrix> mats;
+    std::vector<Layer> layers;
+    size_t total_params = 0;
+    float *w_flat = nullptr, *avg_flat = nullptr, *grad_flat = nullptr;
+    float *skos = nullptr; // [n_mats]
+    float *bias = nullptr;
+    __half *embed16 = nullptr;
+    void *Wf = nullptr;      // [V][D] fast
+    __half *WfT16 = nullptr; // [D][V]
+    // activations
+    std::vector<float *> states; // L+1
+    float *g = nullptr, *dn = nullptr;
+    void *g_fast = nullptr;
+    void *nF_fast = nullptr;
+    __half *nF16 = nullptr;
+    __half *logits = nullptr;
+    int chunk = 0;
+    __half *drg = nullptr, *dout = nullptr;
+    void *dcat = nullptr;
+    float *dscale = nullptr, *dq = nullptr, *dk = nullptr, *dv = nullptr;
+    float *rope = nullptr;
+    unsigned *absmax = nullptr; // [L+2]
+    float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    float *opt_scratch = nullptr; // row_sum2 | row_scale | doubles
+    int64_t max_rows = 0;
+    BatchDev batch;
+    void *pinned = nullptr;
+    size_t pinned_bytes = 0;
+    bool grads_dirty = false; // the flat gradient holds an accumulated, not yet applied gradient
+    bool debug_taps = false;
+    float *grad_taps = nullptr;
+    float last_ms = 0;
+    bool timing_valid = false;
+    int last_targets = 0;
+    // data parallel
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+namespace {
+
+int mfail(ts2_model *m, int code)
+{
+    if (m)
+        m->error = g_last_error;
+    return code;
+}
+
+#define M_TRY(expr)                 \
+    do {                            \
+        int _rc = (expr);           \
+        if (_rc != TS2_OK)          \
+            return mfail(m, _rc);   \
+    } while (0)
+
+template <class T>
+int dalloc(ts2_model *m, T **p, size_t count)
+{
+    void *q = nullptr;
+    size_t bytes = std::max<size_t>(count * sizeof(T), 256);
+    cudaError_t e = cudaMalloc(&q, bytes);
+    if (e != cudaSuccess)
+        return fail(TS2_ERR_CUDA, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    m->allocs.push_back(q);
+    *p = (T *)q;
+    return TS2_OK;
+}
+
+int layer_matrix_count(int type) { return type == TS2_LAYER_ATT ? 5 : type == TS2_LAYER_FFN ? 3 : type == TS2_LAYER_MOE ? 4 : -1; }
+
+Ctx ctx_of(ts2_model *m)
+{
+    Ctx c;
+    c.device = m->device;
+    c.stream = m->stream;
+    c.ft = m->ft;
+    c.s_act = m->s_act;
+    return c;
+}
+
+size_t fast_size(const ts2_model *m) { return m->ft == 0 ? 1 : 2; }
+
+// C = epilogue(A[M][K] . B[N][K]^T), K contiguous in both
+int gemm_tn(ts2_model *m, int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
+            int64_t ldc, const Epilogue &epi)
+{
+    GemmArgs a;
+    a.device = m->device;
+    a.stream = m->stream;
+    a.kind = kind;
+    a.mn_major = false;
+    a.M = M, a.N = N, a.K = K;
+    a.A = A, a.lda = lda, a.B = B, a.ldb = ldb, a.C = C, a.ldc = ldc;
+    a.epi = epi;
+    a.workspace = m->workspace;
+    a.workspace_bytes = m->workspace_bytes;
+    return gemm(a);
+}
+
+// dW[Mo][Ni] = epilogue(dY[T][Mo]^T . X[T][Ni]), both token-major
+int gemm_dw(ts2_model *m, int kind, int64_t Mo, int64_t Ni, int64_t T, const void *dY, int64_t ldy, const void *X, int64_t ldx, float *dW,
+            const Epilogue &epi)
+{
+    GemmArgs a;
+    a.device = m->device;
+    a.stream = m->stream;
+    a.kind = kind;
+    a.mn_major = true;
+    a.M = Mo, a.N = Ni, a.K = T;
+    a.A = dY, a.lda = ldy, a.B = X, a.ldb = ldx, a.C = dW, a.ldc = Ni;
+    a.epi = epi;
+    a.workspace = m->workspace;
+    a.workspace_bytes = m->workspace_bytes;
+    return gemm(a);
+}
+
+int validate(const ts2_model_descr *d)
+{
+    if (!d)
+        return fail(TS2_ERR_INVALID_ARG, "null model description");
+    if (d->dim <= 0 || d->dim % 128)
+        return fail(TS2_ERR_INVALID_ARG, "dim must be a positive multiple of 128 (got %d)", d->dim);
+    if (d->q_dim != 128 || d->tt_dim != 128)
+        return fail(TS2_ERR_UNSUPPORTED, "q_dim and tt_dim must be 128 (got %d, %d)", d->q_dim, d->tt_dim);
+    if (d->head_count <= 0 || d->ffn_tiles < 0 || d->layer_count < 0 || (d->layer_count && !d->layers))
+        return fail(TS2_ERR_INVALID_ARG, "bad head / ffn / layer counts");
+    if (d->label_count <= 0 || d->output_token_count <= 0 || d->output_token_count % 32)
+        return fail(TS2_ERR_INVALID_ARG, "label_count must be positive and output_token_count a positive multiple of 32");
+    if (d->precision != TS2_PREC_FP8 && d->precision != TS2_PREC_F16)
+        return fail(TS2_ERR_UNSUPPORTED, "precision must be TS2_PREC_FP8 or TS2_PREC_F16");
+    for (int l = 0; l < d->layer_count; ++l) {
+        int t = d->layers[l].layer_type;
+        if (t == TS2_LAYER_MOE)
+            return fail(TS2_ERR_UNSUPPORTED, "layer %d: MoE layers are not built into the engine yet", l);
+        if (t != TS2_LAYER_ATT && t != TS2_LAYER_FFN)
+            return fail(TS2_ERR_UNSUPPORTED, "layer %d: unsupported layer type %d", l, t);
+        if (t == TS2_LAYER_FFN && d->ffn_tiles <= 0)
+            return fail(TS2_ERR_INVALID_ARG, "ffn layer with ffn_tiles = 0");
+        if (t == TS2_LAYER_ATT && (d->layers[l].attention_type_id < 0 || d->layers[l].attention_type_id >= d->attention_type_count))
+            return fail(TS2_ERR_INVALID_ARG, "layer %d: attention_type_id out of range", l);
+    }
+    return TS2_OK;
+}
+
+void shapes_of(const ts2_model_descr *d, std::vector<std::pair<int64_t, int64_t>> *out) // (x, y)
+{
+    const int64_t D = d->dim, Q = (int64_t)d->q_dim * d->head_count, TT = (int64_t)d->tt_dim * d->head_count, F = 128ll * d->ffn_tiles;
+    out->clear();
+    out->push_back({D, d->label_count});
+    out->push_back({D, d->output_token_count});
+    for (int l = 0; l < d->layer_count; ++l) {
+        switch (d->layers[l].layer_type) {
+        case TS2_LAYER_ATT:
+            out->push_back({D, Q});
+            out->push_back({D, Q});
+            out->push_back({D, TT});
+            out->push_back({D, TT});
+            out->push_back({TT, D});
+            break;
+        case TS2_LAYER_FFN:
+            out->push_back({D, F});
+            out->push_back({D, F});
+            out->push_back({F, D});
+            break;
+        case TS2_LAYER_MOE: {
+            const int64_t xp = d->expert_dim, e = d->moe_expert_count;
+            out->push_back({D, xp * e});
+            out->push_back({D, xp * e});
+            out->push_back({xp, D * e});
+            out->push_back({D, e});
+            break;
+        }
+        default:
+            break;
+        }
+    }
+}
+
+// ---- requantisation of every matrix + the scale vectors derived from the matrix scales ----
+int requantize_all(ts2_model *m)
+{
+    Ctx c = ctx_of(m);
+    const int D = m->D;
+    float *scratch = m->opt_scratch + 2 * m->max_rows; // doubles live behind the two float vectors
+    // embedding: always fp16 (TEmbedFloat, cfg_precision.h:62)
+    M_TRY(requantize(c, m->mats[0].w, D, m->mats[0].y, 1, m->embed16, D, nullptr, 0, m->mats[0].sko, scratch, false));
+    // final layer: fast copy for the logits, fp16 transposed copy of the same quantized values for dX
+    M_TRY(requantize(c, m->mats[1].w, D, m->V, m->ft, m->Wf, D, m->WfT16, m->V, m->mats[1].sko, scratch, m->ft == 0));
+    const size_t fs = fast_size(m);
+    const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
+    for (Layer &ly : m->layers) {
+        const int W = ly.wide, n = ly.ncat;
+        for (int j = 0; j < n; ++j) {
+            Matrix &mt = m->mats[ly.mat0 + j];
+            M_TRY(requantize(c, mt.w, D, W, m->ft, (uint8_t *)ly.Wcat + (size_t)j * W * D * fs, D, (uint8_t *)ly.WcatT + (size_t)j * W * fs,
+                             (int64_t)n * W, mt.sko, scratch, false));
+        }
+        Matrix &mc = m->mats[ly.mat0 + n];
+        M_TRY(requantize(c, mc.w, W, D, m->ft, ly.Wc, W, ly.WcT, D, mc.sko, scratch, false));
+        // forward column scales: matrices followed by a normalisation (Q, V, Expand) and the gates use the
+        // unit-RMS matrix q/32 (GetDataNoScale); K carries its matrix scale
+        M_TRY(fill_vector(c, ly.fwd_col, n * W, a, nullptr, false));
+        M_TRY(fill_vector(c, ly.bwd_row, n * W, 1.f, nullptr, false));
+        if (ly.type == TS2_LAYER_ATT) {
+            M_TRY(fill_vector(c, ly.fwd_col + W, W, a, m->mats[ly.mat0 + 1].sko, false));
+            for (int j = 0; j < 3; ++j) // dW rows of Q, K, V are divided by their matrix scale
+                M_TRY(fill_vector(c, ly.bwd_row + j * W, W, 1.f, m->mats[ly.mat0 + j].sko, true));
+        } else {
+            M_TRY(fill_vector(c, ly.bwd_row, W, 1.f, m->mats[ly.mat0].sko, true));
+        }
+    }
+    return TS2_OK;
+}
+
+int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const float *bias)
+{
+    const ts2_model_descr &d = m->descr;
+    m->D = d.dim;
+    m->H = d.head_count;
+    m->Q = 128 * d.head_count;
+    m->F = 128 * d.ffn_tiles;
+    m->V = d.output_token_count;
+    m->L = d.layer_count;
+    m->ft = d.precision == TS2_PREC_FP8 ? 0 : 1;
+    m->kind = m->ft == 0 ? KIND_E4M3 : KIND_F16;
+    m->s_act = m->ft == 0 ? 16.f : 1.f;
+    const int D = m->D, T = m->max_nodes, L = m->L;
+    const size_t fs = fast_size(m);
+
+    std::vector<std::pair<int64_t, int64_t>> shapes;
+    shapes_of(&d, &shapes);
+    if ((int)shapes.size() != n_mats)
+        return fail(TS2_ERR_INVALID_ARG, "expected %d matrices, got %d", (int)shapes.size(), n_mats);
+    m->mats.resize(n_mats);
+    size_t off = 0;
+    for (int i = 0; i < n_mats; ++i) {
+        if (!mats[i].data || mats[i].x_size != shapes[i].first || mats[i].y_size != shapes[i].second)
+            return fail(TS2_ERR_INVALID_ARG, "matrix %d: expected [%lld][%lld], got [%lld][%lld]", i, (long long)shapes[i].second,
+                        (long long)shapes[i].first, (long long)mats[i].y_size, (long long)mats[i].x_size);
+        Matrix &mt = m->mats[i];
+        mt.x = shapes[i].first;
+        mt.y = shapes[i].second;
+        mt.row_disp_size = (i < 2) ? (int)mt.y : 1; // per-row dispersion for embedding and final layer (model_params.cpp:150-151)
+        mt.offset = off;
+        off += (size_t)mt.x * mt.y;
+        m->max_rows = std::max(m->max_rows, mt.y);
+    }
+    m->total_params = off;
+    M_TRY(dalloc(m, &m->w_flat, off));
+    M_TRY(dalloc(m, &m->avg_flat, off));
+    M_TRY(dalloc(m, &m->grad_flat, off));
+    M_TRY(dalloc(m, &m->skos, n_mats));
+    TS2_CUDA(cudaMemsetAsync(m->avg_flat, 0, off * 4, m->stream));
+    TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, off * 4, m->stream));
+    for (int i = 0; i < n_mats; ++i) {
+        Matrix &mt = m->mats[i];
+        mt.w = m->w_flat + mt.offset;
+        mt.avg = m->avg_flat + mt.offset;
+        mt.grad = m->grad_flat + mt.offset;
+        mt.sko = m->skos + i;
+        M_TRY(dalloc(m, &mt.row_disp, mt.row_disp_size + 1));
+        mt.sum_weight = mt.row_disp + mt.row_disp_size;
+        TS2_CUDA(cudaMemsetAsync(mt.row_disp, 0, (mt.row_disp_size + 1) * 4, m->stream));
+        TS2_CUDA(cudaMemcpyAsync(mt.w, mats[i].data, (size_t)mt.x * mt.y * 4, cudaMemcpyHostToDevice, m->stream));
+    }
+    M_TRY(dalloc(m, &m->bias, m->V));
+    if (bias)
+        TS2_CUDA(cudaMemcpyAsync(m->bias, bias, (size_t)m->V * 4, cudaMemcpyHostToDevice, m->stream));
+    else
+        TS2_CUDA(cudaMemsetAsync(m->bias, 0, (size_t)m->V * 4, m->stream));
+
+    // quantized weights
+    M_TRY(dalloc(m, &m->embed16, (size_t)d.label_count * D));
+    M_TRY(dalloc(m, (uint8_t **)&m->Wf, (size_t)m->V * D * fs));
+    M_TRY(dalloc(m, &m->WfT16, (size_t)m->V * D));
+    m->layers.resize(L);
+    int mi = 2;
+    int max_wide = m->Q, max_cat = 4 * m->Q;
+    for (int l = 0; l < L; ++l) {
+        Layer &ly = m->layers[l];
+        ly.type = d.layers[l].layer_type;
+        ly.slope = d.layers[l].alibi_slope;
+        ly.att_type = d.layers[l].attention_type_id;
+        ly.mat0 = mi;
+        mi += layer_matrix_count(ly.type);
+        ly.wide = ly.type == TS2_LAYER_ATT ? m->Q : m->F;
+        ly.ncat = ly.type == TS2_LAYER_ATT ? 4 : 2;
+        max_wide = std::max(max_wide, ly.wide);
+        max_cat = std::max(max_cat, ly.ncat * ly.wide);
+        const size_t W = ly.wide, C = (size_t)ly.ncat * ly.wide;
+        M_TRY(dalloc(m, (uint8_t **)&ly.Wcat, C * D * fs));
+        M_TRY(dalloc(m, (uint8_t **)&ly.WcatT, C * D * fs));
+        M_TRY(dalloc(m, (uint8_t **)&ly.Wc, W * D * fs));
+        M_TRY(dalloc(m, (uint8_t **)&ly.WcT, W * D * fs));
+        M_TRY(dalloc(m, &ly.fwd_col, C));
+        M_TRY(dalloc(m, &ly.bwd_row, C));
+        M_TRY(dalloc(m, (uint8_t **)&ly.n_fast, (size_t)T * D * fs));
+        M_TRY(dalloc(m, &ly.cat16, (size_t)T * C));
+        M_TRY(dalloc(m, (uint8_t **)&ly.rg, (size_t)T * W * fs));
+        if (ly.type == TS2_LAYER_ATT) {
+            M_TRY(dalloc(m, &ly.q, (size_t)T * W));
+            M_TRY(dalloc(m, &ly.k, (size_t)T * W));
+            M_TRY(dalloc(m, &ly.v, (size_t)T * W));
+            M_TRY(dalloc(m, &ly.o, (size_t)T * W));
+            M_TRY(dalloc(m, &ly.qscale, (size_t)T * m->H));
+            M_TRY(dalloc(m, &ly.vscale, (size_t)T * m->H));
+            M_TRY(dalloc(m, &ly.lse, (size_t)T * m->H));
+        } else {
+            M_TRY(dalloc(m, &ly.what, (size_t)T * W));
+            M_TRY(dalloc(m, &ly.wscale, (size_t)T * (W / 128)));
+        }
+    }
+    // activations
+    m->states.resize(L + 1);
+    for (int l = 0; l <= L; ++l)
+        M_TRY(dalloc(m, &m->states[l], (size_t)T * D));
+    M_TRY(dalloc(m, &m->g, (size_t)T * D));
+    M_TRY(dalloc(m, &m->dn, (size_t)T * D));
+    M_TRY(dalloc(m, (uint8_t **)&m->g_fast, (size_t)T * D * fs));
+    M_TRY(dalloc(m, (uint8_t **)&m->nF_fast, (size_t)T * D * fs));
+    M_TRY(dalloc(m, &m->nF16, (size_t)T * D));
+    // the final layer is processed in chunks of nodes so that its logits stay a few hundred MB
+    m->chunk = std::min(T, std::max(128, (int)((size_t)(1u << 28) / (size_t)m->V) / 128 * 128));
+    M_TRY(dalloc(m, &m->logits, (size_t)m->chunk * m->V));
+    M_TRY(dalloc(m, &m->drg, (size_t)T * max_wide));
+    M_TRY(dalloc(m, &m->dout, (size_t)T * m->Q));
+    M_TRY(dalloc(m, (uint8_t **)&m->dcat, (size_t)T * max_cat * fs));
+    M_TRY(dalloc(m, &m->dscale, (size_t)T * m->H));
+    M_TRY(dalloc(m, &m->dq, (size_t)T * m->Q));
+    M_TRY(dalloc(m, &m->dk, (size_t)T * m->Q));
+    M_TRY(dalloc(m, &m->dv, (size_t)T * m->Q));
+    M_TRY(dalloc(m, &m->rope, (size_t)T * 128));
+    M_TRY(dalloc(m, &m->absmax, L + 2));
+    M_TRY(dalloc(m, &m->ginv, 4));
+    m->fscale = m->ginv + 1;
+    m->logp = m->ginv + 2;
+    M_TRY(dalloc(m, &m->opt_scratch, (size_t)m->max_rows * 4 + 16));
+    // batch
+    BatchDev &b = m->batch;
+    b.label_cap = (size_t)T * 4;
+    M_TRY(dalloc(m, &b.label_arr, b.label_cap));
+    M_TRY(dalloc(m, &b.label_ptr, (size_t)T + 1));
+    M_TRY(dalloc(m, &b.target, (size_t)T));
+    const int na = std::max(1, d.attention_type_count);
+    b.span_start.resize(na);
+    b.span_finish.resize(na);
+    b.rev_first.resize(na);
+    b.rev_last.resize(na);
+    for (int a = 0; a < na; ++a) {
+        M_TRY(dalloc(m, &b.span_start[a], (size_t)T));
+        M_TRY(dalloc(m, &b.span_finish[a], (size_t)T));
+        M_TRY(dalloc(m, &b.rev_first[a], (size_t)T));
+        M_TRY(dalloc(m, &b.rev_last[a], (size_t)T));
+    }
+    m->pinned_bytes = (b.label_cap + (size_t)T + 1 + (size_t)T + (size_t)na * 4 * T) * 4;
+    TS2_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes));
+
+    // split-K scratch: the largest request of any dW contraction of this model
+    size_t ws = 0;
+    for (Layer &ly : m->layers) {
+        ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, (int64_t)ly.ncat * ly.wide, D, T));
+        ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, D, ly.wide, T));
+    }
+    ws = std::max(ws, gemm_workspace_bytes(m->device, KIND_F16, true, m->V, D, m->chunk));
+    ws = std::max(ws, gemm_workspace_bytes(m->device, KIND_F16, true, m->V, D, 128));
+    // forward / dX contractions with few tiles (tiny models) may split as well
+    ws = std::max<size_t>(ws, (size_t)sm_count(m->device) * 128 * 256 * 4 * 2);
+    M_TRY(dalloc(m, (uint8_t **)&m->workspace, ws));
+    m->workspace_bytes = ws;
+
+    Ctx c = ctx_of(m);
+    M_TRY(fill_rope(c, m->rope, T));
+    M_TRY(requantize_all(m));
+    TS2_CUDA(cudaStreamSynchronize(m->stream));
+    return TS2_OK;
+}
+
+// ---- forward -------------------------------------------------------------------------
+int forward(ts2_model *m)
+{
+    Ctx c = ctx_of(m);
+    const int T = m->batch.node_count, D = m->D, H = m->H;
+    const BatchDev &b = m->batch;
+    M_TRY(embed_forward(c, m->embed16, m->mats[0].sko, b.label_arr, b.label_ptr, T, D, m->states[0]));
+    for (int l = 0; l < m->L; ++l) {
+        Layer &ly = m->layers[l];
+        const int W = ly.wide, C = ly.ncat * W;
+        M_TRY(tilenorm_forward(c, m->states[l], T, D, ly.n_fast, nullptr));
+        // [Q|K|V|Gate] or [wide|gate] = n . Wcat^T * sqrt(1/D)   (MulForward, cpu_util.cpp:7-27)
+        Epilogue e1;
+        e1.col_scale = ly.fwd_col;
+        e1.out_kind = TS2_OUT_F16;
+        M_TRY(gemm_tn(m, m->kind, T, C, D, ly.n_fast, D, ly.Wcat, D, ly.cat16, C, e1));
+        if (ly.type == TS2_LAYER_ATT) {
+            M_TRY(att_post_forward(c, ly.cat16, m->rope, T, H, ly.q, ly.k, ly.v, ly.qscale, ly.vscale));
+            M_TRY(attention_forward(c, ly.q, ly.k, ly.v, b.span_start[ly.att_type], b.span_finish[ly.att_type], T, H, ly.slope, ly.o, ly.lse));
+            M_TRY(att_gate_forward(c, ly.cat16, ly.o, T, W, ly.rg));
+        } else {
+            M_TRY(ffn_act_forward(c, ly.cat16, T, W, ly.what, ly.wscale, ly.rg));
+        }
+        // state_out = state_in + rg . Wc^T * sqrt(1/wide) with Wc = q * sko / 32
+        Epilogue e2;
+        e2.alpha = sqrtf(1.0f / W) / (m->s_act * 32.f);
+        e2.dyn_scale = m->mats[ly.mat0 + ly.ncat].sko;
+        e2.out_kind = TS2_OUT_F32_ADD;
+        e2.c_in = m->states[l];
+        M_TRY(gemm_tn(m, m->kind, T, D, W, ly.rg, W, ly.Wc, W, m->states[l + 1], D, e2));
+    }
+    M_TRY(tilenorm_forward(c, m->states[m->L], T, D, m->nF_fast, m->nF16));
+    return TS2_OK;
+}
+
+// logits of nodes [r0, r0+rows) -> softmax; with backward: dnF rows and the final-layer gradient
+int final_layer(ts2_model *m, bool backward)
+{
+    Ctx c = ctx_of(m);
+    const int T = m->batch.node_count, D = m->D, V = m->V;
+    const size_t fs = fast_size(m);
+    const float gscale = 1024.f;                           // keeps p ~ 1/V inside the fp16 normal range
+    const float gs = (1.f / LOG2F) * LOG2F;                // CalcFinalLayerMult() * LOG2, cpu_transformer.cpp:159
+    const bool tune_final = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_FINAL_LAYER);
+    TS2_CUDA(cudaMemsetAsync(m->logp, 0, 4, m->stream));
+    for (int r0 = 0; r0 < T; r0 += m->chunk) {
+        const int rows = std::min(m->chunk, T - r0);
+        Epilogue e;
+        e.alpha = sqrtf(1.0f / D) / (m->s_act * 32.f) * (1.f / LOG2F); // MulForward scale * CalcFinalLayerMult()
+        e.dyn_scale = m->mats[1].sko;
+        e.out_kind = TS2_OUT_F16;
+        M_TRY(gemm_tn(m, m->kind, rows, V, D, (const uint8_t *)m->nF_fast + (size_t)r0 * D * fs, D, m->Wf, D, m->logits, V, e));
+        M_TRY(softmax_ce(c, m->logits, rows, V, m->bias, m->batch.target + r0, gscale, m->logp, backward));
+        if (!backward)
+            continue;
+        // dnF = g . Wf * sqrt(1/D)   (MulBackwardWithAccum, cpu_transformer.cpp:163)
+        Epilogue ex;
+        ex.alpha = sqrtf(1.0f / D) / 32.f * gs / gscale;
+        ex.dyn_scale = m->mats[1].sko;
+        ex.out_kind = TS2_OUT_F32;
+        M_TRY(gemm_tn(m, KIND_F16, rows, D, V, m->logits, V, m->WfT16, V, m->dn + (size_t)r0 * D, D, ex));
+        if (tune_final) {
+            // dWf += g^T . nF   (SumRankOne, cpu_transformer.cpp:168)
+            Epilogue ew;
+            ew.alpha = gs / gscale;
+            ew.out_kind = TS2_OUT_F32_ADD;
+            M_TRY(gemm_dw(m, KIND_F16, V, D, rows, m->logits, V, m->nF16 + (size_t)r0 * D, D, m->mats[1].grad, ew));
+        }
+    }
+    return TS2_OK;
+}
+
+int tap_gradient(ts2_model *m, int boundary)
+{
+    if (!m->debug_taps)
+        return TS2_OK;
+    const size_t n = (size_t)m->batch.node_count * m->D;
+    TS2_CUDA(cudaMemcpyAsync(m->grad_taps + (size_t)boundary * m->max_nodes * m->D, m->g, n * 4, cudaMemcpyDeviceToDevice, m->stream));
+    return TS2_OK;
+}
+
+int backward(ts2_model *m)
+{
+    Ctx c = ctx_of(m);
+    const int T = m->batch.node_count, D = m->D, H = m->H, L = m->L;
+    const BatchDev &b = m->batch;
+    const bool tune_layers = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_LAYERS);
+    TS2_CUDA(cudaMemsetAsync(m->absmax, 0, (L + 2) * 4, m->stream));
+    M_TRY(final_layer(m, true));
+    M_TRY(tilenorm_backward(c, m->states[L], m->dn, nullptr, 1.f, T, D, m->g, false, m->absmax + L));
+    M_TRY(tap_gradient(m, L));
+    for (int l = L - 1; l >= 0; --l) {
+        Layer &ly = m->layers[l];
+        const int W = ly.wide, C = ly.ncat * W;
+        Matrix &mc = m->mats[ly.mat0 + ly.ncat];
+        // g_fast = g * 2^k; fscale = sqrt(D/W) * sko_c / 2^k turns the scale-free intermediate gradients
+        // below into true ones
+        M_TRY(cast_grad(c, m->g, (size_t)T * D, m->absmax + l + 1, m->g_fast, m->ginv, sqrtf((float)D / (float)W), mc.sko, m->fscale));
+        // drg (scale-free) = g_fast . (q_c/32) / sqrt(D): the true value is drg * fscale
+        // (MulBackwardWithAccum with the contract / combiner matrix)
+        Epilogue e3;
+        e3.alpha = 1.f / (32.f * sqrtf((float)D));
+        e3.out_kind = TS2_OUT_F16;
+        M_TRY(gemm_tn(m, m->kind, T, W, D, m->g_fast, D, ly.WcT, D, m->drg, W, e3));
+        if (tune_layers) {
+            // dWc = g^T . rg   (SumRankOne)
+            Epilogue e6;
+            e6.alpha = 1.f / m->s_act;
+            e6.dyn_scale = m->ginv;
+            e6.out_kind = TS2_OUT_F32_ADD;
+            M_TRY(gemm_dw(m, m->kind, D, W, T, m->g_fast, D, ly.rg, W, mc.grad, e6));
+        }
+        if (ly.type == TS2_LAYER_ATT) {
+            M_TRY(att_gate_backward(c, m->drg, ly.cat16, ly.o, T, W, m->dcat, m->dout, m->dscale));
+            M_TRY(attention_backward(c, ly.q, ly.k, ly.v, m->dout, ly.lse, m->dscale, b.span_start[ly.att_type], b.span_finish[ly.att_type],
+                                     b.rev_first[ly.att_type], b.rev_last[ly.att_type], T, H, ly.slope, m->dq, m->dk, m->dv));
+            M_TRY(att_post_backward(c, m->dq, m->dk, m->dv, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
+                                    m->dcat));
+        } else {
+            M_TRY(ffn_act_backward(c, m->drg, ly.cat16, ly.what, ly.wscale, T, W, m->dcat));
+        }
+        // dn (scale-free) = dcat . (q_cat/32) * sqrt(1/D)
+        Epilogue e4;
+        e4.alpha = sqrtf(1.0f / D) / 32.f;
+        e4.out_kind = TS2_OUT_F32;
+        M_TRY(gemm_tn(m, m->kind, T, D, C, m->dcat, C, ly.WcatT, C, m->dn, D, e4));
+        if (tune_layers) {
+            // dWcat = dcat^T . n * fscale, rows of matrices that are followed by a normalisation divided by sko
+            Epilogue e5;
+            e5.alpha = 1.f / m->s_act;
+            e5.dyn_scale = m->fscale;
+            e5.row_scale = ly.bwd_row;
+            e5.out_kind = TS2_OUT_F32_ADD;
+            M_TRY(gemm_dw(m, m->kind, C, D, T, m->dcat, C, ly.n_fast, D, m->mats[ly.mat0].grad, e5));
+        }
+        M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
+        M_TRY(tap_gradient(m, l));
+    }
+    if (!(m->descr.flags & TS2_MPF_DISABLE_TUNE_EMBED))
+        M_TRY(embed_backward(c, m->g, b.label_arr, b.label_ptr, T, D, m->mats[0].grad));
+    return TS2_OK;
+}
+
+int apply(ts2_model *m, const ts2_training_step *step)
+{
+    Ctx c = ctx_of(m);
+    if (m->comm && m->world > 1) {
+        // data-parallel sum of the flat gradient; ordered after the backward pass by an event
+        TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
+        TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
+        ncclResult_t r = ncclAllReduce(m->grad_flat, m->grad_flat, m->total_params, ncclFloat, ncclSum, m->comm, m->comm_stream);
+        if (r != ncclSuccess)
+            return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+        TS2_CUDA(cudaEventRecord(m->ev_reduced, m->comm_stream));
+        TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_reduced, 0));
+    }
+    for (Matrix &mt : m->mats) {
+        OptMatrix o;
+        o.w = mt.w;
+        o.avg_grad = mt.avg;
+        o.grad = mt.grad;
+        o.x = mt.x;
+        o.y = mt.y;
+        o.row_disp = mt.row_disp;
+        o.row_disp_size = mt.row_disp_size;
+        o.sum_weight = mt.sum_weight;
+        o.sparsity = mt.sparsity;
+        o.row_sum2 = m->opt_scratch;
+        o.row_scale = m->opt_scratch + m->max_rows;
+        o.w_sum2 = nullptr;
+        M_TRY(apply_gradient(c, o, *step));
+    }
+    M_TRY(requantize_all(m));
+    return TS2_OK;
+}
+
+// host side of ts2_set_batch: per-node arrays from the CSR inputs
+int stage_batch(ts2_model *m, const ts2_batch_nodes *nd)
+{
+    const int T = nd->node_count;
+    if (T <= 0 || T > m->max_nodes)
+        return fail(T > m->max_nodes ? TS2_ERR_TOO_LARGE : TS2_ERR_INVALID_ARG, "node_count %d outside (0, %d]", T, m->max_nodes);
+    if (!nd->label_ptr || (nd->label_ptr[T] && !nd->label_arr))
+        return fail(TS2_ERR_INVALID_ARG, "null label arrays");
+    const size_t n_labels = nd->label_ptr[T];
+    if (n_labels > m->batch.label_cap)
+        return fail(TS2_ERR_TOO_LARGE, "%zu labels exceed the capacity %zu", n_labels, m->batch.label_cap);
+    if (nd->attention_type_count < m->descr.attention_type_count)
+        return fail(TS2_ERR_INVALID_ARG, "batch has %d attention types, the model needs %d", nd->attention_type_count,
+                    m->descr.attention_type_count);
+    for (size_t i = 0; i < n_labels; ++i)
+        if ((nd->label_arr[i] & TS2_LABEL_MASK) >= (uint32_t)m->descr.label_count)
+            return fail(TS2_ERR_INVALID_ARG, "label %u out of range", nd->label_arr[i] & TS2_LABEL_MASK);
+    uint32_t *p = (uint32_t *)m->pinned;
+    uint32_t *h_label_arr = p;
+    p += m->batch.label_cap;
+    uint32_t *h_label_ptr = p;
+    p += (size_t)m->max_nodes + 1;
+    int *h_target = (int *)p;
+    p += m->max_nodes;
+    memcpy(h_label_arr, nd->label_arr, n_labels * 4);
+    memcpy(h_label_ptr, nd->label_ptr, ((size_t)T + 1) * 4);
+    for (int t = 0; t < T; ++t)
+        h_target[t] = -1;
+    for (int i = 0; i < nd->target_count; ++i) {
+        const int node = nd->target_node[i], id = nd->target_id[i];
+        if (node < 0 || node >= T || id < 0 || id >= m->V)
+            return fail(TS2_ERR_INVALID_ARG, "target %d: node %d / id %d out of range", i, node, id);
+        if (h_target[node] >= 0)
+            return fail(TS2_ERR_UNSUPPORTED, "node %d has more than one target", node);
+        h_target[node] = id;
+    }
+    const int na = m->descr.attention_type_count;
+    std::vector<int *> h_start(na), h_finish(na), h_first(na), h_last(na);
+    for (int a = 0; a < na; ++a) {
+        h_start[a] = (int *)p;
+        p += m->max_nodes;
+        h_finish[a] = (int *)p;
+        p += m->max_nodes;
+        h_first[a] = (int *)p;
+        p += m->max_nodes;
+        h_last[a] = (int *)p;
+        p += m->max_nodes;
+        const ts2_attention_info &ai = nd->att[a];
+        if (!ai.span_ptr)
+            return fail(TS2_ERR_INVALID_ARG, "attention type %d: null span_ptr", a);
+        bool monotone = true;
+        int ps = 0, pf = -1;
+        for (int t = 0; t < T; ++t) {
+            const int n = ai.span_ptr[t + 1] - ai.span_ptr[t];
+            if (n > 1)
+                return fail(TS2_ERR_UNSUPPORTED, "node %d has %d attention spans; at most one is supported", t, n);
+            int s = 0, f = -1;
+            if (n == 1) {
+                s = ai.span_start[ai.span_ptr[t]];
+                f = ai.span_finish[ai.span_ptr[t]];
+                if (s < 0 || f >= T || f < s)
+                    return fail(TS2_ERR_INVALID_ARG, "node %d: span [%d, %d] out of range", t, s, f);
+                if (s < ps || f < pf)
+                    monotone = false;
+                ps = s;
+                pf = f;
+            }
+            h_start[a][t] = s;
+            h_finish[a][t] = f;
+        }
+        // nodes that attend to key `to`: a superset range [first, last]; the kernels re-check each node's span
+        for (int to = 0; to < T; ++to) {
+            h_first[a][to] = T;
+            h_last[a][to] = -1;
+        }
+        if (monotone) {
+            // starts and finishes never decrease: the attending nodes of a key are contiguous
+            int lo = 0, hi = 0;
+            for (int to = 0; to < T; ++to) {
+                while (lo < T && (h_finish[a][lo] < to))
+                    ++lo; // first node whose span reaches `to` (empty spans have finish -1 ... but keep order)
+                if (hi < lo)
+                    hi = lo;
+                while (hi < T && (h_finish[a][hi] < h_start[a][hi] || h_start[a][hi] <= to))
+                    ++hi; // one past the last node whose span starts at or before `to`
+                h_first[a][to] = lo;
+                h_last[a][to] = hi - 1;
+            }
+        } else {
+            for (int t = 0; t < T; ++t)
+                for (int to = h_start[a][t]; to <= h_finish[a][t]; ++to) {
+                    h_first[a][to] = std::min(h_first[a][to], t);
+                    h_last[a][to] = std::max(h_last[a][to], t);
+                }
+        }
+    }
+    BatchDev &b = m->batch;
+    cudaStream_t s = m->stream;
+    TS2_CUDA(cudaMemcpyAsync(b.label_arr, h_label_arr, std::max<size_t>(n_labels, 1) * 4, cudaMemcpyHostToDevice, s));
+    TS2_CUDA(cudaMemcpyAsync(b.label_ptr, h_label_ptr, ((size_t)T + 1) * 4, cudaMemcpyHostToDevice, s));
+    TS2_CUDA(cudaMemcpyAsync(b.target, h_target, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    for (int a = 0; a < na; ++a) {
+        TS2_CUDA(cudaMemcpyAsync(b.span_start[a], h_start[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
+        TS2_CUDA(cudaMemcpyAsync(b.span_finish[a], h_finish[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
+        TS2_CUDA(cudaMemcpyAsync(b.rev_first[a], h_first[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
+        TS2_CUDA(cudaMemcpyAsync(b.rev_last[a], h_last[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    }
+    b.node_count = T;
+    b.target_count = nd->target_count;
+    return TS2_OK;
+}
+
+int wait_stream(ts2_model *m)
+{
+    // bounded wait: poll the stream for up to 120 s of wall time, then report a timeout
+    cudaError_t e;
+    const auto t0 = std::chrono::steady_clock::now();
+    while ((e = cudaStreamQuery(m->stream)) == cudaErrorNotReady) {
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 120.0)
+            return fail(TS2_ERR_TIMEOUT, "the device did not finish within 120 s");
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 0.002)
+            std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (e != cudaSuccess)
+        return fail(TS2_ERR_CUDA, "stream failed: %s", cudaGetErrorString(e));
+    int32_t *w = device_status_word(m->device);
+    int32_t v = 0;
+    TS2_CUDA(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
+    if (v) {
+        cudaMemset(w, 0, 4);
+        return fail(TS2_ERR_DEVICE_STATUS, "device status word = 0x%x (bit0: a bounded wait in a kernel timed out)", v);
+    }
+    return TS2_OK;
+}
+
+} // namespace
+
+// ---------------------------------------------------------------------------------------
+extern "C" {
+
+int ts2_matrix_count(const ts2_model_descr *descr)
+{
+    int rc = validate(descr);
+    if (rc != TS2_OK)
+        return rc;
+    std::vector<std::pair<int64_t, int64_t>> s;
+    shapes_of(descr, &s);
+    return (int)s.size();
+}
+
+int ts2_matrix_shape(const ts2_model_descr *descr, int index, int64_t *x_size, int64_t *y_size)
+{
+    int rc = validate(descr);
+    if (rc != TS2_OK)
+        return rc;
+    std::vector<std::pair<int64_t, int64_t>> s;
+    shapes_of(descr, &s);
+    if (index < 0 || index >= (int)s.size() || !x_size || !y_size)
+        return fail(TS2_ERR_INVALID_ARG, "matrix index %d out of range", index);
+    *x_size = s[index].first;
+    *y_size = s[index].second;
+    return TS2_OK;
+}
+
+int ts2_create(const ts2_model_descr *descr, const ts2_matrix_view *mats, int n_mats, const float *bias, int device, int max_nodes,
+               ts2_model **out)
+{
+    if (!out)
+        return fail(TS2_ERR_INVALID_ARG, "null out pointer");
+    *out = nullptr;
+    int rc = validate(descr);
+    if (rc != TS2_OK)
+        return rc;
+    if (!mats || max_nodes <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "null matrices or max_nodes <= 0");
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
+        return fail(TS2_ERR_NO_DEVICE, "no CUDA device: this library has no CPU fallback");
+    if (device < 0 || device >= n_dev)
+        return fail(TS2_ERR_INVALID_ARG, "device %d out of range (%d devices)", device, n_dev);
+    cudaDeviceProp prop;
+    TS2_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(TS2_ERR_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only", device, prop.major, prop.minor);
+    TS2_CUDA(cudaSetDevice(device));
+    ts2_model *m = new ts2_model();
+    m->descr = *descr;
+    m->layer_params.assign(descr->layers, descr->layers + descr->layer_count);
+    m->descr.layers = m->layer_params.data();
+    m->device = device;
+    m->max_nodes = (max_nodes + 127) / 128 * 128;
+    cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+    cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking);
+    cudaEventCreate(&m->ev_start);
+    cudaEventCreate(&m->ev_stop);
+    cudaEventCreate(&m->ev_t0);
+    cudaEventCreate(&m->ev_t1);
+    cudaEventCreateWithFlags(&m->ev_grads, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&m->ev_reduced, cudaEventDisableTiming);
+    rc = build_model(m, mats, n_mats, bias);
+    if (rc != TS2_OK) {
+        ts2_destroy(m);
+        return rc;
+    }
+    *out = m;
+    return TS2_OK;
+}
+
+void ts2_destroy(ts2_model *m)
+{
+    if (!m)
+        return;
+    cudaSetDevice(m->device);
+    cudaDeviceSynchronize();
+    if (m->comm)
+        ncclCommDestroy(m->comm);
+    for (void *p : m->allocs)
+        cudaFree(p);
+    if (m->pinned)
+        cudaFreeHost(m->pinned);
+    if (m->ev_start)
+        cudaEventDestroy(m->ev_start);
+    if (m->ev_stop)
+        cudaEventDestroy(m->ev_stop);
+    if (m->ev_t0)
+        cudaEventDestroy(m->ev_t0);
+    if (m->ev_t1)
+        cudaEventDestroy(m->ev_t1);
+    if (m->ev_grads)
+        cudaEventDestroy(m->ev_grads);
+    if (m->ev_reduced)
+        cudaEventDestroy(m->ev_reduced);
+    if (m->stream)
+        cudaStreamDestroy(m->stream);
+    if (m->comm_stream)
+        cudaStreamDestroy(m->comm_stream);
+    delete m;
+}
+
+const char *ts2_last_error(const ts2_model *m)
+{
+    if (m && !m->error.empty())
+        return m->error.c_str();
+    return global_error();
+}
+
+int ts2_set_batch(ts2_model *m, const ts2_batch_nodes *nodes)
+{
+    if (!m || !nodes)
+        return fail(TS2_ERR_INVALID_ARG, "null argument");
+    TS2_CUDA(cudaSetDevice(m->device));
+    // the staging buffer is reused: the previous copy must have left it
+    M_TRY(wait_stream(m));
+    M_TRY(stage_batch(m, nodes));
+    return TS2_OK;
+}
+
+int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model)
+{
+    if (!m || !step)
+        return fail(TS2_ERR_INVALID_ARG, "null argument");
+    if (m->batch.node_count <= 0)
+        return mfail(m, fail(TS2_ERR_INVALID_ARG, "ts2_backprop before ts2_set_batch"));
+    TS2_CUDA(cudaSetDevice(m->device));
+    TS2_CUDA(cudaEventRecord(m->ev_start, m->stream));
+    if (!m->grads_dirty)
+        TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, m->total_params * 4, m->stream));
+    M_TRY(forward(m));
+    M_TRY(backward(m));
+    m->grads_dirty = true;
+    m->last_targets = m->batch.target_count;
+    if (add_to_model == TS2_GRADIENT_APPLY) {
+        M_TRY(apply(m, step));
+        m->grads_dirty = false;
+    }
+    TS2_CUDA(cudaEventRecord(m->ev_stop, m->stream));
+    m->timing_valid = true;
+    return TS2_OK;
+}
+
+int ts2_wait(ts2_model *m)
+{
+    if (!m)
+        return fail(TS2_ERR_INVALID_ARG, "null model");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    return TS2_OK;
+}
+
+int ts2_forward_score(ts2_model *m, float *out_score)
+{
+    if (!m || !out_score)
+        return fail(TS2_ERR_INVALID_ARG, "null argument");
+    if (m->batch.node_count <= 0)
+        return mfail(m, fail(TS2_ERR_INVALID_ARG, "ts2_forward_score before ts2_set_batch"));
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(forward(m));
+    M_TRY(final_layer(m, false));
+    M_TRY(wait_stream(m));
+    float s = 0;
+    TS2_CUDA(cudaMemcpy(&s, m->logp, 4, cudaMemcpyDeviceToHost));
+    *out_score = m->batch.target_count ? s / m->batch.target_count : 0.f;
+    return TS2_OK;
+}
+
+int ts2_avg_train_err(ts2_model *m, float *out_err)
+{
+    if (!m || !out_err)
+        return fail(TS2_ERR_INVALID_ARG, "null argument");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    float s = 0;
+    TS2_CUDA(cudaMemcpy(&s, m->logp, 4, cudaMemcpyDeviceToHost));
+    *out_err = m->last_targets ? -s / m->last_targets : 0.f;
+    return TS2_OK;
+}
+
+int ts2_get_params(ts2_model *m, int what, ts2_matrix_view *mats_out, int n_mats)
+{
+    if (!m || !mats_out || n_mats != (int)m->mats.size())
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_params");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    for (int i = 0; i < n_mats; ++i) {
+        Matrix &mt = m->mats[i];
+        if (!mats_out[i].data)
+            continue;
+        if (mats_out[i].x_size != mt.x || mats_out[i].y_size != mt.y)
+            return mfail(m, fail(TS2_ERR_INVALID_ARG, "matrix %d: shape mismatch", i));
+        const float *src = what == TS2_PARAM_WEIGHTS ? mt.w : what == TS2_PARAM_MOMENTUM ? mt.avg : mt.grad;
+        TS2_CUDA(cudaMemcpy(mats_out[i].data, src, (size_t)mt.x * mt.y * 4, cudaMemcpyDeviceToHost));
+    }
+    return TS2_OK;
+}
+
+int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_mats)
+{
+    if (!m || !mats || n_mats != (int)m->mats.size() || what == TS2_PARAM_GRADIENT)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_set_params");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    for (int i = 0; i < n_mats; ++i) {
+        Matrix &mt = m->mats[i];
+        if (!mats[i].data)
+            continue;
+        if (mats[i].x_size != mt.x || mats[i].y_size != mt.y)
+            return mfail(m, fail(TS2_ERR_INVALID_ARG, "matrix %d: shape mismatch", i));
+        TS2_CUDA(cudaMemcpy(what == TS2_PARAM_WEIGHTS ? mt.w : mt.avg, mats[i].data, (size_t)mt.x * mt.y * 4, cudaMemcpyHostToDevice));
+    }
+    if (what == TS2_PARAM_WEIGHTS) {
+        M_TRY(requantize_all(m));
+        M_TRY(wait_stream(m));
+    }
+    return TS2_OK;
+}
+
+int ts2_get_row_disp(ts2_model *m, int index, float *row_disp, int64_t n, float *sum_weight)
+{
+    if (!m || index < 0 || index >= (int)m->mats.size())
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_row_disp");
+    Matrix &mt = m->mats[index];
+    if (n != mt.row_disp_size)
+        return fail(TS2_ERR_INVALID_ARG, "matrix %d has %d dispersion entries, caller passed %lld", index, mt.row_disp_size, (long long)n);
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    if (row_disp)
+        TS2_CUDA(cudaMemcpy(row_disp, mt.row_disp, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    if (sum_weight)
+        TS2_CUDA(cudaMemcpy(sum_weight, mt.sum_weight, 4, cudaMemcpyDeviceToHost));
+    return TS2_OK;
+}
+
+int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, float *matrix_scale)
+{
+    if (!m || index < 0 || index >= (int)m->mats.size() || !dst)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_fast_weights");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    Matrix &mt = m->mats[index];
+    const void *src = nullptr;
+    size_t es = fast_size(m);
+    if (index == 0) {
+        src = m->embed16;
+        es = 2;
+    } else if (index == 1) {
+        src = m->Wf;
+    } else {
+        for (Layer &ly : m->layers) {
+            const int j = index - ly.mat0;
+            if (j < 0 || j > ly.ncat)
+                continue;
+            src = j < ly.ncat ? (const void *)((const uint8_t *)ly.Wcat + (size_t)j * ly.wide * m->D * es) : ly.Wc;
+            break;
+        }
+    }
+    const size_t bytes = (size_t)mt.x * mt.y * es;
+    if (!src || dst_bytes < (int64_t)bytes)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_get_fast_weights: need %zu bytes", bytes);
+    TS2_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    if (matrix_scale)
+        TS2_CUDA(cudaMemcpy(matrix_scale, mt.sko, 4, cudaMemcpyDeviceToHost));
+    return TS2_OK;
+}
+
+int ts2_set_debug_taps(ts2_model *m, int enable)
+{
+    if (!m)
+        return fail(TS2_ERR_INVALID_ARG, "null model");
+    TS2_CUDA(cudaSetDevice(m->device));
+    if (enable && !m->grad_taps)
+        M_TRY(dalloc(m, &m->grad_taps, (size_t)(m->L + 1) * m->max_nodes * m->D));
+    m->debug_taps = enable != 0;
+    return TS2_OK;
+}
+
+int ts2_get_state_tap(ts2_model *m, int layer, int gradient, float *dst, int64_t n_floats)
+{
+    if (!m || !dst || layer < 0 || layer > m->L)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_state_tap");
+    const size_t n = (size_t)m->batch.node_count * m->D;
+    if ((size_t)n_floats < n)
+        return fail(TS2_ERR_INVALID_ARG, "tap needs %zu floats", n);
+    if (gradient && !m->grad_taps)
+        return fail(TS2_ERR_INVALID_ARG, "gradient taps were not enabled before the step");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    const float *src = gradient ? m->grad_taps + (size_t)layer * m->max_nodes * m->D : m->states[layer];
+    TS2_CUDA(cudaMemcpy(dst, src, n * 4, cudaMemcpyDeviceToHost));
+    return TS2_OK;
+}
+
+int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES])
+{
+    static_assert(sizeof(ncclUniqueId) <= TS2_COMM_ID_BYTES, "id buffer too small");
+    if (!id)
+        return fail(TS2_ERR_INVALID_ARG, "null id");
+    ncclUniqueId u;
+    ncclResult_t r = ncclGetUniqueId(&u);
+    if (r != ncclSuccess)
+        return fail(TS2_ERR_COMM, "ncclGetUniqueId failed: %s", ncclGetErrorString(r));
+    memset(id, 0, TS2_COMM_ID_BYTES);
+    memcpy(id, &u, sizeof(u));
+    return TS2_OK;
+}
+
+int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_COMM_ID_BYTES])
+{
+    if (!m || !id || world_size < 1 || rank < 0 || rank >= world_size)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_comm_init");
+    if (m->comm)
+        return fail(TS2_ERR_INVALID_ARG, "communicator already initialised");
+    TS2_CUDA(cudaSetDevice(m->device));
+    m->rank = rank;
+    m->world = world_size;
+    if (world_size == 1)
+        return TS2_OK;
+    ncclUniqueId u;
+    memcpy(&u, id, sizeof(u));
+    ncclResult_t r = ncclCommInitRank(&m->comm, world_size, u, rank);
+    if (r != ncclSuccess) {
+        m->comm = nullptr;
+        return mfail(m, fail(TS2_ERR_COMM, "ncclCommInitRank failed: %s", ncclGetErrorString(r)));
+    }
+    return TS2_OK;
+}
+
+int64_t ts2_launch_count(ts2_model *, int reset)
+{
+    long long v = reset ? g_launch_count.exchange(0) : g_launch_count.load();
+    return v;
+}
+
+int ts2_last_step_ms(ts2_model *m, float *ms)
+{
+    if (!m || !ms || !m->timing_valid)
+        return fail(TS2_ERR_INVALID_ARG, "no timed step");
+    TS2_CUDA(cudaSetDevice(m->device));
+    TS2_CUDA(cudaEventSynchronize(m->ev_stop));
+    TS2_CUDA(cudaEventElapsedTime(ms, m->ev_start, m->ev_stop));
+    return TS2_OK;
+}
+
+int ts2_timer_begin(ts2_model *m)
+{
+    if (!m)
+        return fail(TS2_ERR_INVALID_ARG, "null model");
+    TS2_CUDA(cudaSetDevice(m->device));
+    TS2_CUDA(cudaEventRecord(m->ev_t0, m->stream));
+    return TS2_OK;
+}
+
+int ts2_timer_end(ts2_model *m, float *ms)
+{
+    if (!m || !ms)
+        return fail(TS2_ERR_INVALID_ARG, "null argument");
+    TS2_CUDA(cudaSetDevice(m->device));
+    TS2_CUDA(cudaEventRecord(m->ev_t1, m->stream));
+    M_TRY(wait_stream(m));
+    TS2_CUDA(cudaEventElapsedTime(ms, m->ev_t0, m->ev_t1));
+    return TS2_OK;
+}
+
+int ts2_set_kernel_timing(ts2_model *, int enable)
+{
+    gemm_timing_enable(enable != 0);
+    return TS2_OK;
+}
+
+int ts2_get_kernel_timing(ts2_model *, int reset, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total)
+{
+    long long n = 0;
+    gemm_timing_get(reset != 0, gemm_ms_total, &n, gemm_flops_total);
+    if (gemm_launches)
+        *gemm_launches = n;
+    return TS2_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,145 @@
+"""Host-side mirror of the reference's IModel / IModelInstance (src/gpt/compute/model.h:22-56)
+over the C ABI.  Method names follow the reference: GetInstance().Init() is set_batch(),
+Backprop(), WaitAllCompute(), GetParams(), ComputeScore(), GetAvrgTrainErr()."""
+import ctypes as C
+from typing import List
+
+import numpy as np
+
+from . import capi, host
+from .device import check
+
+
+class Model:
+    """CreateLocalTransformer (src/gpt/compute/model.cu:257-264) for one B200 driven by this process."""
+
+    def __init__(self, spec: host.ModelSpec, mats: List[np.ndarray], max_nodes: int, device: int = 0, bias=None):
+        self.lib = capi.load_library()
+        self.spec = spec
+        self.device = device
+        descr, self._keep = spec.to_c()
+        views = host.matrix_views(mats)
+        h = C.c_void_p()
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32).ctypes.data_as(C.POINTER(C.c_float))
+        rc = self.lib.ts2_create(C.byref(descr), views, len(mats), b, device, max_nodes, C.byref(h))
+        if rc != capi.TS2_OK:
+            raise capi.Ts2Error(rc, self.lib.ts2_last_error(None).decode())
+        self.h = h
+        self.shapes = spec.matrix_shapes()
+
+    def _check(self, rc):
+        if rc != capi.TS2_OK:
+            raise capi.Ts2Error(rc, self.lib.ts2_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.ts2_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # IModelInstance::GetNodes + Init
+    def set_batch(self, batch: host.Batch):
+        self._check(self.lib.ts2_set_batch(self.h, C.byref(batch.c)))
+
+    # IModel::Backprop
+    def backprop(self, step: capi.TrainingStep, apply: bool = True):
+        self._check(self.lib.ts2_backprop(self.h, C.byref(step),
+                                          capi.GRADIENT_APPLY if apply else capi.GRADIENT_ACCUMULATE))
+
+    # IModel::WaitAllCompute
+    def wait(self):
+        self._check(self.lib.ts2_wait(self.h))
+
+    # IModelInstance::ComputeScore
+    def compute_score(self) -> float:
+        v = C.c_float()
+        self._check(self.lib.ts2_forward_score(self.h, C.byref(v)))
+        return v.value
+
+    # IModel::GetAvrgTrainErr
+    def avg_train_err(self) -> float:
+        v = C.c_float()
+        self._check(self.lib.ts2_avg_train_err(self.h, C.byref(v)))
+        return v.value
+
+    def _get(self, what):
+        outs = [np.empty(s, np.float32) for s in self.shapes]
+        self._check(self.lib.ts2_get_params(self.h, what, host.matrix_views(outs), len(outs)))
+        return outs
+
+    def get_weights(self):
+        return self._get(capi.PARAM_WEIGHTS)
+
+    def get_momentum(self):
+        return self._get(capi.PARAM_MOMENTUM)
+
+    def get_gradients(self):
+        """fp32 weight gradients of the last backprop, before the optimizer: the tensors the
+        reference hands to HostApplyDelta."""
+        return self._get(capi.PARAM_GRADIENT)
+
+    def set_weights(self, mats):
+        self._check(self.lib.ts2_set_params(self.h, capi.PARAM_WEIGHTS, host.matrix_views(mats), len(mats)))
+
+    def get_row_disp(self, index):
+        n = self.shapes[index][0] if index < 2 else 1
+        rd = np.empty(n, np.float32)
+        sw = C.c_float()
+        self._check(self.lib.ts2_get_row_disp(self.h, index, rd.ctypes.data_as(C.POINTER(C.c_float)), n, C.byref(sw)))
+        return rd, sw.value
+
+    def get_fast_weights(self, index):
+        y, x = self.shapes[index]
+        dt = np.float16 if (index == 0 or self.spec.precision == capi.PREC_F16) else np.uint8
+        out = np.empty((y, x), dt)
+        sko = C.c_float()
+        self._check(self.lib.ts2_get_fast_weights(self.h, index, out.ctypes.data, out.nbytes, C.byref(sko)))
+        return out, sko.value
+
+    def set_debug_taps(self, enable=True):
+        self._check(self.lib.ts2_set_debug_taps(self.h, int(enable)))
+
+    def get_state_tap(self, layer, gradient, node_count):
+        out = np.empty((node_count, self.spec.dim), np.float32)
+        self._check(self.lib.ts2_get_state_tap(self.h, layer, int(gradient), out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
+
+    def comm_init(self, rank, world, id_bytes):
+        buf = (C.c_uint8 * capi.COMM_ID_BYTES).from_buffer_copy(id_bytes)
+        self._check(self.lib.ts2_comm_init(self.h, rank, world, buf))
+
+    def last_step_ms(self):
+        v = C.c_float()
+        self._check(self.lib.ts2_last_step_ms(self.h, C.byref(v)))
+        return v.value
+
+    def timer_begin(self):
+        self._check(self.lib.ts2_timer_begin(self.h))
+
+    def timer_end(self) -> float:
+        v = C.c_float()
+        self._check(self.lib.ts2_timer_end(self.h, C.byref(v)))
+        return v.value
+
+    def set_kernel_timing(self, enable=True):
+        self._check(self.lib.ts2_set_kernel_timing(self.h, int(enable)))
+
+    def get_kernel_timing(self, reset=False):
+        ms, n, fl = C.c_double(), C.c_int64(), C.c_double()
+        self._check(self.lib.ts2_get_kernel_timing(self.h, int(reset), C.byref(ms), C.byref(n), C.byref(fl)))
+        return ms.value, n.value, fl.value
+
+    def launch_count(self, reset=False):
+        return self.lib.ts2_launch_count(self.h, int(reset))
+
+
+def comm_unique_id() -> bytes:
+    lib = capi.load_library()
+    buf = (C.c_uint8 * capi.COMM_ID_BYTES)()
+    check(lib.ts2_comm_unique_id(buf))
+    return bytes(buf)
