@@ -258,6 +258,20 @@ size_t ts2_gemm_dw_workspace_bytes(int64_t T, int64_t in_dim, int64_t out_dim);
 int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
                 const void *dY, const void *X, void *dW, float alpha, void *workspace, size_t workspace_bytes);
 
+/* Attention core of one layer over one inclusive key span per node (span_finish < span_start: none):
+ * ComputeValLookup / GradQ / GradK, src/gpt/compute/layer_att_reference.h:41-212; Fp16Att,
+ * Fp16AttGradQ, Fp16AttGradKV, src/gpt/compute/gpu_att_fp16.cu:41-215, gpu_att_fp16.cuh:60-358.
+ * q (normalized, rotated), k (rotated), v (normalized), o, dout: fp16 [T][128*head_count] on the
+ * device; lse[T][head_count] = maxDP + log2(sumWeight); dscale[T][head_count] = sum(dout * o);
+ * dq, dk, dv fp32 [T][128*head_count]; span arrays are host arrays.  variant 0: tensor-core
+ * kernels (what the engine runs); 1: warp-per-row fp32 formulation (second opinion for tests). */
+int ts2_attention_forward(int device, void *stream, int variant, const void *q, const void *k, const void *v,
+                          const int32_t *span_start, const int32_t *span_finish, int T, int head_count, float alibi_slope,
+                          void *o, float *lse);
+int ts2_attention_backward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const void *dout,
+                           const float *lse, const float *dscale, const int32_t *span_start, const int32_t *span_finish, int T,
+                           int head_count, float alibi_slope, float *dq, float *dk, float *dv);
+
 #ifdef __cplusplus
 }
 #endif

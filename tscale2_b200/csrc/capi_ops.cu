@@ -1,9 +1,50 @@
 // extern "C" operator-level entry points of include/ts2_b200.h (device helpers and
 // the contraction kernels).  Plain pointers and sizes only.
 #include "gemm.cuh"
+#include "kernels.cuh"
+#include <vector>
 
 namespace ts2 {
 const char *global_error();
+
+void attention_reverse_ranges(const int *span_start, const int *span_finish, int T, int *rev_first, int *rev_last)
+{
+    for (int to = 0; to < T; ++to) {
+        rev_first[to] = T;
+        rev_last[to] = -1;
+    }
+    bool monotone = true;
+    int ps = 0, pf = -1;
+    for (int t = 0; t < T; ++t) {
+        if (span_finish[t] < span_start[t])
+            continue;
+        if (span_start[t] < ps || span_finish[t] < pf)
+            monotone = false;
+        ps = span_start[t];
+        pf = span_finish[t];
+    }
+    if (monotone) {
+        // starts and finishes never decrease over the nodes that have a span: the nodes attending to a
+        // key are contiguous up to span-less nodes in between
+        int lo = 0, hi = 0;
+        for (int to = 0; to < T; ++to) {
+            while (lo < T && span_finish[lo] < to)
+                ++lo; // first node whose span reaches `to` (span-less nodes have finish -1)
+            if (hi < lo)
+                hi = lo;
+            while (hi < T && (span_finish[hi] < span_start[hi] || span_start[hi] <= to))
+                ++hi; // one past the last node whose span starts at or before `to`
+            rev_first[to] = lo;
+            rev_last[to] = hi - 1;
+        }
+    } else {
+        for (int t = 0; t < T; ++t)
+            for (int to = span_start[t]; to <= span_finish[t]; ++to) {
+                rev_first[to] = std::min(rev_first[to], t);
+                rev_last[to] = std::max(rev_last[to], t);
+            }
+    }
+}
 }
 using namespace ts2;
 
@@ -150,6 +191,56 @@ int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int
     a.workspace = workspace;
     a.workspace_bytes = workspace_bytes;
     return gemm(a);
+}
+
+// attention core on device arrays; span_start / span_finish are host arrays of T ints
+int ts2_attention_forward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const int32_t *span_start,
+                          const int32_t *span_finish, int T, int head_count, float alibi_slope, void *o, float *lse)
+{
+    if (T <= 0 || head_count <= 0 || !q || !k || !v || !o || !lse || !span_start || !span_finish)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_attention_forward: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    int *d = nullptr;
+    TS2_CUDA(cudaMalloc(&d, (size_t)T * 8));
+    TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
+    TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
+    Ctx c;
+    c.device = device;
+    c.stream = (cudaStream_t)stream;
+    int rc = variant == 0 ? attention_forward_mma(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
+                                                  alibi_slope, (__half *)o, lse)
+                          : attention_forward_rowwise(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
+                                                      alibi_slope, (__half *)o, lse);
+    cudaStreamSynchronize(c.stream);
+    cudaFree(d);
+    return rc;
+}
+
+int ts2_attention_backward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const void *dout,
+                           const float *lse, const float *dscale, const int32_t *span_start, const int32_t *span_finish, int T,
+                           int head_count, float alibi_slope, float *dq, float *dk, float *dv)
+{
+    if (T <= 0 || head_count <= 0 || !q || !k || !v || !dout || !lse || !dscale || !span_start || !span_finish || !dq || !dk || !dv)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_attention_backward: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    std::vector<int> rev(2 * (size_t)T);
+    attention_reverse_ranges(span_start, span_finish, T, rev.data(), rev.data() + T);
+    int *d = nullptr;
+    TS2_CUDA(cudaMalloc(&d, (size_t)T * 16));
+    TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
+    TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
+    TS2_CUDA(cudaMemcpy(d + 2 * (size_t)T, rev.data(), (size_t)T * 8, cudaMemcpyHostToDevice));
+    Ctx c;
+    c.device = device;
+    c.stream = (cudaStream_t)stream;
+    const __half *Q = (const __half *)q, *K = (const __half *)k, *V = (const __half *)v, *DO = (const __half *)dout;
+    int rc = variant == 0 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
+                                                   dq, dk, dv)
+                          : attention_backward_rowwise(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count,
+                                                       alibi_slope, dq, dk, dv);
+    cudaStreamSynchronize(c.stream);
+    cudaFree(d);
+    return rc;
 }
 
 } // extern "C"

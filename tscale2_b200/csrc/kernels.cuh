@@ -71,6 +71,20 @@ int attention_backward(const Ctx &c, const __half *q, const __half *k, const __h
                        const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
                        int T, int H, float slope, float *dq, float *dk, float *dv);
 
+// the two formulations behind attention_forward / attention_backward
+int attention_forward_mma(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
+                          int T, int H, float slope, __half *o, float *lse);
+int attention_backward_mma(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                           const float *dscale, const int *span_start, const int *span_finish, const int *rev_first,
+                           const int *rev_last, int T, int H, float slope, float *dq, float *dk, float *dv);
+int attention_forward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start,
+                              const int *span_finish, int T, int H, float slope, __half *o, float *lse);
+int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                               const float *dscale, const int *span_start, const int *span_finish, const int *rev_first,
+                               const int *rev_last, int T, int H, float slope, float *dq, float *dk, float *dv);
+// host: for every key the range [first, last] of nodes whose span may contain it (a superset; kernels re-check)
+void attention_reverse_ranges(const int *span_start, const int *span_finish, int T, int *rev_first, int *rev_last);
+
 // ---- kernels_opt.cu ----------------------------------------------------------------
 // MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel (agpu_cuda.cu:32-134), one matrix.
 struct OptMatrix {

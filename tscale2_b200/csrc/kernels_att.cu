@@ -3,7 +3,9 @@
 // (ComputeValLookup / GradQ / GradK, src/gpt/compute/layer_att_reference.h:41-212):
 //   dp(from,to) = q_from . k_to * sqrt(1/128) * 0.5/ln2 - slope * (from - to)
 //   weights 2^(dp - maxDP) with maxDP >= 0 and an extra zero vector of weight 2^-maxDP.
-// This file holds the warp-per-row formulation (fp32 math, coalesced 8-byte loads).
+// This file holds the warp-per-row formulation (fp32 math, coalesced 8-byte loads), kept as an
+// independent second formulation for the tests; the engine runs the tensor-core kernels of
+// kernels_att_mma.cu.
 #include "kernels.cuh"
 #include "fast_types.cuh"
 
@@ -166,8 +168,8 @@ __global__ void attention_forward_kernel(const __half *__restrict__ q, const __h
     }
 }
 
-int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
-                      int T, int H, float slope, __half *o, float *lse)
+int attention_forward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start,
+                              const int *span_finish, int T, int H, float slope, __half *o, float *lse)
 {
     attention_forward_kernel<<<grid_for(c, (long long)T * H), THREADS, 0, c.stream>>>(q, k, v, span_start, span_finish, T, H, slope, o, lse);
     TS2_CHECK_LAUNCH();
@@ -228,9 +230,9 @@ __global__ void attention_dkv_kernel(const __half *__restrict__ q, const __half 
     }
 }
 
-int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
-                       const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                       int T, int H, float slope, float *dq, float *dk, float *dv)
+int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                               const float *dscale, const int *span_start, const int *span_finish, const int *rev_first,
+                               const int *rev_last, int T, int H, float slope, float *dq, float *dk, float *dv)
 {
     const int grid = grid_for(c, (long long)T * H);
     attention_dq_kernel<<<grid, THREADS, 0, c.stream>>>(q, k, v, dout, lse, dscale, span_start, span_finish, T, H, slope, dq);
@@ -239,6 +241,19 @@ int attention_backward(const Ctx &c, const __half *q, const __half *k, const __h
                                                          slope, dk, dv);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
+}
+
+int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
+                      int T, int H, float slope, __half *o, float *lse)
+{
+    return attention_forward_mma(c, q, k, v, span_start, span_finish, T, H, slope, o, lse);
+}
+
+int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                       const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
+                       int T, int H, float slope, float *dq, float *dk, float *dv)
+{
+    return attention_backward_mma(c, q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H, slope, dq, dk, dv);
 }
 
 } // namespace ts2

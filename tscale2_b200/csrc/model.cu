@@ -687,8 +687,6 @@ int stage_batch(ts2_model *m, const ts2_batch_nodes *nd)
         const ts2_attention_info &ai = nd->att[a];
         if (!ai.span_ptr)
             return fail(TS2_ERR_INVALID_ARG, "attention type %d: null span_ptr", a);
-        bool monotone = true;
-        int ps = 0, pf = -1;
         for (int t = 0; t < T; ++t) {
             const int n = ai.span_ptr[t + 1] - ai.span_ptr[t];
             if (n > 1)
@@ -699,39 +697,11 @@ int stage_batch(ts2_model *m, const ts2_batch_nodes *nd)
                 f = ai.span_finish[ai.span_ptr[t]];
                 if (s < 0 || f >= T || f < s)
                     return fail(TS2_ERR_INVALID_ARG, "node %d: span [%d, %d] out of range", t, s, f);
-                if (s < ps || f < pf)
-                    monotone = false;
-                ps = s;
-                pf = f;
             }
             h_start[a][t] = s;
             h_finish[a][t] = f;
         }
-        // nodes that attend to key `to`: a superset range [first, last]; the kernels re-check each node's span
-        for (int to = 0; to < T; ++to) {
-            h_first[a][to] = T;
-            h_last[a][to] = -1;
-        }
-        if (monotone) {
-            // starts and finishes never decrease: the attending nodes of a key are contiguous
-            int lo = 0, hi = 0;
-            for (int to = 0; to < T; ++to) {
-                while (lo < T && (h_finish[a][lo] < to))
-                    ++lo; // first node whose span reaches `to` (empty spans have finish -1 ... but keep order)
-                if (hi < lo)
-                    hi = lo;
-                while (hi < T && (h_finish[a][hi] < h_start[a][hi] || h_start[a][hi] <= to))
-                    ++hi; // one past the last node whose span starts at or before `to`
-                h_first[a][to] = lo;
-                h_last[a][to] = hi - 1;
-            }
-        } else {
-            for (int t = 0; t < T; ++t)
-                for (int to = h_start[a][t]; to <= h_finish[a][t]; ++to) {
-                    h_first[a][to] = std::min(h_first[a][to], t);
-                    h_last[a][to] = std::max(h_last[a][to], t);
-                }
-        }
+        attention_reverse_ranges(h_start[a], h_finish[a], T, h_first[a], h_last[a]);
     }
     BatchDev &b = m->batch;
     cudaStream_t s = m->stream;
