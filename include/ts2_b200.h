@@ -258,6 +258,21 @@ size_t ts2_gemm_dw_workspace_bytes(int64_t T, int64_t in_dim, int64_t out_dim);
 int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
                 const void *dY, const void *X, void *dW, float alpha, void *workspace, size_t workspace_bytes);
 
+/* The same contraction as ts2_gemm_dw for callers that must not allocate device memory — a host
+ * whose own pools took all of it at start-up, or a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation.  (No counterpart in the reference: its kernels get scratch from the trainer's
+ * pool allocator.)  The split-K scratch is a fixed 16 MiB array inside the library image, present on
+ * every GPU that loads the library; a shape whose partial tiles need more is refused with
+ * TS2_ERR_TOO_LARGE and belongs to ts2_gemm_dw.  The call runs no cudaMalloc / cudaFree and no
+ * allocating library routine.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) and sets the kernel's shared-memory attribute; make that first call
+ * before any stream capture.  All calls share the one array and it keeps whatever the last call
+ * left there (nothing needs to start at zero: each partial tile is fully rewritten before it is
+ * read), so two calls that overlap on the GPU — different streams, or different host threads —
+ * race; serialise them on one stream.  out_kind: TS2_OUT_F32 or TS2_OUT_F32_ADD. */
+int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                        const void *dY, const void *X, void *dW, float alpha);
+
 /* Attention core of one layer over one inclusive key span per node (span_finish < span_start: none):
  * ComputeValLookup / GradQ / GradK, src/gpt/compute/layer_att_reference.h:41-212; Fp16Att,
  * Fp16AttGradQ, Fp16AttGradKV, src/gpt/compute/gpu_att_fp16.cu:41-215, gpu_att_fp16.cuh:60-358.

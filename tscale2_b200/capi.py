@@ -119,6 +119,7 @@ def _declare(lib):
         "ts2_gemm_tn": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, f32, vp, vp]),
         "ts2_gemm_dx": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, vp]),
         "ts2_gemm_dw_workspace_bytes": (C.c_size_t, [i64, i64, i64]),
+        "ts2_gemm_dw_noalloc": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32]),
         "ts2_attention_forward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp]),
         "ts2_attention_backward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),

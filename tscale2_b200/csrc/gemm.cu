@@ -681,4 +681,114 @@ int gemm(const GemmArgs &a)
     return rc;
 }
 
+// ---------------------------------------------------------------------------------
+// dW contraction for callers that may not allocate.
+//
+// Some hosts hand every byte of device memory to their own pools when they start (the trainer this
+// library plugs into does) or run a steady-state loop in which cudaMalloc's device-wide
+// synchronisation would stall their other streams; for them a kernel whose scratch has to be
+// cudaMalloc'ed by someone is unusable.  This variant of ts2_gemm_dw keeps the split-K scratch in
+// a fixed array inside the library image instead.
+static constexpr size_t STATIC_SCRATCH_BYTES = 16u << 20; // 16 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+static __device__ int g_static_status; // bit 0: a bounded wait in the kernel gave up
+
+struct StaticScratch {
+    bool ready = false;
+    float *scratch = nullptr; // device address of g_static_scratch on this device
+    int32_t *status = nullptr;
+};
+static StaticScratch g_static[16];
+static std::mutex g_static_mu;
+
 } // namespace ts2
+
+using namespace ts2;
+
+extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                                   const void *dY, const void *X, void *dW, float alpha)
+{
+    const int kind = prec == TS2_PREC_FP8 ? KIND_E4M3 : prec == TS2_PREC_F16 ? KIND_F16 : prec == TS2_PREC_INT8 ? KIND_I8 : -1;
+    if (kind < 0)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: unknown precision %d", prec);
+    if (T <= 0 || in_dim <= 0 || out_dim <= 0 || !dY || !X || !dW)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: empty problem or null pointer");
+    if (in_dim % 32)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: in_dim must be a multiple of 32 (got %lld)", (long long)in_dim);
+    if (out_kind != TS2_OUT_F32 && out_kind != TS2_OUT_F32_ADD)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: the gradient is fp32 (TS2_OUT_F32 or TS2_OUT_F32_ADD)");
+    if (T >= (1ll << 31) || in_dim >= (1ll << 31) || out_dim >= (1ll << 31))
+        return fail(TS2_ERR_TOO_LARGE, "ts2_gemm_dw_noalloc: dimension exceeds 2^31");
+    if (((uintptr_t)dW & 15) || ((in_dim * 4) & 15))
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: output base and pitch must be multiples of 16 bytes");
+    if (device < 0 || device >= 16)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: device %d out of range", device);
+    TS2_CUDA(cudaSetDevice(device));
+    StaticScratch st;
+    {
+        // set-up, once per device, with that device current: in host code the array's name is only a
+        // handle; the address a kernel can use comes from cudaGetSymbolAddress
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        StaticScratch &slot = g_static[device];
+        if (!slot.ready) {
+            void *p = nullptr, *q = nullptr;
+            TS2_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+            TS2_CUDA(cudaGetSymbolAddress(&q, g_static_status));
+            slot.scratch = (float *)p;
+            slot.status = (int32_t *)q;
+            slot.ready = true;
+        }
+        st = slot;
+    }
+    const Plan pl = make_plan(device, kind, true, out_dim, in_dim, T);
+    const size_t need = pl.splits > 1 ? (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float) : 0;
+    if (need > STATIC_SCRATCH_BYTES)
+        return fail(TS2_ERR_TOO_LARGE,
+                    "ts2_gemm_dw_noalloc: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
+                    "use ts2_gemm_dw with a caller-provided workspace",
+                    need, STATIC_SCRATCH_BYTES);
+    const int es = elem_size(kind), bk = STAGE_ROW_BYTES / es;
+    CUtensorMap tmA, tmB;
+    int rc;
+    if ((rc = make_tmap(&tmA, dY, es, out_dim, T, out_dim, bk)) != TS2_OK)
+        return rc;
+    if ((rc = make_tmap(&tmB, X, es, in_dim, T, in_dim, bk)) != TS2_OK)
+        return rc;
+    GemmParams p;
+    p.M = (int)out_dim;
+    p.N = (int)in_dim;
+    p.m_tiles = pl.m_tiles;
+    p.n_tiles = pl.n_tiles;
+    p.splits = pl.splits;
+    p.k_blocks = pl.k_blocks;
+    p.kb_per_split = pl.kb_per_split;
+    p.idesc = instr_desc(kind, true, pl.bn);
+    p.C = dW;
+    p.ldc = in_dim;
+    p.alpha = alpha;
+    p.dyn_scale = p.dyn_scale2 = p.row_scale = p.col_scale = nullptr;
+    p.c_in = (const float *)dW;
+    p.out_kind = out_kind;
+    // every (tile, split) unit overwrites its whole partial tile before the reduction reads it, so
+    // nothing in the scratch has to start at zero; the status word is only ever OR-ed into
+    p.workspace = st.scratch;
+    p.status = st.status;
+    GemmArgs a;
+    a.device = device;
+    a.stream = (cudaStream_t)stream;
+    const int mma = (kind == KIND_E4M3) ? 0 : (kind == KIND_I8 ? 2 : 1);
+    rc = TS2_ERR_UNSUPPORTED;
+#define TS2_NOALLOC_CASE(BN_, ES_, MMA_)             \
+    if (pl.bn == BN_ && es == ES_ && mma == MMA_)    \
+        rc = launch<BN_, ES_, MMA_, true>(a, pl, tmA, tmB, p);
+    TS2_NOALLOC_CASE(256, 1, 0)
+    TS2_NOALLOC_CASE(128, 1, 0)
+    TS2_NOALLOC_CASE(256, 2, 1)
+    TS2_NOALLOC_CASE(128, 2, 1)
+    TS2_NOALLOC_CASE(256, 1, 2)
+    TS2_NOALLOC_CASE(128, 1, 2)
+#undef TS2_NOALLOC_CASE
+    if (rc == TS2_ERR_UNSUPPORTED)
+        return fail(rc, "ts2_gemm_dw_noalloc: unsupported configuration");
+    return rc;
+}
