@@ -188,6 +188,9 @@ int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, 
  * same boundary captured during the last ts2_backprop (enabled by
  * ts2_set_debug_taps before the call; costs one copy per layer). */
 int ts2_set_debug_taps(ts2_model *m, int enable);
+/* raw copy of an internal per-layer buffer after the last step, for tests: "rg", "dcat", "cat16", "n_fast",
+ * "n_rows", "logits", "ids", "weights", "slot_of", "token_of", "seg_ptr", "moe_g", "drg" (the caller knows the layout) */
+int ts2_debug_read(ts2_model *m, const char *name, int layer, void *dst, int64_t bytes);
 int ts2_get_state_tap(ts2_model *m, int layer, int gradient, float *dst, int64_t n_floats);
 
 /* ------------------------------------------------------------------------- */
@@ -272,6 +275,25 @@ int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int
  * race; serialise them on one stream.  out_kind: TS2_OUT_F32 or TS2_OUT_F32_ADD. */
 int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
                         const void *dY, const void *X, void *dW, float alpha);
+
+/* Grouped forms of the two contractions for expert-sorted rows (the reference's grouped mma.sync
+ * GEMMs with GridZ = experts, src/gpt/compute/moe_matmul.cuh:255-291).  Rows are sorted by expert and each
+ * expert's segment is padded to a multiple of 128 rows.
+ *   ts2_gemm_tn_grouped: C[rows][N] = alpha * A[rows][K] . B[g][N][K]^T where g = tile_group[row / 128]
+ *     (device int array, negative: the tile is skipped and its C rows are left untouched);
+ *   ts2_gemm_dw_grouped: dW[g][out][in] (+)= alpha * dY[seg]^T . X[seg] over the rows
+ *     seg = [seg_ptr[g], seg_ptr[g+1]) (device int array of groups + 1 multiples of 128; empty segments
+ *     leave dW[g] untouched). */
+int ts2_gemm_tn_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t N, int64_t K, const void *A,
+                        const void *B, void *C, float alpha, int groups, const int32_t *tile_group);
+int ts2_gemm_dw_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t in_dim, int64_t out_dim,
+                        const void *dY, const void *X, void *dW, float alpha, int groups, const int32_t *seg_ptr);
+
+/* Expert selection of a mixture-of-experts layer (CpuMoe, src/gpt/compute/layer_moe.cu:287-328;
+ * MoeCalcSampleExpertLists, src/gpt/compute/moe_kernels.cu:54-104): the `selected` largest logits per
+ * node (lowest index wins ties), weights exp((l - lmax)/2) scaled to L2 norm sqrt(expert_count).
+ * Host arrays: logits [T][expert_count] -> ids [T][selected], weights [T][selected]. */
+int ts2_moe_route(int device, const float *logits, int T, int expert_count, int selected, int32_t *ids, float *weights);
 
 /* Attention core of one layer over one inclusive key span per node (span_finish < span_start: none):
  * ComputeValLookup / GradQ / GradK, src/gpt/compute/layer_att_reference.h:41-212; Fp16Att,

@@ -133,3 +133,42 @@ def test_rejects_bad_arguments(lib):
     assert rc == capi.TS2_ERR_INVALID_ARG
     rc = lib.ts2_gemm_tn(0, None, 9, capi.OUT_F32, 128, 128, 128, A.ptr, 128, A.ptr, 128, A.ptr, 128, 1.0, None, None)
     assert rc == capi.TS2_ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("prec", [capi.PREC_FP8, capi.PREC_F16])
+def test_grouped_contractions(lib, prec):
+    """Expert-sorted rows: every 128-row tile uses its expert's weights; per-expert dW over row segments."""
+    rng = np.random.default_rng(31 + prec)
+    E, N, K = 4, 256, 128
+    seg = np.array([0, 128, 128, 512, 640], np.int32)  # expert 1 has no rows
+    rows = 768  # the last 128-row tile belongs to nobody
+    tile_group = np.array([0, 2, 2, 2, 3, -1], np.int32)
+    a_q, a_f = make_operand(rng, (rows, K), prec)
+    a_f[640:] = 0
+    a_q[640:] = 0
+    b_q, b_f = make_operand(rng, (E * N, K), prec)
+    A, B = DeviceBuffer.from_numpy(a_q), DeviceBuffer.from_numpy(b_q)
+    TG, SEG = DeviceBuffer.from_numpy(tile_group), DeviceBuffer.from_numpy(seg)
+    Cb = DeviceBuffer(rows * N * 4)
+    Cb.upload(np.full((rows, N), 7.0, np.float32))
+    check(lib.ts2_gemm_tn_grouped(0, None, prec, capi.OUT_F32, rows, N, K, A.ptr, B.ptr, Cb.ptr, 0.5, E, TG.ptr))
+    sync()
+    got = Cb.download((rows, N), np.float32)
+    for t, g in enumerate(tile_group):
+        r = slice(128 * t, 128 * t + 128)
+        ref = 0.5 * a_f[r].astype(np.float64) @ b_f[g * N:(g + 1) * N].astype(np.float64).T if g >= 0 else np.full((128, N), 7.0)
+        assert rel_l2(got[r], ref) < 2e-5, (t, g)
+    # per-expert weight gradients from token-major operands
+    out_dim, in_dim = 128, 256
+    dy_q, dy_f = make_operand(rng, (rows, out_dim), prec)
+    x_q, x_f = make_operand(rng, (rows, in_dim), prec)
+    DY, X = DeviceBuffer.from_numpy(dy_q), DeviceBuffer.from_numpy(x_q)
+    DW = DeviceBuffer(E * out_dim * in_dim * 4)
+    DW.upload(np.full((E, out_dim, in_dim), 3.0, np.float32))
+    check(lib.ts2_gemm_dw_grouped(0, None, prec, capi.OUT_F32_ADD, rows, in_dim, out_dim, DY.ptr, X.ptr, DW.ptr, 2.0, E, SEG.ptr))
+    sync()
+    got = DW.download((E, out_dim, in_dim), np.float32)
+    for g in range(E):
+        r = slice(seg[g], seg[g + 1])
+        ref = 3.0 + 2.0 * dy_f[r].astype(np.float64).T @ x_f[r].astype(np.float64)
+        assert rel_l2(got[g], ref) < 2e-5, g

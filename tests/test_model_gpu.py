@@ -140,7 +140,12 @@ def test_errors_are_codes_not_aborts():
     with pytest.raises(capi.Ts2Error) as e:
         model.set_batch(host.synthetic_batch(spec, 2, 128, 1))  # 256 nodes > capacity 128
     assert e.value.code == capi.TS2_ERR_TOO_LARGE
-    moe = host.ModelSpec(dim=128, head_count=1, ffn_tiles=1, vocab=128, moe_expert_count=4).add_blocks(1, moe=True)
-    with pytest.raises(capi.Ts2Error) as e:
-        Model(moe, host.init_weights(moe, 1), 128)
-    assert e.value.code == capi.TS2_ERR_UNSUPPORTED
+    rnn = host.ModelSpec(dim=128, head_count=1, ffn_tiles=1, vocab=128).add_blocks(1)
+    rnn_mats = host.init_weights(rnn, 1)
+    rnn.layers[0].layer_type = capi.LAYER_ATT_3LIN  # the RNN attention variant is outside the path
+    descr, keep = rnn.to_c()
+    import ctypes as C
+    h = C.c_void_p()
+    lib = capi.load_library()
+    rc = lib.ts2_create(C.byref(descr), host.matrix_views(rnn_mats), len(rnn_mats), None, 0, 128, C.byref(h))
+    assert rc == capi.TS2_ERR_UNSUPPORTED

@@ -1,0 +1,84 @@
+"""Mixture-of-experts layers: expert selection bit-exact with the oracle's CpuMoe on the same
+logits, and the end-to-end step of a small ATT+FFN / ATT+MoE model against the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+from tscale2_b200 import capi, host
+from tscale2_b200.model import Model
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+
+
+@pytest.mark.parametrize("E,k", [(4, 2), (32, 2), (24, 6), (128, 8)])
+def test_expert_selection_is_bit_exact(oracle_port, E, k):
+    lib = capi.load_library()
+    rng = np.random.default_rng(E + k)
+    T = 1000
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    logits[:50] = np.round(logits[:50])  # plenty of exact ties: the lowest index must win
+    ids = np.zeros((T, k), np.int32)
+    w = np.zeros((T, k), np.float32)
+    rc = lib.ts2_moe_route(0, logits.ctypes.data, T, E, k, ids.ctypes.data, w.ctypes.data)
+    assert rc == 0, lib.ts2_last_error(None)
+    ref = oracle_port.moe_select(logits, k)  # dense [T][E], zero where not selected
+    dense = np.zeros_like(ref)
+    for j in range(k):
+        dense[np.arange(T), ids[:, j]] = w[:, j]
+    assert np.array_equal(dense != 0, ref != 0), "selected expert sets differ"
+    np.testing.assert_allclose(dense, ref, rtol=2e-6, atol=0)
+    # order of the k choices: descending logit, ties by index
+    picked = np.take_along_axis(logits, ids, 1)
+    assert (np.diff(picked, axis=1) <= 0).all()
+
+
+def moe_spec(precision):
+    s = host.ModelSpec(dim=128, head_count=1, ffn_tiles=2, vocab=256, attention_widths=[16, 48], expert_dim=128,
+                       moe_expert_count=4, moe_selected=2, precision=precision)
+    return s.add_blocks(1, attention_type_id=0).add_blocks(1, attention_type_id=1, alibi_slope=0.25, moe=True)
+
+
+@pytest.mark.parametrize("precision,tol", [(capi.PREC_F16, 5e-3), (capi.PREC_FP8, 1e-1)])
+def test_moe_step_matches_oracle(oracle_port, precision, tol):
+    """The model of the golden fixture tiny_moe_e4m3: one ATT+FFN block, one ATT+MoE block (4 experts, 2 selected)."""
+    spec = moe_spec(precision)
+    mats = host.init_weights(spec, 77, select_std=1.0)
+    batch = host.synthetic_batch(spec, 3, 40, 78)
+    quant = oracle.QUANT_E4M3 if precision == capi.PREC_FP8 else oracle.QUANT_HALF
+    ref = oracle_port.backprop(spec, mats, batch, quant, want_states=True)
+    model = Model(spec, mats, batch.node_count)
+    model.set_debug_taps(True)
+    model.set_batch(batch)
+    model.backprop(host.training_step(), apply=False)
+    model.wait()
+    T, L = batch.node_count, len(spec.layers)
+    report = [(f"state[{l}]", rel_l2(model.get_state_tap(l, False, T), ref["states"][l])) for l in range(L + 1)]
+    report += [(f"state_grad[{l}]", rel_l2(model.get_state_tap(l, True, T), ref["state_grads"][l])) for l in range(L, -1, -1)]
+    report += [(n, rel_l2(g, r)) for n, g, r in zip(spec.matrix_names(), model.get_gradients(), ref["grads"])]
+    text = "\n".join(f"{n:24s} {e:.3e}" for n, e in report)
+    print(text)
+    bad = [(n, e) for n, e in report if not e < tol]
+    assert not bad, text
+
+
+def test_moe_step_applies_and_trains(oracle_port):
+    """Apply a few steps on one batch: the training error must fall (optimizer + requantisation of the
+    per-expert weight blocks)."""
+    spec = moe_spec(capi.PREC_FP8)
+    mats = host.init_weights(spec, 5, select_std=1.0)
+    batch = host.synthetic_batch(spec, 3, 40, 6)
+    model = Model(spec, mats, batch.node_count)
+    model.set_batch(batch)
+    errs = []
+    for i in range(6):
+        model.backprop(host.training_step(rate=0.02, iteration=i), apply=True)
+        errs.append(model.avg_train_err())
+    assert errs[-1] < errs[0] - 0.05, errs

@@ -100,6 +100,7 @@ def _declare(lib):
         "ts2_get_row_disp": (i32, [vp, i32, P(f32), i64, P(f32)]),
         "ts2_get_fast_weights": (i32, [vp, i32, vp, i64, P(f32)]),
         "ts2_set_debug_taps": (i32, [vp, i32]),
+        "ts2_debug_read": (i32, [vp, C.c_char_p, i32, vp, i64]),
         "ts2_get_state_tap": (i32, [vp, i32, i32, P(f32), i64]),
         "ts2_comm_unique_id": (i32, [P(C.c_uint8)]),
         "ts2_comm_init": (i32, [vp, i32, i32, P(C.c_uint8)]),
@@ -120,6 +121,9 @@ def _declare(lib):
         "ts2_gemm_dx": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, vp]),
         "ts2_gemm_dw_workspace_bytes": (C.c_size_t, [i64, i64, i64]),
         "ts2_gemm_dw_noalloc": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32]),
+        "ts2_gemm_tn_grouped": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, i32, vp]),
+        "ts2_gemm_dw_grouped": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, i32, vp]),
+        "ts2_moe_route": (i32, [i32, vp, i32, i32, i32, vp, vp]),
         "ts2_attention_forward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp]),
         "ts2_attention_backward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),

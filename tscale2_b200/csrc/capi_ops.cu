@@ -193,6 +193,73 @@ int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int
     return gemm(a);
 }
 
+// grouped contractions of the mixture-of-experts layers (device pointers; tables on the device)
+int ts2_gemm_tn_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t N, int64_t K, const void *A,
+                        const void *B, void *C, float alpha, int groups, const int32_t *tile_group)
+{
+    GemmArgs a;
+    a.device = device;
+    a.stream = (cudaStream_t)stream;
+    a.kind = kind_of(prec);
+    if (a.kind < 0 || groups <= 0 || !tile_group)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_tn_grouped: bad arguments");
+    a.M = rows, a.N = N, a.K = K;
+    a.A = A, a.lda = K, a.B = B, a.ldb = K, a.C = C, a.ldc = N;
+    a.epi.alpha = alpha;
+    a.epi.out_kind = out_kind;
+    a.group_mode = 1;
+    a.groups = groups;
+    a.tile_group = tile_group;
+    a.group_rows_b = (int)N;
+    return gemm(a);
+}
+
+int ts2_gemm_dw_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t in_dim, int64_t out_dim,
+                        const void *dY, const void *X, void *dW, float alpha, int groups, const int32_t *seg_ptr)
+{
+    GemmArgs a;
+    a.device = device;
+    a.stream = (cudaStream_t)stream;
+    a.kind = kind_of(prec);
+    if (a.kind < 0 || groups <= 0 || !seg_ptr)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_grouped: bad arguments");
+    a.mn_major = true;
+    a.M = out_dim, a.N = in_dim, a.K = rows;
+    a.A = dY, a.lda = out_dim, a.B = X, a.ldb = in_dim, a.C = dW, a.ldc = in_dim;
+    a.epi.alpha = alpha;
+    a.epi.out_kind = out_kind;
+    a.group_mode = 2;
+    a.groups = groups;
+    a.group_kptr = seg_ptr;
+    a.c_group_stride = out_dim * in_dim;
+    return gemm(a);
+}
+
+// CpuMoe on the device: logits host [T][E] -> ids host [T][k], weights host [T][k]
+int ts2_moe_route(int device, const float *logits, int T, int expert_count, int selected, int32_t *ids, float *weights)
+{
+    if (!logits || !ids || !weights || T <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_moe_route: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    float *dl = nullptr, *dw = nullptr;
+    int *di = nullptr;
+    TS2_CUDA(cudaMalloc(&dl, (size_t)T * expert_count * 4));
+    TS2_CUDA(cudaMalloc(&dw, (size_t)T * selected * 4));
+    TS2_CUDA(cudaMalloc(&di, (size_t)T * selected * 4));
+    TS2_CUDA(cudaMemcpy(dl, logits, (size_t)T * expert_count * 4, cudaMemcpyHostToDevice));
+    Ctx c;
+    c.device = device;
+    int rc = moe_route(c, dl, expert_count, T, expert_count, selected, di, dw);
+    if (rc == TS2_OK) {
+        cudaMemcpy(ids, di, (size_t)T * selected * 4, cudaMemcpyDeviceToHost);
+        cudaMemcpy(weights, dw, (size_t)T * selected * 4, cudaMemcpyDeviceToHost);
+    }
+    cudaFree(dl);
+    cudaFree(dw);
+    cudaFree(di);
+    return rc;
+}
+
 // attention core on device arrays; span_start / span_finish are host arrays of T ints
 int ts2_attention_forward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const int32_t *span_start,
                           const int32_t *span_finish, int T, int head_count, float alibi_slope, void *o, float *lse)

@@ -17,6 +17,7 @@ struct Fast<0> {
         __nv_fp8x4_e4m3 p(v);
         *(uint32_t *)((uint8_t *)base + idx) = p.__x;
     }
+    static __device__ __forceinline__ void zero4(void *base, size_t idx) { *(uint32_t *)((uint8_t *)base + idx) = 0u; }
     static __device__ __forceinline__ float4 load4(const void *base, size_t idx)
     {
         uint32_t raw = *(const uint32_t *)((const uint8_t *)base + idx);
@@ -35,6 +36,7 @@ struct Fast<1> {
         __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
         *(uint2 *)((__half *)base + idx) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
     }
+    static __device__ __forceinline__ void zero4(void *base, size_t idx) { *(uint2 *)((__half *)base + idx) = make_uint2(0u, 0u); }
     static __device__ __forceinline__ float4 load4(const void *base, size_t idx)
     {
         uint2 raw = *(const uint2 *)((const __half *)base + idx);
@@ -62,20 +64,20 @@ __device__ __forceinline__ float4 axpy4(float a, float4 x, float4 y)
     return make_float4(a * x.x + y.x, a * x.y + y.y, a * x.z + y.z, a * x.w + y.w);
 }
 
-// CpuComputeLolu, src/gpt/compute/cpu_util.cpp:139-151 (LOLU_SCALE = 2)
+// CpuComputeLolu, src/gpt/compute/cpu_util.cpp:139-151 (LOLU_SCALE = 2): exp(2x) / (1 + exp(2x)) with the
+// result pinned to 0 / 1 beyond |2x| > 20.  Written as 1 / (1 + exp(-2x)) with the hardware exponential and
+// reciprocal (relative error ~1e-6, far below the fp16 / e4m3 rounding of the result); the saturation is
+// what the formula gives by itself (exp(20) ~ 4.9e8), so the two branches of the reference are kept only to
+// return exactly 0 and 1.
 __device__ __forceinline__ float lolu_mult(float gate)
 {
-    float arg = gate * 2.f;
-    if (arg < -20.f)
-        return 0.f;
-    if (arg > 20.f)
-        return 1.f;
-    float w = expf(arg);
-    return w / (1.f + w);
+    const float arg = gate * 2.f;
+    const float r = __fdividef(1.f, 1.f + __expf(-arg));
+    return arg < -20.f ? 0.f : (arg > 20.f ? 1.f : r);
 }
 
 // scale of one 128-wide tile: sqrt(128 / sum of squares), 0 for an all-zero tile
-__device__ __forceinline__ float tile_scale(float sum2) { return sum2 == 0.f ? 0.f : sqrtf(128.f / sum2); }
+__device__ __forceinline__ float tile_scale(float sum2) { return sum2 == 0.f ? 0.f : 11.3137085f * rsqrtf(sum2); }
 
 // Weight encoder of the reference's CPU path for e4m3 (ConvertToFp8e4m3,
 // src/gpt/model_params/sse_utils.h:161-204): round half away from zero on the 4th

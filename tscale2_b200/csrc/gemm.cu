@@ -40,7 +40,51 @@ struct GemmParams {
     int out_kind;
     float *workspace;
     int32_t *status;
+    // grouped forms (mixture-of-experts): 0 none; 1 every 128-row M tile belongs to one group (tile_group[m_tile],
+    // negative: skip) and reads B rows [group * group_rows_b + n]; 2 the K range of a unit is the row segment of
+    // its group (group_kptr[g] .. group_kptr[g+1], multiples of the K block) and C moves by c_group_stride per group
+    int group_mode, groups;
+    const int *tile_group;
+    int group_rows_b;
+    const int *group_kptr;
+    long long c_group_stride;
+    int bk;
 };
+
+struct Unit {
+    int m0, n0, kb0, kb1, b_row_off;
+    long long c_off;
+};
+
+// identical in the three roles, so that they agree on which units exist
+__device__ __forceinline__ bool decode_unit(const GemmParams &p, int u, int bn, Unit &t)
+{
+    const int tiles = p.m_tiles * p.n_tiles;
+    t.b_row_off = 0;
+    t.c_off = 0;
+    if (p.group_mode == 2) {
+        const int g = u / tiles, tile = u - g * tiles;
+        t.m0 = (tile % p.m_tiles) * BM;
+        t.n0 = (tile / p.m_tiles) * bn;
+        t.kb0 = __ldg(p.group_kptr + g) / p.bk;
+        t.kb1 = __ldg(p.group_kptr + g + 1) / p.bk;
+        t.c_off = (long long)g * p.c_group_stride;
+        return t.kb1 > t.kb0;
+    }
+    const int tile = u / p.splits, split = u - tile * p.splits;
+    const int mt = tile % p.m_tiles;
+    t.m0 = mt * BM;
+    t.n0 = (tile / p.m_tiles) * bn;
+    t.kb0 = split * p.kb_per_split;
+    t.kb1 = min(p.k_blocks, t.kb0 + p.kb_per_split);
+    if (p.group_mode == 1) {
+        const int g = __ldg(p.tile_group + mt);
+        if (g < 0)
+            return false;
+        t.b_row_off = g * p.group_rows_b;
+    }
+    return true;
+}
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
 {
@@ -131,7 +175,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles = p.m_tiles * p.n_tiles;
-    const int units = tiles * p.splits;
+    const int units = p.group_mode == 2 ? tiles * p.groups : tiles * p.splits;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -141,9 +185,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             int issued = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const int tile = u / p.splits, split = u - tile * p.splits;
-                const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
-                const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+                Unit un;
+                if (!decode_unit(p, u, BN, un))
+                    continue;
+                const int m0 = un.m0, n0 = un.n0 + un.b_row_off, kb0 = un.kb0, kb1 = un.kb1;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag)) {
                         ok = false;
@@ -195,8 +240,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const int tile = u / p.splits, split = u - tile * p.splits;
-                const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+                Unit un;
+                if (!decode_unit(p, u, BN, un))
+                    continue;
+                const int kb0 = un.kb0, kb1 = un.kb1;
                 if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag))
                     break;
                 tc_fence_after();
@@ -252,8 +299,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
-            const int tile = u / p.splits;
-            const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+            Unit un;
+            if (!decode_unit(p, u, BN, un))
+                continue;
+            const int m0 = un.m0, n0 = un.n0;
+            uint8_t *const Cg = (uint8_t *)p.C + un.c_off * ((p.out_kind == TS2_OUT_F32 || p.out_kind == TS2_OUT_F32_ADD) ? 4 : 2);
+            const float *const Cin = p.c_in + un.c_off;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag))
                 break;
             tc_fence_after();
@@ -298,9 +349,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         v[i] *= rs;
                 }
                 if (p.out_kind == TS2_OUT_F32 || p.out_kind == TS2_OUT_F32_ADD) {
-                    float4 *dst = (float4 *)((float *)p.C + row * p.ldc + col);
+                    float4 *dst = (float4 *)((float *)Cg + row * p.ldc + col);
                     if (p.out_kind == TS2_OUT_F32_ADD) {
-                        const float4 *src = (const float4 *)(p.c_in + row * p.ldc + col);
+                        const float4 *src = (const float4 *)(Cin + row * p.ldc + col);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             float4 o = src[i];
@@ -312,7 +363,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
                 } else if (p.out_kind == TS2_OUT_F16) {
-                    uint4 *dst = (uint4 *)((__half *)p.C + row * p.ldc + col);
+                    uint4 *dst = (uint4 *)((__half *)Cg + row * p.ldc + col);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
@@ -320,7 +371,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         dst[i] = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                     }
                 } else {
-                    uint4 *dst = (uint4 *)((__nv_bfloat16 *)p.C + row * p.ldc + col);
+                    uint4 *dst = (uint4 *)((__nv_bfloat16 *)Cg + row * p.ldc + col);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]),
@@ -467,7 +518,7 @@ struct Plan {
     int bn, m_tiles, n_tiles, k_blocks, splits, kb_per_split, grid;
 };
 
-static Plan make_plan(int device, int kind, bool mn, int64_t M, int64_t N, int64_t K)
+static Plan make_plan(int device, int kind, bool mn, int64_t M, int64_t N, int64_t K, int group_mode = 0, int groups = 1)
 {
     Plan pl;
     const int es = elem_size(kind);
@@ -479,13 +530,13 @@ static Plan make_plan(int device, int kind, bool mn, int64_t M, int64_t N, int64
     const int sms = sm_count(device);
     const int tiles = std::max(1, pl.m_tiles * pl.n_tiles); // an empty problem is rejected by gemm(); keep the arithmetic defined
     int splits = 1;
-    if (tiles * 2 <= sms) { // fewer than half the SMs would have work: split K
+    if (group_mode == 0 && tiles * 2 <= sms) { // fewer than half the SMs would have work: split K
         splits = sms / tiles;
         splits = std::min(splits, std::max(1, pl.k_blocks / 8)); // keep at least 8 K blocks per unit
     }
     pl.kb_per_split = std::max(1, (int)ceil_div(pl.k_blocks, splits));
     pl.splits = std::max(1, (int)ceil_div(pl.k_blocks, pl.kb_per_split));
-    pl.grid = std::min(sms, tiles * pl.splits);
+    pl.grid = std::min(sms, tiles * pl.splits * (group_mode == 2 ? std::max(1, groups) : 1));
     return pl;
 }
 
@@ -597,7 +648,11 @@ int gemm(const GemmArgs &a)
     if (a.epi.col_scale && ((uintptr_t)a.epi.col_scale & 15))
         return fail(TS2_ERR_INVALID_ARG, "gemm: col_scale must be 16-byte aligned");
     TS2_CUDA(cudaSetDevice(a.device));
-    Plan pl = make_plan(a.device, a.kind, a.mn_major, a.M, a.N, a.K);
+    if (a.group_mode == 1 && (a.mn_major || !a.tile_group || a.group_rows_b <= 0 || a.groups <= 0))
+        return fail(TS2_ERR_INVALID_ARG, "gemm: bad row-grouped arguments");
+    if (a.group_mode == 2 && (!a.mn_major || !a.group_kptr || a.groups <= 0))
+        return fail(TS2_ERR_INVALID_ARG, "gemm: bad K-grouped arguments");
+    Plan pl = make_plan(a.device, a.kind, a.mn_major, a.M, a.N, a.K, a.group_mode, a.groups);
     if (pl.splits > 1) {
         size_t need = (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float);
         if (!a.workspace || a.workspace_bytes < need)
@@ -609,7 +664,7 @@ int gemm(const GemmArgs &a)
     if (!a.mn_major) {
         if ((rc = make_tmap(&tmA, a.A, es, a.K, a.M, a.lda, BM)) != TS2_OK)
             return rc;
-        if ((rc = make_tmap(&tmB, a.B, es, a.K, a.N, a.ldb, pl.bn)) != TS2_OK)
+        if ((rc = make_tmap(&tmB, a.B, es, a.K, a.group_mode == 1 ? a.N * a.groups : a.N, a.ldb, pl.bn)) != TS2_OK)
             return rc;
     } else {
         if ((rc = make_tmap(&tmA, a.A, es, a.M, a.K, a.lda, bk)) != TS2_OK)
@@ -639,6 +694,13 @@ int gemm(const GemmArgs &a)
     p.status = device_status_word(a.device);
     if (!p.status)
         return fail(TS2_ERR_CUDA, "gemm: no device status word");
+    p.group_mode = a.group_mode;
+    p.groups = a.groups;
+    p.tile_group = a.tile_group;
+    p.group_rows_b = a.group_rows_b;
+    p.group_kptr = a.group_kptr;
+    p.c_group_stride = a.c_group_stride;
+    p.bk = bk;
 
     cudaEvent_t ea = nullptr, eb = nullptr;
     bool timed;
@@ -773,6 +835,13 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
     // nothing in the scratch has to start at zero; the status word is only ever OR-ed into
     p.workspace = st.scratch;
     p.status = st.status;
+    p.group_mode = 0;
+    p.groups = 1;
+    p.tile_group = nullptr;
+    p.group_rows_b = 0;
+    p.group_kptr = nullptr;
+    p.c_group_stride = 0;
+    p.bk = bk;
     GemmArgs a;
     a.device = device;
     a.stream = (cudaStream_t)stream;

@@ -33,6 +33,13 @@ struct GemmArgs {
     void *C = nullptr;
     int64_t ldc = 0;
     Epilogue epi;
+    // grouped forms for mixture-of-experts layers (see GemmParams in gemm.cu)
+    int group_mode = 0; // 1: B rows chosen per 128-row M tile (tile_group), N = rows of B per group; 2: K segment per group
+    int groups = 0;
+    const int *tile_group = nullptr; // device, one entry per M tile, negative = skip the tile
+    int group_rows_b = 0;
+    const int *group_kptr = nullptr; // device, groups + 1 row offsets (multiples of 128)
+    int64_t c_group_stride = 0;      // elements of C between groups (mode 2)
     void *workspace = nullptr; // split-K partial tiles (fp32); needed when gemm_splits() > 1
     size_t workspace_bytes = 0;
 };

@@ -85,6 +85,23 @@ int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, c
 // host: for every key the range [first, last] of nodes whose span may contain it (a superset; kernels re-check)
 void attention_reverse_ranges(const int *span_start, const int *span_finish, int T, int *rev_first, int *rev_last);
 
+// ---- kernels_moe.cu ----------------------------------------------------------------
+// CpuMoe (layer_moe.cu:287-328): ids[T][k] and weights[T][k] from router logits [T][ld]
+int moe_route(const Ctx &c, const float *logits, int ld, int T, int E, int k, int *ids, float *weights);
+// expert-sorted slot tables (segments padded to 128 rows): seg_ptr[E+1], tile_group[max_rows/128] (-1: unused),
+// slot_of[T*k], token_of[max_rows] (-1: unused), weight_of[max_rows]; scratch: hist and block_base, ceil(T/256)*E ints each
+int moe_build_slots(const Ctx &c, const int *ids, const float *weights, int T, int k, int E, int max_rows, int *hist_scratch,
+                    int *block_base_scratch, int *seg_ptr, int *tile_group, int *slot_of, int *token_of, float *weight_of);
+int moe_gather_rows(const Ctx &c, const void *src, const int *token_of, int rows, int row_bytes, void *dst);
+int moe_act_forward(const Ctx &c, const __half *cat, const int *token_of, const float *weight_of, int rows, int X, __half *what,
+                    float *wscale, void *rg);
+int moe_act_backward(const Ctx &c, const __half *drg, const __half *cat, const __half *what, const float *wscale, const int *token_of,
+                     const float *weight_of, int rows, int X, void *dcat, float *dmoe_part);
+// out[t] = (in ? in[t] : out[t]) + sum_j y[slot_of[t*k+j]]
+int moe_combine(const Ctx &c, const float *y, const int *slot_of, int T, int k, int D, const float *in, float *out);
+int moe_router_backward(const Ctx &c, const float *dmoe_part, int tiles, const int *ids, const float *weights, const int *slot_of, int T,
+                        int k, int E, int ld, void *dl);
+
 // ---- kernels_opt.cu ----------------------------------------------------------------
 // MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel (agpu_cuda.cu:32-134), one matrix.
 struct OptMatrix {
@@ -105,6 +122,11 @@ int apply_gradient(const Ctx &c, const OptMatrix &m, const ts2_training_step &st
 // dstT[x][ldT] (optionally widened to fp16); sko written to *sko_out; scratch holds y doubles.
 int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant /*0 e4m3, 1 fp16*/, void *dst, int64_t ld, void *dstT,
                int64_t ldT, float *sko_out, float *scratch_y_doubles, bool transposed_as_half);
+// the two halves of requantize: the matrix scale of a whole matrix, and the conversion of a block of its rows
+// with a given scale (expert blocks of a mixture-of-experts matrix share the matrix scale)
+int matrix_sko(const Ctx &c, const float *w, int64_t x, int64_t y, float *sko_out, float *scratch_y_doubles);
+int convert_block(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, void *dst, int64_t ld, void *dstT, int64_t ldT,
+                  const float *sko, bool transposed_as_half);
 int fill_vector(const Ctx &c, float *dst, int n, float value, const float *dyn, bool reciprocal_dyn);
 
 } // namespace ts2

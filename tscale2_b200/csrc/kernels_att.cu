@@ -21,10 +21,15 @@ static int grid_for(const Ctx &c, long long warp_items)
     return (int)std::max<long long>(1, std::min(blocks, cap));
 }
 
-#define WARP_ITEM_LOOP(total)                                                                 \
+#define WARP_BATCH_LOOP(total, R)                                                             \
     const int lane = threadIdx.x & 31;                                                        \
-    for (long long item = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5); item < (total); \
-         item += (long long)gridDim.x * WARPS)
+    const unsigned wstride = gridDim.x * WARPS, total_items = (unsigned)(total);             \
+    for (unsigned base = blockIdx.x * WARPS + (threadIdx.x >> 5); base < total_items; base += wstride * (R))
+
+#define WARP_ITEM_LOOP(total) \
+    const int lane = threadIdx.x & 31; \
+    for (unsigned item = blockIdx.x * WARPS + (threadIdx.x >> 5), total_items = (unsigned)(total); item < total_items; \
+         item += gridDim.x * WARPS)
 
 // AttDotScale = CalcDotScale(128) * ATT_DOTPRODUCT_SCALE / LOG2 (layer_att_reference.h:30-33)
 __host__ __device__ inline float att_dot_scale() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
@@ -61,20 +66,38 @@ __global__ void att_post_forward_kernel(const __half *__restrict__ qkvg, const f
                                         float *__restrict__ qscale, float *__restrict__ vscale)
 {
     const int Q = H * TILE;
-    WARP_ITEM_LOOP((long long)T * H)
+    constexpr int R = 2; // two (node, head) items in flight per warp
+    WARP_BATCH_LOOP((long long)T * H, R)
     {
-        const size_t t = item / H;
-        const int h = (int)(item % H), off = h * TILE + lane * 4;
-        const __half *src = qkvg + t * 4 * Q;
-        const float4 qs = load_half4(src + off), ks = load_half4(src + Q + off), vs = load_half4(src + 2 * Q + off);
-        const float4 cs = *(const float4 *)(rope + t * 128 + lane * 4);
-        const float sq = tile_scale(warp_sum(dot4(qs, qs))), sv = tile_scale(warp_sum(dot4(vs, vs)));
-        store_half4(q + t * Q + off, rope_apply(scale4(qs, sq), cs, 1.f));
-        store_half4(k + t * Q + off, rope_apply(ks, cs, 1.f));
-        store_half4(v + t * Q + off, scale4(vs, sv));
-        if (lane == 0) {
-            qscale[t * H + h] = sq;
-            vscale[t * H + h] = sv;
+        float4 qs[R], ks[R], vs[R], cs[R];
+        size_t t[R];
+        int h[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / H : 0;
+            h[r] = ok[r] ? (int)(item % H) : 0;
+            const __half *src = qkvg + t[r] * 4 * Q + h[r] * TILE + lane * 4;
+            qs[r] = ok[r] ? load_half4(src) : make_float4(0, 0, 0, 0);
+            ks[r] = ok[r] ? load_half4(src + Q) : make_float4(0, 0, 0, 0);
+            vs[r] = ok[r] ? load_half4(src + 2 * Q) : make_float4(0, 0, 0, 0);
+            cs[r] = ok[r] ? *(const float4 *)(rope + t[r] * 128 + lane * 4) : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const int off = h[r] * TILE + lane * 4;
+            const float sq = tile_scale(warp_sum(dot4(qs[r], qs[r]))), sv = tile_scale(warp_sum(dot4(vs[r], vs[r])));
+            store_half4(q + t[r] * Q + off, rope_apply(scale4(qs[r], sq), cs[r], 1.f));
+            store_half4(k + t[r] * Q + off, rope_apply(ks[r], cs[r], 1.f));
+            store_half4(v + t[r] * Q + off, scale4(vs[r], sv));
+            if (lane == 0) {
+                qscale[t[r] * H + h[r]] = sq;
+                vscale[t[r] * H + h[r]] = sv;
+            }
         }
     }
 }
@@ -95,29 +118,49 @@ __global__ void att_post_backward_kernel(const float *__restrict__ dq, const flo
 {
     const int Q = H * TILE;
     const float kfold = __ldg(sko_k);
-    WARP_ITEM_LOOP((long long)T * H)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * H, R)
     {
-        const size_t t = item / H;
-        const int h = (int)(item % H), off = h * TILE + lane * 4;
-        const float4 cs = *(const float4 *)(rope + t * 128 + lane * 4);
-        // q: tile-norm backward in the rotated frame (the rotation is orthogonal), then rotate back
-        const float4 qv = load_half4(q + t * Q + off);
-        const float4 gq = *(const float4 *)(dq + t * Q + off);
-        const float pq = warp_sum(dot4(qv, gq)) * (1.f / 128);
-        const float sq = qscale[t * H + h];
-        float4 r = rope_apply(make_float4(gq.x - qv.x * pq, gq.y - qv.y * pq, gq.z - qv.z * pq, gq.w - qv.w * pq), cs, -1.f);
-        Fast<FT>::store4(d4, t * 4 * Q + off, scale4(r, sq));
-        // k: rotate back; the matrix scale of K is folded in here so that the 4-way dX contraction
-        // can use scale-free weights for every block
-        const float4 gk = rope_apply(*(const float4 *)(dk + t * Q + off), cs, -1.f);
-        Fast<FT>::store4(d4, t * 4 * Q + Q + off, scale4(gk, kfold));
-        // v: tile-norm backward
-        const float4 vv = load_half4(v + t * Q + off);
-        const float4 gv = *(const float4 *)(dv + t * Q + off);
-        const float pv = warp_sum(dot4(vv, gv)) * (1.f / 128);
-        const float sv = vscale[t * H + h];
-        Fast<FT>::store4(d4, t * 4 * Q + 2 * Q + off,
-                         make_float4(sv * (gv.x - vv.x * pv), sv * (gv.y - vv.y * pv), sv * (gv.z - vv.z * pv), sv * (gv.w - vv.w * pv)));
+        float4 cs[R], qv[R], gq[R], gk[R], vv[R], gv[R];
+        float sq[R], sv[R];
+        size_t t[R];
+        int off[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / H : 0;
+            const int h = ok[r] ? (int)(item % H) : 0;
+            off[r] = h * TILE + lane * 4;
+            const float4 z = make_float4(0, 0, 0, 0);
+            cs[r] = ok[r] ? *(const float4 *)(rope + t[r] * 128 + lane * 4) : z;
+            qv[r] = ok[r] ? load_half4(q + t[r] * Q + off[r]) : z;
+            gq[r] = ok[r] ? *(const float4 *)(dq + t[r] * Q + off[r]) : z;
+            gk[r] = ok[r] ? *(const float4 *)(dk + t[r] * Q + off[r]) : z;
+            vv[r] = ok[r] ? load_half4(v + t[r] * Q + off[r]) : z;
+            gv[r] = ok[r] ? *(const float4 *)(dv + t[r] * Q + off[r]) : z;
+            sq[r] = ok[r] ? qscale[t[r] * H + h] : 0.f;
+            sv[r] = ok[r] ? vscale[t[r] * H + h] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            // q: tile-norm backward in the rotated frame (the rotation is orthogonal), then rotate back
+            const float pq = warp_sum(dot4(qv[r], gq[r])) * (1.f / 128);
+            const float4 rq = rope_apply(
+                make_float4(gq[r].x - qv[r].x * pq, gq[r].y - qv[r].y * pq, gq[r].z - qv[r].z * pq, gq[r].w - qv[r].w * pq), cs[r], -1.f);
+            Fast<FT>::store4(d4, t[r] * 4 * Q + off[r], scale4(rq, sq[r]));
+            // k: rotate back; the matrix scale of K is folded in here so that the 4-way dX contraction
+            // can use scale-free weights for every block
+            Fast<FT>::store4(d4, t[r] * 4 * Q + Q + off[r], scale4(rope_apply(gk[r], cs[r], -1.f), kfold));
+            // v: tile-norm backward
+            const float pv = warp_sum(dot4(vv[r], gv[r])) * (1.f / 128);
+            Fast<FT>::store4(d4, t[r] * 4 * Q + 2 * Q + off[r],
+                             make_float4(sv[r] * (gv[r].x - vv[r].x * pv), sv[r] * (gv[r].y - vv[r].y * pv),
+                                         sv[r] * (gv[r].z - vv[r].z * pv), sv[r] * (gv[r].w - vv[r].w * pv)));
+        }
     }
 }
 

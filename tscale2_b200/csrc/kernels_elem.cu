@@ -18,10 +18,17 @@ static int grid_for(const Ctx &c, long long warp_items)
     return (int)std::max<long long>(1, std::min(blocks, cap));
 }
 
-#define WARP_ITEM_LOOP(total)                                                                              \
+// R items per warp and iteration: all loads of the R items are issued before any of them is
+// consumed, which keeps enough bytes in flight per SM to approach HBM bandwidth
+#define WARP_BATCH_LOOP(total, R)                                                                          \
     const int lane = threadIdx.x & 31;                                                                     \
-    for (long long item = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5); item < (total);              \
-         item += (long long)gridDim.x * WARPS)
+    const unsigned wstride = gridDim.x * WARPS, total_items = (unsigned)(total);                          \
+    for (unsigned base = blockIdx.x * WARPS + (threadIdx.x >> 5); base < total_items; base += wstride * (R))
+
+#define WARP_ITEM_LOOP(total) \
+    const int lane = threadIdx.x & 31; \
+    for (unsigned item = blockIdx.x * WARPS + (threadIdx.x >> 5), total_items = (unsigned)(total); item < total_items; \
+         item += gridDim.x * WARPS)
 
 // ---------------------------------------------------------------------------------
 __global__ void embed_forward_kernel(const __half *__restrict__ embed, const float *__restrict__ sko,
@@ -87,15 +94,29 @@ __global__ void tilenorm_forward_kernel(const float *__restrict__ x, int T, int 
                                         __half *__restrict__ n16)
 {
     const int tiles = D / TILE;
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t idx = (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4;
-        const float4 v = *(const float4 *)(x + idx);
-        const float scale = tile_scale(warp_sum(dot4(v, v)));
-        const float4 nv = scale4(v, scale);
-        Fast<FT>::store4(n_fast, idx, scale4(nv, s_act));
-        if (n16)
-            store_half4(n16 + idx, nv);
+        float4 v[R];
+        size_t idx[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            idx[r] = ok[r] ? (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4 : 0;
+            v[r] = ok[r] ? *(const float4 *)(x + idx[r]) : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const float scale = tile_scale(warp_sum(dot4(v[r], v[r])));
+            const float4 nv = scale4(v[r], scale);
+            Fast<FT>::store4(n_fast, idx[r], scale4(nv, s_act));
+            if (n16)
+                store_half4(n16 + idx[r], nv);
+        }
     }
 }
 
@@ -116,25 +137,38 @@ __global__ void tilenorm_backward_kernel(const float *__restrict__ x, const floa
     const int tiles = D / TILE;
     const float a = dn_alpha * (dyn ? __ldg(dyn) : 1.f);
     float local_max = 0.f;
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t idx = (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4;
-        const float4 xv = *(const float4 *)(x + idx);
-        const float4 dv = scale4(*(const float4 *)(dn + idx), a);
-        const float sum2 = warp_sum(dot4(xv, xv));
-        const float dp = warp_sum(dot4(xv, dv));
-        float4 r = make_float4(0, 0, 0, 0);
-        if (sum2 != 0.f) {
-            const float sigma = dp / sum2, scale = sqrtf(128.f / sum2);
-            r = make_float4(scale * (dv.x - xv.x * sigma), scale * (dv.y - xv.y * sigma), scale * (dv.z - xv.z * sigma),
-                            scale * (dv.w - xv.w * sigma));
+        float4 xv[R], dv[R], o[R];
+        size_t idx[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            idx[r] = ok[r] ? (size_t)(item / tiles) * D + (item % tiles) * TILE + lane * 4 : 0;
+            xv[r] = ok[r] ? *(const float4 *)(x + idx[r]) : make_float4(0, 0, 0, 0);
+            dv[r] = ok[r] ? *(const float4 *)(dn + idx[r]) : make_float4(0, 0, 0, 0);
+            o[r] = (ok[r] && add) ? *(const float4 *)(g + idx[r]) : make_float4(0, 0, 0, 0);
         }
-        if (add) {
-            const float4 o = *(const float4 *)(g + idx);
-            r = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const float4 d = scale4(dv[r], a);
+            const float sum2 = warp_sum(dot4(xv[r], xv[r]));
+            const float dp = warp_sum(dot4(xv[r], d));
+            float4 res = make_float4(0, 0, 0, 0);
+            if (sum2 != 0.f) {
+                const float sigma = dp / sum2, scale = sqrtf(128.f / sum2);
+                res = make_float4(scale * (d.x - xv[r].x * sigma), scale * (d.y - xv[r].y * sigma), scale * (d.z - xv[r].z * sigma),
+                                  scale * (d.w - xv[r].w * sigma));
+            }
+            res = make_float4(o[r].x + res.x, o[r].y + res.y, o[r].z + res.z, o[r].w + res.w);
+            *(float4 *)(g + idx[r]) = res;
+            local_max = fmaxf(local_max, fmaxf(fmaxf(fabsf(res.x), fabsf(res.y)), fmaxf(fabsf(res.z), fabsf(res.w))));
         }
-        *(float4 *)(g + idx) = r;
-        local_max = fmaxf(local_max, fmaxf(fmaxf(fabsf(r.x), fabsf(r.y)), fmaxf(fabsf(r.z), fabsf(r.w))));
     }
     if (absmax) {
         __shared__ float block_max[WARPS];
@@ -183,9 +217,16 @@ __global__ void cast_grad_kernel(const float *__restrict__ g, size_t n4, const u
         if (fscale)
             *fscale = f_static * (sko ? *sko : 1.f) / mult;
     }
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        const float4 v = *(const float4 *)(g + i * 4);
-        Fast<FT>::store4(out, i * 4, scale4(v, mult));
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += stride * 4) {
+        float4 v[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            v[r] = (i0 + r * stride < n4) ? *(const float4 *)(g + (i0 + r * stride) * 4) : make_float4(0, 0, 0, 0);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (i0 + r * stride < n4)
+                Fast<FT>::store4(out, (i0 + r * stride) * 4, scale4(v[r], mult));
     }
 }
 
@@ -208,19 +249,37 @@ __global__ void ffn_act_forward_kernel(const __half *__restrict__ wg, int T, int
                                        float *__restrict__ wscale, void *__restrict__ rg)
 {
     const int tiles = F / TILE;
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t t = item / tiles;
-        const int tile = (int)(item % tiles), off = tile * TILE + lane * 4;
-        const float4 wide = load_half4(wg + t * 2 * F + off);
-        const float4 gate = load_half4(wg + t * 2 * F + F + off);
-        const float scale = tile_scale(warp_sum(dot4(wide, wide)));
-        const float4 wn = scale4(wide, scale);
-        store_half4(what + t * F + off, wn);
-        if (lane == 0)
-            wscale[t * tiles + tile] = scale;
-        const float4 r = make_float4(lolu_mult(gate.x) * wn.x, lolu_mult(gate.y) * wn.y, lolu_mult(gate.z) * wn.z, lolu_mult(gate.w) * wn.w);
-        Fast<FT>::store4(rg, t * F + off, scale4(r, s_act));
+        float4 wide[R], gate[R];
+        size_t t[R];
+        int tile[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            tile[r] = ok[r] ? (int)(item % tiles) : 0;
+            const int off = tile[r] * TILE + lane * 4;
+            wide[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + off) : make_float4(0, 0, 0, 0);
+            gate[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + F + off) : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const int off = tile[r] * TILE + lane * 4;
+            const float scale = tile_scale(warp_sum(dot4(wide[r], wide[r])));
+            const float4 wn = scale4(wide[r], scale);
+            store_half4(what + t[r] * F + off, wn);
+            if (lane == 0)
+                wscale[t[r] * tiles + tile[r]] = scale;
+            const float4 res = make_float4(lolu_mult(gate[r].x) * wn.x, lolu_mult(gate[r].y) * wn.y, lolu_mult(gate[r].z) * wn.z,
+                                           lolu_mult(gate[r].w) * wn.w);
+            Fast<FT>::store4(rg, t[r] * F + off, scale4(res, s_act));
+        }
     }
 }
 
@@ -240,24 +299,42 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
                                         const float *__restrict__ wscale, int T, int F, void *__restrict__ d2)
 {
     const int tiles = F / TILE;
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t t = item / tiles;
-        const int tile = (int)(item % tiles), off = tile * TILE + lane * 4;
-        const float4 g = load_half4(drg + t * F + off);
-        const float4 gate = load_half4(wg + t * 2 * F + F + off);
-        const float4 wn = load_half4(what + t * F + off);
-        const float scale = wscale[t * tiles + tile];
-        const float4 m = make_float4(lolu_mult(gate.x), lolu_mult(gate.y), lolu_mult(gate.z), lolu_mult(gate.w));
-        const float4 dgate = make_float4(g.x * wn.x * m.x * (1 - m.x) * 2.f, g.y * wn.y * m.y * (1 - m.y) * 2.f,
-                                         g.z * wn.z * m.z * (1 - m.z) * 2.f, g.w * wn.w * m.w * (1 - m.w) * 2.f);
-        const float4 dwn = make_float4(g.x * m.x, g.y * m.y, g.z * m.z, g.w * m.w);
-        // tile-norm backward expressed with the normalized vector: scale * (d - wn * (wn . d) / 128)
-        const float proj = warp_sum(dot4(wn, dwn)) * (1.f / 128);
-        const float4 dwide = make_float4(scale * (dwn.x - wn.x * proj), scale * (dwn.y - wn.y * proj), scale * (dwn.z - wn.z * proj),
-                                         scale * (dwn.w - wn.w * proj));
-        Fast<FT>::store4(d2, t * 2 * F + off, dwide);
-        Fast<FT>::store4(d2, t * 2 * F + F + off, dgate);
+        float4 g[R], gate[R], wn[R];
+        float scale[R];
+        size_t t[R];
+        int off[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            const int tile = ok[r] ? (int)(item % tiles) : 0;
+            off[r] = tile * TILE + lane * 4;
+            g[r] = ok[r] ? load_half4(drg + t[r] * F + off[r]) : make_float4(0, 0, 0, 0);
+            gate[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + F + off[r]) : make_float4(0, 0, 0, 0);
+            wn[r] = ok[r] ? load_half4(what + t[r] * F + off[r]) : make_float4(0, 0, 0, 0);
+            scale[r] = ok[r] ? wscale[t[r] * tiles + tile] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const float4 m = make_float4(lolu_mult(gate[r].x), lolu_mult(gate[r].y), lolu_mult(gate[r].z), lolu_mult(gate[r].w));
+            const float4 dgate = make_float4(g[r].x * wn[r].x * m.x * (1 - m.x) * 2.f, g[r].y * wn[r].y * m.y * (1 - m.y) * 2.f,
+                                             g[r].z * wn[r].z * m.z * (1 - m.z) * 2.f, g[r].w * wn[r].w * m.w * (1 - m.w) * 2.f);
+            const float4 dwn = make_float4(g[r].x * m.x, g[r].y * m.y, g[r].z * m.z, g[r].w * m.w);
+            // tile-norm backward expressed with the normalized vector: scale * (d - wn * (wn . d) / 128)
+            const float proj = warp_sum(dot4(wn[r], dwn)) * (1.f / 128);
+            const float sc = scale[r];
+            const float4 dwide = make_float4(sc * (dwn.x - wn[r].x * proj), sc * (dwn.y - wn[r].y * proj), sc * (dwn.z - wn[r].z * proj),
+                                             sc * (dwn.w - wn[r].w * proj));
+            Fast<FT>::store4(d2, t[r] * 2 * F + off[r], dwide);
+            Fast<FT>::store4(d2, t[r] * 2 * F + F + off[r], dgate);
+        }
     }
 }
 
@@ -278,14 +355,30 @@ __global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const _
                                         void *__restrict__ rg)
 {
     const int tiles = Q / TILE;
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t t = item / tiles;
-        const int off = (int)(item % tiles) * TILE + lane * 4;
-        const float4 gate = load_half4(qkvg + t * 4 * Q + 3 * Q + off);
-        const float4 ov = load_half4(o + t * Q + off);
-        const float4 r = make_float4(lolu_mult(gate.x) * ov.x, lolu_mult(gate.y) * ov.y, lolu_mult(gate.z) * ov.z, lolu_mult(gate.w) * ov.w);
-        Fast<FT>::store4(rg, t * Q + off, scale4(r, s_act));
+        float4 gate[R], ov[R];
+        size_t t[R];
+        int off[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            off[r] = (ok[r] ? (int)(item % tiles) : 0) * TILE + lane * 4;
+            gate[r] = ok[r] ? load_half4(qkvg + t[r] * 4 * Q + 3 * Q + off[r]) : make_float4(0, 0, 0, 0);
+            ov[r] = ok[r] ? load_half4(o + t[r] * Q + off[r]) : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const float4 res = make_float4(lolu_mult(gate[r].x) * ov[r].x, lolu_mult(gate[r].y) * ov[r].y, lolu_mult(gate[r].z) * ov[r].z,
+                                           lolu_mult(gate[r].w) * ov[r].w);
+            Fast<FT>::store4(rg, t[r] * Q + off[r], scale4(res, s_act));
+        }
     }
 }
 
@@ -305,22 +398,39 @@ __global__ void att_gate_backward_kernel(const __half *__restrict__ drg, const _
                                          int T, int Q, void *__restrict__ d4, __half *__restrict__ dout, float *__restrict__ dscale)
 {
     const int tiles = Q / TILE; // = heads
-    WARP_ITEM_LOOP((long long)T * tiles)
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
     {
-        const size_t t = item / tiles;
-        const int h = (int)(item % tiles), off = h * TILE + lane * 4;
-        const float4 g = load_half4(drg + t * Q + off);
-        const float4 gate = load_half4(qkvg + t * 4 * Q + 3 * Q + off);
-        const float4 ov = load_half4(o + t * Q + off);
-        const float4 m = make_float4(lolu_mult(gate.x), lolu_mult(gate.y), lolu_mult(gate.z), lolu_mult(gate.w));
-        const float4 dgate = make_float4(g.x * ov.x * m.x * (1 - m.x) * 2.f, g.y * ov.y * m.y * (1 - m.y) * 2.f,
-                                         g.z * ov.z * m.z * (1 - m.z) * 2.f, g.w * ov.w * m.w * (1 - m.w) * 2.f);
-        const float4 dov = make_float4(g.x * m.x, g.y * m.y, g.z * m.z, g.w * m.w);
-        Fast<FT>::store4(d4, t * 4 * Q + 3 * Q + off, dgate);
-        store_half4(dout + t * Q + off, dov);
-        const float ds = warp_sum(dot4(dov, ov));
-        if (lane == 0)
-            dscale[t * tiles + h] = ds;
+        float4 g[R], gate[R], ov[R];
+        size_t t[R];
+        int h[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            h[r] = ok[r] ? (int)(item % tiles) : 0;
+            const int off = h[r] * TILE + lane * 4;
+            g[r] = ok[r] ? load_half4(drg + t[r] * Q + off) : make_float4(0, 0, 0, 0);
+            gate[r] = ok[r] ? load_half4(qkvg + t[r] * 4 * Q + 3 * Q + off) : make_float4(0, 0, 0, 0);
+            ov[r] = ok[r] ? load_half4(o + t[r] * Q + off) : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const int off = h[r] * TILE + lane * 4;
+            const float4 m = make_float4(lolu_mult(gate[r].x), lolu_mult(gate[r].y), lolu_mult(gate[r].z), lolu_mult(gate[r].w));
+            const float4 dgate = make_float4(g[r].x * ov[r].x * m.x * (1 - m.x) * 2.f, g[r].y * ov[r].y * m.y * (1 - m.y) * 2.f,
+                                             g[r].z * ov[r].z * m.z * (1 - m.z) * 2.f, g[r].w * ov[r].w * m.w * (1 - m.w) * 2.f);
+            const float4 dov = make_float4(g[r].x * m.x, g[r].y * m.y, g[r].z * m.z, g[r].w * m.w);
+            Fast<FT>::store4(d4, t[r] * 4 * Q + 3 * Q + off, dgate);
+            store_half4(dout + t[r] * Q + off, dov);
+            const float ds = warp_sum(dot4(dov, ov[r]));
+            if (lane == 0)
+                dscale[t[r] * tiles + h[r]] = ds;
+        }
     }
 }
 
@@ -355,14 +465,22 @@ __global__ void softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, 
             continue;
         }
         float mx = 0.f; // the reference starts the maximum at 0 and takes it over the logits without bias
-        for (int i = tid; i < V / 8; i += nthr) {
-            uint4 raw = ((const uint4 *)src)[i];
-            ((uint4 *)row_s)[i] = raw;
-            const __half2 *h = (const __half2 *)&raw;
+        for (int i0 = tid; i0 < V / 8; i0 += nthr * 4) {
+            uint4 raw[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 f = __half22float2(h[j]);
-                mx = fmaxf(mx, fmaxf(f.x, f.y));
+            for (int u = 0; u < 4; ++u)
+                raw[u] = (i0 + u * nthr < V / 8) ? ((const uint4 *)src)[i0 + u * nthr] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + u * nthr >= V / 8)
+                    continue;
+                ((uint4 *)row_s)[i0 + u * nthr] = raw[u];
+                const __half2 *h = (const __half2 *)&raw[u];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = __half22float2(h[j]);
+                    mx = fmaxf(mx, fmaxf(f.x, f.y));
+                }
             }
         }
         mx = warp_max(mx);

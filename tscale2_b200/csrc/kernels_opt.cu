@@ -198,8 +198,7 @@ __global__ void convert_kernel(const float *__restrict__ w, long long x, long lo
     }
 }
 
-int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, void *dst, int64_t ld, void *dstT, int64_t ldT,
-               float *sko_out, float *scratch, bool transposed_as_half)
+int matrix_sko(const Ctx &c, const float *w, int64_t x, int64_t y, float *sko_out, float *scratch)
 {
     // scratch holds y doubles
     const int grid = (int)std::max<long long>(1, std::min<long long>(ceil_div(y, WARPS), (long long)sm_count(c.device) * 8));
@@ -207,6 +206,21 @@ int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, vo
     TS2_CHECK_LAUNCH();
     sko_kernel<<<1, 1024, 0, c.stream>>>((const double *)scratch, x, y, sko_out);
     TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, void *dst, int64_t ld, void *dstT, int64_t ldT,
+               float *sko_out, float *scratch, bool transposed_as_half)
+{
+    int rc = matrix_sko(c, w, x, y, sko_out, scratch);
+    if (rc != TS2_OK)
+        return rc;
+    return convert_block(c, w, x, y, quant, dst, ld, dstT, ldT, sko_out, transposed_as_half);
+}
+
+int convert_block(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, void *dst, int64_t ld, void *dstT, int64_t ldT,
+                  const float *sko_out, bool transposed_as_half)
+{
     dim3 g((unsigned)ceil_div(x, 32), (unsigned)ceil_div(y, 32)), b(32, 8);
     if (quant == 0 && transposed_as_half)
         convert_kernel<0, true><<<g, b, 0, c.stream>>>(w, x, y, sko_out, dst, ld, dstT, ldT);

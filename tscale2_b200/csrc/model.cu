@@ -55,7 +55,15 @@ struct Layer {
     float *qscale = nullptr, *vscale = nullptr, *lse = nullptr;
     __half *what = nullptr;                 // ffn: normalized wide
     float *wscale = nullptr;
-    void *rg = nullptr;                     // [T][wide]
+    void *rg = nullptr;                     // [T][wide]  (MoE: [rows][X])
+    // mixture of experts: wide = expert width X, ncat = 2; quantized weights are per expert:
+    // Wcat [E][2X][D], WcatT [E][D][2X], Wc [E][D][X], WcT [E][X][D]; select matrix padded to epad rows / columns
+    void *Wsel = nullptr, *WselT = nullptr; // [epad][D], [D][epad]
+    float *bwd_row_e = nullptr;             // [X] 1 / sko of the expand matrix
+    void *n_rows = nullptr;                 // [rows][D] gathered normalized state
+    float *logits = nullptr;                // [T][epad]
+    int *ids = nullptr, *slot_of = nullptr, *token_of = nullptr, *tile_group = nullptr, *seg_ptr = nullptr;
+    float *weights = nullptr, *weight_of = nullptr;
 };
 
 struct BatchDev {
@@ -103,6 +111,11 @@ struct ts2_model {
     void *dcat = nullptr;
     float *dscale = nullptr, *dq = nullptr, *dk = nullptr, *dv = nullptr;
     float *rope = nullptr;
+    // mixture-of-experts scratch shared by the layers
+    int E = 0, K = 0, X = 0, epad = 0, moe_rows = 0;
+    float *moe_y = nullptr, *dmoe_part = nullptr;
+    void *moe_g = nullptr, *moe_dl = nullptr;
+    int *moe_hist = nullptr, *moe_base = nullptr;
     unsigned *absmax = nullptr; // [L+2]
     float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
     void *workspace = nullptr;
@@ -200,6 +213,44 @@ int gemm_dw(ts2_model *m, int kind, int64_t Mo, int64_t Ni, int64_t T, const voi
     return gemm(a);
 }
 
+// rows of A are expert-sorted: every 128-row tile reads the weights of its expert (B has E * N rows)
+int gemm_rows_grouped(ts2_model *m, const Layer &ly, int64_t rows, int64_t N, int64_t K, const void *A, int64_t lda, const void *B,
+                      int64_t ldb, void *C, int64_t ldc, const Epilogue &epi)
+{
+    GemmArgs a;
+    a.device = m->device;
+    a.stream = m->stream;
+    a.kind = m->kind;
+    a.mn_major = false;
+    a.M = rows, a.N = N, a.K = K;
+    a.A = A, a.lda = lda, a.B = B, a.ldb = ldb, a.C = C, a.ldc = ldc;
+    a.epi = epi;
+    a.group_mode = 1;
+    a.groups = m->E;
+    a.tile_group = ly.tile_group;
+    a.group_rows_b = (int)N;
+    return gemm(a);
+}
+
+// per-expert weight gradients: dW_e[Mo][Ni] = dY_e^T . X_e over the rows of expert e's segment
+int gemm_k_grouped(ts2_model *m, const Layer &ly, int64_t Mo, int64_t Ni, int64_t rows, const void *dY, int64_t ldy, const void *X,
+                   int64_t ldx, float *dW, int64_t stride, const Epilogue &epi)
+{
+    GemmArgs a;
+    a.device = m->device;
+    a.stream = m->stream;
+    a.kind = m->kind;
+    a.mn_major = true;
+    a.M = Mo, a.N = Ni, a.K = rows;
+    a.A = dY, a.lda = ldy, a.B = X, a.ldb = ldx, a.C = dW, a.ldc = Ni;
+    a.epi = epi;
+    a.group_mode = 2;
+    a.groups = m->E;
+    a.group_kptr = ly.seg_ptr;
+    a.c_group_stride = stride;
+    return gemm(a);
+}
+
 int validate(const ts2_model_descr *d)
 {
     if (!d)
@@ -216,8 +267,14 @@ int validate(const ts2_model_descr *d)
         return fail(TS2_ERR_UNSUPPORTED, "precision must be TS2_PREC_FP8 or TS2_PREC_F16");
     for (int l = 0; l < d->layer_count; ++l) {
         int t = d->layers[l].layer_type;
-        if (t == TS2_LAYER_MOE)
-            return fail(TS2_ERR_UNSUPPORTED, "layer %d: MoE layers are not built into the engine yet", l);
+        if (t == TS2_LAYER_MOE) {
+            if (d->moe_expert_count < 1 || d->moe_expert_count > 128 || d->moe_selected < 1 || d->moe_selected > 8 ||
+                d->moe_selected > d->moe_expert_count || d->expert_dim <= 0 || d->expert_dim % 128)
+                return fail(TS2_ERR_UNSUPPORTED,
+                            "layer %d: MoE needs 1..128 experts, 1..8 selected, expert_dim a multiple of 128 (got %d, %d, %d)", l,
+                            d->moe_expert_count, d->moe_selected, d->expert_dim);
+            continue;
+        }
         if (t != TS2_LAYER_ATT && t != TS2_LAYER_FFN)
             return fail(TS2_ERR_UNSUPPORTED, "layer %d: unsupported layer type %d", l, t);
         if (t == TS2_LAYER_FFN && d->ffn_tiles <= 0)
@@ -276,6 +333,25 @@ int requantize_all(ts2_model *m)
     const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
     for (Layer &ly : m->layers) {
         const int W = ly.wide, n = ly.ncat;
+        if (ly.type == TS2_LAYER_MOE) {
+            const int E = m->E, X = m->X;
+            Matrix &me = m->mats[ly.mat0], &mg = m->mats[ly.mat0 + 1], &mc = m->mats[ly.mat0 + 2], &ms = m->mats[ly.mat0 + 3];
+            M_TRY(matrix_sko(c, me.w, D, (int64_t)E * X, me.sko, scratch));
+            M_TRY(matrix_sko(c, mg.w, D, (int64_t)E * X, mg.sko, scratch));
+            M_TRY(matrix_sko(c, mc.w, X, (int64_t)E * D, mc.sko, scratch));
+            for (int e = 0; e < E; ++e) {
+                uint8_t *cat = (uint8_t *)ly.Wcat + (size_t)e * 2 * X * D * fs, *catT = (uint8_t *)ly.WcatT + (size_t)e * D * 2 * X * fs;
+                M_TRY(convert_block(c, me.w + (size_t)e * X * D, D, X, m->ft, cat, D, catT, 2 * X, me.sko, false));
+                M_TRY(convert_block(c, mg.w + (size_t)e * X * D, D, X, m->ft, cat + (size_t)X * D * fs, D, catT + (size_t)X * fs, 2 * X,
+                                    mg.sko, false));
+                M_TRY(convert_block(c, mc.w + (size_t)e * D * X, X, D, m->ft, (uint8_t *)ly.Wc + (size_t)e * D * X * fs, X,
+                                    (uint8_t *)ly.WcT + (size_t)e * X * D * fs, D, mc.sko, false));
+            }
+            M_TRY(requantize(c, ms.w, D, E, m->ft, ly.Wsel, D, ly.WselT, m->epad, ms.sko, scratch, false));
+            M_TRY(fill_vector(c, ly.fwd_col, 2 * X, a, nullptr, false));
+            M_TRY(fill_vector(c, ly.bwd_row_e, X, 1.f, me.sko, true));
+            continue;
+        }
         for (int j = 0; j < n; ++j) {
             Matrix &mt = m->mats[ly.mat0 + j];
             M_TRY(requantize(c, mt.w, D, W, m->ft, (uint8_t *)ly.Wcat + (size_t)j * W * D * fs, D, (uint8_t *)ly.WcatT + (size_t)j * W * fs,
@@ -310,6 +386,11 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     m->ft = d.precision == TS2_PREC_FP8 ? 0 : 1;
     m->kind = m->ft == 0 ? KIND_E4M3 : KIND_F16;
     m->s_act = m->ft == 0 ? 16.f : 1.f;
+    m->E = d.moe_expert_count;
+    m->K = d.moe_selected;
+    m->X = d.expert_dim;
+    m->epad = (m->E + 31) / 32 * 32;
+    m->moe_rows = (m->K * m->max_nodes + 127) / 128 * 128 + 128 * m->E;
     const int D = m->D, T = m->max_nodes, L = m->L;
     const size_t fs = fast_size(m);
 
@@ -362,6 +443,7 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     m->layers.resize(L);
     int mi = 2;
     int max_wide = m->Q, max_cat = 4 * m->Q;
+    bool has_moe = false;
     for (int l = 0; l < L; ++l) {
         Layer &ly = m->layers[l];
         ly.type = d.layers[l].layer_type;
@@ -369,8 +451,37 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         ly.att_type = d.layers[l].attention_type_id;
         ly.mat0 = mi;
         mi += layer_matrix_count(ly.type);
-        ly.wide = ly.type == TS2_LAYER_ATT ? m->Q : m->F;
+        ly.wide = ly.type == TS2_LAYER_ATT ? m->Q : (ly.type == TS2_LAYER_FFN ? m->F : m->X);
         ly.ncat = ly.type == TS2_LAYER_ATT ? 4 : 2;
+        if (ly.type == TS2_LAYER_MOE) {
+            has_moe = true;
+            const size_t E = m->E, X = m->X, R = m->moe_rows;
+            M_TRY(dalloc(m, (uint8_t **)&ly.Wcat, E * 2 * X * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.WcatT, E * 2 * X * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.Wc, E * X * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.WcT, E * X * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.Wsel, (size_t)m->epad * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.WselT, (size_t)m->epad * D * fs));
+            TS2_CUDA(cudaMemsetAsync(ly.Wsel, 0, (size_t)m->epad * D * fs, m->stream));
+            TS2_CUDA(cudaMemsetAsync(ly.WselT, 0, (size_t)m->epad * D * fs, m->stream));
+            M_TRY(dalloc(m, &ly.fwd_col, 2 * X));
+            M_TRY(dalloc(m, &ly.bwd_row_e, X));
+            M_TRY(dalloc(m, (uint8_t **)&ly.n_fast, (size_t)T * D * fs));
+            M_TRY(dalloc(m, (uint8_t **)&ly.n_rows, R * D * fs));
+            M_TRY(dalloc(m, &ly.cat16, R * 2 * X));
+            M_TRY(dalloc(m, &ly.what, R * X));
+            M_TRY(dalloc(m, &ly.wscale, R * (X / 128)));
+            M_TRY(dalloc(m, (uint8_t **)&ly.rg, R * X * fs));
+            M_TRY(dalloc(m, &ly.logits, (size_t)T * m->epad));
+            M_TRY(dalloc(m, &ly.ids, (size_t)T * m->K));
+            M_TRY(dalloc(m, &ly.weights, (size_t)T * m->K));
+            M_TRY(dalloc(m, &ly.slot_of, (size_t)T * m->K));
+            M_TRY(dalloc(m, &ly.token_of, R));
+            M_TRY(dalloc(m, &ly.weight_of, R));
+            M_TRY(dalloc(m, &ly.tile_group, R / 128));
+            M_TRY(dalloc(m, &ly.seg_ptr, E + 1));
+            continue;
+        }
         max_wide = std::max(max_wide, ly.wide);
         max_cat = std::max(max_cat, ly.ncat * ly.wide);
         const size_t W = ly.wide, C = (size_t)ly.ncat * ly.wide;
@@ -408,9 +519,22 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     // the final layer is processed in chunks of nodes so that its logits stay a few hundred MB
     m->chunk = std::min(T, std::max(128, (int)((size_t)(1u << 28) / (size_t)m->V) / 128 * 128));
     M_TRY(dalloc(m, &m->logits, (size_t)m->chunk * m->V));
-    M_TRY(dalloc(m, &m->drg, (size_t)T * max_wide));
+    size_t drg_elems = (size_t)T * max_wide, dcat_elems = (size_t)T * max_cat;
+    if (has_moe) {
+        const size_t R = m->moe_rows, X = m->X;
+        drg_elems = std::max(drg_elems, R * X);
+        dcat_elems = std::max(dcat_elems, R * 2 * X);
+        M_TRY(dalloc(m, &m->moe_y, R * D));
+        M_TRY(dalloc(m, (uint8_t **)&m->moe_g, R * D * fs));
+        M_TRY(dalloc(m, &m->dmoe_part, R * (X / 128)));
+        M_TRY(dalloc(m, (uint8_t **)&m->moe_dl, (size_t)T * m->epad * fs));
+        const size_t nb = (size_t)(T + 255) / 256 * m->E;
+        M_TRY(dalloc(m, &m->moe_hist, nb));
+        M_TRY(dalloc(m, &m->moe_base, nb));
+    }
+    M_TRY(dalloc(m, &m->drg, drg_elems));
     M_TRY(dalloc(m, &m->dout, (size_t)T * m->Q));
-    M_TRY(dalloc(m, (uint8_t **)&m->dcat, (size_t)T * max_cat * fs));
+    M_TRY(dalloc(m, (uint8_t **)&m->dcat, dcat_elems * fs));
     M_TRY(dalloc(m, &m->dscale, (size_t)T * m->H));
     M_TRY(dalloc(m, &m->dq, (size_t)T * m->Q));
     M_TRY(dalloc(m, &m->dk, (size_t)T * m->Q));
@@ -444,6 +568,8 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     // split-K scratch: the largest request of any dW contraction of this model
     size_t ws = 0;
     for (Layer &ly : m->layers) {
+        if (ly.type == TS2_LAYER_MOE)
+            continue; // the grouped contractions never split K
         ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, (int64_t)ly.ncat * ly.wide, D, T));
         ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, D, ly.wide, T));
     }
@@ -472,6 +598,32 @@ int forward(ts2_model *m)
         Layer &ly = m->layers[l];
         const int W = ly.wide, C = ly.ncat * W;
         M_TRY(tilenorm_forward(c, m->states[l], T, D, ly.n_fast, nullptr));
+        if (ly.type == TS2_LAYER_MOE) {
+            // TMoELayer::ComputeForward, layer_moe.cu:459-486, on expert-sorted rows
+            const int E = m->E, K = m->K, X = m->X, rows = (K * T + 127) / 128 * 128 + 128 * E;
+            const size_t fs = fast_size(m);
+            Epilogue es;
+            es.alpha = sqrtf(1.0f / D) / (m->s_act * 32.f); // select matrix is used without its scale
+            es.out_kind = TS2_OUT_F32;
+            M_TRY(gemm_tn(m, m->kind, T, m->epad, D, ly.n_fast, D, ly.Wsel, D, ly.logits, m->epad, es));
+            M_TRY(moe_route(c, ly.logits, m->epad, T, E, K, ly.ids, ly.weights));
+            M_TRY(moe_build_slots(c, ly.ids, ly.weights, T, K, E, rows, m->moe_hist, m->moe_base, ly.seg_ptr, ly.tile_group, ly.slot_of,
+                                  ly.token_of, ly.weight_of));
+            M_TRY(moe_gather_rows(c, ly.n_fast, ly.token_of, rows, (int)(D * fs), ly.n_rows));
+            Epilogue e1;
+            e1.col_scale = ly.fwd_col;
+            e1.out_kind = TS2_OUT_F16;
+            M_TRY(gemm_rows_grouped(m, ly, rows, 2 * X, D, ly.n_rows, D, ly.Wcat, D, ly.cat16, 2 * X, e1));
+            M_TRY(moe_act_forward(c, ly.cat16, ly.token_of, ly.weight_of, rows, X, ly.what, ly.wscale, ly.rg));
+            // the contract matrix is [D][E*X] for the CPU path: its dot scale is sqrt(1 / (E*X))
+            Epilogue e2;
+            e2.alpha = sqrtf(1.0f / ((float)E * X)) / (m->s_act * 32.f);
+            e2.dyn_scale = m->mats[ly.mat0 + 2].sko;
+            e2.out_kind = TS2_OUT_F32;
+            M_TRY(gemm_rows_grouped(m, ly, rows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
+            M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+            continue;
+        }
         // [Q|K|V|Gate] or [wide|gate] = n . Wcat^T * sqrt(1/D)   (MulForward, cpu_util.cpp:7-27)
         Epilogue e1;
         e1.col_scale = ly.fwd_col;
@@ -556,6 +708,58 @@ int backward(ts2_model *m)
         Layer &ly = m->layers[l];
         const int W = ly.wide, C = ly.ncat * W;
         Matrix &mc = m->mats[ly.mat0 + ly.ncat];
+        if (ly.type == TS2_LAYER_MOE) {
+            // TMoELayer::ComputeBackward, layer_moe.cu:488-537, on expert-sorted rows
+            const int E = m->E, K = m->K, X = m->X, rows = (K * T + 127) / 128 * 128 + 128 * E;
+            const size_t fs = fast_size(m);
+            M_TRY(cast_grad(c, m->g, (size_t)T * D, m->absmax + l + 1, m->g_fast, m->ginv, sqrtf((float)D / ((float)E * X)), mc.sko,
+                            m->fscale));
+            M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->moe_g));
+            Epilogue e3;
+            e3.alpha = 1.f / (32.f * sqrtf((float)D));
+            e3.out_kind = TS2_OUT_F16;
+            M_TRY(gemm_rows_grouped(m, ly, rows, X, D, m->moe_g, D, ly.WcT, D, m->drg, X, e3));
+            if (tune_layers) {
+                Epilogue e6;
+                e6.alpha = 1.f / m->s_act;
+                e6.dyn_scale = m->ginv;
+                e6.out_kind = TS2_OUT_F32_ADD;
+                M_TRY(gemm_k_grouped(m, ly, D, X, rows, m->moe_g, D, ly.rg, X, mc.grad, (int64_t)D * X, e6));
+            }
+            M_TRY(moe_act_backward(c, m->drg, ly.cat16, ly.what, ly.wscale, ly.token_of, ly.weight_of, rows, X, m->dcat, m->dmoe_part));
+            M_TRY(moe_router_backward(c, m->dmoe_part, X / 128, ly.ids, ly.weights, ly.slot_of, T, K, E, m->epad, m->moe_dl));
+            // router: dn = dl . Sel * sqrt(1/D) (scale-free matrix), dW_sel = dl^T . n
+            Epilogue er;
+            er.alpha = sqrtf(1.0f / D) / 32.f;
+            er.out_kind = TS2_OUT_F32;
+            M_TRY(gemm_tn(m, m->kind, T, D, m->epad, m->moe_dl, m->epad, ly.WselT, m->epad, m->dn, D, er));
+            if (tune_layers) {
+                Epilogue ew;
+                ew.alpha = 1.f / m->s_act;
+                ew.dyn_scale = m->fscale;
+                ew.out_kind = TS2_OUT_F32_ADD;
+                M_TRY(gemm_dw(m, m->kind, E, D, T, m->moe_dl, m->epad, ly.n_fast, D, m->mats[ly.mat0 + 3].grad, ew));
+            }
+            Epilogue e4;
+            e4.alpha = sqrtf(1.0f / D) / 32.f;
+            e4.out_kind = TS2_OUT_F32;
+            M_TRY(gemm_rows_grouped(m, ly, rows, D, 2 * X, m->dcat, 2 * X, ly.WcatT, 2 * X, m->moe_y, D, e4));
+            M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, nullptr, m->dn));
+            if (tune_layers) {
+                Epilogue e5;
+                e5.alpha = 1.f / m->s_act;
+                e5.dyn_scale = m->fscale;
+                e5.out_kind = TS2_OUT_F32_ADD;
+                Epilogue e5e = e5;
+                e5e.row_scale = ly.bwd_row_e; // expand is followed by a normalisation: rows divided by its matrix scale
+                M_TRY(gemm_k_grouped(m, ly, X, D, rows, m->dcat, 2 * X, ly.n_rows, D, m->mats[ly.mat0].grad, (int64_t)X * D, e5e));
+                M_TRY(gemm_k_grouped(m, ly, X, D, rows, (const uint8_t *)m->dcat + (size_t)X * fs, 2 * X, ly.n_rows, D,
+                                     m->mats[ly.mat0 + 1].grad, (int64_t)X * D, e5));
+            }
+            M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
+            M_TRY(tap_gradient(m, l));
+            continue;
+        }
         // g_fast = g * 2^k; fscale = sqrt(D/W) * sko_c / 2^k turns the scale-free intermediate gradients
         // below into true ones
         M_TRY(cast_grad(c, m->g, (size_t)T * D, m->absmax + l + 1, m->g_fast, m->ginv, sqrtf((float)D / (float)W), mc.sko, m->fscale));
@@ -996,8 +1200,8 @@ int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, 
     } else {
         for (Layer &ly : m->layers) {
             const int j = index - ly.mat0;
-            if (j < 0 || j > ly.ncat)
-                continue;
+            if (ly.type == TS2_LAYER_MOE || j < 0 || j > ly.ncat)
+                continue; // expert matrices are stored per expert, not in matrix order
             src = j < ly.ncat ? (const void *)((const uint8_t *)ly.Wcat + (size_t)j * ly.wide * m->D * es) : ly.Wc;
             break;
         }
@@ -1035,6 +1239,25 @@ int ts2_get_state_tap(ts2_model *m, int layer, int gradient, float *dst, int64_t
     M_TRY(wait_stream(m));
     const float *src = gradient ? m->grad_taps + (size_t)layer * m->max_nodes * m->D : m->states[layer];
     TS2_CUDA(cudaMemcpy(dst, src, n * 4, cudaMemcpyDeviceToHost));
+    return TS2_OK;
+}
+
+int ts2_debug_read(ts2_model *m, const char *name, int layer, void *dst, int64_t bytes)
+{
+    if (!m || !name || !dst || layer < 0 || layer >= m->L)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_debug_read");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    const Layer &ly = m->layers[layer];
+    const std::string n = name;
+    const void *src = n == "rg" ? ly.rg : n == "dcat" ? m->dcat : n == "token_of" ? (const void *)ly.token_of
+                      : n == "seg_ptr" ? (const void *)ly.seg_ptr : n == "slot_of" ? (const void *)ly.slot_of
+                      : n == "ids" ? (const void *)ly.ids : n == "weights" ? (const void *)ly.weights
+                      : n == "cat16" ? (const void *)ly.cat16 : n == "n_fast" ? ly.n_fast : n == "n_rows" ? ly.n_rows
+                      : n == "logits" ? (const void *)ly.logits : n == "moe_g" ? m->moe_g : n == "drg" ? (const void *)m->drg : nullptr;
+    if (!src)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_debug_read: unknown or absent buffer '%s'", name);
+    TS2_CUDA(cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost));
     return TS2_OK;
 }
 

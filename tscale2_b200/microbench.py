@@ -1,0 +1,84 @@
+"""Operator-level micro-benchmarks through the C ABI (no torch): the contraction kernels at the
+shapes of BASELINE config 2 (backward GEMM microbench) or any other shape, and the attention core.
+
+    python -m tscale2_b200.microbench --op dx --prec fp8 --M 16384 --N 4096 --K 4096
+    python -m tscale2_b200.microbench --op dw --prec int8 --M 4096 --N 4096 --K 16384   # dW[M][N], K tokens
+    python -m tscale2_b200.microbench --op config2
+
+Times with CUDA events around each launch on the launching stream (ts2_set_kernel_timing); operands are
+random bytes of the operand format (no NaN codes), larger than L2 for the config-2 shapes.  One JSON line
+per measurement."""
+import argparse
+import ctypes as C
+import json
+
+import numpy as np
+
+from . import capi
+from .device import DeviceBuffer, check, sync
+
+PREC = {"fp8": (capi.PREC_FP8, 1), "f16": (capi.PREC_F16, 2), "int8": (capi.PREC_INT8, 1)}
+
+
+def _operand(rng, n_elems, es):
+    if es == 1:
+        return rng.integers(0, 256, n_elems, dtype=np.uint8) & np.uint8(0xBF)  # clears bit 6: |e4m3| < 2, no NaN; any int8
+    return rng.standard_normal(n_elems).astype(np.float16)
+
+
+def time_gemm(lib, op, prec_name, M, N, K, iters, warmup=3):
+    prec, es = PREC[prec_name]
+    rng = np.random.default_rng(1)
+    A = DeviceBuffer.from_numpy(_operand(rng, M * K, es))
+    B = DeviceBuffer.from_numpy(_operand(rng, N * K, es))
+    if op == "dw":
+        Cb = DeviceBuffer(M * N * 4)
+        ws_bytes = lib.ts2_gemm_dw_workspace_bytes(K, N, M)
+        WS = DeviceBuffer(max(ws_bytes, 16))
+
+        def run():
+            check(lib.ts2_gemm_dw(0, None, prec, capi.OUT_F32, K, N, M, A.ptr, B.ptr, Cb.ptr, 1.0, WS.ptr, ws_bytes))
+    else:
+        Cb = DeviceBuffer(M * N * 2)
+
+        def run():
+            check(lib.ts2_gemm_tn(0, None, prec, capi.OUT_BF16, M, N, K, A.ptr, K, B.ptr, K, Cb.ptr, N, 1.0, None, None))
+    for _ in range(warmup):
+        run()
+    sync()
+    check(lib.ts2_set_kernel_timing(None, 1))
+    lib.ts2_get_kernel_timing(None, 1, None, None, None)
+    for _ in range(iters):
+        run()
+    sync()
+    ms, n, fl = C.c_double(), C.c_int64(), C.c_double()
+    check(lib.ts2_get_kernel_timing(None, 1, C.byref(ms), C.byref(n), C.byref(fl)))
+    check(lib.ts2_set_kernel_timing(None, 0))
+    per = ms.value / max(n.value, 1)
+    return {"op": op, "prec": prec_name, "M": M, "N": N, "K": K, "ms": per, "tflops": 2.0 * M * N * K / per / 1e9,
+            "launches": n.value, "layout": "dW[M][N] = dY[K][M]^T . X[K][N] (token-major operands)" if op == "dw"
+            else "C[M][N] = A[M][K] . B[N][K]^T"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="config2", choices=["dx", "tn", "dw", "config2"])
+    ap.add_argument("--prec", default="fp8", choices=sorted(PREC))
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    lib = capi.load_library()
+    if args.op == "config2":
+        # BASELINE config 2: T = 16384 tokens, 4096 x 4096 weights: dX = dY.W^T (M=T, N=in, K=out), dW = X^T.dY (K = T)
+        for prec in ("fp8", "int8", "f16"):
+            print(json.dumps(time_gemm(lib, "dx", prec, 16384, 4096, 4096, args.iters, args.warmup)), flush=True)
+            print(json.dumps(time_gemm(lib, "dw", prec, 4096, 4096, 16384, args.iters, args.warmup)), flush=True)
+    else:
+        print(json.dumps(time_gemm(lib, "tn" if args.op == "dx" else args.op, args.prec, args.M, args.N, args.K, args.iters, args.warmup)))
+
+
+if __name__ == "__main__":
+    main()
