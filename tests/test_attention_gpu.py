@@ -52,7 +52,7 @@ def run_device(lib, variant, q, k, v, dout, start, finish, H, slope):
     return o.astype(np.float32), lse, DQ.download(shape, np.float32), DK.download(shape, np.float32), DV.download(shape, np.float32)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("T,frag,width,H,slope", [(128, 128, 128, 1, 0.0), (300, 100, 48, 2, 0.5), (512, 256, 1000, 2, 0.0),
                                                   (70, 35, 20, 1, 0.25), (640, 640, 64, 1, 0.0)])
 def test_attention_matches_oracle(oracle_port, variant, T, frag, width, H, slope):
@@ -85,7 +85,7 @@ def test_arbitrary_single_spans(oracle_port):
     start[none], finish[none] = 0, -1
     ref = oracle_port.attention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), H, 0.0, csr(start, finish),
                                 dout.astype(np.float32))
-    for variant in (0, 1):
+    for variant in (0, 1, 2):
         o, lse, dq, dk, dv = run_device(lib, variant, q, k, v, dout, start, finish, H, 0.0)
         assert rel_l2(o, ref["val"]) < 1.5e-3
         assert rel_l2(dq, ref["dq"]) < 3e-3 and rel_l2(dk, ref["dk"]) < 3e-3 and rel_l2(dv, ref["dv"]) < 3e-3

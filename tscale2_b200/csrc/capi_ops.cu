@@ -274,9 +274,11 @@ int ts2_attention_forward(int device, void *stream, int variant, const void *q, 
     Ctx c;
     c.device = device;
     c.stream = (cudaStream_t)stream;
-    int rc = variant == 0 ? attention_forward_mma(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
-                                                  alibi_slope, (__half *)o, lse)
-                          : attention_forward_rowwise(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
+    int rc = variant == 2 ? attention_forward_tc(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
+                                                 alibi_slope, (__half *)o, lse)
+             : variant == 0 ? attention_forward_mma(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
+                                                    alibi_slope, (__half *)o, lse)
+                            : attention_forward_rowwise(c, (const __half *)q, (const __half *)k, (const __half *)v, d, d + T, T, head_count,
                                                       alibi_slope, (__half *)o, lse);
     cudaStreamSynchronize(c.stream);
     cudaFree(d);
@@ -301,7 +303,7 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
     c.device = device;
     c.stream = (cudaStream_t)stream;
     const __half *Q = (const __half *)q, *K = (const __half *)k, *V = (const __half *)v, *DO = (const __half *)dout;
-    int rc = variant == 0 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
+    int rc = variant != 1 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
                                                    dq, dk, dv)
                           : attention_backward_rowwise(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count,
                                                        alibi_slope, dq, dk, dv);

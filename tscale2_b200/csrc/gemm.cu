@@ -490,6 +490,11 @@ static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, i
     return TS2_OK;
 }
 
+int make_tensor_map(::CUtensorMap_st *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows)
+{
+    return make_tmap(tm, base, es, inner, rows, ld, box_rows);
+}
+
 static int elem_size(int kind) { return (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1; }
 
 static uint32_t instr_desc(int kind, bool mn, int bn)

@@ -3,6 +3,7 @@
 // contractions of the training step.
 #pragma once
 #include "common.cuh"
+struct CUtensorMap_st;
 
 namespace ts2 {
 
@@ -48,6 +49,10 @@ struct GemmArgs {
 int gemm_splits(int device, int kind, bool mn_major, int64_t M, int64_t N, int64_t K);
 size_t gemm_workspace_bytes(int device, int kind, bool mn_major, int64_t M, int64_t N, int64_t K);
 int gemm(const GemmArgs &a);
+
+// 2-D TMA descriptor over a row-major [rows][ld] array of es-byte elements: box = 128 bytes x box_rows, 128-byte swizzle,
+// out-of-range elements read as zero
+int make_tensor_map(::CUtensorMap_st *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows);
 
 // accumulated device time of the contraction kernel (enabled by gemm_timing_enable)
 void gemm_timing_enable(bool on);

@@ -289,7 +289,7 @@ int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, c
 int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
                       int T, int H, float slope, __half *o, float *lse)
 {
-    return attention_forward_mma(c, q, k, v, span_start, span_finish, T, H, slope, o, lse);
+    return attention_forward_tc(c, q, k, v, span_start, span_finish, T, H, slope, o, lse);
 }
 
 int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
