@@ -303,7 +303,9 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
     c.device = device;
     c.stream = (cudaStream_t)stream;
     const __half *Q = (const __half *)q, *K = (const __half *)k, *V = (const __half *)v, *DO = (const __half *)dout;
-    int rc = variant != 1 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
+    int rc = variant == 2 ? attention_backward_tc(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
+                                                  dq, dk, dv)
+             : variant == 0 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
                                                    dq, dk, dv)
                           : attention_backward_rowwise(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count,
                                                        alibi_slope, dq, dk, dv);

@@ -79,6 +79,9 @@ int attention_backward_mma(const Ctx &c, const __half *q, const __half *k, const
                            const int *rev_last, int T, int H, float slope, float *dq, float *dk, float *dv);
 int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
                          int T, int H, float slope, __half *o, float *lse);
+int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                          const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
+                          int T, int H, float slope, float *dq, float *dk, float *dv);
 int attention_forward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start,
                               const int *span_finish, int T, int H, float slope, __half *o, float *lse);
 int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,

@@ -4,8 +4,8 @@
 //   dp(from,to) = q_from . k_to * sqrt(1/128) * 0.5/ln2 - slope * (from - to)
 //   weights 2^(dp - maxDP) with maxDP >= 0 and an extra zero vector of weight 2^-maxDP.
 // This file holds the warp-per-row formulation (fp32 math, coalesced 8-byte loads), kept as an
-// independent second formulation for the tests; the engine runs the tensor-core kernels of
-// kernels_att_mma.cu.
+// independent second formulation for the tests; the engine runs the tcgen05 kernels of
+// kernels_att_tc.cu (kernels_att_mma.cu holds an mma.sync formulation, also kept for the tests).
 #include "kernels.cuh"
 #include "fast_types.cuh"
 
@@ -296,7 +296,7 @@ int attention_backward(const Ctx &c, const __half *q, const __half *k, const __h
                        const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
                        int T, int H, float slope, float *dq, float *dk, float *dv)
 {
-    return attention_backward_mma(c, q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H, slope, dq, dk, dv);
+    return attention_backward_tc(c, q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H, slope, dq, dk, dv);
 }
 
 } // namespace ts2
