@@ -104,6 +104,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
                  "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
                  : "memory");
 }
+// 2-D tiled TMA store shared -> global (rows / columns outside the tensor are clipped), bulk-group completion
+__device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

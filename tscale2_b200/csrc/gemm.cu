@@ -4,8 +4,10 @@
 //                 128B-swizzled shared-memory stages, completion on mbarriers
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one elected thread), releases
 //                 stages and publishes accumulators with tcgen05.commit
-//   warps 2..5  : epilogue — tcgen05.ld the fp32/int32 accumulator (128 lanes x BN
-//                 columns) out of TMEM, apply scales, convert, store
+//   warps 2..9  : epilogue — tcgen05.ld the fp32/int32 accumulator (128 lanes x BN
+//                 columns; two warps per lane quarter, half of the columns each) out of
+//                 TMEM, apply scales, convert, stage 32-row blocks in shared memory and
+//                 write them with TMA stores (direct stores for the accumulate form)
 // Two TMEM accumulators (2 x BN columns) let the epilogue of one tile overlap the
 // main loop of the next.  Work units are (tile, K-split); partial tiles of split
 // units go to an fp32 workspace and are combined by reduce_splitk_kernel in a fixed
@@ -25,7 +27,7 @@ namespace ts2 {
 
 static constexpr int BM = 128;
 static constexpr int STAGE_ROW_BYTES = 128; // one swizzle row
-static constexpr int NUM_THREADS = 192;
+static constexpr int NUM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 
 struct GemmParams {
     int M, N;
@@ -49,6 +51,7 @@ struct GemmParams {
     const int *group_kptr;
     long long c_group_stride;
     int bk;
+    int tma_store; // the epilogue stages 32-row blocks in shared memory and writes them with TMA (tmC)
 };
 
 struct Unit {
@@ -125,13 +128,15 @@ struct SmemLayout {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // barriers + alignment slack
+    static constexpr int STAGING_OFFSET = BAR_OFFSET + 1024;     // epilogue staging: 8 warps x 4 KB
+    static constexpr int TOTAL = STAGING_OFFSET + 4 * 2 * 4096 + 1024; // + alignment slack
 };
 
 // ES: element size in bytes; MMA: 0 = f8f6f4, 1 = f16 (fp16/bf16), 2 = i8; MN: operand layout
 template <int BN, int ES, int MMA, bool MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, const GemmParams p)
 {
     using L = SmemLayout<BN>;
     constexpr int STAGES = L::STAGES;
@@ -157,7 +162,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 4);
+            mbar_init(tempty0 + 8 * a, 8);
         }
         mbar_init(drain, 1);
         *abort_flag = 0;
@@ -298,6 +303,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             alpha *= __ldg(p.dyn_scale2);
         int acc = 0;
         uint32_t acc_phase = 0;
+        // the two warps of a quarter split the tile's columns: warps 2-5 take the first half, 6-9 the second
+        const int half = (warp - 2) >> 2;
+        constexpr int CHUNKS = BN / 32;
+        const int c_begin = half * (CHUNKS / 2), c_end = c_begin + CHUNKS / 2;
+        uint8_t *const stg_warp = smem + L::STAGING_OFFSET + (warp - 2) * 4096;
+        const bool out16 = p.out_kind == TS2_OUT_F16 || p.out_kind == TS2_OUT_BF16;
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
             Unit un;
             if (!decode_unit(p, u, BN, un))
@@ -316,7 +327,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 rs = __ldg(p.row_scale + row);
             rs *= alpha;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_begin; c < c_end; ++c) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c * 32, r);
                 tmem_ld_wait();
@@ -330,6 +341,66 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    continue;
+                }
+                if (p.tma_store) {
+                    // coalesced path: the warp's 32 rows x 128 bytes go through a swizzled staging block and one TMA
+                    // store; 16-bit outputs fill a block with two 32-column chunks.  Rows >= M and columns >= N are
+                    // clipped by the TMA unit.
+                    if (col < p.N) {
+                        if (p.col_scale) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                float4 cs = __ldg((const float4 *)(p.col_scale + col) + i);
+                                v[4 * i] *= cs.x * rs;
+                                v[4 * i + 1] *= cs.y * rs;
+                                v[4 * i + 2] *= cs.z * rs;
+                                v[4 * i + 3] *= cs.w * rs;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                v[i] *= rs;
+                        }
+                    }
+                    const bool first = !out16 || !(c & 1), last = !out16 || (c & 1);
+                    if (first) {
+                        if (lane == 0)
+                            bulk_wait_read<0>(); // the previous store of this warp has read the staging block
+                        __syncwarp();
+                    }
+                    uint8_t *blk = stg_warp, *srow = blk + lane * 128;
+                    if (!out16) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *(float4 *)(srow + ((i ^ (lane & 7)) << 4)) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 pk;
+                            if (p.out_kind == TS2_OUT_F16) {
+                                __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
+                                        h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                                pk = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                            } else {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]),
+                                               h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]),
+                                               h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]),
+                                               h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                                pk = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                            }
+                            *(uint4 *)(srow + ((((c & 1) * 4 + i) ^ (lane & 7)) << 4)) = pk;
+                        }
+                    }
+                    if (last) {
+                        fence_proxy_async();
+                        __syncwarp();
+                        const int col_blk = out16 ? col - 32 : col;
+                        if (lane == 0 && col_blk < p.N) {
+                            tma_store_2d(&tmC, smem_u32(blk), col_blk, m0 + quarter * 32);
+                            bulk_commit();
+                        }
+                    }
                     continue;
                 }
                 if (row >= p.M || col >= p.N)
@@ -390,6 +461,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (acc == 0)
                 acc_phase ^= 1;
         }
+        if (p.tma_store && lane == 0)
+            bulk_wait_read<0>(); // the staging blocks must outlive the stores that read them
     }
 
     tc_fence_before();
@@ -482,7 +555,7 @@ static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, i
     cuuint64_t strides[1] = {(cuuint64_t)(ld * es)};
     cuuint32_t box[2] = {(cuuint32_t)(STAGE_ROW_BYTES / es), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUtensorMapDataType dt = (es == 1) ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    CUtensorMapDataType dt = (es == 1) ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (es == 2) ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     CUresult r = fn(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -619,7 +692,8 @@ static cudaEvent_t pooled_event()
 }
 
 template <int BN, int ES, int MMA, bool MN>
-static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p)
+static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
+                  const GemmParams &p)
 {
     auto kern = gemm_kernel<BN, ES, MMA, MN>;
     static bool configured[16] = {};
@@ -627,7 +701,7 @@ static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, con
         TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL));
         configured[a.device & 15] = true;
     }
-    kern<<<pl.grid, NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, p);
+    kern<<<pl.grid, NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, tmC, p);
     TS2_CHECK_LAUNCH();
     if (pl.splits > 1) {
         const long long total = (long long)pl.m_tiles * pl.n_tiles * BM * BN / 4;
@@ -706,6 +780,15 @@ int gemm(const GemmArgs &a)
     p.group_kptr = a.group_kptr;
     p.c_group_stride = a.c_group_stride;
     p.bk = bk;
+    // coalesced TMA-store epilogue for plain stores (the accumulate form reads C anyway; split units go to the workspace;
+    // per-group C offsets of mode 2 are not expressible as one 2-D map)
+    CUtensorMap tmC = tmA;
+    p.tma_store = 0;
+    if (pl.splits == 1 && a.group_mode != 2 && a.epi.out_kind != TS2_OUT_F32_ADD) {
+        if ((rc = make_tmap(&tmC, a.C, out_es, a.N, a.M, a.ldc, 32)) != TS2_OK)
+            return rc;
+        p.tma_store = 1;
+    }
 
     cudaEvent_t ea = nullptr, eb = nullptr;
     bool timed;
@@ -723,7 +806,7 @@ int gemm(const GemmArgs &a)
     const int mma = (a.kind == KIND_E4M3) ? 0 : (a.kind == KIND_I8 ? 2 : 1);
 #define TS2_GEMM_CASE(BN_, ES_, MMA_, MN_)                                   \
     if (pl.bn == BN_ && es == ES_ && mma == MMA_ && a.mn_major == MN_)       \
-        rc = launch<BN_, ES_, MMA_, MN_>(a, pl, tmA, tmB, p);
+        rc = launch<BN_, ES_, MMA_, MN_>(a, pl, tmA, tmB, tmC, p);
     rc = TS2_ERR_UNSUPPORTED;
     TS2_GEMM_CASE(256, 1, 0, false)
     TS2_GEMM_CASE(128, 1, 0, false)
@@ -847,6 +930,7 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
     p.group_kptr = nullptr;
     p.c_group_stride = 0;
     p.bk = bk;
+    p.tma_store = 0;
     GemmArgs a;
     a.device = device;
     a.stream = (cudaStream_t)stream;
@@ -854,7 +938,7 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
     rc = TS2_ERR_UNSUPPORTED;
 #define TS2_NOALLOC_CASE(BN_, ES_, MMA_)             \
     if (pl.bn == BN_ && es == ES_ && mma == MMA_)    \
-        rc = launch<BN_, ES_, MMA_, true>(a, pl, tmA, tmB, p);
+        rc = launch<BN_, ES_, MMA_, true>(a, pl, tmA, tmB, tmA, p);
     TS2_NOALLOC_CASE(256, 1, 0)
     TS2_NOALLOC_CASE(128, 1, 0)
     TS2_NOALLOC_CASE(256, 2, 1)
