@@ -4,13 +4,17 @@
 // Same math and the same inputs / outputs as kernels_att_mma.cu (see there for the references
 // into src/gpt/compute/layer_att_reference.h and gpu_att_fp16.cu).
 //
-// Forward, one CTA per (128 nodes, head), 192 threads:
-//   warp 0     TMA producer: Q block once, then K / V tiles through a 2-stage ring
-//   warp 1     TMEM owner and MMA issuer: S = Q . K^T (128 x 64, fp32 in TMEM), later O += P . V
-//   warps 2-5  softmax: thread = node row (TMEM lane), so row maximum and row sum are thread-local;
-//              writes P (fp16) into a swizzled K-major shared-memory tile for the second MMA and
-//              rescales O in TMEM only when a row's maximum grew by more than 8 (2^8 headroom in
-//              fp16 P and fp32 sums), which keeps tcgen05.ld/st of O off the common path
+// Forward, one CTA per (128 nodes, head), 320 threads:
+//   warp 0     TMA producer: Q block once, then K and V tiles through two 2-stage rings (a K stage is
+//              free again as soon as its S product is done, long before the V stage of the same tile)
+//   warp 1     TMEM owner and MMA issuer: S = Q . K^T (128 x 64, fp32, two buffers in TMEM, so the
+//              product of tile j+1 runs while tile j is in the softmax), later O += P . V
+//   warps 2-9  softmax: two warps per TMEM lane quarter, thread = (node row, 32 of the tile's 64 keys);
+//              the pair agrees on the row maximum through shared memory (rounded up to bf16, so both
+//              use the same reference), writes P (fp16) into a swizzled K-major shared-memory tile
+//              for the second MMA and rescales O in TMEM only when a row's maximum grew by more
+//              than 8 (2^8 headroom in fp16 P and fp32 sums), which keeps tcgen05.ld/st of O off
+//              the common path
 // The zero "sink" vector of the reference is the initial state m = 0, l = 1.
 // Two CTAs fit an SM (112 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps
 // the other's MMAs.  Every wait is bounded (see mbar_wait); a give-up raises the status word.
@@ -24,14 +28,28 @@ namespace ts2 {
 static constexpr int TC_BM = 128;  // node rows per CTA
 static constexpr int TC_BN = 64;   // keys per tile
 static constexpr int TC_HD = 128;  // head width
-static constexpr int TC_THREADS = 192;
+static constexpr int TC_THREADS = 320;
 static constexpr int Q_BYTES = TC_BM * TC_HD * 2;   // 32 KB: two 128-byte-wide atoms of 128 rows
 static constexpr int KV_BYTES = TC_BN * TC_HD * 2;  // 16 KB: two atoms of 64 rows
 static constexpr int P_BYTES = TC_BM * TC_BN * 2;   // 16 KB: one atom of 128 rows
 // 112 KB of tiles + 128 B of barriers: two CTAs per SM (2 x (114816 + 1024 reserved) <= 228 KB)
-static constexpr int FWD_SMEM = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 128;
+static constexpr int FWD_XCH_OFF = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 128; // row maxima of the two column halves, bf16
+static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * TC_BM * 2;
 
 __host__ __device__ inline float att_dot_scale_tc() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
+
+#ifdef __CUDACC__
+// barrier of the two warps that share TMEM lane quarter q (ids 2..5; compile-time ids keep the CTA at 6 barriers)
+__device__ __forceinline__ void pair_barrier(int q)
+{
+    switch (q) {
+    case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+    }
+}
+#endif
 
 struct AttTcParams {
     int T, H;
@@ -42,7 +60,7 @@ struct AttTcParams {
     int32_t *status;
 };
 
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TC_THREADS, 2)
     att_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const AttTcParams p)
 {
@@ -55,9 +73,9 @@ __global__ void __launch_bounds__(TC_THREADS)
     }
     const uint32_t sQ = smem_u32(smem), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES, sP = sV + 2 * KV_BYTES;
     uint64_t *bars = (uint64_t *)(smem + Q_BYTES + 4 * KV_BYTES + P_BYTES);
-    const uint32_t q_full = smem_u32(bars), kv_full0 = smem_u32(bars + 1), kv_empty0 = smem_u32(bars + 3), s_full = smem_u32(bars + 5),
-                   p_full = smem_u32(bars + 6), o_ready = smem_u32(bars + 7);
-    uint32_t *tmem_slot = (uint32_t *)(bars + 8);
+    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 3), v_full0 = smem_u32(bars + 5),
+                   v_empty0 = smem_u32(bars + 7), s_full0 = smem_u32(bars + 9), p_full = smem_u32(bars + 11), o_ready = smem_u32(bars + 12);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     int &s_lo = *(int *)(tmem_slot + 2), &s_hi = *(int *)(tmem_slot + 3);
 
@@ -82,11 +100,13 @@ __global__ void __launch_bounds__(TC_THREADS)
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(kv_full0 + 8 * s, 1);
-            mbar_init(kv_empty0 + 8 * s, 1);
+            mbar_init(k_full0 + 8 * s, 1);
+            mbar_init(k_empty0 + 8 * s, 1);
+            mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1);
+            mbar_init(s_full0 + 8 * s, 1);
         }
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        mbar_init(p_full, 256);
         mbar_init(o_ready, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -102,101 +122,131 @@ __global__ void __launch_bounds__(TC_THREADS)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + TC_BN;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 2 * TC_BN; // S buffers at columns 0 and 64
     const int lo = s_lo, hi = s_hi;
     const int tile0 = hi >= lo ? lo / TC_BN : 0, tile1 = hi >= lo ? hi / TC_BN : -1; // no keys: no tiles
     const int col0 = h * TC_HD;
 
+    const int n_tiles = tile1 - tile0 + 1;
     if (warp == 0) {
-        if (lane == 0 && tile1 >= tile0) {
+        if (lane == 0 && n_tiles > 0) {
             mbar_arrive_expect_tx(q_full, Q_BYTES);
             tma_load_2d(sQ, &tmQ, q_full, col0, t0);
             tma_load_2d(sQ + Q_BYTES / 2, &tmQ, q_full, col0 + 64, t0);
-            for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
-                const int st = j & 1;
-                if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag))
-                    break;
-                const uint32_t fb = kv_full0 + 8 * st;
-                mbar_arrive_expect_tx(fb, 2 * KV_BYTES);
-                const uint32_t dk = sK + st * KV_BYTES, dv = sV + st * KV_BYTES;
-                tma_load_2d(dk, &tmK, fb, col0, tile * TC_BN);
-                tma_load_2d(dk + KV_BYTES / 2, &tmK, fb, col0 + 64, tile * TC_BN);
-                tma_load_2d(dv, &tmV, fb, col0, tile * TC_BN);
-                tma_load_2d(dv + KV_BYTES / 2, &tmV, fb, col0 + 64, tile * TC_BN);
+            // order of need: K(0), then for every tile K(j+1) before V(j)
+            bool ok = true;
+            for (int j = -1; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    const int jj = j + 1, st = jj & 1;
+                    if (!(ok = mbar_wait(k_empty0 + 8 * st, ((jj >> 1) & 1) ^ 1, abort_flag)))
+                        break;
+                    const uint32_t fb = k_full0 + 8 * st, dk = sK + st * KV_BYTES;
+                    mbar_arrive_expect_tx(fb, KV_BYTES);
+                    tma_load_2d(dk, &tmK, fb, col0, (tile0 + jj) * TC_BN);
+                    tma_load_2d(dk + KV_BYTES / 2, &tmK, fb, col0 + 64, (tile0 + jj) * TC_BN);
+                }
+                if (j >= 0) {
+                    const int st = j & 1;
+                    if (!(ok = mbar_wait(v_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag)))
+                        break;
+                    const uint32_t fb = v_full0 + 8 * st, dv = sV + st * KV_BYTES;
+                    mbar_arrive_expect_tx(fb, KV_BYTES);
+                    tma_load_2d(dv, &tmV, fb, col0, (tile0 + j) * TC_BN);
+                    tma_load_2d(dv + KV_BYTES / 2, &tmV, fb, col0 + 64, (tile0 + j) * TC_BN);
+                }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && tile1 >= tile0) {
+        if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = umma_idesc_f16(TC_BN, false, false);
             constexpr uint32_t idesc_pv = umma_idesc_f16(TC_HD, false, true);
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            for (int tile = tile0, j = 0; tile <= tile1 && ok; ++tile, ++j) {
-                const int st = j & 1;
-                if (!mbar_wait(kv_full0 + 8 * st, (j >> 1) & 1, abort_flag))
-                    break;
-                tc_fence_after();
-                // S = Q . K^T: 8 steps of 16 head dims; Q and K tiles are two 64-dim atoms each
+            // descriptors differ from these bases only in the 16-byte-granular start address (the low field; shared
+            // memory addresses stay below 2^18, so adding to it never carries into the next field)
+            const uint64_t dq = umma_smem_desc(sQ, 16, 1024), dk = umma_smem_desc(sK, 16, 1024), dp = umma_smem_desc(sP, 16, 1024),
+                           dv = umma_smem_desc(sV, KV_BYTES / 2, 1024);
+            auto issue_qk = [&](int jj) { // S[jj & 1] = Q . K(jj)^T: 8 steps of 16 head dims; two 64-dim atoms per operand
+                const uint64_t kb = dk + (uint64_t)((jj & 1) * (KV_BYTES >> 4));
+                const uint32_t d = tmem_S + (jj & 1) * TC_BN;
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint64_t a = umma_smem_desc(sQ + (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                    const uint64_t b = umma_smem_desc(sK + st * KV_BYTES + (k >> 2) * (KV_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                    umma_f16(tmem_S, a, b, idesc_qk, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 8; ++k)
+                    umma_f16(d, dq + (uint64_t)(((k >> 2) * (Q_BYTES / 2) + (k & 3) * 32) >> 4),
+                             kb + (uint64_t)(((k >> 2) * (KV_BYTES / 2) + (k & 3) * 32) >> 4), idesc_qk, k > 0 ? 1u : 0u);
+            };
+            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full0, 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+                tc_commit(s_full0);
+                tc_commit(k_empty0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j & 1;
+                if (j + 1 < n_tiles) {
+                    // the S buffer of tile j+1 was last read by the softmax of tile j-1, which has arrived at p_full
+                    const int sn = (j + 1) & 1;
+                    if (!mbar_wait(k_full0 + 8 * sn, ((j + 1) >> 1) & 1, abort_flag))
+                        break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                    tc_commit(s_full0 + 8 * sn);
+                    tc_commit(k_empty0 + 8 * sn);
                 }
-                tc_commit(s_full);
-                if (!mbar_wait(p_full, j & 1, abort_flag))
+                if (!mbar_wait(p_full, j & 1, abort_flag) || !mbar_wait(v_full0 + 8 * st, (j >> 1) & 1, abort_flag))
                     break;
                 tc_fence_after();
                 // O += P . V: 4 steps of 16 keys; V tile is MN-major for this product (dims contiguous)
+                const uint64_t vb = dv + (uint64_t)(st * (KV_BYTES >> 4));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint64_t a = umma_smem_desc(sP + k * 32, 16, 1024);
-                    const uint64_t b = umma_smem_desc(sV + st * KV_BYTES + k * 16 * 128, KV_BYTES / 2, 1024);
-                    umma_f16(tmem_O, a, b, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                }
-                tc_commit(kv_empty0 + 8 * st);
+                for (int k = 0; k < 4; ++k)
+                    umma_f16(tmem_O, dp + (uint64_t)(k * 2), vb + (uint64_t)(k * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                tc_commit(v_empty0 + 8 * st);
                 tc_commit(o_ready);
             }
         }
     } else {
         // ------------------------------ softmax warps -----------------------------
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane, t = t0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int st_row = t < T ? p.span_start[t] : 0, fi_row = t < T ? p.span_finish[t] : -1;
         const float ds = att_dot_scale_tc(), slope = p.slope;
-        float m_used = 0.f, l = 1.f; // the zero vector of weight 2^-m
+        __nv_bfloat16 *xch = (__nv_bfloat16 *)(smem + FWD_XCH_OFF); // [half][row]
+        float m_used = 0.f, l = half == 0 ? 1.f : 0.f; // the zero vector of weight 2^-m, counted once per row
         bool ok = true;
         for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag));
-            if (!ok)
-                break;
+            // after a failed wait a warp keeps walking the loop, because its partner counts on one pair barrier per
+            // tile, but touches neither TMEM nor the P tile any more
+            if (ok)
+                ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag));
             tc_fence_after();
-            float s[TC_BN];
-            {
-                uint32_t r0[32], r1[32];
-                tmem_ld32(tmem_S + lane_addr, r0);
-                tmem_ld32(tmem_S + lane_addr + 32, r1);
+            float s[32];
+            if (ok) {
+                uint32_t r0[32];
+                tmem_ld32(tmem_S + lane_addr + (j & 1) * TC_BN + half * 32, r0);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 32; ++i)
                     s[i] = __uint_as_float(r0[i]);
-                    s[32 + i] = __uint_as_float(r1[i]);
-                }
-            }
-            const int key0 = tile * TC_BN;
-            // four independent chains keep the single warp per scheduler busy
-            float mx4[4] = {m_used, m_used, m_used, m_used};
-            const bool inside = key0 >= st_row && key0 + TC_BN - 1 <= fi_row; // whole tile visible from this row
-            if (slope == 0.f && inside) {
+            } else {
 #pragma unroll
-                for (int i = 0; i < TC_BN; ++i) {
-                    s[i] *= ds;
-                    mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-                }
+                for (int i = 0; i < 32; ++i)
+                    s[i] = 0.f;
+            }
+            const int key0 = tile * TC_BN + half * 32;
+            // four independent chains keep the warps busy
+            float mx4[4] = {m_used, m_used, m_used, m_used};
+            const bool inside = key0 >= st_row && key0 + 31 <= fi_row; // all 32 keys visible from this row
+            const bool plain = slope == 0.f && inside; // then s stays the raw product and the scale rides in the exponent's fma
+            if (plain) {
+                float r4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    r4[i & 3] = fmaxf(r4[i & 3], s[i]);
+                mx4[0] = fmaxf(m_used, fmaxf(fmaxf(r4[0], r4[1]), fmaxf(r4[2], r4[3])) * ds);
             } else {
                 const float base = slope * (float)(t - key0);
 #pragma unroll
-                for (int i = 0; i < TC_BN; ++i) {
+                for (int i = 0; i < 32; ++i) {
                     const int key = key0 + i;
                     float x = fmaf(s[i], ds, fmaf(slope, (float)i, -base));
                     x = (key >= st_row && key <= fi_row) ? x : -INFINITY;
@@ -204,7 +254,14 @@ __global__ void __launch_bounds__(TC_THREADS)
                     mx4[i & 3] = fmaxf(mx4[i & 3], x);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // agree on the row maximum with the warp that holds the other 32 keys; rounding up to bf16 makes the
+            // exchanged value the reference both use (a reference above the true maximum only makes P smaller).
+            // The slot is free again by the time it is rewritten: the next S tile is issued only after all 256
+            // threads arrived at p_full, which each does after reading its partner's slot.
+            const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            xch[half * TC_BM + row] = mine;
+            pair_barrier(quarter);
+            const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(half ^ 1) * TC_BM + row]));
             // rescale only when some row of the warp outgrew its reference maximum by more than 8
             const bool need = mx > m_used + 8.f;
             const bool warp_need = __any_sync(0xffffffffu, need);
@@ -215,23 +272,24 @@ __global__ void __launch_bounds__(TC_THREADS)
                 l *= rs;
             }
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const float es = plain ? ds : 1.f;
 #pragma unroll
-            for (int i = 0; i < TC_BN; ++i) {
+            for (int i = 0; i < 32; ++i) {
                 float pv;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pv) : "f"(s[i] - m_used));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pv) : "f"(fmaf(s[i], es, -m_used)));
                 s[i] = pv;
                 sum4[i & 3] += pv;
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // the previous P . V must have finished before P is overwritten or O is touched
-            if (j > 0)
+            if (ok && j > 0)
                 ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1, abort_flag));
             if (!ok)
-                break;
+                continue;
             tc_fence_after();
             if (warp_need && j > 0) {
 #pragma unroll 1
-                for (int c = 0; c < TC_HD / 32; ++c) {
+                for (int c = 2 * half; c < 2 * half + 2; ++c) { // each warp of the pair rescales 64 of the 128 columns
                     uint32_t r[32];
                     tmem_ld32(tmem_O + lane_addr + c * 32, r);
                     tmem_ld_wait();
@@ -246,10 +304,11 @@ __global__ void __launch_bounds__(TC_THREADS)
             {
                 uint8_t *prow = smem + Q_BYTES + 4 * KV_BYTES + row * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     __half2 h0 = __floats2half2_rn(s[8 * c], s[8 * c + 1]), h1 = __floats2half2_rn(s[8 * c + 2], s[8 * c + 3]),
                             h2 = __floats2half2_rn(s[8 * c + 4], s[8 * c + 5]), h3 = __floats2half2_rn(s[8 * c + 6], s[8 * c + 7]);
-                    *(uint4 *)(prow + ((c ^ (row & 7)) << 4)) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                    *(uint4 *)(prow + (((half * 4 + c) ^ (row & 7)) << 4)) =
+                        make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                 }
             }
             fence_proxy_async(); // generic-proxy writes of P become visible to the tensor core's async proxy
@@ -257,15 +316,20 @@ __global__ void __launch_bounds__(TC_THREADS)
             mbar_arrive(p_full);
         }
         // epilogue: O / l and lse
-        const int n_tiles = tile1 - tile0 + 1;
         if (n_tiles > 0 && ok)
             ok = mbar_wait(o_ready, (n_tiles - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
+        // row sum = the two halves' partial sums (same reference maximum); the P tile is free by now (all threads
+        // of the pair are past the last tile when they reach the barrier) and lends its first 1 KB for the exchange
+        float *lx = (float *)(smem + Q_BYTES + 4 * KV_BYTES);
+        lx[half * TC_BM + row] = l;
+        pair_barrier(quarter);
+        l += lx[(half ^ 1) * TC_BM + row];
         const float inv = 1.f / l;
         __half *dst = p.o + (size_t)t * (H * TC_HD) + h * TC_HD;
 #pragma unroll 1
-        for (int c = 0; c < TC_HD / 32; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
             uint32_t r[32];
             if (n_tiles > 0 && ok) {
                 tmem_ld32(tmem_O + lane_addr + c * 32, r);
@@ -286,7 +350,7 @@ __global__ void __launch_bounds__(TC_THREADS)
                 }
             }
         }
-        if (t < T)
+        if (t < T && half == 0)
             p.lse[(size_t)t * H + h] = m_used + log2f(l);
     }
     tc_fence_before();
@@ -343,6 +407,9 @@ int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const _
 // In the transposed modes the per-node quantities (span, lse, dscale) belong to the columns; the
 // compute warps stage them in shared memory per tile (span bounds relative to the key block, one
 // byte each).  112 KB of tiles per CTA, 256 TMEM columns: two CTAs per SM.
+// 10 warps: TMA, MMA, and 8 compute warps (two per TMEM lane quarter, 32 of the tile's 64 columns each)
+static constexpr int BWD_THREADS = 320;
+
 struct AttBwdParams {
     int T, H;
     float slope;
@@ -367,7 +434,7 @@ struct BwdLayout {
 };
 
 template <int MODE>
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(BWD_THREADS, 2)
     att_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                       const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2, const AttBwdParams p)
 {
@@ -415,7 +482,7 @@ __global__ void __launch_bounds__(TC_THREADS)
             mbar_init(st_empty0 + 8 * s, 1);
         }
         mbar_init(s_full, 1);
-        mbar_init(g_full, 128);
+        mbar_init(g_full, 256);
         mbar_init(acc_ready, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -503,7 +570,7 @@ __global__ void __launch_bounds__(TC_THREADS)
         }
     } else {
         // ------------------------------ compute warps -----------------------------
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane, ctid = threadIdx.x - 64;
         const int rr = r0 + row; // node (MODE 0) or key (MODE 1, 2) of this thread
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
@@ -520,7 +587,7 @@ __global__ void __launch_bounds__(TC_THREADS)
         for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
             const int c0 = tile * TC_BN; // first streamed row (key for MODE 0, node otherwise)
             if (TRANSPOSED) {
-                asm volatile("bar.sync 1, 128;" ::: "memory"); // everyone is done with the previous tile's column data
+                asm volatile("bar.sync 1, 256;" ::: "memory"); // everyone is done with the previous tile's column data
                 if (ctid < TC_BN) {
                     const int t = c0 + ctid;
                     const bool in = t < T;
@@ -531,9 +598,9 @@ __global__ void __launch_bounds__(TC_THREADS)
                     m_st[ctid] = (uint8_t)min(max(st - r0, 0), 128);
                     m_fi[ctid] = (uint8_t)min(max(fi - r0 + 1, 0), 128);
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
             }
-            // after a failed wait the thread keeps walking the loop (the named barriers above need all 128
+            // after a failed wait the thread keeps walking the loop (the named barriers above need all 256
             // threads) but touches neither TMEM nor the G tile; the decision is made per warp because the
             // TMEM loads are warp-collective
             if (ok)
@@ -546,8 +613,7 @@ __global__ void __launch_bounds__(TC_THREADS)
                 continue;
             tc_fence_after();
             uint8_t *grow = smem + L::G_OFF + row * 128;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            {
                 uint32_t rs[32], rp[32];
                 tmem_ld32(tmem_S + lane_addr + half * 32, rs);
                 if (NEED_DP)
@@ -594,7 +660,7 @@ __global__ void __launch_bounds__(TC_THREADS)
         tc_fence_after();
         float *dst = p.out + (size_t)rr * (H * TC_HD) + col0;
 #pragma unroll 1
-        for (int c = 0; c < TC_HD / 32; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) { // each warp of the quarter writes 64 of the 128 columns
             uint32_t r[32];
             if (n_tiles > 0 && ok) {
                 tmem_ld32(tmem_ACC + lane_addr + c * 32, r);
@@ -640,7 +706,7 @@ static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const
     if ((rc = make_tensor_map(&tB2, b2, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
         return rc;
     dim3 grid((unsigned)ceil_div(p.T, TC_BM), (unsigned)p.H);
-    kern<<<grid, TC_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, p);
+    kern<<<grid, BWD_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
