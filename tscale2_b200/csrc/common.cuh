@@ -110,6 +110,13 @@ __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1)
                  : "memory");
 }
+// untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), completion on an mbarrier
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read()
@@ -158,6 +165,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
@@ -189,6 +208,25 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
                  "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// Four MMAs along K issued as one block by one thread: the descriptors advance by a_step / b_step (in 16-byte
+// units) in their low word, which holds the start address (shared-memory addresses stay below 2^18, so the
+// sum never carries out of the field).  The first MMA accumulates iff acc_first, the others always.
+__device__ __forceinline__ void umma_f16_x4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc_first,
+                                            uint32_t a_step, uint32_t b_step)
+{
+    asm volatile("{\n\t.reg .pred p, t;\n\t.reg .b32 alo, ahi, blo, bhi;\n\t.reg .b64 da, db;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, %4, %4;\n\t"
+                 "mov.b64 {alo, ahi}, %1;\n\tmov.b64 {blo, bhi}, %2;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+                 "add.u32 alo, alo, %5;\n\tadd.u32 blo, blo, %6;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t"
+                 "add.u32 alo, alo, %5;\n\tadd.u32 blo, blo, %6;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t"
+                 "add.u32 alo, alo, %5;\n\tadd.u32 blo, blo, %6;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t}" ::"r"(tmem_d),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc_first), "r"(a_step), "r"(b_step)
                  : "memory");
 }
 // instruction descriptor for kind::f16: fp32 accumulator, fp16 operands, M = 128

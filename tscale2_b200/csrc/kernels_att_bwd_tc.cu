@@ -1,0 +1,415 @@
+// tcgen05 attention backward for head width 128 (sm_100a): one kernel template for the three gradients.
+// Same math, inputs and outputs as the mma.sync formulation in kernels_att_mma.cu (see there for the
+// references into src/gpt/compute/layer_att_reference.h and gpu_att_fp16.cu).
+//
+// A CTA owns 256 resident rows (nodes for dQ, keys for dK / dV) as two blocks of 128, and streams 64-row
+// tiles of the other side once for both blocks (half the L2 traffic of one block per CTA):
+//   first MMAs   S = A1 . B1^T  (and dP = A2 . B2^T)           128 x 64 each, fp32 in TMEM
+//   compute      G = dS  or  P  (fp16, written to a swizzled K-major shared-memory tile)
+//   second MMA   ACC += G . B1 (dQ, dK)  or  G . B2 (dV)       128 x 128 in TMEM, B read MN-major
+//   MODE 0 (dQ): A1 = Q, A2 = dO resident; B1 = K, B2 = V streamed; rows are nodes
+//   MODE 1 (dK): A1 = K, A2 = V  resident; B1 = Q, B2 = dO streamed; rows are keys (transposed problem)
+//   MODE 2 (dV): A1 = K resident;          B1 = Q, B2 = dO streamed; rows are keys; no dP
+// Each block has its own MMA issuer thread, its own 8 compute warps (two per TMEM lane quarter, 32 of the
+// tile's 64 columns each) and its own 256 TMEM columns, so while one block's compute warps turn S into G the
+// tensor cores run the other block's products.  20 warps: TMA producer, 2 MMA issuers, 1 idle, 16 compute.
+// In the transposed modes the per-node quantities belong to the columns; a small kernel packs them once per
+// call as {-lse, -dscale * c2, span start, span length} per (head, node) and the producer brings the 1 KB of
+// each streamed tile next to it with a bulk copy.  Every wait is bounded (see mbar_wait); a give-up raises
+// the status word.
+#include "att_tc.cuh"
+#include <mutex>
+
+namespace ts2 {
+
+static constexpr int BW_ROWS = 2 * TC_BM;
+static constexpr int BW_THREADS = 128 + 2 * 256;
+static constexpr int META_TILE_BYTES = TC_BN * 16;
+
+struct AttBwdParams {
+    int T, H, Tpad;
+    float slope;
+    const int *span_start, *span_finish, *rev_first, *rev_last;
+    const float *lse, *dscale;
+    const float4 *meta; // [H][Tpad], transposed modes
+    float *out;         // dq, dk or dv: fp32 [T][128 H]
+    int32_t *status;
+};
+
+template <int MODE>
+struct BwdLayout {
+    static constexpr bool NEED_DP = MODE != 2;
+    static constexpr bool TRANSPOSED = MODE != 0;
+    static constexpr int STAGES = NEED_DP ? 2 : 3;
+    static constexpr int A1_OFF = 0;
+    static constexpr int A2_OFF = A1_OFF + 2 * Q_BYTES;
+    static constexpr int RES_BYTES = (NEED_DP ? 4 : 2) * Q_BYTES;
+    static constexpr int STAGE_OFF = RES_BYTES;
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    static constexpr int G_OFF = STAGE_OFF + STAGES * STAGE_BYTES;
+    static constexpr int META_OFF = G_OFF + 2 * P_BYTES;
+    static constexpr int BAR_OFF = META_OFF + STAGES * META_TILE_BYTES;
+    static constexpr int SMEM = BAR_OFF + 256;
+};
+static_assert(BwdLayout<0>::SMEM <= 232448 && BwdLayout<2>::SMEM <= 232448, "shared memory budget");
+
+// {-lse, -dscale * c2, start, finish - start} per (head, node); nodes past T and nodes with an empty span get a
+// start no key index reaches
+__global__ void att_pack_meta_kernel(const float *__restrict__ lse, const float *__restrict__ dscale, const int *__restrict__ span_start,
+                                     const int *__restrict__ span_finish, int T, int Tpad, int H, float c2, float4 *__restrict__ meta)
+{
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= Tpad * H)
+        return;
+    const int h = idx / Tpad, t = idx - h * Tpad;
+    float4 m = make_float4(0.f, 0.f, __int_as_float(0x40000000), __int_as_float(0));
+    if (t < T) {
+        const int st = span_start[t], fi = span_finish[t];
+        if (fi >= st)
+            m = make_float4(-lse[(size_t)t * H + h], -dscale[(size_t)t * H + h] * c2, __int_as_float(st), __int_as_float(fi - st));
+    }
+    meta[idx] = m;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+    att_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+                      const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2, const AttBwdParams p)
+{
+    using L = BwdLayout<MODE>;
+    constexpr bool NEED_DP = L::NEED_DP, TRANSPOSED = L::TRANSPOSED;
+    constexpr int STAGES = L::STAGES;
+    extern __shared__ __align__(1024) uint8_t att_bwd_smem[];
+    uint8_t *smem = att_bwd_smem;
+    if (smem_u32(smem) & 1023) { // the swizzled tiles need a 1024-byte aligned base; refuse instead of computing garbage
+        if (threadIdx.x == 0)
+            atomicOr(p.status, TS2_STATUS_BAD_ARG);
+        return;
+    }
+    const uint32_t sA1 = smem_u32(smem) + L::A1_OFF, sA2 = smem_u32(smem) + L::A2_OFF, sStage = smem_u32(smem) + L::STAGE_OFF,
+                   sG = smem_u32(smem) + L::G_OFF, sMeta = smem_u32(smem) + L::META_OFF;
+    uint64_t *bars = (uint64_t *)(smem + L::BAR_OFF);
+    const uint32_t res_full = smem_u32(bars), st_full0 = smem_u32(bars + 1), st_empty0 = smem_u32(bars + 4), s_full0 = smem_u32(bars + 7),
+                   g_full0 = smem_u32(bars + 9), acc_ready0 = smem_u32(bars + 11);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    int *rng = (int *)(tmem_slot + 2); // lo, hi of block 0; lo, hi of block 1
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int T = p.T, H = p.H, h = blockIdx.y, r0 = blockIdx.x * BW_ROWS;
+
+    // range of streamed rows each block has to visit
+    if (threadIdx.x < 4)
+        rng[threadIdx.x] = (threadIdx.x & 1) ? -1 : 0x7fffffff;
+    __syncthreads();
+    if (threadIdx.x < BW_ROWS && r0 + (int)threadIdx.x < T) {
+        const int r = r0 + threadIdx.x, b = threadIdx.x >> 7;
+        const int a = TRANSPOSED ? p.rev_first[r] : p.span_start[r], e = TRANSPOSED ? p.rev_last[r] : p.span_finish[r];
+        if (e >= a) {
+            atomicMin(&rng[2 * b], a);
+            atomicMax(&rng[2 * b + 1], e);
+        }
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(res_full, 1);
+        for (int s = 0; s < 3; ++s) {
+            mbar_init(st_full0 + 8 * s, 1);
+            mbar_init(st_empty0 + 8 * s, 2); // both MMA issuers release a stage
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full0 + 8 * b, 1);
+            mbar_init(g_full0 + 8 * b, 256);
+            mbar_init(acc_ready0 + 8 * b, 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB1);
+        prefetch_tmap(&tmB2);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // tile ranges: per block [tlo, thi] (empty: tlo > thi), and their union [u0, u0 + n)
+    const bool any0 = rng[1] >= rng[0], any1 = rng[3] >= rng[2];
+    const int tlo0 = any0 ? rng[0] / TC_BN : 0x3fffffff, thi0 = any0 ? rng[1] / TC_BN : -1;
+    const int tlo1 = any1 ? rng[2] / TC_BN : 0x3fffffff, thi1 = any1 ? rng[3] / TC_BN : -1;
+    const int u0 = min(tlo0, tlo1), u1 = max(thi0, thi1);
+    const int n = u1 >= u0 ? u1 - u0 + 1 : 0;
+    const int col0 = h * TC_HD;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && n > 0) {
+            mbar_arrive_expect_tx(res_full, L::RES_BYTES);
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                tma_load_2d(sA1 + b * Q_BYTES, &tmA1, res_full, col0, r0 + b * TC_BM);
+                tma_load_2d(sA1 + b * Q_BYTES + Q_BYTES / 2, &tmA1, res_full, col0 + 64, r0 + b * TC_BM);
+                if (NEED_DP) {
+                    tma_load_2d(sA2 + b * Q_BYTES, &tmA2, res_full, col0, r0 + b * TC_BM);
+                    tma_load_2d(sA2 + b * Q_BYTES + Q_BYTES / 2, &tmA2, res_full, col0 + 64, r0 + b * TC_BM);
+                }
+            }
+            for (int j = 0; j < n; ++j) {
+                const int st = j % STAGES, row = (u0 + j) * TC_BN;
+                if (!mbar_wait(st_empty0 + 8 * st, ((j / STAGES) & 1) ^ 1, abort_flag))
+                    break;
+                const uint32_t fb = st_full0 + 8 * st;
+                mbar_arrive_expect_tx(fb, L::STAGE_BYTES + (TRANSPOSED ? META_TILE_BYTES : 0));
+                const uint32_t d1 = sStage + st * L::STAGE_BYTES, d2 = d1 + KV_BYTES;
+                tma_load_2d(d1, &tmB1, fb, col0, row);
+                tma_load_2d(d1 + KV_BYTES / 2, &tmB1, fb, col0 + 64, row);
+                tma_load_2d(d2, &tmB2, fb, col0, row);
+                tma_load_2d(d2 + KV_BYTES / 2, &tmB2, fb, col0 + 64, row);
+                if (TRANSPOSED)
+                    bulk_load(sMeta + st * META_TILE_BYTES, p.meta + (size_t)h * p.Tpad + row, META_TILE_BYTES, fb);
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------ MMA issuer of block b ---------------------
+        if (lane == 0 && n > 0) {
+            const int b = warp - 1, my_lo = b ? tlo1 : tlo0, my_hi = b ? thi1 : thi0;
+            constexpr uint32_t idesc_s = umma_idesc_f16(TC_BN, false, false);
+            constexpr uint32_t idesc_acc = umma_idesc_f16(TC_HD, false, true);
+            const uint32_t tS = tmem_base + b * 256, tDP = tS + TC_BN, tACC = tS + 2 * TC_BN;
+            const uint64_t dA1 = umma_smem_desc(sA1 + b * Q_BYTES, 16, 1024), dA2 = umma_smem_desc(sA2 + b * Q_BYTES, 16, 1024),
+                           dG = umma_smem_desc(sG + b * P_BYTES, 16, 1024);
+            const uint32_t s_full = s_full0 + 8 * b, g_full = g_full0 + 8 * b, acc_ready = acc_ready0 + 8 * b;
+            bool ok = mbar_wait(res_full, 0, abort_flag);
+            int k = 0; // tiles of this block so far
+            for (int j = 0; j < n && ok; ++j) {
+                const int st = j % STAGES, tile = u0 + j;
+                // also a block that skips the tile waits for it, so that it never runs a ring phase ahead
+                if (!mbar_wait(st_full0 + 8 * st, (j / STAGES) & 1, abort_flag))
+                    break;
+                if (tile >= my_lo && tile <= my_hi) {
+                    tc_fence_after();
+                    const uint32_t b1 = sStage + st * L::STAGE_BYTES, b2 = b1 + KV_BYTES;
+                    const uint64_t dB1 = umma_smem_desc(b1, 16, 1024), dB2 = umma_smem_desc(b2, 16, 1024);
+                    // 8 steps of 16 head dims; operands are two 64-dim atoms each
+                    umma_f16_x4(tS, dA1, dB1, idesc_s, 0u, 2u, 2u);
+                    umma_f16_x4(tS, dA1 + (Q_BYTES / 2 >> 4), dB1 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
+                    if (NEED_DP) {
+                        umma_f16_x4(tDP, dA2, dB2, idesc_s, 0u, 2u, 2u);
+                        umma_f16_x4(tDP, dA2 + (Q_BYTES / 2 >> 4), dB2 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
+                    }
+                    tc_commit(s_full);
+                    if (!mbar_wait(g_full, k & 1, abort_flag))
+                        break;
+                    tc_fence_after();
+                    // ACC += G . B: 4 steps of 16 streamed rows; the streamed tile read MN-major (its 128 columns are
+                    // the output columns), 16 rows = 2048 bytes per step
+                    const uint64_t dB = umma_smem_desc(MODE == 2 ? b2 : b1, KV_BYTES / 2, 1024);
+                    umma_f16_x4(tACC, dG, dB, idesc_acc, k > 0 ? 1u : 0u, 2u, 128u);
+                    tc_commit(acc_ready);
+                    ++k;
+                }
+                tc_commit(st_empty0 + 8 * st);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ compute warps of block b ------------------
+        const int b = (warp - 4) >> 3, half = ((warp - 4) & 7) >> 2, quarter = warp & 3;
+        const int my_lo = b ? tlo1 : tlo0, my_hi = b ? thi1 : thi0;
+        const int row = quarter * 32 + lane;
+        const int rr = r0 + b * TC_BM + row; // node (MODE 0) or key (MODE 1, 2) of this thread
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tS = tmem_base + b * 256 + lane_addr + half * 32, tDP = tS + TC_BN, tACC = tmem_base + b * 256 + 2 * TC_BN + lane_addr;
+        const uint32_t s_full = s_full0 + 8 * b, g_full = g_full0 + 8 * b, acc_ready = acc_ready0 + 8 * b;
+        const float ds = att_dot_scale_tc(), c2 = ds * 0.693147f, slope = p.slope;
+        int st_row = 0, len_row = -1;
+        float nlse_row = 0.f, ndc_row = 0.f;
+        if (!TRANSPOSED && rr < T) {
+            st_row = p.span_start[rr];
+            len_row = p.span_finish[rr] - st_row;
+            nlse_row = -p.lse[(size_t)rr * H + h];
+            ndc_row = -p.dscale[(size_t)rr * H + h] * c2;
+        }
+        uint8_t *grow = smem + L::G_OFF + b * P_BYTES + row * 128;
+        bool ok = true;
+        int k = 0;
+        for (int j = 0; j < n; ++j) {
+            const int tile = u0 + j;
+            if (tile < my_lo || tile > my_hi)
+                continue;
+            // s_full also says that the previous second MMA of this block is done with G: its issuer commits in order
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full, k & 1, abort_flag));
+            if (!ok)
+                break;
+            tc_fence_after();
+            const int c0 = tile * TC_BN + half * 32; // first streamed row of this thread's columns
+            const float4 *mt = (const float4 *)(smem + L::META_OFF + (j % STAGES) * META_TILE_BYTES) + half * 32;
+            // two passes of 16 columns: few enough live registers that the compiler can interleave the per-element
+            // chains (shared-memory load -> fma -> ex2 -> select -> fma -> multiply -> convert)
+#pragma unroll
+            for (int q16 = 0; q16 < 2; ++q16) {
+                uint32_t rs[16], rp[16];
+                tmem_ld16(tS + q16 * 16, rs);
+                if (NEED_DP)
+                    tmem_ld16(tDP + q16 * 16, rp);
+                tmem_ld_wait();
+                float g[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c = c0 + q16 * 16 + i;
+                    float off, ndc;
+                    bool valid;
+                    if (!TRANSPOSED) {
+                        off = nlse_row;
+                        ndc = ndc_row;
+                        valid = (unsigned)(c - st_row) <= (unsigned)len_row && len_row >= 0;
+                        if (slope != 0.f)
+                            off -= slope * (float)(rr - c);
+                    } else {
+                        const float4 m = mt[q16 * 16 + i];
+                        off = m.x;
+                        ndc = m.y;
+                        valid = (unsigned)(rr - __float_as_int(m.z)) <= (unsigned)__float_as_int(m.w);
+                        if (slope != 0.f)
+                            off -= slope * (float)(c - rr);
+                    }
+                    float w;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(fmaf(__uint_as_float(rs[i]), ds, off)));
+                    w = valid ? w : 0.f;
+                    g[i] = NEED_DP ? w * fmaf(__uint_as_float(rp[i]), c2, ndc) : w;
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const __half2 h0 = __floats2half2_rn(g[8 * c], g[8 * c + 1]), h1 = __floats2half2_rn(g[8 * c + 2], g[8 * c + 3]),
+                                  h2 = __floats2half2_rn(g[8 * c + 4], g[8 * c + 5]), h3 = __floats2half2_rn(g[8 * c + 6], g[8 * c + 7]);
+                    *(uint4 *)(grow + (((half * 4 + q16 * 2 + c) ^ (row & 7)) << 4)) =
+                        make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
+                }
+            }
+            fence_proxy_async(); // generic-proxy writes of G become visible to the tensor core's async proxy
+            tc_fence_before();
+            mbar_arrive(g_full);
+            ++k;
+        }
+        // epilogue: this thread's 64 columns of the accumulator row -> fp32 output
+        if (k > 0 && ok)
+            ok = mbar_wait(acc_ready, (k - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        float *dst = p.out + (size_t)rr * (H * TC_HD) + col0;
+#pragma unroll 1
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+            uint32_t r[32];
+            if (k > 0 && ok) {
+                tmem_ld32(tACC + c * 32, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    r[i] = 0u;
+            }
+            if (rr < T) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    *(uint4 *)(dst + c * 32 + i * 4) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, 512);
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicOr(p.status, TS2_STATUS_WAIT_TIMEOUT);
+}
+
+template <int MODE>
+static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p)
+{
+    auto kern = att_bwd_tc_kernel<MODE>;
+    static bool configured[16] = {};
+    if (!configured[c.device & 15]) {
+        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout<MODE>::SMEM));
+        configured[c.device & 15] = true;
+    }
+    const int Q = p.H * TC_HD;
+    CUtensorMap tA1, tA2, tB1, tB2;
+    int rc;
+    if ((rc = make_tensor_map(&tA1, a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
+        return rc;
+    if ((rc = make_tensor_map(&tA2, a2 ? a2 : a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
+        return rc;
+    if ((rc = make_tensor_map(&tB1, b1, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
+        return rc;
+    if ((rc = make_tensor_map(&tB2, b2, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
+        return rc;
+    dim3 grid((unsigned)ceil_div(p.T, BW_ROWS), (unsigned)p.H);
+    kern<<<grid, BW_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, p);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// per-device buffer of the packed per-node quantities, grown on demand (never inside a steady-state step:
+// the node count of a model is fixed)
+static int meta_buffer(int device, size_t bytes, float4 **out)
+{
+    static std::mutex mu;
+    static float4 *buf[16] = {};
+    static size_t cap[16] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    const int d = device & 15;
+    if (cap[d] < bytes) {
+        if (buf[d]) {
+            TS2_CUDA(cudaDeviceSynchronize());
+            TS2_CUDA(cudaFree(buf[d]));
+            buf[d] = nullptr;
+            cap[d] = 0;
+        }
+        TS2_CUDA(cudaMalloc(&buf[d], bytes));
+        cap[d] = bytes;
+    }
+    *out = buf[d];
+    return TS2_OK;
+}
+
+int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
+                          const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
+                          int T, int H, float slope, float *dq, float *dk, float *dv)
+{
+    AttBwdParams p;
+    p.T = T;
+    p.H = H;
+    p.Tpad = (int)ceil_div(T, TC_BN) * TC_BN;
+    p.slope = slope;
+    p.span_start = span_start;
+    p.span_finish = span_finish;
+    p.rev_first = rev_first;
+    p.rev_last = rev_last;
+    p.lse = lse;
+    p.dscale = dscale;
+    p.status = device_status_word(c.device);
+    if (!p.status)
+        return fail(TS2_ERR_CUDA, "attention: no device status word");
+    int rc;
+    float4 *meta = nullptr;
+    if ((rc = meta_buffer(c.device, (size_t)p.Tpad * H * sizeof(float4), &meta)) != TS2_OK)
+        return rc;
+    p.meta = meta;
+    {
+        const int total = p.Tpad * H;
+        att_pack_meta_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, c.stream>>>(lse, dscale, span_start, span_finish, T, p.Tpad, H,
+                                                                                  att_dot_scale_tc() * 0.693147f, meta);
+        TS2_CHECK_LAUNCH();
+    }
+    p.out = dq;
+    if ((rc = launch_bwd_tc<0>(c, q, dout, k, v, p)) != TS2_OK)
+        return rc;
+    p.out = dk;
+    if ((rc = launch_bwd_tc<1>(c, k, v, q, dout, p)) != TS2_OK)
+        return rc;
+    p.out = dv;
+    return launch_bwd_tc<2>(c, k, nullptr, q, dout, p);
+}
+
+} // namespace ts2

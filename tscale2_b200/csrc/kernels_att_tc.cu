@@ -18,38 +18,14 @@
 // The zero "sink" vector of the reference is the initial state m = 0, l = 1.
 // Two CTAs fit an SM (112 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps
 // the other's MMAs.  Every wait is bounded (see mbar_wait); a give-up raises the status word.
-#include "kernels.cuh"
-#include "gemm.cuh"
-#include "fast_types.cuh"
-#include <cuda.h>
+#include "att_tc.cuh"
 
 namespace ts2 {
 
-static constexpr int TC_BM = 128;  // node rows per CTA
-static constexpr int TC_BN = 64;   // keys per tile
-static constexpr int TC_HD = 128;  // head width
 static constexpr int TC_THREADS = 320;
-static constexpr int Q_BYTES = TC_BM * TC_HD * 2;   // 32 KB: two 128-byte-wide atoms of 128 rows
-static constexpr int KV_BYTES = TC_BN * TC_HD * 2;  // 16 KB: two atoms of 64 rows
-static constexpr int P_BYTES = TC_BM * TC_BN * 2;   // 16 KB: one atom of 128 rows
 // 112 KB of tiles + 128 B of barriers: two CTAs per SM (2 x (114816 + 1024 reserved) <= 228 KB)
 static constexpr int FWD_XCH_OFF = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 128; // row maxima of the two column halves, bf16
 static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * TC_BM * 2;
-
-__host__ __device__ inline float att_dot_scale_tc() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
-
-#ifdef __CUDACC__
-// barrier of the two warps that share TMEM lane quarter q (ids 2..5; compile-time ids keep the CTA at 6 barriers)
-__device__ __forceinline__ void pair_barrier(int q)
-{
-    switch (q) {
-    case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
-    case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
-    case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
-    default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
-    }
-}
-#endif
 
 struct AttTcParams {
     int T, H;
@@ -393,350 +369,6 @@ int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const _
     att_fwd_tc_kernel<<<grid, TC_THREADS, FWD_SMEM, c.stream>>>(tmQ, tmK, tmV, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
-}
-
-// ---------------------------------------------------------------------------------------
-// Backward: one kernel template for the three gradients.  A CTA owns a resident block of 128 rows
-// (nodes for dQ, keys for dK / dV) and streams 64-row tiles of the other side:
-//   first MMAs   S = A1 . B1^T  (and dP = A2 . B2^T)           128 x 64 each, fp32 in TMEM
-//   compute      G = dS  or  P  (fp16, written to a swizzled K-major shared-memory tile)
-//   second MMA   ACC += G . B1 (dQ, dK)  or  G . B2 (dV)       128 x 128 in TMEM, B read MN-major
-//   MODE 0 (dQ): A1 = Q, A2 = dO resident; B1 = K, B2 = V streamed; rows are nodes
-//   MODE 1 (dK): A1 = K, A2 = V  resident; B1 = Q, B2 = dO streamed; rows are keys (transposed problem)
-//   MODE 2 (dV): A1 = K resident;          B1 = Q, B2 = dO streamed; rows are keys; no dP
-// In the transposed modes the per-node quantities (span, lse, dscale) belong to the columns; the
-// compute warps stage them in shared memory per tile (span bounds relative to the key block, one
-// byte each).  112 KB of tiles per CTA, 256 TMEM columns: two CTAs per SM.
-// 10 warps: TMA, MMA, and 8 compute warps (two per TMEM lane quarter, 32 of the tile's 64 columns each)
-static constexpr int BWD_THREADS = 320;
-
-struct AttBwdParams {
-    int T, H;
-    float slope;
-    const int *span_start, *span_finish, *rev_first, *rev_last;
-    const float *lse, *dscale;
-    float *out; // dq, dk or dv: fp32 [T][128 H]
-    int32_t *status;
-};
-
-template <int MODE>
-struct BwdLayout {
-    static constexpr bool NEED_DP = MODE != 2;
-    static constexpr bool TRANSPOSED = MODE != 0;
-    static constexpr int STAGES = NEED_DP ? 1 : 2;
-    static constexpr int RES_BYTES = NEED_DP ? 2 * Q_BYTES : Q_BYTES;
-    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int G_OFF = RES_BYTES + STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFF = G_OFF + P_BYTES;
-    static constexpr int META_OFF = BAR_OFF + 128;
-    static constexpr int META_BYTES = TRANSPOSED ? 64 * 10 : 0; // lse, dscale (fp32), start, finish (bytes)
-    static constexpr int SMEM = META_OFF + META_BYTES;
-};
-
-template <int MODE>
-__global__ void __launch_bounds__(BWD_THREADS, 2)
-    att_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
-                      const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2, const AttBwdParams p)
-{
-    using L = BwdLayout<MODE>;
-    constexpr bool NEED_DP = L::NEED_DP, TRANSPOSED = L::TRANSPOSED;
-    constexpr int STAGES = L::STAGES;
-    extern __shared__ __align__(1024) uint8_t att_tc_smem[];
-    uint8_t *smem = att_tc_smem;
-    if (smem_u32(smem) & 1023) {
-        if (threadIdx.x == 0)
-            atomicOr(p.status, TS2_STATUS_BAD_ARG);
-        return;
-    }
-    const uint32_t sA1 = smem_u32(smem), sA2 = sA1 + Q_BYTES, sStage = sA1 + L::RES_BYTES, sG = sA1 + L::G_OFF;
-    uint64_t *bars = (uint64_t *)(smem + L::BAR_OFF);
-    const uint32_t res_full = smem_u32(bars), st_full0 = smem_u32(bars + 1), st_empty0 = smem_u32(bars + 3), s_full = smem_u32(bars + 5),
-                   g_full = smem_u32(bars + 6), acc_ready = smem_u32(bars + 7);
-    uint32_t *tmem_slot = (uint32_t *)(bars + 8);
-    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
-    int &s_lo = *(int *)(tmem_slot + 2), &s_hi = *(int *)(tmem_slot + 3);
-    float *m_lse = (float *)(smem + L::META_OFF), *m_dsc = m_lse + 64;
-    uint8_t *m_st = (uint8_t *)(m_dsc + 64), *m_fi = m_st + 64;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int T = p.T, H = p.H, h = blockIdx.y, r0 = blockIdx.x * TC_BM;
-
-    // range of streamed rows this block has to visit
-    if (threadIdx.x == 0) {
-        s_lo = 0x7fffffff;
-        s_hi = -1;
-    }
-    __syncthreads();
-    if (threadIdx.x < TC_BM && r0 + (int)threadIdx.x < T) {
-        const int r = r0 + threadIdx.x;
-        const int a = TRANSPOSED ? p.rev_first[r] : p.span_start[r], b = TRANSPOSED ? p.rev_last[r] : p.span_finish[r];
-        if (b >= a) {
-            atomicMin(&s_lo, a);
-            atomicMax(&s_hi, b);
-        }
-    }
-    if (threadIdx.x == 0) {
-        mbar_init(res_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(st_full0 + 8 * s, 1);
-            mbar_init(st_empty0 + 8 * s, 1);
-        }
-        mbar_init(s_full, 1);
-        mbar_init(g_full, 256);
-        mbar_init(acc_ready, 1);
-        *abort_flag = 0;
-        fence_barrier_init();
-        prefetch_tmap(&tmA1);
-        prefetch_tmap(&tmB1);
-        prefetch_tmap(&tmB2);
-    }
-    if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 256);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base, tmem_DP = tmem_base + TC_BN, tmem_ACC = tmem_base + 2 * TC_BN;
-    const int lo = s_lo, hi = s_hi;
-    const int tile0 = hi >= lo ? lo / TC_BN : 0, tile1 = hi >= lo ? hi / TC_BN : -1;
-    const int col0 = h * TC_HD;
-
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0 && tile1 >= tile0) {
-            mbar_arrive_expect_tx(res_full, L::RES_BYTES);
-            tma_load_2d(sA1, &tmA1, res_full, col0, r0);
-            tma_load_2d(sA1 + Q_BYTES / 2, &tmA1, res_full, col0 + 64, r0);
-            if (NEED_DP) {
-                tma_load_2d(sA2, &tmA2, res_full, col0, r0);
-                tma_load_2d(sA2 + Q_BYTES / 2, &tmA2, res_full, col0 + 64, r0);
-            }
-            for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
-                const int st = j % STAGES;
-                if (!mbar_wait(st_empty0 + 8 * st, ((j / STAGES) & 1) ^ 1, abort_flag))
-                    break;
-                const uint32_t fb = st_full0 + 8 * st;
-                mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
-                const uint32_t d1 = sStage + st * L::STAGE_BYTES, d2 = d1 + KV_BYTES;
-                tma_load_2d(d1, &tmB1, fb, col0, tile * TC_BN);
-                tma_load_2d(d1 + KV_BYTES / 2, &tmB1, fb, col0 + 64, tile * TC_BN);
-                tma_load_2d(d2, &tmB2, fb, col0, tile * TC_BN);
-                tma_load_2d(d2 + KV_BYTES / 2, &tmB2, fb, col0 + 64, tile * TC_BN);
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0 && tile1 >= tile0) {
-            constexpr uint32_t idesc_s = umma_idesc_f16(TC_BN, false, false);
-            constexpr uint32_t idesc_acc = umma_idesc_f16(TC_HD, false, true);
-            bool ok = mbar_wait(res_full, 0, abort_flag);
-            for (int tile = tile0, j = 0; tile <= tile1 && ok; ++tile, ++j) {
-                const int st = j % STAGES;
-                if (!mbar_wait(st_full0 + 8 * st, (j / STAGES) & 1, abort_flag))
-                    break;
-                tc_fence_after();
-                const uint32_t b1 = sStage + st * L::STAGE_BYTES, b2 = b1 + KV_BYTES;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint64_t a = umma_smem_desc(sA1 + (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                    const uint64_t b = umma_smem_desc(b1 + (k >> 2) * (KV_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                    umma_f16(tmem_S, a, b, idesc_s, k > 0 ? 1u : 0u);
-                }
-                if (NEED_DP) {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const uint64_t a = umma_smem_desc(sA2 + (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                        const uint64_t b = umma_smem_desc(b2 + (k >> 2) * (KV_BYTES / 2) + (k & 3) * 32, 16, 1024);
-                        umma_f16(tmem_DP, a, b, idesc_s, k > 0 ? 1u : 0u);
-                    }
-                }
-                tc_commit(s_full);
-                if (!mbar_wait(g_full, j & 1, abort_flag))
-                    break;
-                tc_fence_after();
-                // ACC += G . B (the streamed tile read MN-major: its 128 columns are the output columns)
-                const uint32_t bacc = (MODE == 2) ? b2 : b1;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint64_t a = umma_smem_desc(sG + k * 32, 16, 1024);
-                    const uint64_t b = umma_smem_desc(bacc + k * 16 * 128, KV_BYTES / 2, 1024);
-                    umma_f16(tmem_ACC, a, b, idesc_acc, (j > 0 || k > 0) ? 1u : 0u);
-                }
-                tc_commit(st_empty0 + 8 * st);
-                tc_commit(acc_ready);
-            }
-        }
-    } else {
-        // ------------------------------ compute warps -----------------------------
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
-        const int row = quarter * 32 + lane, ctid = threadIdx.x - 64;
-        const int rr = r0 + row; // node (MODE 0) or key (MODE 1, 2) of this thread
-        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const float ds = att_dot_scale_tc(), c2 = ds * 0.693147f, slope = p.slope;
-        int st_row = 0, fi_row = -1;
-        float lse_row = 0.f, dsc_row = 0.f;
-        if (!TRANSPOSED && rr < T) {
-            st_row = p.span_start[rr];
-            fi_row = p.span_finish[rr];
-            lse_row = p.lse[(size_t)rr * H + h];
-            dsc_row = p.dscale[(size_t)rr * H + h];
-        }
-        bool ok = true;
-        for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
-            const int c0 = tile * TC_BN; // first streamed row (key for MODE 0, node otherwise)
-            if (TRANSPOSED) {
-                asm volatile("bar.sync 1, 256;" ::: "memory"); // everyone is done with the previous tile's column data
-                if (ctid < TC_BN) {
-                    const int t = c0 + ctid;
-                    const bool in = t < T;
-                    m_lse[ctid] = in ? p.lse[(size_t)t * H + h] : 0.f;
-                    m_dsc[ctid] = in ? p.dscale[(size_t)t * H + h] : 0.f;
-                    const int st = in ? p.span_start[t] : 1, fi = in ? p.span_finish[t] : 0;
-                    // span of the node relative to this key block: key row r is visible iff m_st <= r < m_fi
-                    m_st[ctid] = (uint8_t)min(max(st - r0, 0), 128);
-                    m_fi[ctid] = (uint8_t)min(max(fi - r0 + 1, 0), 128);
-                }
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-            }
-            // after a failed wait the thread keeps walking the loop (the named barriers above need all 256
-            // threads) but touches neither TMEM nor the G tile; the decision is made per warp because the
-            // TMEM loads are warp-collective
-            if (ok)
-                ok = mbar_wait(s_full, j & 1, abort_flag);
-            // the previous second MMA must be done with G before it is overwritten
-            if (ok && j > 0)
-                ok = mbar_wait(acc_ready, (j - 1) & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok)
-                continue;
-            tc_fence_after();
-            uint8_t *grow = smem + L::G_OFF + row * 128;
-            {
-                uint32_t rs[32], rp[32];
-                tmem_ld32(tmem_S + lane_addr + half * 32, rs);
-                if (NEED_DP)
-                    tmem_ld32(tmem_DP + lane_addr + half * 32, rp);
-                tmem_ld_wait();
-                float g[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int c = c0 + half * 32 + i;
-                    float x, w, lse_c, dsc_c;
-                    bool valid;
-                    if (!TRANSPOSED) {
-                        x = fmaf(__uint_as_float(rs[i]), ds, -slope * (float)(rr - c));
-                        valid = c >= st_row && c <= fi_row;
-                        lse_c = lse_row;
-                        dsc_c = dsc_row;
-                    } else {
-                        x = fmaf(__uint_as_float(rs[i]), ds, -slope * (float)(c - rr));
-                        valid = row >= (int)m_st[half * 32 + i] && row < (int)m_fi[half * 32 + i];
-                        lse_c = m_lse[half * 32 + i];
-                        dsc_c = m_dsc[half * 32 + i];
-                    }
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(x - lse_c));
-                    w = valid ? w : 0.f;
-                    g[i] = NEED_DP ? w * (__uint_as_float(rp[i]) - dsc_c) * c2 : w;
-                }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    __half2 h0 = __floats2half2_rn(g[8 * c], g[8 * c + 1]), h1 = __floats2half2_rn(g[8 * c + 2], g[8 * c + 3]),
-                            h2 = __floats2half2_rn(g[8 * c + 4], g[8 * c + 5]), h3 = __floats2half2_rn(g[8 * c + 6], g[8 * c + 7]);
-                    *(uint4 *)(grow + (((half * 4 + c) ^ (row & 7)) << 4)) =
-                        make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
-                }
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            mbar_arrive(g_full);
-        }
-        // epilogue: the accumulator row of this thread -> fp32 output
-        const int n_tiles = tile1 - tile0 + 1;
-        if (n_tiles > 0 && ok)
-            ok = mbar_wait(acc_ready, (n_tiles - 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        tc_fence_after();
-        float *dst = p.out + (size_t)rr * (H * TC_HD) + col0;
-#pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) { // each warp of the quarter writes 64 of the 128 columns
-            uint32_t r[32];
-            if (n_tiles > 0 && ok) {
-                tmem_ld32(tmem_ACC + lane_addr + c * 32, r);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    r[i] = 0u;
-            }
-            if (rr < T) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    *(uint4 *)(dst + c * 32 + i * 4) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1)
-        tmem_dealloc(tmem_base, 256);
-    if (threadIdx.x == 0 && *abort_flag)
-        atomicOr(p.status, TS2_STATUS_WAIT_TIMEOUT);
-}
-
-template <int MODE>
-static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p)
-{
-    auto kern = att_bwd_tc_kernel<MODE>;
-    static bool configured[16] = {};
-    if (!configured[c.device & 15]) {
-        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout<MODE>::SMEM));
-        configured[c.device & 15] = true;
-    }
-    const int Q = p.H * TC_HD;
-    CUtensorMap tA1, tA2, tB1, tB2;
-    int rc;
-    if ((rc = make_tensor_map(&tA1, a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
-        return rc;
-    if ((rc = make_tensor_map(&tA2, a2 ? a2 : a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
-        return rc;
-    if ((rc = make_tensor_map(&tB1, b1, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
-        return rc;
-    if ((rc = make_tensor_map(&tB2, b2, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
-        return rc;
-    dim3 grid((unsigned)ceil_div(p.T, TC_BM), (unsigned)p.H);
-    kern<<<grid, BWD_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, p);
-    TS2_CHECK_LAUNCH();
-    return TS2_OK;
-}
-
-int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
-                          const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                          int T, int H, float slope, float *dq, float *dk, float *dv)
-{
-    AttBwdParams p;
-    p.T = T;
-    p.H = H;
-    p.slope = slope;
-    p.span_start = span_start;
-    p.span_finish = span_finish;
-    p.rev_first = rev_first;
-    p.rev_last = rev_last;
-    p.lse = lse;
-    p.dscale = dscale;
-    p.status = device_status_word(c.device);
-    if (!p.status)
-        return fail(TS2_ERR_CUDA, "attention: no device status word");
-    int rc;
-    p.out = dq;
-    if ((rc = launch_bwd_tc<0>(c, q, dout, k, v, p)) != TS2_OK)
-        return rc;
-    p.out = dk;
-    if ((rc = launch_bwd_tc<1>(c, k, v, q, dout, p)) != TS2_OK)
-        return rc;
-    p.out = dv;
-    return launch_bwd_tc<2>(c, k, nullptr, q, dout, p);
 }
 
 } // namespace ts2
