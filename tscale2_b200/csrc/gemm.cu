@@ -363,18 +363,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 v[i] *= rs;
                         }
                     }
-                    const bool first = !out16 || !(c & 1), last = !out16 || (c & 1);
-                    if (first) {
+                    // Two 2 KB blocks per warp (32 rows x 64 bytes, 64-byte swizzle: 16-byte chunk j of row r sits at
+                    // j ^ ((r >> 1) & 3)), used in turn: before a block is refilled, all bulk groups but the most recent
+                    // one must have read their source, i.e. the store that last used this block.  A group is committed
+                    // for every fill, also when the store itself is clipped away, so that this count stays right.
+                    const int sw = (lane >> 1) & 3;
+                    if (out16) {
+                        uint8_t *blk = stg_warp + (c & 1) * 2048, *srow = blk + lane * 64;
                         if (lane == 0)
-                            bulk_wait_read<0>(); // the previous store of this warp has read the staging block
+                            bulk_wait_read<1>();
                         __syncwarp();
-                    }
-                    uint8_t *blk = stg_warp, *srow = blk + lane * 128;
-                    if (!out16) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            *(float4 *)(srow + ((i ^ (lane & 7)) << 4)) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                    } else {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint4 pk;
@@ -389,16 +387,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                                h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
                                 pk = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                             }
-                            *(uint4 *)(srow + ((((c & 1) * 4 + i) ^ (lane & 7)) << 4)) = pk;
+                            *(uint4 *)(srow + ((i ^ sw) << 4)) = pk;
                         }
-                    }
-                    if (last) {
                         fence_proxy_async();
                         __syncwarp();
-                        const int col_blk = out16 ? col - 32 : col;
-                        if (lane == 0 && col_blk < p.N) {
-                            tma_store_2d(&tmC, smem_u32(blk), col_blk, m0 + quarter * 32);
+                        if (lane == 0) {
+                            if (col < p.N)
+                                tma_store_2d(&tmC, smem_u32(blk), col, m0 + quarter * 32);
                             bulk_commit();
+                        }
+                    } else {
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) { // 16 fp32 columns per block
+                            uint8_t *blk = stg_warp + hb * 2048, *srow = blk + lane * 64;
+                            if (lane == 0)
+                                bulk_wait_read<1>();
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                *(float4 *)(srow + ((i ^ sw) << 4)) =
+                                    make_float4(v[16 * hb + 4 * i], v[16 * hb + 4 * i + 1], v[16 * hb + 4 * i + 2], v[16 * hb + 4 * i + 3]);
+                            fence_proxy_async();
+                            __syncwarp();
+                            if (lane == 0) {
+                                if (col + 16 * hb < p.N)
+                                    tma_store_2d(&tmC, smem_u32(blk), col + 16 * hb, m0 + quarter * 32);
+                                bulk_commit();
+                            }
                         }
                     }
                     continue;
@@ -543,8 +558,9 @@ static EncodeTiledFn encode_fn()
     return fn;
 }
 
-// 2-D map over a row-major [rows][ld] array of es-byte elements; box = 128 bytes x box_rows
-static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows)
+// 2-D map over a row-major [rows][ld] array of es-byte elements; box = row_bytes (128 or 64, swizzled alike) x box_rows
+static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows,
+                     int row_bytes = STAGE_ROW_BYTES)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn)
@@ -553,11 +569,12 @@ static int make_tmap(CUtensorMap *tm, const void *base, int es, int64_t inner, i
         return fail(TS2_ERR_INVALID_ARG, "operand base and row pitch must be multiples of 16 bytes");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)(ld * es)};
-    cuuint32_t box[2] = {(cuuint32_t)(STAGE_ROW_BYTES / es), (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)(row_bytes / es), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMapDataType dt = (es == 1) ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (es == 2) ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     CUresult r = fn(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(TS2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return TS2_OK;
@@ -785,7 +802,7 @@ int gemm(const GemmArgs &a)
     CUtensorMap tmC = tmA;
     p.tma_store = 0;
     if (pl.splits == 1 && a.group_mode != 2 && a.epi.out_kind != TS2_OUT_F32_ADD) {
-        if ((rc = make_tmap(&tmC, a.C, out_es, a.N, a.M, a.ldc, 32)) != TS2_OK)
+        if ((rc = make_tmap(&tmC, a.C, out_es, a.N, a.M, a.ldc, 32, 64)) != TS2_OK)
             return rc;
         p.tma_store = 1;
     }
