@@ -448,33 +448,37 @@ int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const
 
 // ---------------------------------------------------------------------------------
 // One block per row; the row of fp16 logits is staged in shared memory, read once
-// from HBM and overwritten once with the gradient.
-__global__ void softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, const float *__restrict__ bias,
-                                  const int *__restrict__ target, float gscale, float *__restrict__ logp_sum, int write_grad)
+// from HBM and overwritten once with the gradient.  Three passes over the staged row,
+// all in 16-byte vectors: maximum; e = 2^(x + bias - max) with its fp32 sum, e kept in
+// place as fp16; gradient (onehot - e / sum) * gscale.  One exponential per logit.
+__global__ void __launch_bounds__(512, 2)
+    softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, const float *__restrict__ bias, const int *__restrict__ target,
+                      float gscale, float *__restrict__ logp_sum, int write_grad)
 {
-    extern __shared__ __half row_s[];
+    extern __shared__ uint4 row_s4[];
     __shared__ float red[32];
-    const int tid = threadIdx.x, nthr = blockDim.x;
+    __shared__ float x_tgt_s;
+    const int tid = threadIdx.x, nthr = blockDim.x, nvec = V / 8;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-        __half *src = logits + (size_t)row * V;
+        uint4 *src = (uint4 *)(logits + (size_t)row * V);
         const int tgt = target[row];
         if (tgt < 0) {
             if (write_grad)
-                for (int i = tid; i < V / 8; i += nthr)
-                    ((uint4 *)src)[i] = make_uint4(0, 0, 0, 0);
+                for (int i = tid; i < nvec; i += nthr)
+                    src[i] = make_uint4(0, 0, 0, 0);
             continue;
         }
         float mx = 0.f; // the reference starts the maximum at 0 and takes it over the logits without bias
-        for (int i0 = tid; i0 < V / 8; i0 += nthr * 4) {
+        for (int i0 = tid; i0 < nvec; i0 += nthr * 4) {
             uint4 raw[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                raw[u] = (i0 + u * nthr < V / 8) ? ((const uint4 *)src)[i0 + u * nthr] : make_uint4(0, 0, 0, 0);
+                raw[u] = (i0 + u * nthr < nvec) ? src[i0 + u * nthr] : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                if (i0 + u * nthr >= V / 8)
+                if (i0 + u * nthr >= nvec)
                     continue;
-                ((uint4 *)row_s)[i0 + u * nthr] = raw[u];
+                row_s4[i0 + u * nthr] = raw[u];
                 const __half2 *h = (const __half2 *)&raw[u];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -491,10 +495,34 @@ __global__ void softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, 
         for (int i = 0; i < nthr / 32; ++i)
             mx = fmaxf(mx, red[i]);
         __syncthreads();
-        float sum = 0.f;
-        for (int i = tid; i < V; i += nthr)
-            sum += exp2f(__half2float(row_s[i]) + (bias ? bias[i] : 0.f) - mx);
-        sum = warp_sum(sum);
+        float sum0 = 0.f, sum1 = 0.f;
+        for (int i = tid; i < nvec; i += nthr) { // every thread revisits the vectors it staged itself
+            uint4 raw = row_s4[i];
+            __half2 *h = (__half2 *)&raw;
+            float bv[8];
+            if (bias) {
+                const float4 b0 = __ldg((const float4 *)(bias + 8 * i)), b1 = __ldg((const float4 *)(bias + 8 * i) + 1);
+                bv[0] = b0.x, bv[1] = b0.y, bv[2] = b0.z, bv[3] = b0.w, bv[4] = b1.x, bv[5] = b1.y, bv[6] = b1.z, bv[7] = b1.w;
+            }
+            const int trel = tgt - 8 * i; // position of the target inside this vector, if 0..7
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                const float x0 = f.x + (bias ? bv[2 * j] : 0.f), x1 = f.y + (bias ? bv[2 * j + 1] : 0.f);
+                if (trel == 2 * j)
+                    x_tgt_s = x0;
+                if (trel == 2 * j + 1)
+                    x_tgt_s = x1;
+                float e0, e1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 - mx));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 - mx));
+                sum0 += e0;
+                sum1 += e1;
+                h[j] = __floats2half2_rn(e0, e1);
+            }
+            row_s4[i] = raw;
+        }
+        float sum = warp_sum(sum0 + sum1);
         if ((tid & 31) == 0)
             red[tid >> 5] = sum;
         __syncthreads();
@@ -502,17 +530,20 @@ __global__ void softmax_ce_kernel(__half *__restrict__ logits, int rows, int V, 
         for (int i = 0; i < nthr / 32; ++i)
             sum += red[i];
         const float inv = 1.f / sum;
-        if (tid == 0) {
-            const float lt = __half2float(row_s[tgt]) + (bias ? bias[tgt] : 0.f) - mx;
-            atomicAdd(logp_sum, lt * 0.69314718f - logf(sum));
-        }
+        if (tid == 0)
+            atomicAdd(logp_sum, (x_tgt_s - mx) * 0.69314718f - logf(sum));
         if (write_grad) {
-            for (int i = tid; i < V / 2; i += nthr) {
-                const float2 f = __half22float2(((const __half2 *)row_s)[i]);
-                float p0 = exp2f(f.x + (bias ? bias[2 * i] : 0.f) - mx) * inv;
-                float p1 = exp2f(f.y + (bias ? bias[2 * i + 1] : 0.f) - mx) * inv;
-                float g0 = ((2 * i == tgt) ? 1.f : 0.f) - p0, g1 = ((2 * i + 1 == tgt) ? 1.f : 0.f) - p1;
-                ((__half2 *)src)[i] = __floats2half2_rn(g0 * gscale, g1 * gscale);
+            const float ninv = -inv * gscale;
+            for (int i = tid; i < nvec; i += nthr) {
+                uint4 raw = row_s4[i];
+                __half2 *h = (__half2 *)&raw;
+                const int trel = tgt - 8 * i;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 e = __half22float2(h[j]);
+                    h[j] = __floats2half2_rn(fmaf(e.x, ninv, trel == 2 * j ? gscale : 0.f), fmaf(e.y, ninv, trel == 2 * j + 1 ? gscale : 0.f));
+                }
+                src[i] = raw;
             }
         }
         __syncthreads();
