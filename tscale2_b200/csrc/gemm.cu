@@ -32,6 +32,7 @@ static constexpr int NUM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps 
 struct GemmParams {
     int M, N;
     int m_tiles, n_tiles, splits;
+    int n_fast;        // tile order: consecutive tiles walk N first (the CTAs of a wave share A rows) or M first (share B rows)
     int k_blocks;      // total K blocks (one block = one pipeline stage)
     int kb_per_split;
     uint32_t idesc;
@@ -59,6 +60,20 @@ struct Unit {
     long long c_off;
 };
 
+// Tile index -> tile coordinates.  The CTAs of a wave work on consecutive tiles, so the fast index decides which
+// operand they share through L2: the host picks the order that streams the larger operand from HBM once and
+// re-reads the smaller one (which stays in L2).
+__device__ __forceinline__ void tile_coords(const GemmParams &p, int tile, int &mt, int &nt)
+{
+    if (p.n_fast) {
+        nt = tile % p.n_tiles;
+        mt = tile / p.n_tiles;
+    } else {
+        mt = tile % p.m_tiles;
+        nt = tile / p.m_tiles;
+    }
+}
+
 // identical in the three roles, so that they agree on which units exist
 __device__ __forceinline__ bool decode_unit(const GemmParams &p, int u, int bn, Unit &t)
 {
@@ -75,9 +90,10 @@ __device__ __forceinline__ bool decode_unit(const GemmParams &p, int u, int bn, 
         return t.kb1 > t.kb0;
     }
     const int tile = u / p.splits, split = u - tile * p.splits;
-    const int mt = tile % p.m_tiles;
+    int mt, nt;
+    tile_coords(p, tile, mt, nt);
     t.m0 = mt * BM;
-    t.n0 = (tile / p.m_tiles) * bn;
+    t.n0 = nt * bn;
     t.kb0 = split * p.kb_per_split;
     t.kb1 = min(p.k_blocks, t.kb0 + p.kb_per_split);
     if (p.group_mode == 1) {
@@ -503,8 +519,10 @@ __global__ void reduce_splitk_kernel(const GemmParams p)
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int tile = (int)(i / vec_per_tile), e = (int)(i % vec_per_tile);
         const int r = e / (BN / 4), c = (e % (BN / 4)) * 4;
-        const long long row = (long long)(tile % p.m_tiles) * BM + r;
-        const int col = (tile / p.m_tiles) * BN + c;
+        int mt, nt;
+        tile_coords(p, tile, mt, nt);
+        const long long row = (long long)mt * BM + r;
+        const int col = nt * BN + c;
         if (row >= p.M || col >= p.N)
             continue;
         float4 s = make_float4(0, 0, 0, 0);
@@ -773,6 +791,7 @@ int gemm(const GemmArgs &a)
     p.N = (int)a.N;
     p.m_tiles = pl.m_tiles;
     p.n_tiles = pl.n_tiles;
+    p.n_fast = a.M > a.N ? 1 : 0; // operand bytes are M x K and N x K of the same element size
     p.splits = pl.splits;
     p.k_blocks = pl.k_blocks;
     p.kb_per_split = pl.kb_per_split;
@@ -926,6 +945,7 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
     p.N = (int)in_dim;
     p.m_tiles = pl.m_tiles;
     p.n_tiles = pl.n_tiles;
+    p.n_fast = out_dim > in_dim ? 1 : 0;
     p.splits = pl.splits;
     p.k_blocks = pl.k_blocks;
     p.kb_per_split = pl.kb_per_split;
