@@ -33,6 +33,10 @@ WORKLOADS = {
 }
 
 
+# average DRAM bytes per contraction launch from one ncu capture of a whole step (see profiles/)
+NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH = {("c3_dense12_d768", "fp8"): 510758939}
+
+
 def make_spec(w, precision):
     return host.ModelSpec(dim=w["dim"], head_count=w["heads"], ffn_tiles=w["ffn_tiles"], vocab=w["vocab"],
                           attention_widths=[w["seq"]], precision=precision).add_blocks(w["blocks"])
@@ -214,6 +218,7 @@ def main():
     launches = model.launch_count()
     barrier()
     clocks = sampler.stop()
+    gemm_bytes = model.get_kernel_bytes()
     gemm_ms, gemm_n, gemm_flops = model.get_kernel_timing(reset=True)
     model.set_kernel_timing(False)
 
@@ -257,8 +262,15 @@ def main():
     else:
         peak = peaks["bf16_tflops_sustained"]
         peak_note = f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src})"
+    # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of the 183 contraction launches of one step
+    # of this workload, averaged (ncu capture summarised in profiles/gemm_dram_traffic_c3_dense12_d768_step.md);
+    # the algorithmic bytes next to it are counted by the library at launch time over the timed region
+    traffic = NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.precision))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None, "kernel": "gemm_kernel (tcgen05)",
+                "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                "algorithmic_bytes_per_launch": gemm_bytes / gemm_n if gemm_n else None,
+                "hbm_gbs_algorithmic": gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else None,
+                "hbm_peak_gbs": peaks.get("hbm_gbs"), "kernel": "gemm_kernel (tcgen05)",
                 "launches_per_step": gemm_n / args.steps, "share_of_step": gemm_ms / ms_max, "peak_source": peak_note,
                 "step_flops_per_token": fpt, "step_tflops": value / world * fpt / 1e12}
     line = {"metric": "train tokens/s (fwd+bwd)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

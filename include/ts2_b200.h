@@ -216,6 +216,9 @@ int ts2_timer_end(ts2_model *m, float *ms);
  * when profiling is enabled (adds a pair of events per launch) */
 int ts2_set_kernel_timing(ts2_model *m, int enable);
 int ts2_get_kernel_timing(ts2_model *m, int reset, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total);
+/* algorithmic bytes (both operands once, output once, residual input once) of the contraction launches timed
+ * since the last reset; read it before ts2_get_kernel_timing(reset = 1).  No reference counterpart (measurement). */
+int ts2_get_kernel_bytes(ts2_model *m, double *gemm_bytes_total);
 
 /* ------------------------------------------------------------------------- */
 /* operator-level entry points (device pointers unless named host_*); these

@@ -668,11 +668,11 @@ static std::mutex g_time_mu;
 static bool g_time_on = false;
 struct TimedLaunch {
     cudaEvent_t a, b;
-    double flops;
+    double flops, bytes;
 };
 static std::vector<TimedLaunch> g_timed;
 static std::vector<cudaEvent_t> g_event_pool;
-static double g_ms_total = 0, g_flops_total = 0;
+static double g_ms_total = 0, g_flops_total = 0, g_bytes_total = 0;
 static long long g_timed_launches = 0;
 
 void gemm_timing_enable(bool on)
@@ -689,6 +689,7 @@ static void timing_collect_locked()
             if (cudaEventElapsedTime(&ms, t.a, t.b) == cudaSuccess) {
                 g_ms_total += ms;
                 g_flops_total += t.flops;
+                g_bytes_total += t.bytes;
                 ++g_timed_launches;
             }
         }
@@ -698,7 +699,7 @@ static void timing_collect_locked()
     g_timed.clear();
 }
 
-void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total)
+void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total, double *bytes_total)
 {
     std::lock_guard<std::mutex> lk(g_time_mu);
     timing_collect_locked();
@@ -708,8 +709,10 @@ void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *
         *launches = g_timed_launches;
     if (flops_total)
         *flops_total = g_flops_total;
+    if (bytes_total)
+        *bytes_total = g_bytes_total;
     if (reset) {
-        g_ms_total = g_flops_total = 0;
+        g_ms_total = g_flops_total = g_bytes_total = 0;
         g_timed_launches = 0;
     }
 }
@@ -862,7 +865,10 @@ int gemm(const GemmArgs &a)
     if (timed) {
         cudaEventRecord(eb, a.stream);
         std::lock_guard<std::mutex> lk(g_time_mu);
-        g_timed.push_back({ea, eb, 2.0 * (double)a.M * (double)a.N * (double)a.K});
+        // algorithmic bytes: both operands once, the output once, the residual input of the accumulate form once
+        const double mn = (double)a.M * (double)a.N;
+        const double bytes = ((double)a.M + (double)a.N) * (double)a.K * es + mn * out_es + (a.epi.out_kind == TS2_OUT_F32_ADD ? mn * 4 : 0);
+        g_timed.push_back({ea, eb, 2.0 * mn * (double)a.K, bytes});
     }
     return rc;
 }

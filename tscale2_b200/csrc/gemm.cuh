@@ -56,6 +56,6 @@ int make_tensor_map(::CUtensorMap_st *tm, const void *base, int es, int64_t inne
 
 // accumulated device time of the contraction kernel (enabled by gemm_timing_enable)
 void gemm_timing_enable(bool on);
-void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total);
+void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total, double *bytes_total = nullptr);
 
 } // namespace ts2

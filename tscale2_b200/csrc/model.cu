@@ -1338,6 +1338,12 @@ int ts2_set_kernel_timing(ts2_model *, int enable)
     return TS2_OK;
 }
 
+int ts2_get_kernel_bytes(ts2_model *, double *gemm_bytes_total)
+{
+    gemm_timing_get(false, nullptr, nullptr, nullptr, gemm_bytes_total);
+    return TS2_OK;
+}
+
 int ts2_get_kernel_timing(ts2_model *, int reset, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total)
 {
     long long n = 0;

@@ -134,6 +134,13 @@ class Model:
         self._check(self.lib.ts2_get_kernel_timing(self.h, int(reset), C.byref(ms), C.byref(n), C.byref(fl)))
         return ms.value, n.value, fl.value
 
+    def get_kernel_bytes(self):
+        """Algorithmic bytes of the contraction launches timed since the last reset (read before a resetting
+        get_kernel_timing)."""
+        v = C.c_double()
+        self._check(self.lib.ts2_get_kernel_bytes(self.h, C.byref(v)))
+        return v.value
+
     def launch_count(self, reset=False):
         return self.lib.ts2_launch_count(self.h, int(reset))
 
