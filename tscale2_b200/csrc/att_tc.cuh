@@ -17,17 +17,5 @@ static constexpr int P_BYTES = TC_BM * TC_BN * 2;   // 16 KB: one atom of 128 ro
 
 __host__ __device__ inline float att_dot_scale_tc() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
 
-#ifdef __CUDACC__
-// barrier of the two warps that share TMEM lane quarter q (ids 2..5; compile-time ids keep the CTA at 6 barriers)
-__device__ __forceinline__ void pair_barrier(int q)
-{
-    switch (q) {
-    case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
-    case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
-    case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
-    default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
-    }
-}
-#endif
 
 } // namespace ts2

@@ -235,6 +235,17 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int n, bool a_mn, bool b_m
     return (1u << 4) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// barrier of the two warps that share TMEM lane quarter q (ids 2..5; compile-time ids keep the CTA at 6 barriers)
+__device__ __forceinline__ void pair_barrier(int q)
+{
+    switch (q) {
+    case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

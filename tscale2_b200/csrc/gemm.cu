@@ -19,6 +19,7 @@
 // token-major through MN-major shared-memory descriptors, also the per-step transposes
 // (src/gpt/compute/matmul_fwdbwd.cuh:149-162,169-280).
 #include "gemm.cuh"
+#include "fast_types.cuh"
 #include <cuda.h>
 #include <vector>
 #include <mutex>
@@ -28,6 +29,7 @@ namespace ts2 {
 static constexpr int BM = 128;
 static constexpr int STAGE_ROW_BYTES = 128; // one swizzle row
 static constexpr int NUM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
+static constexpr int NUM_THREADS_GATED = 576; // the gated-activation epilogue does more per element: 16 epilogue warps
 
 struct GemmParams {
     int M, N;
@@ -53,10 +55,18 @@ struct GemmParams {
     long long c_group_stride;
     int bk;
     int tma_store; // the epilogue stages 32-row blocks in shared memory and writes them with TMA (tmC)
+    // gated-activation form (see Epilogue in gemm.cuh): a tile is 128 "wide" columns [nt * 128, +128) and the 128
+    // "gate" columns pair_stride further on
+    int pair_stride = 0;
+    void *act_out = nullptr;
+    long long act_ld = 0;
+    float *act_scale = nullptr;
+    float act_mult = 1.f;
+    int act_f16 = 0;
 };
 
 struct Unit {
-    int m0, n0, kb0, kb1, b_row_off;
+    int m0, n0, nt, kb0, kb1, b_row_off;
     long long c_off;
 };
 
@@ -93,7 +103,8 @@ __device__ __forceinline__ bool decode_unit(const GemmParams &p, int u, int bn, 
     int mt, nt;
     tile_coords(p, tile, mt, nt);
     t.m0 = mt * BM;
-    t.n0 = nt * bn;
+    t.n0 = nt * (p.pair_stride ? bn / 2 : bn);
+    t.nt = nt;
     t.kb0 = split * p.kb_per_split;
     t.kb1 = min(p.k_blocks, t.kb0 + p.kb_per_split);
     if (p.group_mode == 1) {
@@ -149,8 +160,10 @@ struct SmemLayout {
 };
 
 // ES: element size in bytes; MMA: 0 = f8f6f4, 1 = f16 (fp16/bf16), 2 = i8; MN: operand layout
-template <int BN, int ES, int MMA, bool MN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// GATED: the gated-activation epilogue (Epilogue::pair_stride) is compiled in; a separate instantiation keeps its
+// registers out of the plain kernels
+template <int BN, int ES, int MMA, bool MN, bool GATED = false>
+__global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const GemmParams p)
 {
@@ -178,7 +191,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 8);
+            mbar_init(tempty0 + 8 * a, GATED ? 16 : 8); // one arrival per epilogue warp
         }
         mbar_init(drain, 1);
         *abort_flag = 0;
@@ -221,7 +234,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const int k0 = kb * BK;
                     if constexpr (!MN) {
                         tma_load_2d(sa, &tmA, fb, k0, m0);
-                        tma_load_2d(sb, &tmB, fb, k0, n0);
+                        if (GATED) { // two boxes of BN / 2 rows: wide rows, gate rows
+                            tma_load_2d(sb, &tmB, fb, k0, n0);
+                            tma_load_2d(sb + (BN / 2) * STAGE_ROW_BYTES, &tmB, fb, k0, p.pair_stride + n0);
+                        } else {
+                            tma_load_2d(sb, &tmB, fb, k0, n0);
+                        }
                     } else {
                         // one box per 128-byte atom along M / N, each BK rows of the token-major operand
 #pragma unroll
@@ -342,6 +360,117 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (p.splits == 1 && p.row_scale && row < p.M)
                 rs = __ldg(p.row_scale + row);
             rs *= alpha;
+            if constexpr (GATED) {
+                // Gated-activation form.  TMEM columns [0, 128) hold the wide tile, [128, 256) the gate tile.  Sixteen
+                // epilogue warps, four per lane quarter: warp part j takes wide columns [32 j, +32) and the gate columns
+                // under them, and reads the other 96 wide columns once more for the sum of squares of the whole
+                // 128-wide tile (cheaper than an exchange between warps, and no barrier a failed wait could break).
+                const int part = (warp - 2) >> 2;
+                const int wcol = n0 + part * 32, gcol = p.pair_stride + wcol; // first wide / gate column of this warp
+                uint8_t *const blk = smem + L::STAGING_OFFSET + (warp - 2) * 2048;
+                auto scaled32 = [&](int chunk, int col, float *v) { // 32 accumulator columns -> scaled values
+                    uint32_t r[32];
+                    tmem_ld32(taddr + chunk * 32, r);
+                    tmem_ld_wait();
+                    if (p.col_scale) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 cs = __ldg((const float4 *)(p.col_scale + col) + i);
+                            v[4 * i] = __uint_as_float(r[4 * i]) * rs * cs.x, v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * rs * cs.y;
+                            v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * rs * cs.z, v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * rs * cs.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            v[i] = __uint_as_float(r[i]) * rs;
+                    }
+                };
+                // 32 fp16 columns -> the warp's staging block -> TMA store (rows >= M, columns >= N clipped)
+                auto stage_store16 = [&](const float *v, int col) {
+                    uint8_t *srow = blk + lane * 64;
+                    const int sw = (lane >> 1) & 3;
+                    if (lane == 0)
+                        bulk_wait_read<0>(); // the previous store has read the block
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
+                                h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                        *(uint4 *)(srow + ((i ^ sw) << 4)) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (col < p.N)
+                            tma_store_2d(&tmC, smem_u32(blk), col, m0 + quarter * 32);
+                        bulk_commit();
+                    }
+                };
+                float wv[32], sum2 = 0.f;
+                scaled32(part, wcol, wv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    sum2 = fmaf(wv[i], wv[i], sum2);
+#pragma unroll 1
+                for (int oc = 1; oc < 4; ++oc) {
+                    const int ch = (part + oc) & 3;
+                    float ov[32];
+                    scaled32(ch, n0 + ch * 32, ov);
+                    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        s4[i & 3] = fmaf(ov[i], ov[i], s4[i & 3]);
+                    sum2 += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+                }
+                const float tscale = tile_scale(sum2);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    wv[i] *= tscale;
+                if (part == 0 && row < p.M)
+                    p.act_scale[row * p.n_tiles + un.nt] = tscale;
+                stage_store16(wv, wcol);
+                float gv[32];
+                scaled32(4 + part, gcol, gv);
+                stage_store16(gv, gcol);
+                if (row < p.M) {
+                    const size_t aidx = (size_t)row * p.act_ld + wcol;
+                    if (p.act_f16) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            Fast<1>::store4(p.act_out, aidx + 4 * i,
+                                            make_float4(lolu_mult(gv[4 * i]) * wv[4 * i] * p.act_mult, lolu_mult(gv[4 * i + 1]) * wv[4 * i + 1] * p.act_mult,
+                                                        lolu_mult(gv[4 * i + 2]) * wv[4 * i + 2] * p.act_mult,
+                                                        lolu_mult(gv[4 * i + 3]) * wv[4 * i + 3] * p.act_mult));
+                    } else {
+                        // sigmoid(2 g) = 0.5 + 0.5 tanh(g): one MUFU op; its 2^-11 error is far below the e4m3 step
+                        const float hm = 0.5f * p.act_mult;
+                        auto gated = [&](int e) {
+                            float th;
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(gv[e]));
+                            return fmaf(th, hm, hm) * wv[e];
+                        };
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) { // 16 e4m3 bytes per store
+                            uint32_t w4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int e = 16 * j + 4 * i;
+                                __nv_fp8x4_e4m3 pk(make_float4(gated(e), gated(e + 1), gated(e + 2), gated(e + 3)));
+                                w4[i] = pk.__x;
+                            }
+                            *(uint4 *)((uint8_t *)p.act_out + aidx + 16 * j) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(tempty0 + 8 * acc);
+                acc ^= 1;
+                if (acc == 0)
+                    acc_phase ^= 1;
+                continue;
+            }
 #pragma unroll 1
             for (int c = c_begin; c < c_end; ++c) {
                 uint32_t r[32];
@@ -729,17 +858,17 @@ static cudaEvent_t pooled_event()
     return e;
 }
 
-template <int BN, int ES, int MMA, bool MN>
+template <int BN, int ES, int MMA, bool MN, bool GATED = false>
 static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                   const GemmParams &p)
 {
-    auto kern = gemm_kernel<BN, ES, MMA, MN>;
+    auto kern = gemm_kernel<BN, ES, MMA, MN, GATED>;
     static bool configured[16] = {};
     if (!configured[a.device & 15]) {
         TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL));
         configured[a.device & 15] = true;
     }
-    kern<<<pl.grid, NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, tmC, p);
+    kern<<<pl.grid, GATED ? NUM_THREADS_GATED : NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, tmC, p);
     TS2_CHECK_LAUNCH();
     if (pl.splits > 1) {
         const long long total = (long long)pl.m_tiles * pl.n_tiles * BM * BN / 4;
@@ -769,7 +898,20 @@ int gemm(const GemmArgs &a)
         return fail(TS2_ERR_INVALID_ARG, "gemm: bad row-grouped arguments");
     if (a.group_mode == 2 && (!a.mn_major || !a.group_kptr || a.groups <= 0))
         return fail(TS2_ERR_INVALID_ARG, "gemm: bad K-grouped arguments");
+    const bool paired = a.epi.pair_stride != 0;
+    if (paired && (a.mn_major || a.group_mode || a.kind == KIND_I8 || a.epi.out_kind != TS2_OUT_F16 || a.N != 2 * a.epi.pair_stride ||
+                   a.epi.pair_stride % 128 || !a.epi.act_out || !a.epi.act_scale || a.epi.act_ld < a.epi.pair_stride ||
+                   (a.epi.act_ld * (a.epi.act_f16 ? 2 : 1)) % 16 || ((uintptr_t)a.epi.act_out & 15)))
+        return fail(TS2_ERR_INVALID_ARG, "gemm: bad gated-activation arguments");
     Plan pl = make_plan(a.device, a.kind, a.mn_major, a.M, a.N, a.K, a.group_mode, a.groups);
+    if (paired) { // one tile = 128 wide + 128 gate columns, never split along K (the epilogue needs whole sums)
+        if (pl.bn != 256)
+            return fail(TS2_ERR_UNSUPPORTED, "gemm: the gated-activation form needs 256-column tiles");
+        pl.n_tiles = (int)(a.epi.pair_stride / 128);
+        pl.splits = 1;
+        pl.kb_per_split = pl.k_blocks;
+        pl.grid = std::min(sm_count(a.device), pl.m_tiles * pl.n_tiles);
+    }
     if (pl.splits > 1) {
         size_t need = (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float);
         if (!a.workspace || a.workspace_bytes < need)
@@ -781,7 +923,7 @@ int gemm(const GemmArgs &a)
     if (!a.mn_major) {
         if ((rc = make_tmap(&tmA, a.A, es, a.K, a.M, a.lda, BM)) != TS2_OK)
             return rc;
-        if ((rc = make_tmap(&tmB, a.B, es, a.K, a.group_mode == 1 ? a.N * a.groups : a.N, a.ldb, pl.bn)) != TS2_OK)
+        if ((rc = make_tmap(&tmB, a.B, es, a.K, a.group_mode == 1 ? a.N * a.groups : a.N, a.ldb, paired ? pl.bn / 2 : pl.bn)) != TS2_OK)
             return rc;
     } else {
         if ((rc = make_tmap(&tmA, a.A, es, a.M, a.K, a.lda, bk)) != TS2_OK)
@@ -819,6 +961,12 @@ int gemm(const GemmArgs &a)
     p.group_kptr = a.group_kptr;
     p.c_group_stride = a.c_group_stride;
     p.bk = bk;
+    p.pair_stride = (int)a.epi.pair_stride;
+    p.act_out = a.epi.act_out;
+    p.act_ld = a.epi.act_ld;
+    p.act_scale = a.epi.act_scale;
+    p.act_mult = a.epi.act_mult;
+    p.act_f16 = a.epi.act_f16 ? 1 : 0;
     // coalesced TMA-store epilogue for plain stores (the accumulate form reads C anyway; split units go to the workspace;
     // per-group C offsets of mode 2 are not expressible as one 2-D map)
     CUtensorMap tmC = tmA;
@@ -847,6 +995,12 @@ int gemm(const GemmArgs &a)
     if (pl.bn == BN_ && es == ES_ && mma == MMA_ && a.mn_major == MN_)       \
         rc = launch<BN_, ES_, MMA_, MN_>(a, pl, tmA, tmB, tmC, p);
     rc = TS2_ERR_UNSUPPORTED;
+    if (paired) {
+        if (es == 1 && mma == 0)
+            rc = launch<256, 1, 0, false, true>(a, pl, tmA, tmB, tmC, p);
+        else if (es == 2 && mma == 1)
+            rc = launch<256, 2, 1, false, true>(a, pl, tmA, tmB, tmC, p);
+    } else {
     TS2_GEMM_CASE(256, 1, 0, false)
     TS2_GEMM_CASE(128, 1, 0, false)
     TS2_GEMM_CASE(256, 1, 0, true)
@@ -859,6 +1013,7 @@ int gemm(const GemmArgs &a)
     TS2_GEMM_CASE(128, 1, 2, false)
     TS2_GEMM_CASE(256, 1, 2, true)
     TS2_GEMM_CASE(128, 1, 2, true)
+    }
 #undef TS2_GEMM_CASE
     if (rc == TS2_ERR_UNSUPPORTED)
         return fail(rc, "gemm: unsupported configuration");

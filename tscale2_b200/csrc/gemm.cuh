@@ -17,6 +17,17 @@ struct Epilogue {
     const float *col_scale = nullptr;  // [N] device
     const float *c_in = nullptr;       // TS2_OUT_F32_ADD: C = c_in + result (same pitch as C); null: in place
     int out_kind = TS2_OUT_F32;
+    // Gated-activation form (FFN expansion, K-major fp16 output only): B holds two row blocks, "wide" rows [0, pair_stride)
+    // and "gate" rows [pair_stride, 2 pair_stride), N = 2 pair_stride.  A tile covers 128 columns of each, and the
+    // epilogue applies the 128-wide tile normalisation to the wide half, stores the normalised wide and the raw gate
+    // values as fp16 in C (same columns as the plain form), the tile scale in act_scale[M][pair_stride / 128] and
+    // act_mult * sigmoid(2 gate) * normalised wide in act_out[M][act_ld] (e4m3 bytes, or fp16 when act_f16).
+    int64_t pair_stride = 0;
+    void *act_out = nullptr;
+    int64_t act_ld = 0;
+    float *act_scale = nullptr;
+    float act_mult = 1.f;
+    bool act_f16 = false;
 };
 
 struct GemmArgs {

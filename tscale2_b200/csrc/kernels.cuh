@@ -40,7 +40,9 @@ int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, vo
 // wg: [T][2F] fp16 = [wide | gate]; what: normalized wide fp16 [T][F]; wscale [T][F/128]; rg fast [T][F]
 int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, float *wscale, void *rg);
 // BackpropLoLU + NormalizeStateBackward of the wide vector (layer_ffn.cu:232-236): d2 fast [T][2F] = [dwide | dgate]
-int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, const float *wscale, int T, int F, void *d2);
+// what: normalised wide values, row pitch what_ld (the wide half of wg when the contraction's epilogue wrote them there)
+int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, int what_ld, const float *wscale, int T, int F,
+                     void *d2);
 
 // attention gate: rg = sigmoid(2 gate) * o  (LoLU, cpu_util.cpp:139-168); gate inside qkvg [T][4Q] at column 3Q
 int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg);

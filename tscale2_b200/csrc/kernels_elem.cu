@@ -296,7 +296,7 @@ int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, 
 
 template <int FT>
 __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __half *__restrict__ wg, const __half *__restrict__ what,
-                                        const float *__restrict__ wscale, int T, int F, void *__restrict__ d2)
+                                        int what_ld, const float *__restrict__ wscale, int T, int F, void *__restrict__ d2)
 {
     const int tiles = F / TILE;
     constexpr int R = 2;
@@ -316,7 +316,7 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
             off[r] = tile * TILE + lane * 4;
             g[r] = ok[r] ? load_half4(drg + t[r] * F + off[r]) : make_float4(0, 0, 0, 0);
             gate[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + F + off[r]) : make_float4(0, 0, 0, 0);
-            wn[r] = ok[r] ? load_half4(what + t[r] * F + off[r]) : make_float4(0, 0, 0, 0);
+            wn[r] = ok[r] ? load_half4(what + t[r] * what_ld + off[r]) : make_float4(0, 0, 0, 0);
             scale[r] = ok[r] ? wscale[t[r] * tiles + tile] : 0.f;
         }
 #pragma unroll
@@ -338,13 +338,14 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
     }
 }
 
-int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, const float *wscale, int T, int F, void *d2)
+int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, int what_ld, const float *wscale, int T, int F,
+                     void *d2)
 {
     const int grid = grid_for(c, (long long)T * (F / TILE));
     if (c.ft == 0)
-        ffn_act_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, wscale, T, F, d2);
+        ffn_act_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, what_ld, wscale, T, F, d2);
     else
-        ffn_act_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, wscale, T, F, d2);
+        ffn_act_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, what_ld, wscale, T, F, d2);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

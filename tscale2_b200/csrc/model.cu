@@ -503,7 +503,6 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
             M_TRY(dalloc(m, &ly.vscale, (size_t)T * m->H));
             M_TRY(dalloc(m, &ly.lse, (size_t)T * m->H));
         } else {
-            M_TRY(dalloc(m, &ly.what, (size_t)T * W));
             M_TRY(dalloc(m, &ly.wscale, (size_t)T * (W / 128)));
         }
     }
@@ -628,13 +627,23 @@ int forward(ts2_model *m)
         Epilogue e1;
         e1.col_scale = ly.fwd_col;
         e1.out_kind = TS2_OUT_F16;
+        if (ly.type != TS2_LAYER_ATT) {
+            // FFN: the contraction's epilogue normalises the wide tiles, applies the gate and writes rg itself
+            // (LoLU of the reference: sigmoid(2 gate) * tilenorm(wide)); cat16 then holds [normalised wide | gate]
+            e1.pair_stride = W;
+            e1.col_scale = nullptr; // both matrices are used without their scale: the uniform factor rides in alpha
+            e1.alpha = sqrtf(1.0f / D) / (m->s_act * 32.f);
+            e1.act_out = ly.rg;
+            e1.act_ld = W;
+            e1.act_scale = ly.wscale;
+            e1.act_mult = m->s_act;
+            e1.act_f16 = m->ft != 0;
+        }
         M_TRY(gemm_tn(m, m->kind, T, C, D, ly.n_fast, D, ly.Wcat, D, ly.cat16, C, e1));
         if (ly.type == TS2_LAYER_ATT) {
             M_TRY(att_post_forward(c, ly.cat16, m->rope, T, H, ly.q, ly.k, ly.v, ly.qscale, ly.vscale));
             M_TRY(attention_forward(c, ly.q, ly.k, ly.v, b.span_start[ly.att_type], b.span_finish[ly.att_type], T, H, ly.slope, ly.o, ly.lse));
             M_TRY(att_gate_forward(c, ly.cat16, ly.o, T, W, ly.rg));
-        } else {
-            M_TRY(ffn_act_forward(c, ly.cat16, T, W, ly.what, ly.wscale, ly.rg));
         }
         // state_out = state_in + rg . Wc^T * sqrt(1/wide) with Wc = q * sko / 32
         Epilogue e2;
@@ -784,7 +793,7 @@ int backward(ts2_model *m)
             M_TRY(att_post_backward(c, m->dq, m->dk, m->dv, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
                                     m->dcat));
         } else {
-            M_TRY(ffn_act_backward(c, m->drg, ly.cat16, ly.what, ly.wscale, T, W, m->dcat));
+            M_TRY(ffn_act_backward(c, m->drg, ly.cat16, ly.cat16, 2 * W, ly.wscale, T, W, m->dcat));
         }
         // dn (scale-free) = dcat . (q_cat/32) * sqrt(1/D)
         Epilogue e4;
