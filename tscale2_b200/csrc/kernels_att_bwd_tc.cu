@@ -40,18 +40,17 @@ template <int MODE>
 struct BwdLayout {
     static constexpr bool NEED_DP = MODE != 2;
     static constexpr bool TRANSPOSED = MODE != 0;
-    static constexpr int STAGES = NEED_DP ? 2 : 3;
+    static constexpr int STAGES = MODE == 1 ? 2 : 3; // what fits: mode 1 has four resident tiles and the per-node records
     static constexpr int A1_OFF = 0;
     static constexpr int A2_OFF = A1_OFF + 2 * Q_BYTES;
     static constexpr int RES_BYTES = (NEED_DP ? 4 : 2) * Q_BYTES;
     static constexpr int STAGE_OFF = RES_BYTES;
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int G_OFF = STAGE_OFF + STAGES * STAGE_BYTES;
-    static constexpr int META_OFF = G_OFF + 2 * P_BYTES;
-    static constexpr int BAR_OFF = META_OFF + STAGES * META_TILE_BYTES;
+    static constexpr int META_OFF = STAGE_OFF + STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFF = META_OFF + (TRANSPOSED ? STAGES * META_TILE_BYTES : 0);
     static constexpr int SMEM = BAR_OFF + 256;
 };
-static_assert(BwdLayout<0>::SMEM <= 232448 && BwdLayout<2>::SMEM <= 232448, "shared memory budget");
+static_assert(BwdLayout<0>::SMEM <= 232448 && BwdLayout<1>::SMEM <= 232448 && BwdLayout<2>::SMEM <= 232448, "shared memory budget");
 
 // {-lse, -dscale * c2, start, finish - start} per (head, node); nodes past T and nodes with an empty span get a
 // start no key index reaches
@@ -87,7 +86,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         return;
     }
     const uint32_t sA1 = smem_u32(smem) + L::A1_OFF, sA2 = smem_u32(smem) + L::A2_OFF, sStage = smem_u32(smem) + L::STAGE_OFF,
-                   sG = smem_u32(smem) + L::G_OFF, sMeta = smem_u32(smem) + L::META_OFF;
+                   sMeta = smem_u32(smem) + L::META_OFF;
     uint64_t *bars = (uint64_t *)(smem + L::BAR_OFF);
     const uint32_t res_full = smem_u32(bars), st_full0 = smem_u32(bars + 1), st_empty0 = smem_u32(bars + 4), s_full0 = smem_u32(bars + 7),
                    g_full0 = smem_u32(bars + 9), acc_ready0 = smem_u32(bars + 11);
@@ -178,8 +177,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             constexpr uint32_t idesc_s = umma_idesc_f16(TC_BN, false, false);
             constexpr uint32_t idesc_acc = umma_idesc_f16(TC_HD, false, true);
             const uint32_t tS = tmem_base + b * 256, tDP = tS + TC_BN, tACC = tS + 2 * TC_BN;
-            const uint64_t dA1 = umma_smem_desc(sA1 + b * Q_BYTES, 16, 1024), dA2 = umma_smem_desc(sA2 + b * Q_BYTES, 16, 1024),
-                           dG = umma_smem_desc(sG + b * P_BYTES, 16, 1024);
+            const uint64_t dA1 = umma_smem_desc(sA1 + b * Q_BYTES, 16, 1024), dA2 = umma_smem_desc(sA2 + b * Q_BYTES, 16, 1024);
             const uint32_t s_full = s_full0 + 8 * b, g_full = g_full0 + 8 * b, acc_ready = acc_ready0 + 8 * b;
             bool ok = mbar_wait(res_full, 0, abort_flag);
             int k = 0; // tiles of this block so far
@@ -203,10 +201,15 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                     if (!mbar_wait(g_full, k & 1, abort_flag))
                         break;
                     tc_fence_after();
-                    // ACC += G . B: 4 steps of 16 streamed rows; the streamed tile read MN-major (its 128 columns are
-                    // the output columns), 16 rows = 2048 bytes per step
+                    // ACC += G . B: 4 steps of 16 streamed rows.  G is read from tensor memory, where the compute warps
+                    // left it in place of the S values they consumed (fp16 pairs: streamed rows 0-15 in columns 0-7,
+                    // 16-31 in 8-15, 32-47 in 32-39, 48-63 in 40-47); the streamed tile is read MN-major (its 128
+                    // columns are the output columns), 16 rows = 2048 bytes per step.  The MMAs of one thread execute
+                    // in issue order, so the next tile's S product overwrites these columns only after this read.
                     const uint64_t dB = umma_smem_desc(MODE == 2 ? b2 : b1, KV_BYTES / 2, 1024);
-                    umma_f16_x4(tACC, dG, dB, idesc_acc, k > 0 ? 1u : 0u, 2u, 128u);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_f16_ts(tACC, tS + (kk >> 1) * 32 + (kk & 1) * 8, dB + (uint64_t)(kk * 128), idesc_acc, (k > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(acc_ready);
                     ++k;
                 }
@@ -231,7 +234,6 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             nlse_row = -p.lse[(size_t)rr * H + h];
             ndc_row = -p.dscale[(size_t)rr * H + h] * c2;
         }
-        uint8_t *grow = smem + L::G_OFF + b * P_BYTES + row * 128;
         bool ok = true;
         int k = 0;
         for (int j = 0; j < n; ++j) {
@@ -279,15 +281,16 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                     w = valid ? w : 0.f;
                     g[i] = NEED_DP ? w * fmaf(__uint_as_float(rp[i]), c2, ndc) : w;
                 }
+                // G replaces the S values this thread has just consumed: 16 fp16 values = 8 columns of its own lane
+                uint32_t packed[8];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const __half2 h0 = __floats2half2_rn(g[8 * c], g[8 * c + 1]), h1 = __floats2half2_rn(g[8 * c + 2], g[8 * c + 3]),
-                                  h2 = __floats2half2_rn(g[8 * c + 4], g[8 * c + 5]), h3 = __floats2half2_rn(g[8 * c + 6], g[8 * c + 7]);
-                    *(uint4 *)(grow + (((half * 4 + q16 * 2 + c) ^ (row & 7)) << 4)) =
-                        make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
+                for (int i = 0; i < 8; ++i) {
+                    const __half2 hv = __floats2half2_rn(g[2 * i], g[2 * i + 1]);
+                    packed[i] = *(const uint32_t *)&hv;
                 }
+                tmem_st8(tS + q16 * 8, packed);
             }
-            fence_proxy_async(); // generic-proxy writes of G become visible to the tensor core's async proxy
+            tmem_st_wait();
             tc_fence_before();
             mbar_arrive(g_full);
             ++k;
