@@ -87,6 +87,12 @@ struct ts2_model {
     int kind = KIND_E4M3;
     float s_act = 16.f;
     cudaStream_t stream = nullptr, comm_stream = nullptr;
+    // The optimizer and the requantiser are hundreds of small launches, one chain per matrix; the chains of different
+    // layers are independent and run on OPT_LANES streams forked from / joined to the main stream by events
+    static constexpr int OPT_LANES = 8;
+    cudaStream_t opt_stream[OPT_LANES] = {};
+    cudaEvent_t ev_opt_fork = nullptr, ev_opt_join[OPT_LANES] = {};
+    std::vector<int> mat_lane; // lane of every matrix: a layer's matrices share one (its scale vectors depend on all of them)
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr, ev_grads = nullptr, ev_reduced = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
     std::string error;
     std::vector<void *> allocs;
@@ -120,7 +126,8 @@ struct ts2_model {
     float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
-    float *opt_scratch = nullptr; // row_sum2 | row_scale | doubles
+    float *opt_scratch = nullptr; // per lane: row_sum2 | row_scale | doubles
+    size_t opt_scratch_stride = 0;
     int64_t max_rows = 0;
     BatchDev batch;
     void *pinned = nullptr;
@@ -320,19 +327,49 @@ void shapes_of(const ts2_model_descr *d, std::vector<std::pair<int64_t, int64_t>
 }
 
 // ---- requantisation of every matrix + the scale vectors derived from the matrix scales ----
-int requantize_all(ts2_model *m)
+// optimizer lanes: every lane stream waits for what the main stream has queued so far ...
+int opt_fork(ts2_model *m)
+{
+    TS2_CUDA(cudaEventRecord(m->ev_opt_fork, m->stream));
+    for (int i = 0; i < ts2_model::OPT_LANES; ++i)
+        TS2_CUDA(cudaStreamWaitEvent(m->opt_stream[i], m->ev_opt_fork, 0));
+    return TS2_OK;
+}
+// ... and the main stream waits for all lanes
+int opt_join(ts2_model *m)
+{
+    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
+        TS2_CUDA(cudaEventRecord(m->ev_opt_join[i], m->opt_stream[i]));
+        TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_opt_join[i], 0));
+    }
+    return TS2_OK;
+}
+// stream and scratch (doubles behind the two float vectors) of a matrix's lane
+static Ctx lane_ctx(ts2_model *m, int mat, float **scratch)
 {
     Ctx c = ctx_of(m);
+    const int lane = m->mat_lane[mat];
+    c.stream = m->opt_stream[lane];
+    *scratch = m->opt_scratch + lane * m->opt_scratch_stride + 2 * m->max_rows;
+    return c;
+}
+
+// between opt_fork and opt_join
+int requantize_all(ts2_model *m)
+{
     const int D = m->D;
-    float *scratch = m->opt_scratch + 2 * m->max_rows; // doubles live behind the two float vectors
+    float *scratch = nullptr;
+    Ctx c = lane_ctx(m, 0, &scratch);
     // embedding: always fp16 (TEmbedFloat, cfg_precision.h:62)
     M_TRY(requantize(c, m->mats[0].w, D, m->mats[0].y, 1, m->embed16, D, nullptr, 0, m->mats[0].sko, scratch, false));
     // final layer: fast copy for the logits, fp16 transposed copy of the same quantized values for dX
+    c = lane_ctx(m, 1, &scratch);
     M_TRY(requantize(c, m->mats[1].w, D, m->V, m->ft, m->Wf, D, m->WfT16, m->V, m->mats[1].sko, scratch, m->ft == 0));
     const size_t fs = fast_size(m);
     const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
     for (Layer &ly : m->layers) {
         const int W = ly.wide, n = ly.ncat;
+        c = lane_ctx(m, ly.mat0, &scratch);
         if (ly.type == TS2_LAYER_MOE) {
             const int E = m->E, X = m->X;
             Matrix &me = m->mats[ly.mat0], &mg = m->mats[ly.mat0 + 1], &mc = m->mats[ly.mat0 + 2], &ms = m->mats[ly.mat0 + 3];
@@ -543,7 +580,8 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     M_TRY(dalloc(m, &m->ginv, 4));
     m->fscale = m->ginv + 1;
     m->logp = m->ginv + 2;
-    M_TRY(dalloc(m, &m->opt_scratch, (size_t)m->max_rows * 4 + 16));
+    m->opt_scratch_stride = (size_t)m->max_rows * 4 + 16;
+    M_TRY(dalloc(m, &m->opt_scratch, m->opt_scratch_stride * ts2_model::OPT_LANES));
     // batch
     BatchDev &b = m->batch;
     b.label_cap = (size_t)T * 4;
@@ -581,7 +619,16 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
 
     Ctx c = ctx_of(m);
     M_TRY(fill_rope(c, m->rope, T));
+    m->mat_lane.assign(m->mats.size(), 0);
+    m->mat_lane[1] = 1 % ts2_model::OPT_LANES;
+    for (size_t l = 0; l < m->layers.size(); ++l) {
+        const size_t end = l + 1 < m->layers.size() ? (size_t)m->layers[l + 1].mat0 : m->mats.size();
+        for (size_t i = m->layers[l].mat0; i < end; ++i)
+            m->mat_lane[i] = (int)((l + 2) % ts2_model::OPT_LANES);
+    }
+    M_TRY(opt_fork(m));
     M_TRY(requantize_all(m));
+    M_TRY(opt_join(m));
     TS2_CUDA(cudaStreamSynchronize(m->stream));
     return TS2_OK;
 }
@@ -819,7 +866,6 @@ int backward(ts2_model *m)
 
 int apply(ts2_model *m, const ts2_training_step *step)
 {
-    Ctx c = ctx_of(m);
     if (m->comm && m->world > 1) {
         // data-parallel sum of the flat gradient; ordered after the backward pass by an event
         TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
@@ -830,7 +876,12 @@ int apply(ts2_model *m, const ts2_training_step *step)
         TS2_CUDA(cudaEventRecord(m->ev_reduced, m->comm_stream));
         TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_reduced, 0));
     }
-    for (Matrix &mt : m->mats) {
+    M_TRY(opt_fork(m));
+    for (size_t mi = 0; mi < m->mats.size(); ++mi) {
+        Matrix &mt = m->mats[mi];
+        float *lane_doubles = nullptr;
+        Ctx c = lane_ctx(m, (int)mi, &lane_doubles);
+        float *lane_scratch = lane_doubles - 2 * m->max_rows;
         OptMatrix o;
         o.w = mt.w;
         o.avg_grad = mt.avg;
@@ -841,12 +892,13 @@ int apply(ts2_model *m, const ts2_training_step *step)
         o.row_disp_size = mt.row_disp_size;
         o.sum_weight = mt.sum_weight;
         o.sparsity = mt.sparsity;
-        o.row_sum2 = m->opt_scratch;
-        o.row_scale = m->opt_scratch + m->max_rows;
+        o.row_sum2 = lane_scratch;
+        o.row_scale = lane_scratch + m->max_rows;
         o.w_sum2 = nullptr;
         M_TRY(apply_gradient(c, o, *step));
     }
     M_TRY(requantize_all(m));
+    M_TRY(opt_join(m));
     return TS2_OK;
 }
 
@@ -1013,6 +1065,11 @@ int ts2_create(const ts2_model_descr *descr, const ts2_matrix_view *mats, int n_
     m->max_nodes = (max_nodes + 127) / 128 * 128;
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
+        cudaStreamCreateWithFlags(&m->opt_stream[i], cudaStreamNonBlocking);
+        cudaEventCreateWithFlags(&m->ev_opt_join[i], cudaEventDisableTiming);
+    }
+    cudaEventCreateWithFlags(&m->ev_opt_fork, cudaEventDisableTiming);
     cudaEventCreate(&m->ev_start);
     cudaEventCreate(&m->ev_stop);
     cudaEventCreate(&m->ev_t0);
@@ -1056,6 +1113,14 @@ void ts2_destroy(ts2_model *m)
         cudaStreamDestroy(m->stream);
     if (m->comm_stream)
         cudaStreamDestroy(m->comm_stream);
+    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
+        if (m->opt_stream[i])
+            cudaStreamDestroy(m->opt_stream[i]);
+        if (m->ev_opt_join[i])
+            cudaEventDestroy(m->ev_opt_join[i]);
+    }
+    if (m->ev_opt_fork)
+        cudaEventDestroy(m->ev_opt_fork);
     delete m;
 }
 
@@ -1170,7 +1235,9 @@ int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_ma
         TS2_CUDA(cudaMemcpy(what == TS2_PARAM_WEIGHTS ? mt.w : mt.avg, mats[i].data, (size_t)mt.x * mt.y * 4, cudaMemcpyHostToDevice));
     }
     if (what == TS2_PARAM_WEIGHTS) {
+        M_TRY(opt_fork(m));
         M_TRY(requantize_all(m));
+        M_TRY(opt_join(m));
         M_TRY(wait_stream(m));
     }
     return TS2_OK;
