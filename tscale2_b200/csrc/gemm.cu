@@ -350,6 +350,16 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
             const int m0 = un.m0, n0 = un.n0;
             uint8_t *const Cg = (uint8_t *)p.C + un.c_off * ((p.out_kind == TS2_OUT_F32 || p.out_kind == TS2_OUT_F32_ADD) ? 4 : 2);
             const float *const Cin = p.c_in + un.c_off;
+            if (p.out_kind == TS2_OUT_F32_ADD && p.splits == 1) {
+                // the residual input of this tile is known long before its accumulator is: pull this thread's 128-byte
+                // pieces into L2 while the main loop runs, so that the loads below do not pay the HBM latency per chunk
+                const long long prow = m0 + quarter * 32 + lane;
+                if (prow < p.M) {
+                    for (int c = c_begin; c < c_end; ++c)
+                        if (n0 + c * 32 < p.N)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(Cin + prow * p.ldc + n0 + c * 32));
+                }
+            }
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag))
                 break;
             tc_fence_after();
@@ -506,6 +516,17 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 v[i] *= rs;
+                        }
+                        if (p.out_kind == TS2_OUT_F32_ADD && row < p.M) {
+                            // accumulate form: the residual input comes by plain loads (this thread's 128-byte piece of
+                            // its row, prefetched into L2 above); the sum leaves through the staging blocks like a plain
+                            // output, so that HBM sees whole lines instead of 16-byte pieces of 32 rows per store
+                            const float4 *src = (const float4 *)(Cin + row * p.ldc + col);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float4 o = src[i];
+                                v[4 * i] += o.x, v[4 * i + 1] += o.y, v[4 * i + 2] += o.z, v[4 * i + 3] += o.w;
+                            }
                         }
                     }
                     // Two 2 KB blocks per warp (32 rows x 64 bytes, 64-byte swizzle: 16-byte chunk j of row r sits at
@@ -967,11 +988,11 @@ int gemm(const GemmArgs &a)
     p.act_scale = a.epi.act_scale;
     p.act_mult = a.epi.act_mult;
     p.act_f16 = a.epi.act_f16 ? 1 : 0;
-    // coalesced TMA-store epilogue for plain stores (the accumulate form reads C anyway; split units go to the workspace;
+    // coalesced TMA-store epilogue (the accumulate form adds its residual input first; split units go to the workspace;
     // per-group C offsets of mode 2 are not expressible as one 2-D map)
     CUtensorMap tmC = tmA;
     p.tma_store = 0;
-    if (pl.splits == 1 && a.group_mode != 2 && a.epi.out_kind != TS2_OUT_F32_ADD) {
+    if (pl.splits == 1 && a.group_mode != 2) {
         if ((rc = make_tmap(&tmC, a.C, out_es, a.N, a.M, a.ldc, 32, 64)) != TS2_OK)
             return rc;
         p.tma_store = 1;
