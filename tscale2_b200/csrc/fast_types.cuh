@@ -76,6 +76,19 @@ __device__ __forceinline__ float lolu_mult(float gate)
     return arg < -20.f ? 0.f : (arg > 20.f ? 1.f : r);
 }
 
+// The same multiplier where the result is stored as e4m3 (FT == 0): sigmoid(2 g) = 0.5 + 0.5 tanh(g) with the
+// one-instruction tanh (relative error 2^-11, far below the e4m3 step); the fp16 pipeline keeps the exact form.
+template <int FT>
+__device__ __forceinline__ float lolu_mult_ft(float gate)
+{
+    if (FT == 0) {
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(gate));
+        return fmaf(th, 0.5f, 0.5f);
+    }
+    return lolu_mult(gate);
+}
+
 // scale of one 128-wide tile: sqrt(128 / sum of squares), 0 for an all-zero tile
 __device__ __forceinline__ float tile_scale(float sum2) { return sum2 == 0.f ? 0.f : 11.3137085f * rsqrtf(sum2); }
 

@@ -38,7 +38,6 @@ int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, vo
 
 // FFN activation (LoLU + tile-norm of the wide vector), TFFLayer::ComputeForward layer_ffn.cu:190-211.
 // wg: [T][2F] fp16 = [wide | gate]; what: normalized wide fp16 [T][F]; wscale [T][F/128]; rg fast [T][F]
-int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, float *wscale, void *rg);
 // BackpropLoLU + NormalizeStateBackward of the wide vector (layer_ffn.cu:232-236): d2 fast [T][2F] = [dwide | dgate]
 // what: normalised wide values, row pitch what_ld (the wide half of wg when the contraction's epilogue wrote them there)
 int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, int what_ld, const float *wscale, int T, int F,

@@ -244,56 +244,7 @@ int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, vo
 }
 
 // ---------------------------------------------------------------------------------
-template <int FT>
-__global__ void ffn_act_forward_kernel(const __half *__restrict__ wg, int T, int F, float s_act, __half *__restrict__ what,
-                                       float *__restrict__ wscale, void *__restrict__ rg)
-{
-    const int tiles = F / TILE;
-    constexpr int R = 2;
-    WARP_BATCH_LOOP((long long)T * tiles, R)
-    {
-        float4 wide[R], gate[R];
-        size_t t[R];
-        int tile[R];
-        bool ok[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const unsigned item = base + r * wstride;
-            ok[r] = item < total_items;
-            t[r] = ok[r] ? item / tiles : 0;
-            tile[r] = ok[r] ? (int)(item % tiles) : 0;
-            const int off = tile[r] * TILE + lane * 4;
-            wide[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + off) : make_float4(0, 0, 0, 0);
-            gate[r] = ok[r] ? load_half4(wg + t[r] * 2 * F + F + off) : make_float4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (!ok[r])
-                continue;
-            const int off = tile[r] * TILE + lane * 4;
-            const float scale = tile_scale(warp_sum(dot4(wide[r], wide[r])));
-            const float4 wn = scale4(wide[r], scale);
-            store_half4(what + t[r] * F + off, wn);
-            if (lane == 0)
-                wscale[t[r] * tiles + tile[r]] = scale;
-            const float4 res = make_float4(lolu_mult(gate[r].x) * wn.x, lolu_mult(gate[r].y) * wn.y, lolu_mult(gate[r].z) * wn.z,
-                                           lolu_mult(gate[r].w) * wn.w);
-            Fast<FT>::store4(rg, t[r] * F + off, scale4(res, s_act));
-        }
-    }
-}
-
-int ffn_act_forward(const Ctx &c, const __half *wg, int T, int F, __half *what, float *wscale, void *rg)
-{
-    const int grid = grid_for(c, (long long)T * (F / TILE));
-    if (c.ft == 0)
-        ffn_act_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(wg, T, F, c.s_act, what, wscale, rg);
-    else
-        ffn_act_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(wg, T, F, c.s_act, what, wscale, rg);
-    TS2_CHECK_LAUNCH();
-    return TS2_OK;
-}
-
+// (the forward FFN activation lives in the contraction's gated epilogue, gemm.cu)
 template <int FT>
 __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __half *__restrict__ wg, const __half *__restrict__ what,
                                         int what_ld, const float *__restrict__ wscale, int T, int F, void *__restrict__ d2)
@@ -323,7 +274,7 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
         for (int r = 0; r < R; ++r) {
             if (!ok[r])
                 continue;
-            const float4 m = make_float4(lolu_mult(gate[r].x), lolu_mult(gate[r].y), lolu_mult(gate[r].z), lolu_mult(gate[r].w));
+            const float4 m = make_float4(lolu_mult_ft<FT>(gate[r].x), lolu_mult_ft<FT>(gate[r].y), lolu_mult_ft<FT>(gate[r].z), lolu_mult_ft<FT>(gate[r].w));
             const float4 dgate = make_float4(g[r].x * wn[r].x * m.x * (1 - m.x) * 2.f, g[r].y * wn[r].y * m.y * (1 - m.y) * 2.f,
                                              g[r].z * wn[r].z * m.z * (1 - m.z) * 2.f, g[r].w * wn[r].w * m.w * (1 - m.w) * 2.f);
             const float4 dwn = make_float4(g[r].x * m.x, g[r].y * m.y, g[r].z * m.z, g[r].w * m.w);
@@ -376,8 +327,8 @@ __global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const _
         for (int r = 0; r < R; ++r) {
             if (!ok[r])
                 continue;
-            const float4 res = make_float4(lolu_mult(gate[r].x) * ov[r].x, lolu_mult(gate[r].y) * ov[r].y, lolu_mult(gate[r].z) * ov[r].z,
-                                           lolu_mult(gate[r].w) * ov[r].w);
+            const float4 res = make_float4(lolu_mult_ft<FT>(gate[r].x) * ov[r].x, lolu_mult_ft<FT>(gate[r].y) * ov[r].y,
+                                           lolu_mult_ft<FT>(gate[r].z) * ov[r].z, lolu_mult_ft<FT>(gate[r].w) * ov[r].w);
             Fast<FT>::store4(rg, t[r] * Q + off[r], scale4(res, s_act));
         }
     }
@@ -422,7 +373,7 @@ __global__ void att_gate_backward_kernel(const __half *__restrict__ drg, const _
             if (!ok[r])
                 continue;
             const int off = h[r] * TILE + lane * 4;
-            const float4 m = make_float4(lolu_mult(gate[r].x), lolu_mult(gate[r].y), lolu_mult(gate[r].z), lolu_mult(gate[r].w));
+            const float4 m = make_float4(lolu_mult_ft<FT>(gate[r].x), lolu_mult_ft<FT>(gate[r].y), lolu_mult_ft<FT>(gate[r].z), lolu_mult_ft<FT>(gate[r].w));
             const float4 dgate = make_float4(g[r].x * ov[r].x * m.x * (1 - m.x) * 2.f, g[r].y * ov[r].y * m.y * (1 - m.y) * 2.f,
                                              g[r].z * ov[r].z * m.z * (1 - m.z) * 2.f, g[r].w * ov[r].w * m.w * (1 - m.w) * 2.f);
             const float4 dov = make_float4(g[r].x * m.x, g[r].y * m.y, g[r].z * m.z, g[r].w * m.w);
