@@ -237,6 +237,9 @@ def main():
     e2e_ms = model.timer_end()
     barrier()
 
+    if not np.isfinite(loss):
+        # a step that produced a non-finite loss did not do the work it is timed for: no number
+        raise SystemExit(f"bench: training loss is {loss} after the timed steps; refusing to report a throughput")
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

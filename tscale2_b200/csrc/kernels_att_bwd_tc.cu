@@ -194,6 +194,11 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                     umma_f16_x4(tS, dA1, dB1, idesc_s, 0u, 2u, 2u);
                     umma_f16_x4(tS, dA1 + (Q_BYTES / 2 >> 4), dB1 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
                     if (NEED_DP) {
+                        // the dP columns still hold G of the previous tile, the A operand of its second MMA: that MMA
+                        // must be complete before these may write there (it was issued eight MMAs ago, so this wait
+                        // is normally over before it starts)
+                        if (k > 0 && !mbar_wait(acc_ready, (k - 1) & 1, abort_flag))
+                            break;
                         umma_f16_x4(tDP, dA2, dB2, idesc_s, 0u, 2u, 2u);
                         umma_f16_x4(tDP, dA2 + (Q_BYTES / 2 >> 4), dB2 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
                     }
@@ -202,14 +207,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                         break;
                     tc_fence_after();
                     // ACC += G . B: 4 steps of 16 streamed rows.  G is read from tensor memory, where the compute warps
-                    // left it in place of the S values they consumed (fp16 pairs: streamed rows 0-15 in columns 0-7,
-                    // 16-31 in 8-15, 32-47 in 32-39, 48-63 in 40-47); the streamed tile is read MN-major (its 128
-                    // columns are the output columns), 16 rows = 2048 bytes per step.  The MMAs of one thread execute
-                    // in issue order, so the next tile's S product overwrites these columns only after this read.
+                    // left it in the dP columns (in place of the dP values they consumed; mode 2 has no dP and the
+                    // columns are free): fp16 pairs, streamed rows 0-15 in columns 0-7, 16-31 in 8-15, 32-47 in 32-39,
+                    // 48-63 in 40-47.  The streamed tile is read MN-major (its 128 columns are the output columns),
+                    // 16 rows = 2048 bytes per step.
                     const uint64_t dB = umma_smem_desc(MODE == 2 ? b2 : b1, KV_BYTES / 2, 1024);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_f16_ts(tACC, tS + (kk >> 1) * 32 + (kk & 1) * 8, dB + (uint64_t)(kk * 128), idesc_acc, (k > 0 || kk > 0) ? 1u : 0u);
+                        umma_f16_ts(tACC, tDP + (kk >> 1) * 32 + (kk & 1) * 8, dB + (uint64_t)(kk * 128), idesc_acc, (k > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(acc_ready);
                     ++k;
                 }
@@ -281,14 +286,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                     w = valid ? w : 0.f;
                     g[i] = NEED_DP ? w * fmaf(__uint_as_float(rp[i]), c2, ndc) : w;
                 }
-                // G replaces the S values this thread has just consumed: 16 fp16 values = 8 columns of its own lane
+                // G goes where this thread's dP values were (its own lane, its own columns): 16 fp16 values = 8 columns
                 uint32_t packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const __half2 hv = __floats2half2_rn(g[2 * i], g[2 * i + 1]);
                     packed[i] = *(const uint32_t *)&hv;
                 }
-                tmem_st8(tS + q16 * 8, packed);
+                tmem_st8(tDP + q16 * 8, packed);
             }
             tmem_st_wait();
             tc_fence_before();

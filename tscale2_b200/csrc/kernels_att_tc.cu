@@ -11,10 +11,10 @@
 //              product of tile j+1 runs while tile j is in the softmax), later O += P . V
 //   warps 2-9  softmax: two warps per TMEM lane quarter, thread = (node row, 32 of the tile's 64 keys);
 //              the pair agrees on the row maximum through shared memory (rounded up to bf16, so both
-//              use the same reference), leaves P (fp16) in tensor memory in place of the S values it
-//              consumed (the A operand of the second MMA) and rescales O in TMEM only when a row's
-//              maximum grew by more than 8 (2^8 headroom in fp16 P and fp32 sums), which keeps
-//              tcgen05.ld/st of O off the common path
+//              use the same reference), writes P (fp16) into a swizzled K-major shared-memory tile
+//              for the second MMA and rescales O in TMEM only when a row's maximum grew by more
+//              than 8 (2^8 headroom in fp16 P and fp32 sums), which keeps tcgen05.ld/st of O off
+//              the common path
 // The zero "sink" vector of the reference is the initial state m = 0, l = 1.
 // Two CTAs fit an SM (112 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps
 // the other's MMAs.  Every wait is bounded (see mbar_wait); a give-up raises the status word.
@@ -23,9 +23,9 @@
 namespace ts2 {
 
 static constexpr int TC_THREADS = 320;
-// 112 KB of tiles + 128 B of barriers: two CTAs per SM (2 x (114816 + 1024 reserved) <= 228 KB)
+// 112 KB of tiles + 128 B of barriers + 1 KB of exchange slots: two CTAs per SM (2 x (115840 + 1024 reserved) <= 228 KB)
 static constexpr int FWD_XCH_OFF = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 128; // row maxima of the two column halves, bf16
-static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * TC_BM * 2;
+static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * 2 * TC_BM * 2; // two sets, used in turn
 
 struct AttTcParams {
     int T, H;
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             atomicOr(p.status, TS2_STATUS_BAD_ARG);
         return;
     }
-    const uint32_t sQ = smem_u32(smem), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES;
+    const uint32_t sQ = smem_u32(smem), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES, sP = sV + 2 * KV_BYTES;
     uint64_t *bars = (uint64_t *)(smem + Q_BYTES + 4 * KV_BYTES + P_BYTES);
     const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 3), v_full0 = smem_u32(bars + 5),
                    v_empty0 = smem_u32(bars + 7), s_full0 = smem_u32(bars + 9), p_full = smem_u32(bars + 11), o_ready = smem_u32(bars + 12);
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             constexpr uint32_t idesc_pv = umma_idesc_f16(TC_HD, false, true);
             // descriptors differ from these bases only in the 16-byte-granular start address (the low field; shared
             // memory addresses stay below 2^18, so adding to it never carries into the next field)
-            const uint64_t dq = umma_smem_desc(sQ, 16, 1024), dk = umma_smem_desc(sK, 16, 1024),
+            const uint64_t dq = umma_smem_desc(sQ, 16, 1024), dk = umma_smem_desc(sK, 16, 1024), dp = umma_smem_desc(sP, 16, 1024),
                            dv = umma_smem_desc(sV, KV_BYTES / 2, 1024);
             auto issue_qk = [&](int jj) { // S[jj & 1] = Q . K(jj)^T: 8 steps of 16 head dims; two 64-dim atoms per operand
                 const uint64_t kb = dk + (uint64_t)((jj & 1) * (KV_BYTES >> 4));
@@ -173,9 +173,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 // O += P . V: 4 steps of 16 keys; V tile is MN-major for this product (dims contiguous)
                 const uint64_t vb = dv + (uint64_t)(st * (KV_BYTES >> 4));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) // P from tensor memory: keys 0-15 in columns 0-7 of the S buffer, 16-31 in 8-15, 32-47 in 32-39, 48-63 in 40-47
-                    umma_f16_ts(tmem_O, tmem_S + (j & 1) * TC_BN + (k >> 1) * 32 + (k & 1) * 8, vb + (uint64_t)(k * 128), idesc_pv,
-                                (j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)
+                    umma_f16(tmem_O, dp + (uint64_t)(k * 2), vb + (uint64_t)(k * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                 tc_commit(v_empty0 + 8 * st);
                 tc_commit(o_ready);
             }
@@ -187,7 +186,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int st_row = t < T ? p.span_start[t] : 0, fi_row = t < T ? p.span_finish[t] : -1;
         const float ds = att_dot_scale_tc(), slope = p.slope;
-        __nv_bfloat16 *xch = (__nv_bfloat16 *)(smem + FWD_XCH_OFF); // [half][row]
+        __nv_bfloat16 *xch_all = (__nv_bfloat16 *)(smem + FWD_XCH_OFF); // [tile parity][half][row]
         float m_used = 0.f, l = half == 0 ? 1.f : 0.f; // the zero vector of weight 2^-m, counted once per row
         bool ok = true;
         for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
@@ -233,9 +232,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             }
             // agree on the row maximum with the warp that holds the other 32 keys; rounding up to bf16 makes the
             // exchanged value the reference both use (a reference above the true maximum only makes P smaller).
-            // The slot is free again by the time it is rewritten: the next S tile is issued only after all 256
-            // threads arrived at p_full, which each does after reading its partner's slot.
+            // Two sets used in turn: a warp that runs ahead into the next tile (S is double-buffered) writes the other
+            // set, and it cannot get to the tile after that before its partner has passed the next pair barrier.
             const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            __nv_bfloat16 *xch = xch_all + (j & 1) * 2 * TC_BM;
             xch[half * TC_BM + row] = mine;
             pair_barrier(quarter);
             const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(half ^ 1) * TC_BM + row]));
@@ -258,14 +258,15 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 sum4[i & 3] += pv;
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            // the previous P . V must have finished before P is overwritten or O is touched; this wait is also what keeps
+            // a warp from arriving at p_full for tile j + 1 before every warp has arrived for tile j (p_full counts
+            // 256 arrivals per phase, and with two S buffers a fast warp could otherwise get there)
+            if (ok && j > 0)
+                ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1, abort_flag));
             if (!ok)
                 continue;
+            tc_fence_after();
             if (warp_need && j > 0) {
-                // the previous P . V must have finished before O is touched
-                ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1, abort_flag));
-                if (!ok)
-                    continue;
-                tc_fence_after();
 #pragma unroll 1
                 for (int c = 2 * half; c < 2 * half + 2; ++c) { // each warp of the pair rescales 64 of the 128 columns
                     uint32_t r[32];
@@ -278,20 +279,18 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 }
                 tmem_st_wait();
             }
-            // P replaces the S values this thread has consumed: 32 fp16 values = 16 columns of its own lane in the same
-            // S buffer, from where the second MMA reads its A operand (no shared-memory tile, no proxy fence).  The
-            // buffer is overwritten by the S product of tile j + 2, issued after this tile's P . V by the same thread.
+            // P row -> swizzled K-major tile: 8 chunks of 8 halves, chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)
+            {
+                uint8_t *prow = smem + Q_BYTES + 4 * KV_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t packed[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const __half2 hv = __floats2half2_rn(s[16 * c + 2 * i], s[16 * c + 2 * i + 1]);
-                    packed[i] = *(const uint32_t *)&hv;
+                for (int c = 0; c < 4; ++c) {
+                    __half2 h0 = __floats2half2_rn(s[8 * c], s[8 * c + 1]), h1 = __floats2half2_rn(s[8 * c + 2], s[8 * c + 3]),
+                            h2 = __floats2half2_rn(s[8 * c + 4], s[8 * c + 5]), h3 = __floats2half2_rn(s[8 * c + 6], s[8 * c + 7]);
+                    *(uint4 *)(prow + (((half * 4 + c) ^ (row & 7)) << 4)) =
+                        make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                 }
-                tmem_st8(tmem_S + lane_addr + (j & 1) * TC_BN + half * 32 + c * 8, packed);
             }
-            tmem_st_wait();
+            fence_proxy_async(); // generic-proxy writes of P become visible to the tensor core's async proxy
             tc_fence_before();
             mbar_arrive(p_full);
         }
