@@ -149,3 +149,25 @@ def test_errors_are_codes_not_aborts():
     lib = capi.load_library()
     rc = lib.ts2_create(C.byref(descr), host.matrix_views(rnn_mats), len(rnn_mats), None, 0, 128, C.byref(h))
     assert rc == capi.TS2_ERR_UNSUPPORTED
+
+
+def test_many_waves_step_is_finite_and_agrees_between_precisions():
+    """16384 nodes (hundreds of CTAs per kernel, several waves, up to 8 attention tiles per row block): the training
+    error of the e4m3 and the fp16 pipelines must both be finite and close, before and after three applied steps.
+    The oracle cases above are one wave of a few CTAs; an ordering bug between warps or CTAs only shows at size."""
+    errs = {}
+    for precision in (capi.PREC_FP8, capi.PREC_F16):
+        spec = host.ModelSpec(dim=256, head_count=2, ffn_tiles=8, vocab=4096, attention_widths=[512],
+                              precision=precision).add_blocks(2)
+        mats = host.init_weights(spec, 3)
+        batch = host.synthetic_batch(spec, 32, 512, 4)
+        model = Model(spec, mats, batch.node_count)
+        model.set_batch(batch)
+        out = []
+        for i in range(4):
+            model.backprop(host.training_step(rate=0.01, iteration=i), apply=True)
+            out.append(model.avg_train_err())
+        errs[precision] = out
+    a, b = np.array(errs[capi.PREC_FP8]), np.array(errs[capi.PREC_F16])
+    assert np.isfinite(a).all() and np.isfinite(b).all(), (a, b)
+    assert np.abs(a - b).max() < 0.05, (a, b)

@@ -23,9 +23,9 @@
 namespace ts2 {
 
 static constexpr int TC_THREADS = 320;
-// 112 KB of tiles + 128 B of barriers + 1 KB of exchange slots: two CTAs per SM (2 x (115840 + 1024 reserved) <= 228 KB)
+// 112 KB of tiles + 128 B of barriers + 512 B of exchange slots: two CTAs per SM (2 x (115328 + 1024 reserved) <= 228 KB)
 static constexpr int FWD_XCH_OFF = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 128; // row maxima of the two column halves, bf16
-static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * 2 * TC_BM * 2; // two sets, used in turn
+static constexpr int FWD_SMEM = FWD_XCH_OFF + 2 * TC_BM * 2;
 
 struct AttTcParams {
     int T, H;
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int st_row = t < T ? p.span_start[t] : 0, fi_row = t < T ? p.span_finish[t] : -1;
         const float ds = att_dot_scale_tc(), slope = p.slope;
-        __nv_bfloat16 *xch_all = (__nv_bfloat16 *)(smem + FWD_XCH_OFF); // [tile parity][half][row]
+        __nv_bfloat16 *xch = (__nv_bfloat16 *)(smem + FWD_XCH_OFF); // [half][row]
         float m_used = 0.f, l = half == 0 ? 1.f : 0.f; // the zero vector of weight 2^-m, counted once per row
         bool ok = true;
         for (int tile = tile0, j = 0; tile <= tile1; ++tile, ++j) {
@@ -194,6 +194,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             // tile, but touches neither TMEM nor the P tile any more
             if (ok)
                 ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag));
+            // S is double-buffered, so a warp that is done with tile j - 1 may find this tile's S ready before a slower
+            // warp has finished tile j - 1.  It goes on only when all 256 threads have arrived at p_full for that tile:
+            // then its partner has read the exchange slot it is about to rewrite, and its own arrival below cannot be
+            // counted for the previous phase.  (The phase cannot have completed without this thread's own arrival, so
+            // the parity test is unambiguous.)
+            if (ok && j > 0)
+                ok = __all_sync(0xffffffffu, mbar_wait(p_full, (j - 1) & 1, abort_flag));
             tc_fence_after();
             float s[32];
             if (ok) {
@@ -232,10 +239,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             }
             // agree on the row maximum with the warp that holds the other 32 keys; rounding up to bf16 makes the
             // exchanged value the reference both use (a reference above the true maximum only makes P smaller).
-            // Two sets used in turn: a warp that runs ahead into the next tile (S is double-buffered) writes the other
-            // set, and it cannot get to the tile after that before its partner has passed the next pair barrier.
+            // The slot is free: every thread has arrived at p_full for the previous tile (waited for above), which each
+            // does after reading its partner's slot.
             const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
-            __nv_bfloat16 *xch = xch_all + (j & 1) * 2 * TC_BM;
             xch[half * TC_BM + row] = mine;
             pair_barrier(quarter);
             const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(half ^ 1) * TC_BM + row]));
@@ -258,9 +264,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 sum4[i & 3] += pv;
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            // the previous P . V must have finished before P is overwritten or O is touched; this wait is also what keeps
-            // a warp from arriving at p_full for tile j + 1 before every warp has arrived for tile j (p_full counts
-            // 256 arrivals per phase, and with two S buffers a fast warp could otherwise get there)
+            // the previous P . V must have finished before P is overwritten or O is touched
             if (ok && j > 0)
                 ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1, abort_flag));
             if (!ok)
