@@ -34,7 +34,7 @@ WORKLOADS = {
 
 
 # average DRAM bytes per contraction launch from one ncu capture of a whole step (see profiles/)
-NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH = {("c3_dense12_d768", "fp8"): 510758939}
+NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH = {("c3_dense12_d768", "fp8"): 533793211}
 
 
 def make_spec(w, precision):
