@@ -133,6 +133,7 @@ struct ts2_model {
     void *pinned = nullptr;
     size_t pinned_bytes = 0;
     bool grads_dirty = false; // the flat gradient holds an accumulated, not yet applied gradient
+    bool reduce_in_backward = false; // this backward pass is followed by apply(): all-reduce every layer's gradient as soon as it is complete
     bool debug_taps = false;
     float *grad_taps = nullptr;
     float last_ms = 0;
@@ -750,6 +751,22 @@ int tap_gradient(ts2_model *m, int boundary)
     return TS2_OK;
 }
 
+// data-parallel sum of the gradients of matrices [m0, m1) (contiguous in the flat buffer) on the communication
+// stream, ordered after what the main stream has queued so far; the backward pass goes on meanwhile
+static int reduce_matrices(ts2_model *m, int m0, int m1)
+{
+    if (!m->reduce_in_backward)
+        return TS2_OK;
+    const size_t off = m->mats[m0].offset;
+    const size_t end = m1 < (int)m->mats.size() ? m->mats[m1].offset : m->total_params;
+    TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
+    TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
+    ncclResult_t r = ncclAllReduce(m->grad_flat + off, m->grad_flat + off, end - off, ncclFloat, ncclSum, m->comm, m->comm_stream);
+    if (r != ncclSuccess)
+        return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+    return TS2_OK;
+}
+
 int backward(ts2_model *m)
 {
     Ctx c = ctx_of(m);
@@ -758,6 +775,7 @@ int backward(ts2_model *m)
     const bool tune_layers = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_LAYERS);
     TS2_CUDA(cudaMemsetAsync(m->absmax, 0, (L + 2) * 4, m->stream));
     M_TRY(final_layer(m, true));
+    M_TRY(reduce_matrices(m, 1, 2));
     M_TRY(tilenorm_backward(c, m->states[L], m->dn, nullptr, 1.f, T, D, m->g, false, m->absmax + L));
     M_TRY(tap_gradient(m, L));
     for (int l = L - 1; l >= 0; --l) {
@@ -812,6 +830,7 @@ int backward(ts2_model *m)
                 M_TRY(gemm_k_grouped(m, ly, X, D, rows, (const uint8_t *)m->dcat + (size_t)X * fs, 2 * X, ly.n_rows, D,
                                      m->mats[ly.mat0 + 1].grad, (int64_t)X * D, e5));
             }
+            M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
             M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
             M_TRY(tap_gradient(m, l));
             continue;
@@ -856,23 +875,28 @@ int backward(ts2_model *m)
             e5.out_kind = TS2_OUT_F32_ADD;
             M_TRY(gemm_dw(m, m->kind, C, D, T, m->dcat, C, ly.n_fast, D, m->mats[ly.mat0].grad, e5));
         }
+        M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
         M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
         M_TRY(tap_gradient(m, l));
     }
     if (!(m->descr.flags & TS2_MPF_DISABLE_TUNE_EMBED))
         M_TRY(embed_backward(c, m->g, b.label_arr, b.label_ptr, T, D, m->mats[0].grad));
+    M_TRY(reduce_matrices(m, 0, 1));
     return TS2_OK;
 }
 
 int apply(ts2_model *m, const ts2_training_step *step)
 {
     if (m->comm && m->world > 1) {
-        // data-parallel sum of the flat gradient; ordered after the backward pass by an event
-        TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
-        TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
-        ncclResult_t r = ncclAllReduce(m->grad_flat, m->grad_flat, m->total_params, ncclFloat, ncclSum, m->comm, m->comm_stream);
-        if (r != ncclSuccess)
-            return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+        // data-parallel sum of the gradient: queued per layer on the communication stream during the backward pass
+        // (reduce_matrices), so that only the last pieces are still in flight here
+        if (!m->reduce_in_backward) {
+            TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
+            TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
+            ncclResult_t r = ncclAllReduce(m->grad_flat, m->grad_flat, m->total_params, ncclFloat, ncclSum, m->comm, m->comm_stream);
+            if (r != ncclSuccess)
+                return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+        }
         TS2_CUDA(cudaEventRecord(m->ev_reduced, m->comm_stream));
         TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_reduced, 0));
     }
@@ -1153,11 +1177,20 @@ int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model)
     if (!m->grads_dirty)
         TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, m->total_params * 4, m->stream));
     M_TRY(forward(m));
-    M_TRY(backward(m));
+    // an accumulated gradient of earlier calls sits in the same buffer: the per-layer sums below then cover it too
+    m->reduce_in_backward = add_to_model == TS2_GRADIENT_APPLY && m->comm && m->world > 1;
+    const int brc = backward(m);
+    m->reduce_in_backward = false;
+    if (brc != TS2_OK)
+        return brc;
     m->grads_dirty = true;
     m->last_targets = m->batch.target_count;
     if (add_to_model == TS2_GRADIENT_APPLY) {
-        M_TRY(apply(m, step));
+        m->reduce_in_backward = m->comm && m->world > 1; // tells apply() that the sums are already queued
+        const int arc = apply(m, step);
+        m->reduce_in_backward = false;
+        if (arc != TS2_OK)
+            return arc;
         m->grads_dirty = false;
     }
     TS2_CUDA(cudaEventRecord(m->ev_stop, m->stream));
