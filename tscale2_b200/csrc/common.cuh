@@ -117,6 +117,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
                  "r"(bar)
                  : "memory");
 }
+// untiled bulk copy shared -> global (bulk-group completion), same alignment rules
+__device__ __forceinline__ void bulk_store(void *dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read()

@@ -502,11 +502,170 @@ __global__ void __launch_bounds__(512, 2)
     }
 }
 
+// The same three passes with the row traffic taken off the threads: one block per SM keeps two rows in shared memory;
+// while it works on one, the next arrives by a bulk copy (mbarrier completion) and the previous one leaves by a bulk
+// store, so HBM stays busy through the compute passes.  Used when two rows fit (vocabulary up to ~56 k).
+__global__ void __launch_bounds__(1024, 1)
+    softmax_ce_pipe_kernel(__half *__restrict__ logits, int rows, int V, const float *__restrict__ bias, const int *__restrict__ target,
+                           float gscale, float *__restrict__ logp_sum, int write_grad, int32_t *status)
+{
+    extern __shared__ __align__(128) uint8_t sm_rows[];
+    __shared__ float red[32];
+    __shared__ float x_tgt_s;
+    __shared__ uint64_t full_bar[2];
+    __shared__ int abort_s;
+    const int tid = threadIdx.x, nthr = blockDim.x, nvec = V / 8;
+    const uint32_t row_bytes = (uint32_t)V * 2;
+    const uint32_t buf_bytes = (row_bytes + 127) & ~127u;
+    if (tid == 0) {
+        mbar_init(smem_u32(&full_bar[0]), 1);
+        mbar_init(smem_u32(&full_bar[1]), 1);
+        abort_s = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    volatile int *abort_flag = &abort_s;
+    const int first = blockIdx.x, step = gridDim.x;
+    if (tid == 0 && first < rows) {
+        mbar_arrive_expect_tx(smem_u32(&full_bar[0]), row_bytes);
+        bulk_load(smem_u32(sm_rows), logits + (size_t)first * V, row_bytes, smem_u32(&full_bar[0]));
+    }
+    int it = 0;
+    for (int row = first; row < rows; row += step, ++it) {
+        const int b = it & 1;
+        uint4 *row_s4 = (uint4 *)(sm_rows + (size_t)b * buf_bytes);
+        uint4 *dst = (uint4 *)(logits + (size_t)row * V);
+        const int tgt = target[row];
+        const bool ok = mbar_wait(smem_u32(&full_bar[b]), (it >> 1) & 1, abort_flag);
+        if (!__syncthreads_and(ok))
+            break;
+        float mx = 0.f; // the reference starts the maximum at 0 and takes it over the logits without bias
+        if (tgt >= 0) {
+            for (int i = tid; i < nvec; i += nthr) {
+                const uint4 raw = row_s4[i];
+                const __half2 *h = (const __half2 *)&raw;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    mx = fmaxf(mx, fmaxf(f.x, f.y));
+                }
+            }
+        }
+        // the other buffer: its row left by a bulk store at the end of the previous iteration, which has had the pass
+        // above to read shared memory; once it has, the next row may come in
+        if (tid == 0 && row + step < rows) {
+            bulk_wait_read<0>();
+            mbar_arrive_expect_tx(smem_u32(&full_bar[b ^ 1]), row_bytes);
+            bulk_load(smem_u32(sm_rows + (size_t)(b ^ 1) * buf_bytes), logits + (size_t)(row + step) * V, row_bytes, smem_u32(&full_bar[b ^ 1]));
+        }
+        if (tgt < 0) { // no target: zero gradient
+            if (write_grad) {
+                for (int i = tid; i < nvec; i += nthr)
+                    row_s4[i] = make_uint4(0, 0, 0, 0);
+                fence_proxy_async();
+                __syncthreads();
+                if (tid == 0) {
+                    bulk_store(dst, smem_u32(row_s4), row_bytes);
+                    bulk_commit();
+                }
+            }
+            continue;
+        }
+        mx = warp_max(mx);
+        if ((tid & 31) == 0)
+            red[tid >> 5] = mx;
+        __syncthreads();
+        mx = 0.f;
+        for (int i = 0; i < nthr / 32; ++i)
+            mx = fmaxf(mx, red[i]);
+        __syncthreads();
+        float sum0 = 0.f, sum1 = 0.f;
+        for (int i = tid; i < nvec; i += nthr) {
+            uint4 raw = row_s4[i];
+            __half2 *h = (__half2 *)&raw;
+            float bv[8];
+            if (bias) {
+                const float4 b0 = __ldg((const float4 *)(bias + 8 * i)), b1 = __ldg((const float4 *)(bias + 8 * i) + 1);
+                bv[0] = b0.x, bv[1] = b0.y, bv[2] = b0.z, bv[3] = b0.w, bv[4] = b1.x, bv[5] = b1.y, bv[6] = b1.z, bv[7] = b1.w;
+            }
+            const int trel = tgt - 8 * i; // position of the target inside this vector, if 0..7
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                const float x0 = f.x + (bias ? bv[2 * j] : 0.f), x1 = f.y + (bias ? bv[2 * j + 1] : 0.f);
+                if (trel == 2 * j)
+                    x_tgt_s = x0;
+                if (trel == 2 * j + 1)
+                    x_tgt_s = x1;
+                float e0, e1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 - mx));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 - mx));
+                sum0 += e0;
+                sum1 += e1;
+                h[j] = __floats2half2_rn(e0, e1);
+            }
+            row_s4[i] = raw;
+        }
+        float sum = warp_sum(sum0 + sum1);
+        if ((tid & 31) == 0)
+            red[tid >> 5] = sum;
+        __syncthreads();
+        sum = 0.f;
+        for (int i = 0; i < nthr / 32; ++i)
+            sum += red[i];
+        const float inv = 1.f / sum;
+        if (tid == 0)
+            atomicAdd(logp_sum, (x_tgt_s - mx) * 0.69314718f - logf(sum));
+        if (write_grad) {
+            const float ninv = -inv * gscale;
+            for (int i = tid; i < nvec; i += nthr) { // every thread revisits the vectors it wrote itself
+                uint4 raw = row_s4[i];
+                __half2 *h = (__half2 *)&raw;
+                const int trel = tgt - 8 * i;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 e = __half22float2(h[j]);
+                    h[j] = __floats2half2_rn(fmaf(e.x, ninv, trel == 2 * j ? gscale : 0.f), fmaf(e.y, ninv, trel == 2 * j + 1 ? gscale : 0.f));
+                }
+                row_s4[i] = raw;
+            }
+            fence_proxy_async(); // the bulk store reads shared memory through the async proxy
+            __syncthreads();
+            if (tid == 0) {
+                bulk_store(dst, smem_u32(row_s4), row_bytes);
+                bulk_commit();
+            }
+        } else {
+            __syncthreads(); // red[] and x_tgt_s are reused by the next row
+        }
+    }
+    if (tid == 0) {
+        bulk_wait_read<0>(); // shared memory must outlive the stores that read it
+        if (abort_s)
+            atomicOr(status, TS2_STATUS_WAIT_TIMEOUT);
+    }
+}
+
 int softmax_ce(const Ctx &c, __half *logits, int rows, int V, const float *bias, const int *target, float gscale, float *logp_sum,
                bool write_grad)
 {
     if (V % 8)
         return fail(TS2_ERR_INVALID_ARG, "softmax_ce: vocabulary must be a multiple of 8");
+    const size_t two_rows = 2 * (((size_t)V * sizeof(__half) + 127) & ~(size_t)127);
+    if (two_rows <= 224 * 1024) {
+        static bool configured_pipe[16] = {};
+        if (!configured_pipe[c.device & 15]) {
+            TS2_CUDA(cudaFuncSetAttribute(softmax_ce_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+            configured_pipe[c.device & 15] = true;
+        }
+        int32_t *status = device_status_word(c.device);
+        if (!status)
+            return fail(TS2_ERR_CUDA, "softmax_ce: no device status word");
+        const int grid = std::min(rows, sm_count(c.device));
+        softmax_ce_pipe_kernel<<<grid, 1024, two_rows, c.stream>>>(logits, rows, V, bias, target, gscale, logp_sum, write_grad ? 1 : 0, status);
+        TS2_CHECK_LAUNCH();
+        return TS2_OK;
+    }
     const size_t smem = (size_t)V * sizeof(__half);
     static bool configured[16] = {};
     if (smem > 48 * 1024 && !configured[c.device & 15]) {
