@@ -541,15 +541,13 @@ __global__ void __launch_bounds__(1024, 1)
             break;
         float mx = 0.f; // the reference starts the maximum at 0 and takes it over the logits without bias
         if (tgt >= 0) {
+            __half2 m2 = __float2half2_rn(0.f); // the values are fp16: their maximum is exact in packed fp16 arithmetic
             for (int i = tid; i < nvec; i += nthr) {
                 const uint4 raw = row_s4[i];
                 const __half2 *h = (const __half2 *)&raw;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(h[j]);
-                    mx = fmaxf(mx, fmaxf(f.x, f.y));
-                }
+                m2 = __hmax2(m2, __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3])));
             }
+            mx = fmaxf(__low2float(m2), __high2float(m2));
         }
         // the other buffer: its row left by a bulk store at the end of the previous iteration, which has had the pass
         // above to read shared memory; once it has, the next row may come in
@@ -588,15 +586,16 @@ __global__ void __launch_bounds__(1024, 1)
                 const float4 b0 = __ldg((const float4 *)(bias + 8 * i)), b1 = __ldg((const float4 *)(bias + 8 * i) + 1);
                 bv[0] = b0.x, bv[1] = b0.y, bv[2] = b0.z, bv[3] = b0.w, bv[4] = b1.x, bv[5] = b1.y, bv[6] = b1.z, bv[7] = b1.w;
             }
-            const int trel = tgt - 8 * i; // position of the target inside this vector, if 0..7
+            if (i == (tgt >> 3)) { // the vector that holds the target's logit: keep it before it is overwritten
+                const int kk = tgt & 7;
+                const uint32_t wsel = (kk >> 1) == 0 ? raw.x : (kk >> 1) == 1 ? raw.y : (kk >> 1) == 2 ? raw.z : raw.w;
+                const __half_raw hr = {(unsigned short)((kk & 1) ? (wsel >> 16) : (wsel & 0xffffu))};
+                x_tgt_s = __half2float(__half(hr)) + (bias ? __ldg(bias + tgt) : 0.f);
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(h[j]);
                 const float x0 = f.x + (bias ? bv[2 * j] : 0.f), x1 = f.y + (bias ? bv[2 * j + 1] : 0.f);
-                if (trel == 2 * j)
-                    x_tgt_s = x0;
-                if (trel == 2 * j + 1)
-                    x_tgt_s = x1;
                 float e0, e1;
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 - mx));
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 - mx));
@@ -621,11 +620,25 @@ __global__ void __launch_bounds__(1024, 1)
             for (int i = tid; i < nvec; i += nthr) { // every thread revisits the vectors it wrote itself
                 uint4 raw = row_s4[i];
                 __half2 *h = (__half2 *)&raw;
-                const int trel = tgt - 8 * i;
+                float gt = 0.f; // gradient of the target's logit, computed in fp32 from the same e before it is replaced
+                if (i == (tgt >> 3)) {
+                    const int kk = tgt & 7;
+                    const uint32_t wsel = (kk >> 1) == 0 ? raw.x : (kk >> 1) == 1 ? raw.y : (kk >> 1) == 2 ? raw.z : raw.w;
+                    const __half_raw hr = {(unsigned short)((kk & 1) ? (wsel >> 16) : (wsel & 0xffffu))};
+                    gt = fmaf(__half2float(__half(hr)), ninv, gscale);
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 e = __half22float2(h[j]);
-                    h[j] = __floats2half2_rn(fmaf(e.x, ninv, trel == 2 * j ? gscale : 0.f), fmaf(e.y, ninv, trel == 2 * j + 1 ? gscale : 0.f));
+                    h[j] = __floats2half2_rn(e.x * ninv, e.y * ninv);
+                }
+                if (i == (tgt >> 3)) {
+                    const int kk = tgt & 7;
+                    const unsigned short gb = __half_as_ushort(__float2half_rn(gt));
+                    auto patch = [&](uint32_t w, int idx) {
+                        return (kk >> 1) != idx ? w : (kk & 1) ? ((w & 0x0000ffffu) | ((uint32_t)gb << 16)) : ((w & 0xffff0000u) | gb);
+                    };
+                    raw.x = patch(raw.x, 0), raw.y = patch(raw.y, 1), raw.z = patch(raw.z, 2), raw.w = patch(raw.w, 3);
                 }
                 row_s4[i] = raw;
             }
