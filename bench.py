@@ -30,6 +30,12 @@ WORKLOADS = {
     "c3_dense12_d768": dict(dim=768, heads=12, ffn_tiles=24, vocab=50304, blocks=12, seq=1024, seqs=64),
     # BASELINE.json configs[0], for quick checks
     "c1_dense2_d256": dict(dim=256, heads=4, ffn_tiles=8, vocab=4096, blocks=2, seq=128, seqs=4),
+    # BASELINE.json configs[3]: 12 attention + mixture-of-experts blocks, 32 experts of width 1024, 2 selected;
+    # every rank holds all experts (no expert-parallel exchange)
+    "c4_moe12_d1024": dict(dim=1024, heads=16, ffn_tiles=8, vocab=50304, blocks=12, seq=1024, seqs=32, experts=32, selected=2,
+                           expert_dim=1024),
+    # BASELINE.json configs[4]: 24 blocks, dim 2048, 16 heads, FFN 8192, 8 sequences of 4096 tokens per GPU
+    "c5_dense24_d2048": dict(dim=2048, heads=16, ffn_tiles=64, vocab=50304, blocks=24, seq=4096, seqs=8),
 }
 
 
@@ -38,8 +44,11 @@ NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH = {("c3_dense12_d768", "fp8"): 533793211}
 
 
 def make_spec(w, precision):
-    return host.ModelSpec(dim=w["dim"], head_count=w["heads"], ffn_tiles=w["ffn_tiles"], vocab=w["vocab"],
-                          attention_widths=[w["seq"]], precision=precision).add_blocks(w["blocks"])
+    moe = "experts" in w
+    spec = host.ModelSpec(dim=w["dim"], head_count=w["heads"], ffn_tiles=w["ffn_tiles"], vocab=w["vocab"],
+                          attention_widths=[w["seq"]], precision=precision, expert_dim=w.get("expert_dim", 128),
+                          moe_expert_count=w.get("experts", 0), moe_selected=w.get("selected", 2))
+    return spec.add_blocks(w["blocks"], moe=moe)
 
 
 def flops_per_token(w):
@@ -47,7 +56,11 @@ def flops_per_token(w):
     linear layer (2 forward, 4 backward) plus the attention core (forward 4*w*128*H per token at
     mean causal width w = seq/2, backward 2.5x)."""
     d, q, f = w["dim"], 128 * w["heads"], 128 * w["ffn_tiles"]
-    p = w["blocks"] * (5 * d * q + 3 * d * f) + w["vocab"] * d
+    if "experts" in w:  # per token: the selected experts' three matrices and the router
+        ffn = 3 * d * w["expert_dim"] * w["selected"] + d * w["experts"]
+    else:
+        ffn = 3 * d * f
+    p = w["blocks"] * (5 * d * q + ffn) + w["vocab"] * d
     att = w["blocks"] * 3.5 * 4 * (w["seq"] / 2) * q
     return 6.0 * p + att, 4.0 * p
 
@@ -158,6 +171,8 @@ def main():
               "ffn": 128 * w["ffn_tiles"], "vocab": w["vocab"], "seq_len": w["seq"], "sequences_per_gpu": w["seqs"],
               "global_tokens_per_step": tokens_per_gpu * args.gpus, "parallelism": f"dp{args.gpus}",
               "l2": "inputs larger than L2 (activations of one step are several GB)"}
+    if "experts" in w:
+        config.update({"experts": w["experts"], "experts_selected": w["selected"], "expert_ffn": w["expert_dim"]})
 
     if args.impl == "reference":
         if rank != 0:
@@ -183,7 +198,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     precision = capi.PREC_FP8 if args.precision == "fp8" else capi.PREC_F16
     spec = make_spec(w, precision)
-    mats = host.init_weights(spec, 1000)  # same weights on every rank
+    # same weights on every rank; router weights N(0, 1) for the mixture-of-experts workload (BASELINE.json configs[3])
+    mats = host.init_weights(spec, 1000, select_std=1.0 if "experts" in w else None)
     model = Model(spec, mats, tokens_per_gpu, device=local_rank)
     del mats
     if world > 1:
