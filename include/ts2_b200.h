@@ -232,6 +232,11 @@ int ts2_dev_upload(int device, void *dst, const void *host_src, size_t bytes);
 int ts2_dev_download(int device, void *host_dst, const void *src, size_t bytes);
 int ts2_dev_memset(int device, void *dst, int value, size_t bytes);
 int ts2_dev_sync(int device);
+/* Self-test of the bounded waits (no reference counterpart): launches one CTA that waits on a barrier nothing arrives
+ * at.  The wait gives up after its limit (under a second), the kernel sets the time-out bit of the device status word
+ * and returns; the call reports it like ts2_dev_sync: TS2_ERR_DEVICE_STATUS is the expected result, and the context
+ * stays usable (nothing traps, nothing spins without a limit). */
+int ts2_selftest_wait_limit(int device);
 
 /* C[M][N] (+)= alpha * A[M][K] · B[N][K]^T — both operands K-contiguous.
  * Replaces Fp8MatMul / Int8MatMul / Fp16MatMul (src/lib/cuda/cuda_fp8.cuh:123-228,

@@ -123,6 +123,33 @@ int ts2_dev_sync(int device)
     return TS2_OK;
 }
 
+// One CTA waits, with the library's bounded wait, on an mbarrier nothing ever arrives at: the wait gives up after its
+// limit (about 1.5e9 clocks, under a second), the kernel ORs the time-out bit into the status word and returns.
+__global__ void wait_limit_selftest_kernel(int32_t *status)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_s;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_s = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(smem_u32(&bar), 0, &abort_s))
+        atomicOr(status, TS2_STATUS_WAIT_TIMEOUT);
+}
+
+int ts2_selftest_wait_limit(int device)
+{
+    TS2_CUDA(cudaSetDevice(device));
+    int32_t *w = device_status_word(device);
+    if (!w)
+        return fail(TS2_ERR_CUDA, "no device status word");
+    wait_limit_selftest_kernel<<<1, 32>>>(w);
+    TS2_CHECK_LAUNCH();
+    return ts2_dev_sync(device);
+}
+
 int ts2_gemm_tn(int device, void *stream, int prec, int out_kind, int64_t M, int64_t N, int64_t K, const void *A,
                 int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc, float alpha, const float *row_scale,
                 const float *col_scale)
