@@ -413,11 +413,8 @@ int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const 
     p.out = dq;
     if ((rc = launch_bwd_tc<0>(c, q, dout, k, v, p)) != TS2_OK)
         return rc;
-    p.out = dk;
-    if ((rc = launch_bwd_tc<1>(c, k, v, q, dout, p)) != TS2_OK)
-        return rc;
-    p.out = dv;
-    return launch_bwd_tc<2>(c, k, nullptr, q, dout, p);
+    // dK and dV from one kernel that shares S and the streamed tiles (kernels_att_bwd_kv_tc.cu)
+    return attention_backward_kv_tc(c, q, k, v, dout, meta, p.Tpad, rev_first, rev_last, T, H, slope, dk, dv);
 }
 
 } // namespace ts2
