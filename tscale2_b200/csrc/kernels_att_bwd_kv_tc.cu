@@ -39,7 +39,8 @@ struct AttBwdKvParams {
 
 __global__ void __launch_bounds__(KV_THREADS, 1)
     att_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                         const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO, const AttBwdKvParams p)
+                         const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                         const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, const AttBwdKvParams p)
 {
     extern __shared__ __align__(1024) uint8_t att_kv_smem[];
     uint8_t *smem = att_kv_smem;
@@ -238,14 +239,16 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
                 break;
             mbar_arrive(g_full);
         }
-        // epilogue: this thread's 32 columns of both accumulator rows -> fp32 outputs
+        // epilogue: both accumulators -> fp32 outputs.  A warp's 32 rows x 32 columns go through a 4 KB block of the
+        // (now idle) stage area, rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7)),
+        // and one TMA store each: direct stores would write 16 bytes into each of 32 different lines per instruction.
+        // Rows past T are clipped by the TMA unit.
         if (n > 0 && ok)
             ok = mbar_wait(all_done, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
-            float *dst = (which ? p.dv : p.dk) + (size_t)rr * (H * TC_HD) + col0 + part * 32;
             uint32_t r[32];
             if (n > 0 && ok) {
                 tmem_ld32((which ? tDV : tDK) + lane_addr + part * 32, r);
@@ -255,12 +258,19 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
                 for (int i = 0; i < 32; ++i)
                     r[i] = 0u;
             }
-            if (rr < T) {
+            uint8_t *blk = smem + KV_STAGE_OFF + ((warp - 4) * 2 + which) * 4096, *srow = blk + lane * 128;
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    *(uint4 *)(dst + i * 4) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            for (int i = 0; i < 8; ++i)
+                *(uint4 *)(srow + ((i ^ (lane & 7)) << 4)) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(which ? (const void *)&tmDV : (const void *)&tmDK, smem_u32(blk), col0 + part * 32, r0 + quarter * 32);
+                bulk_commit();
             }
         }
+        if (lane == 0)
+            bulk_wait_read<0>(); // shared memory must outlive the stores that read it
     }
     tc_fence_before();
     __syncthreads();
@@ -279,7 +289,7 @@ int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, con
         configured[c.device & 15] = true;
     }
     const int Q = H * TC_HD;
-    CUtensorMap tK, tV, tQ, tDO;
+    CUtensorMap tK, tV, tQ, tDO, tDK, tDV;
     int rc;
     if ((rc = make_tensor_map(&tK, k, 2, Q, T, Q, TC_BM)) != TS2_OK)
         return rc;
@@ -288,6 +298,11 @@ int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, con
     if ((rc = make_tensor_map(&tQ, q, 2, Q, T, Q, TC_BN)) != TS2_OK)
         return rc;
     if ((rc = make_tensor_map(&tDO, dout, 2, Q, T, Q, TC_BN)) != TS2_OK)
+        return rc;
+    // outputs: boxes of 32 fp32 columns x 32 rows
+    if ((rc = make_tensor_map(&tDK, dk, 4, Q, T, Q, 32)) != TS2_OK)
+        return rc;
+    if ((rc = make_tensor_map(&tDV, dv, 4, Q, T, Q, 32)) != TS2_OK)
         return rc;
     AttBwdKvParams p;
     p.T = T;
@@ -303,7 +318,7 @@ int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, con
     if (!p.status)
         return fail(TS2_ERR_CUDA, "attention: no device status word");
     dim3 grid((unsigned)ceil_div(T, TC_BM), (unsigned)H);
-    att_bwd_kv_tc_kernel<<<grid, KV_THREADS, KV_SMEM, c.stream>>>(tK, tV, tQ, tDO, p);
+    att_bwd_kv_tc_kernel<<<grid, KV_THREADS, KV_SMEM, c.stream>>>(tK, tV, tQ, tDO, tDK, tDV, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
