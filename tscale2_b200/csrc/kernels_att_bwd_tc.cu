@@ -73,7 +73,8 @@ __global__ void att_pack_meta_kernel(const float *__restrict__ lse, const float 
 template <int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
     att_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
-                      const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2, const AttBwdParams p)
+                      const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+                      const __grid_constant__ CUtensorMap tmOut, const AttBwdParams p)
 {
     using L = BwdLayout<MODE>;
     constexpr bool NEED_DP = L::NEED_DP, TRANSPOSED = L::TRANSPOSED;
@@ -303,9 +304,17 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         // epilogue: this thread's 64 columns of the accumulator row -> fp32 output
         if (k > 0 && ok)
             ok = mbar_wait(acc_ready, (k - 1) & 1, abort_flag);
+        // the staging blocks below lie in the resident tile, which the producer fills for both blocks whenever the CTA
+        // has any tile: a block without tiles of its own must see that copy landed before it writes there
+        if (n > 0 && ok)
+            ok = mbar_wait(res_full, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        float *dst = p.out + (size_t)rr * (H * TC_HD) + col0;
+        // A warp's 32 rows x 32 columns go through a 4 KB block of the block's own resident A1 tile (idle now: every MMA
+        // of this block is complete), rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r at
+        // c ^ (r & 7)), and one TMA store: direct stores would write 16 bytes into each of 32 different lines per
+        // instruction.  Rows past T are clipped by the TMA unit.
+        uint8_t *blk = smem + L::A1_OFF + b * Q_BYTES + ((warp - 4) & 7) * 4096, *srow = blk + lane * 128;
 #pragma unroll 1
         for (int c = 2 * half; c < 2 * half + 2; ++c) {
             uint32_t r[32];
@@ -317,12 +326,21 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                 for (int i = 0; i < 32; ++i)
                     r[i] = 0u;
             }
-            if (rr < T) {
+            if (lane == 0)
+                bulk_wait_read<0>(); // the previous store has read the block
+            __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    *(uint4 *)(dst + c * 32 + i * 4) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            for (int i = 0; i < 8; ++i)
+                *(uint4 *)(srow + ((i ^ (lane & 7)) << 4)) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&tmOut, smem_u32(blk), col0 + c * 32, r0 + b * TC_BM + quarter * 32);
+                bulk_commit();
             }
         }
+        if (lane == 0)
+            bulk_wait_read<0>(); // shared memory must outlive the stores that read it
     }
     tc_fence_before();
     __syncthreads();
@@ -342,7 +360,7 @@ static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const
         configured[c.device & 15] = true;
     }
     const int Q = p.H * TC_HD;
-    CUtensorMap tA1, tA2, tB1, tB2;
+    CUtensorMap tA1, tA2, tB1, tB2, tOut;
     int rc;
     if ((rc = make_tensor_map(&tA1, a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
         return rc;
@@ -352,8 +370,10 @@ static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const
         return rc;
     if ((rc = make_tensor_map(&tB2, b2, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
         return rc;
+    if ((rc = make_tensor_map(&tOut, p.out, 4, Q, p.T, Q, 32)) != TS2_OK) // boxes of 32 fp32 columns x 32 rows
+        return rc;
     dim3 grid((unsigned)ceil_div(p.T, BW_ROWS), (unsigned)p.H);
-    kern<<<grid, BW_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, p);
+    kern<<<grid, BW_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, tOut, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

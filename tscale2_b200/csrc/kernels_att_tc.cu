@@ -38,7 +38,7 @@ struct AttTcParams {
 
 __global__ void __launch_bounds__(TC_THREADS, 2)
     att_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                      const __grid_constant__ CUtensorMap tmV, const AttTcParams p)
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttTcParams p)
 {
     extern __shared__ __align__(1024) uint8_t att_tc_smem[];
     uint8_t *smem = att_tc_smem;
@@ -310,9 +310,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
         pair_barrier(quarter);
         l += lx[(half ^ 1) * TC_BM + row];
         const float inv = 1.f / l;
-        __half *dst = p.o + (size_t)t * (H * TC_HD) + h * TC_HD;
+        // A warp's 32 rows x 64 fp16 columns go through a 4 KB block of the Q tile (idle now: every MMA is complete),
+        // rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7)), and one TMA store:
+        // direct stores would write 16 bytes into each of 32 different lines per instruction.  Rows past T are clipped.
+        uint8_t *blk = smem + (warp - 2) * 4096, *srow = blk + lane * 128;
 #pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+        for (int cc = 0; cc < 2; ++cc) {
+            const int c = 2 * half + cc;
             uint32_t r[32];
             if (n_tiles > 0 && ok) {
                 tmem_ld32(tmem_O + lane_addr + c * 32, r);
@@ -322,16 +326,21 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 for (int i = 0; i < 32; ++i)
                     r[i] = 0u;
             }
-            if (t < T) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
-                            h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
-                            h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
-                            h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-                    *(uint4 *)(dst + c * 32 + i * 8) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
-                }
+            for (int i = 0; i < 4; ++i) {
+                __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
+                        h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
+                        h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
+                        h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+                *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
             }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&tmO, smem_u32(blk), h * TC_HD + half * 64, t0 + quarter * 32);
+            bulk_commit();
+            bulk_wait_read<0>(); // shared memory must outlive the store that reads it
         }
         if (t < T && half == 0)
             p.lse[(size_t)t * H + h] = m_used + log2f(l);
@@ -353,13 +362,15 @@ int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const _
         configured[c.device & 15] = true;
     }
     const int Q = H * TC_HD;
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmO;
     int rc;
     if ((rc = make_tensor_map(&tmQ, q, 2, Q, T, Q, TC_BM)) != TS2_OK)
         return rc;
     if ((rc = make_tensor_map(&tmK, k, 2, Q, T, Q, TC_BN)) != TS2_OK)
         return rc;
     if ((rc = make_tensor_map(&tmV, v, 2, Q, T, Q, TC_BN)) != TS2_OK)
+        return rc;
+    if ((rc = make_tensor_map(&tmO, o, 2, Q, T, Q, 32)) != TS2_OK) // output: boxes of 64 fp16 columns x 32 rows
         return rc;
     AttTcParams p;
     p.T = T;
@@ -373,7 +384,7 @@ int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const _
     if (!p.status)
         return fail(TS2_ERR_CUDA, "attention: no device status word");
     dim3 grid((unsigned)ceil_div(T, TC_BM), (unsigned)H);
-    att_fwd_tc_kernel<<<grid, TC_THREADS, FWD_SMEM, c.stream>>>(tmQ, tmK, tmV, p);
+    att_fwd_tc_kernel<<<grid, TC_THREADS, FWD_SMEM, c.stream>>>(tmQ, tmK, tmV, tmO, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
