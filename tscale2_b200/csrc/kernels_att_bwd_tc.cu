@@ -1,22 +1,17 @@
-// tcgen05 attention backward for head width 128 (sm_100a): one kernel template for the three gradients.
-// Same math, inputs and outputs as the mma.sync formulation in kernels_att_mma.cu (see there for the
-// references into src/gpt/compute/layer_att_reference.h and gpu_att_fp16.cu).
+// tcgen05 attention backward for head width 128 (sm_100a): dQ, the packing of the per-node records, and the entry
+// point of the backward pass (dK and dV come from kernels_att_bwd_kv_tc.cu).  Same math, inputs and outputs as the
+// mma.sync formulation in kernels_att_mma.cu (see there for the references into
+// src/gpt/compute/layer_att_reference.h and gpu_att_fp16.cu).
 //
-// A CTA owns 256 resident rows (nodes for dQ, keys for dK / dV) as two blocks of 128, and streams 64-row
-// tiles of the other side once for both blocks (half the L2 traffic of one block per CTA):
-//   first MMAs   S = A1 . B1^T  (and dP = A2 . B2^T)           128 x 64 each, fp32 in TMEM
-//   compute      G = dS  or  P  (fp16, written to a swizzled K-major shared-memory tile)
-//   second MMA   ACC += G . B1 (dQ, dK)  or  G . B2 (dV)       128 x 128 in TMEM, B read MN-major
-//   MODE 0 (dQ): A1 = Q, A2 = dO resident; B1 = K, B2 = V streamed; rows are nodes
-//   MODE 1 (dK): A1 = K, A2 = V  resident; B1 = Q, B2 = dO streamed; rows are keys (transposed problem)
-//   MODE 2 (dV): A1 = K resident;          B1 = Q, B2 = dO streamed; rows are keys; no dP
-// Each block has its own MMA issuer thread, its own 8 compute warps (two per TMEM lane quarter, 32 of the
-// tile's 64 columns each) and its own 256 TMEM columns, so while one block's compute warps turn S into G the
-// tensor cores run the other block's products.  20 warps: TMA producer, 2 MMA issuers, 1 idle, 16 compute.
-// In the transposed modes the per-node quantities belong to the columns; a small kernel packs them once per
-// call as {-lse, -dscale * c2, span start, span length} per (head, node) and the producer brings the 1 KB of
-// each streamed tile next to it with a bulk copy.  Every wait is bounded (see mbar_wait); a give-up raises
-// the status word.
+// dQ: a CTA owns 256 resident nodes (Q and dO rows) as two blocks of 128, and streams 64-key tiles of K and V once
+// for both blocks (half the L2 traffic of one block per CTA):
+//   first MMAs   S = Q . K^T  and  dP = dO . V^T               128 x 64 each, fp32 in TMEM
+//   compute      G = P (dP - dscale) c2                        fp16, left in TMEM in place of the dP values
+//   second MMA   dQ += G . K                                   128 x 128 in TMEM, G the TMEM A operand, K read MN-major
+// Each block has its own MMA issuer thread, its own 8 compute warps (two per TMEM lane quarter, 32 of the tile's 64
+// keys each) and its own 256 TMEM columns.  20 warps: TMA producer, 2 MMA issuers, 1 idle, 16 compute.  (One block per
+// CTA with two S / dP pairs, the structure of the dK / dV kernel, was measured slower here: twice the CTAs and twice
+// the streamed bytes.)  Every wait is bounded (see mbar_wait); a give-up raises the status word.
 #include "att_tc.cuh"
 #include <mutex>
 
@@ -24,33 +19,27 @@ namespace ts2 {
 
 static constexpr int BW_ROWS = 2 * TC_BM;
 static constexpr int BW_THREADS = 128 + 2 * 256;
-static constexpr int META_TILE_BYTES = TC_BN * 16;
 
 struct AttBwdParams {
-    int T, H, Tpad;
+    int T, H;
     float slope;
-    const int *span_start, *span_finish, *rev_first, *rev_last;
+    const int *span_start, *span_finish;
     const float *lse, *dscale;
-    const float4 *meta; // [H][Tpad], transposed modes
-    float *out;         // dq, dk or dv: fp32 [T][128 H]
+    float *out; // dq: fp32 [T][128 H]
     int32_t *status;
 };
 
-template <int MODE>
 struct BwdLayout {
-    static constexpr bool NEED_DP = MODE != 2;
-    static constexpr bool TRANSPOSED = MODE != 0;
-    static constexpr int STAGES = MODE == 1 ? 2 : 3; // what fits: mode 1 has four resident tiles and the per-node records
+    static constexpr int STAGES = 3;
     static constexpr int A1_OFF = 0;
     static constexpr int A2_OFF = A1_OFF + 2 * Q_BYTES;
-    static constexpr int RES_BYTES = (NEED_DP ? 4 : 2) * Q_BYTES;
+    static constexpr int RES_BYTES = 4 * Q_BYTES; // Q and dO of both blocks
     static constexpr int STAGE_OFF = RES_BYTES;
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int META_OFF = STAGE_OFF + STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFF = META_OFF + (TRANSPOSED ? STAGES * META_TILE_BYTES : 0);
+    static constexpr int BAR_OFF = STAGE_OFF + STAGES * STAGE_BYTES;
     static constexpr int SMEM = BAR_OFF + 256;
 };
-static_assert(BwdLayout<0>::SMEM <= 232448 && BwdLayout<1>::SMEM <= 232448 && BwdLayout<2>::SMEM <= 232448, "shared memory budget");
+static_assert(BwdLayout::SMEM <= 232448, "shared memory budget");
 
 // {-lse, -dscale * c2, start, finish - start} per (head, node); nodes past T and nodes with an empty span get a
 // start no key index reaches
@@ -70,14 +59,12 @@ __global__ void att_pack_meta_kernel(const float *__restrict__ lse, const float 
     meta[idx] = m;
 }
 
-template <int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
-    att_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+    att_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                       const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
                       const __grid_constant__ CUtensorMap tmOut, const AttBwdParams p)
 {
-    using L = BwdLayout<MODE>;
-    constexpr bool NEED_DP = L::NEED_DP, TRANSPOSED = L::TRANSPOSED;
+    using L = BwdLayout;
     constexpr int STAGES = L::STAGES;
     extern __shared__ __align__(1024) uint8_t att_bwd_smem[];
     uint8_t *smem = att_bwd_smem;
@@ -86,8 +73,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             atomicOr(p.status, TS2_STATUS_BAD_ARG);
         return;
     }
-    const uint32_t sA1 = smem_u32(smem) + L::A1_OFF, sA2 = smem_u32(smem) + L::A2_OFF, sStage = smem_u32(smem) + L::STAGE_OFF,
-                   sMeta = smem_u32(smem) + L::META_OFF;
+    const uint32_t sA1 = smem_u32(smem) + L::A1_OFF, sA2 = smem_u32(smem) + L::A2_OFF, sStage = smem_u32(smem) + L::STAGE_OFF;
     uint64_t *bars = (uint64_t *)(smem + L::BAR_OFF);
     const uint32_t res_full = smem_u32(bars), st_full0 = smem_u32(bars + 1), st_empty0 = smem_u32(bars + 4), s_full0 = smem_u32(bars + 7),
                    g_full0 = smem_u32(bars + 9), acc_ready0 = smem_u32(bars + 11);
@@ -104,7 +90,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
     __syncthreads();
     if (threadIdx.x < BW_ROWS && r0 + (int)threadIdx.x < T) {
         const int r = r0 + threadIdx.x, b = threadIdx.x >> 7;
-        const int a = TRANSPOSED ? p.rev_first[r] : p.span_start[r], e = TRANSPOSED ? p.rev_last[r] : p.span_finish[r];
+        const int a = p.span_start[r], e = p.span_finish[r];
         if (e >= a) {
             atomicMin(&rng[2 * b], a);
             atomicMax(&rng[2 * b + 1], e);
@@ -151,24 +137,20 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             for (int b = 0; b < 2; ++b) {
                 tma_load_2d(sA1 + b * Q_BYTES, &tmA1, res_full, col0, r0 + b * TC_BM);
                 tma_load_2d(sA1 + b * Q_BYTES + Q_BYTES / 2, &tmA1, res_full, col0 + 64, r0 + b * TC_BM);
-                if (NEED_DP) {
-                    tma_load_2d(sA2 + b * Q_BYTES, &tmA2, res_full, col0, r0 + b * TC_BM);
-                    tma_load_2d(sA2 + b * Q_BYTES + Q_BYTES / 2, &tmA2, res_full, col0 + 64, r0 + b * TC_BM);
-                }
+                tma_load_2d(sA2 + b * Q_BYTES, &tmA2, res_full, col0, r0 + b * TC_BM);
+                tma_load_2d(sA2 + b * Q_BYTES + Q_BYTES / 2, &tmA2, res_full, col0 + 64, r0 + b * TC_BM);
             }
             for (int j = 0; j < n; ++j) {
                 const int st = j % STAGES, row = (u0 + j) * TC_BN;
                 if (!mbar_wait(st_empty0 + 8 * st, ((j / STAGES) & 1) ^ 1, abort_flag))
                     break;
                 const uint32_t fb = st_full0 + 8 * st;
-                mbar_arrive_expect_tx(fb, L::STAGE_BYTES + (TRANSPOSED ? META_TILE_BYTES : 0));
+                mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
                 const uint32_t d1 = sStage + st * L::STAGE_BYTES, d2 = d1 + KV_BYTES;
                 tma_load_2d(d1, &tmB1, fb, col0, row);
                 tma_load_2d(d1 + KV_BYTES / 2, &tmB1, fb, col0 + 64, row);
                 tma_load_2d(d2, &tmB2, fb, col0, row);
                 tma_load_2d(d2 + KV_BYTES / 2, &tmB2, fb, col0 + 64, row);
-                if (TRANSPOSED)
-                    bulk_load(sMeta + st * META_TILE_BYTES, p.meta + (size_t)h * p.Tpad + row, META_TILE_BYTES, fb);
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -194,25 +176,22 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                     // 8 steps of 16 head dims; operands are two 64-dim atoms each
                     umma_f16_x4(tS, dA1, dB1, idesc_s, 0u, 2u, 2u);
                     umma_f16_x4(tS, dA1 + (Q_BYTES / 2 >> 4), dB1 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
-                    if (NEED_DP) {
-                        // the dP columns still hold G of the previous tile, the A operand of its second MMA: that MMA
-                        // must be complete before these may write there (it was issued eight MMAs ago, so this wait
-                        // is normally over before it starts)
-                        if (k > 0 && !mbar_wait(acc_ready, (k - 1) & 1, abort_flag))
-                            break;
-                        umma_f16_x4(tDP, dA2, dB2, idesc_s, 0u, 2u, 2u);
-                        umma_f16_x4(tDP, dA2 + (Q_BYTES / 2 >> 4), dB2 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
-                    }
+                    // the dP columns still hold G of the previous tile, the A operand of its second MMA: that MMA must be
+                    // complete before these may write there (it was issued eight MMAs ago, so this wait is normally over
+                    // before it starts)
+                    if (k > 0 && !mbar_wait(acc_ready, (k - 1) & 1, abort_flag))
+                        break;
+                    umma_f16_x4(tDP, dA2, dB2, idesc_s, 0u, 2u, 2u);
+                    umma_f16_x4(tDP, dA2 + (Q_BYTES / 2 >> 4), dB2 + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
                     tc_commit(s_full);
                     if (!mbar_wait(g_full, k & 1, abort_flag))
                         break;
                     tc_fence_after();
-                    // ACC += G . B: 4 steps of 16 streamed rows.  G is read from tensor memory, where the compute warps
-                    // left it in the dP columns (in place of the dP values they consumed; mode 2 has no dP and the
-                    // columns are free): fp16 pairs, streamed rows 0-15 in columns 0-7, 16-31 in 8-15, 32-47 in 32-39,
-                    // 48-63 in 40-47.  The streamed tile is read MN-major (its 128 columns are the output columns),
-                    // 16 rows = 2048 bytes per step.
-                    const uint64_t dB = umma_smem_desc(MODE == 2 ? b2 : b1, KV_BYTES / 2, 1024);
+                    // dQ += G . K: 4 steps of 16 keys.  G is read from tensor memory, where the compute warps left it in the dP
+                    // columns (in place of the dP values they consumed): fp16 pairs, keys 0-15 in columns 0-7, 16-31 in
+                    // 8-15, 32-47 in 32-39, 48-63 in 40-47.  The K tile is read MN-major (its 128 columns are the output
+                    // columns), 16 rows = 2048 bytes per step.
+                    const uint64_t dB = umma_smem_desc(b1, KV_BYTES / 2, 1024);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         umma_f16_ts(tACC, tDP + (kk >> 1) * 32 + (kk & 1) * 8, dB + (uint64_t)(kk * 128), idesc_acc, (k > 0 || kk > 0) ? 1u : 0u);
@@ -227,14 +206,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         const int b = (warp - 4) >> 3, half = ((warp - 4) & 7) >> 2, quarter = warp & 3;
         const int my_lo = b ? tlo1 : tlo0, my_hi = b ? thi1 : thi0;
         const int row = quarter * 32 + lane;
-        const int rr = r0 + b * TC_BM + row; // node (MODE 0) or key (MODE 1, 2) of this thread
+        const int rr = r0 + b * TC_BM + row; // node of this thread
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t tS = tmem_base + b * 256 + lane_addr + half * 32, tDP = tS + TC_BN, tACC = tmem_base + b * 256 + 2 * TC_BN + lane_addr;
         const uint32_t s_full = s_full0 + 8 * b, g_full = g_full0 + 8 * b, acc_ready = acc_ready0 + 8 * b;
         const float ds = att_dot_scale_tc(), c2 = ds * 0.693147f, slope = p.slope;
         int st_row = 0, len_row = -1;
         float nlse_row = 0.f, ndc_row = 0.f;
-        if (!TRANSPOSED && rr < T) {
+        if (rr < T) {
             st_row = p.span_start[rr];
             len_row = p.span_finish[rr] - st_row;
             nlse_row = -p.lse[(size_t)rr * H + h];
@@ -251,41 +230,27 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             if (!ok)
                 break;
             tc_fence_after();
-            const int c0 = tile * TC_BN + half * 32; // first streamed row of this thread's columns
-            const float4 *mt = (const float4 *)(smem + L::META_OFF + (j % STAGES) * META_TILE_BYTES) + half * 32;
+            const int c0 = tile * TC_BN + half * 32; // first key of this thread's columns
             // two passes of 16 columns: few enough live registers that the compiler can interleave the per-element
-            // chains (shared-memory load -> fma -> ex2 -> select -> fma -> multiply -> convert)
+            // chains (fma -> ex2 -> select -> fma -> multiply -> convert)
 #pragma unroll
             for (int q16 = 0; q16 < 2; ++q16) {
                 uint32_t rs[16], rp[16];
                 tmem_ld16(tS + q16 * 16, rs);
-                if (NEED_DP)
-                    tmem_ld16(tDP + q16 * 16, rp);
+                tmem_ld16(tDP + q16 * 16, rp);
                 tmem_ld_wait();
                 float g[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int c = c0 + q16 * 16 + i;
-                    float off, ndc;
-                    bool valid;
-                    if (!TRANSPOSED) {
-                        off = nlse_row;
-                        ndc = ndc_row;
-                        valid = (unsigned)(c - st_row) <= (unsigned)len_row && len_row >= 0;
-                        if (slope != 0.f)
-                            off -= slope * (float)(rr - c);
-                    } else {
-                        const float4 m = mt[q16 * 16 + i];
-                        off = m.x;
-                        ndc = m.y;
-                        valid = (unsigned)(rr - __float_as_int(m.z)) <= (unsigned)__float_as_int(m.w);
-                        if (slope != 0.f)
-                            off -= slope * (float)(c - rr);
-                    }
+                    float off = nlse_row;
+                    const bool valid = (unsigned)(c - st_row) <= (unsigned)len_row && len_row >= 0;
+                    if (slope != 0.f)
+                        off -= slope * (float)(rr - c);
                     float w;
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(fmaf(__uint_as_float(rs[i]), ds, off)));
                     w = valid ? w : 0.f;
-                    g[i] = NEED_DP ? w * fmaf(__uint_as_float(rp[i]), c2, ndc) : w;
+                    g[i] = w * fmaf(__uint_as_float(rp[i]), c2, ndc_row);
                 }
                 // G goes where this thread's dP values were (its own lane, its own columns): 16 fp16 values = 8 columns
                 uint32_t packed[8];
@@ -350,13 +315,13 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         atomicOr(p.status, TS2_STATUS_WAIT_TIMEOUT);
 }
 
-template <int MODE>
-static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p)
+// a1 = Q, a2 = dO (resident), b1 = K, b2 = V (streamed)
+static int launch_bwd_dq(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p)
 {
-    auto kern = att_bwd_tc_kernel<MODE>;
+    auto kern = att_bwd_dq_tc_kernel;
     static bool configured[16] = {};
     if (!configured[c.device & 15]) {
-        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout<MODE>::SMEM));
+        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout::SMEM));
         configured[c.device & 15] = true;
     }
     const int Q = p.H * TC_HD;
@@ -364,7 +329,7 @@ static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const
     int rc;
     if ((rc = make_tensor_map(&tA1, a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
         return rc;
-    if ((rc = make_tensor_map(&tA2, a2 ? a2 : a1, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
+    if ((rc = make_tensor_map(&tA2, a2, 2, Q, p.T, Q, TC_BM)) != TS2_OK)
         return rc;
     if ((rc = make_tensor_map(&tB1, b1, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
         return rc;
@@ -373,7 +338,7 @@ static int launch_bwd_tc(const Ctx &c, const __half *a1, const __half *a2, const
     if ((rc = make_tensor_map(&tOut, p.out, 4, Q, p.T, Q, 32)) != TS2_OK) // boxes of 32 fp32 columns x 32 rows
         return rc;
     dim3 grid((unsigned)ceil_div(p.T, BW_ROWS), (unsigned)p.H);
-    kern<<<grid, BW_THREADS, BwdLayout<MODE>::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, tOut, p);
+    kern<<<grid, BW_THREADS, BwdLayout::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, tOut, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
@@ -408,12 +373,10 @@ int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const 
     AttBwdParams p;
     p.T = T;
     p.H = H;
-    p.Tpad = (int)ceil_div(T, TC_BN) * TC_BN;
+    const int Tpad = (int)ceil_div(T, TC_BN) * TC_BN;
     p.slope = slope;
     p.span_start = span_start;
     p.span_finish = span_finish;
-    p.rev_first = rev_first;
-    p.rev_last = rev_last;
     p.lse = lse;
     p.dscale = dscale;
     p.status = device_status_word(c.device);
@@ -421,20 +384,19 @@ int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const 
         return fail(TS2_ERR_CUDA, "attention: no device status word");
     int rc;
     float4 *meta = nullptr;
-    if ((rc = meta_buffer(c.device, (size_t)p.Tpad * H * sizeof(float4), &meta)) != TS2_OK)
+    if ((rc = meta_buffer(c.device, (size_t)Tpad * H * sizeof(float4), &meta)) != TS2_OK)
         return rc;
-    p.meta = meta;
     {
-        const int total = p.Tpad * H;
-        att_pack_meta_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, c.stream>>>(lse, dscale, span_start, span_finish, T, p.Tpad, H,
+        const int total = Tpad * H;
+        att_pack_meta_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, c.stream>>>(lse, dscale, span_start, span_finish, T, Tpad, H,
                                                                                   att_dot_scale_tc() * 0.693147f, meta);
         TS2_CHECK_LAUNCH();
     }
     p.out = dq;
-    if ((rc = launch_bwd_tc<0>(c, q, dout, k, v, p)) != TS2_OK)
+    if ((rc = launch_bwd_dq(c, q, dout, k, v, p)) != TS2_OK)
         return rc;
     // dK and dV from one kernel that shares S and the streamed tiles (kernels_att_bwd_kv_tc.cu)
-    return attention_backward_kv_tc(c, q, k, v, dout, meta, p.Tpad, rev_first, rev_last, T, H, slope, dk, dv);
+    return attention_backward_kv_tc(c, q, k, v, dout, meta, Tpad, rev_first, rev_last, T, H, slope, dk, dv);
 }
 
 } // namespace ts2
