@@ -308,15 +308,16 @@ int ts2_moe_route(int device, const float *logits, int T, int expert_count, int 
  * Fp16AttGradQ, Fp16AttGradKV, src/gpt/compute/gpu_att_fp16.cu:41-215, gpu_att_fp16.cuh:60-358.
  * q (normalized, rotated), k (rotated), v (normalized), o, dout: fp16 [T][128*head_count] on the
  * device; lse[T][head_count] = maxDP + log2(sumWeight); dscale[T][head_count] = sum(dout * o);
- * dq, dk, dv fp32 [T][128*head_count]; span arrays are host arrays.  variant 2: tcgen05 kernels
- * (what the engine runs); 0: mma.sync kernels; 1: warp-per-row fp32 formulation (0 and 1 are second
- * opinions for the tests). */
+ * dq, dk, dv fp32 [T][128*head_count]; span arrays are host arrays.  variant 2: tcgen05 kernels;
+ * 3 (backward only): the same kernels with dq, dk, dv written as fp16, the form the engine runs
+ * (its next kernel reads them once); 0: mma.sync kernels; 1: warp-per-row fp32 formulation (0 and
+ * 1 are second opinions for the tests). */
 int ts2_attention_forward(int device, void *stream, int variant, const void *q, const void *k, const void *v,
                           const int32_t *span_start, const int32_t *span_finish, int T, int head_count, float alibi_slope,
                           void *o, float *lse);
 int ts2_attention_backward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const void *dout,
                            const float *lse, const float *dscale, const int32_t *span_start, const int32_t *span_finish, int T,
-                           int head_count, float alibi_slope, float *dq, float *dk, float *dv);
+                           int head_count, float alibi_slope, void *dq, void *dk, void *dv);
 
 #ifdef __cplusplus
 }

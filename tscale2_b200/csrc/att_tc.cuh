@@ -17,7 +17,8 @@ static constexpr int P_BYTES = TC_BM * TC_BN * 2;   // 16 KB: one atom of 128 ro
 
 // dK and dV together (kernels_att_bwd_kv_tc.cu); meta: the packed per-node records of att_pack_meta_kernel
 int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float4 *meta,
-                             int Tpad, const int *rev_first, const int *rev_last, int T, int H, float slope, float *dk, float *dv);
+                             int Tpad, const int *rev_first, const int *rev_last, int T, int H, float slope, void *dk, void *dv,
+                             bool out16);
 
 __host__ __device__ inline float att_dot_scale_tc() { return sqrtf(1.0f / 128) * (0.5f / 0.693147f) * 1.0f; }
 

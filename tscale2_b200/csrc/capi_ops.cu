@@ -314,7 +314,7 @@ int ts2_attention_forward(int device, void *stream, int variant, const void *q, 
 
 int ts2_attention_backward(int device, void *stream, int variant, const void *q, const void *k, const void *v, const void *dout,
                            const float *lse, const float *dscale, const int32_t *span_start, const int32_t *span_finish, int T,
-                           int head_count, float alibi_slope, float *dq, float *dk, float *dv)
+                           int head_count, float alibi_slope, void *dq, void *dk, void *dv)
 {
     if (T <= 0 || head_count <= 0 || !q || !k || !v || !dout || !lse || !dscale || !span_start || !span_finish || !dq || !dk || !dv)
         return fail(TS2_ERR_INVALID_ARG, "ts2_attention_backward: bad arguments");
@@ -330,12 +330,14 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
     c.device = device;
     c.stream = (cudaStream_t)stream;
     const __half *Q = (const __half *)q, *K = (const __half *)k, *V = (const __half *)v, *DO = (const __half *)dout;
-    int rc = variant == 2 ? attention_backward_tc(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
-                                                  dq, dk, dv)
+    float *fq = (float *)dq, *fk = (float *)dk, *fv = (float *)dv;
+    int rc = variant == 2 || variant == 3
+                 ? attention_backward_tc(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope, dq, dk, dv,
+                                         variant == 3)
              : variant == 0 ? attention_backward_mma(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count, alibi_slope,
-                                                   dq, dk, dv)
+                                                   fq, fk, fv)
                           : attention_backward_rowwise(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count,
-                                                       alibi_slope, dq, dk, dv);
+                                                       alibi_slope, fq, fk, fv);
     cudaStreamSynchronize(c.stream);
     cudaFree(d);
     return rc;

@@ -60,17 +60,18 @@ int softmax_ce(const Ctx &c, __half *logits, int rows, int V, const float *bias,
 int att_post_forward(const Ctx &c, const __half *qkvg, const float *rope, int T, int H, __half *q, __half *k, __half *v, float *qscale,
                      float *vscale);
 // inverse of the above for gradients (layer_att.cu:464-470): writes d4[:, 0:3Q] (fast)
-int att_post_backward(const Ctx &c, const float *dq, const float *dk, const float *dv, const __half *q, const __half *v,
+// grads16: dq, dk, dv are fp16 (the tcgen05 attention kernels' engine form) instead of fp32
+int att_post_backward(const Ctx &c, const void *dq, const void *dk, const void *dv, bool grads16, const __half *q, const __half *v,
                       const float *qscale, const float *vscale, const float *rope, const float *sko_k, int T, int H, void *d4);
 int fill_rope(const Ctx &c, float *rope, int T);
 
 // attention over one span per node (ComputeValLookup / GradQ / GradK, layer_att_reference.h:41-212)
-// o [T][Q] fp16, lse [T][H] = maxDP + log2(sumWeight)
+// o [T][Q] fp16, lse [T][H] = maxDP + log2(sumWeight); dq, dk, dv fp32, or fp16 with grads16
 int attention_forward(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
                       int T, int H, float slope, __half *o, float *lse);
 int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
                        const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                       int T, int H, float slope, float *dq, float *dk, float *dv);
+                       int T, int H, float slope, void *dq, void *dk, void *dv, bool grads16 = false);
 
 // the two formulations behind attention_forward / attention_backward
 int attention_forward_mma(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start, const int *span_finish,
@@ -82,7 +83,7 @@ int attention_forward_tc(const Ctx &c, const __half *q, const __half *k, const _
                          int T, int H, float slope, __half *o, float *lse);
 int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
                           const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                          int T, int H, float slope, float *dq, float *dk, float *dv);
+                          int T, int H, float slope, void *dq, void *dk, void *dv, bool grads16 = false);
 int attention_forward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const int *span_start,
                               const int *span_finish, int T, int H, float slope, __half *o, float *lse);
 int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,

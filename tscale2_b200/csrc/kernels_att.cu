@@ -110,8 +110,22 @@ int att_post_forward(const Ctx &c, const __half *qkvg, const float *rope, int T,
     return TS2_OK;
 }
 
-template <int FT>
-__global__ void att_post_backward_kernel(const float *__restrict__ dq, const float *__restrict__ dk, const float *__restrict__ dv,
+// GT: type of the incoming gradients (float or __half)
+template <typename GT>
+__device__ __forceinline__ float4 load_grad4(const GT *p);
+template <>
+__device__ __forceinline__ float4 load_grad4<float>(const float *p)
+{
+    return *(const float4 *)p;
+}
+template <>
+__device__ __forceinline__ float4 load_grad4<__half>(const __half *p)
+{
+    return load_half4(p);
+}
+
+template <int FT, typename GT>
+__global__ void att_post_backward_kernel(const GT *__restrict__ dq, const GT *__restrict__ dk, const GT *__restrict__ dv,
                                          const __half *__restrict__ q, const __half *__restrict__ v, const float *__restrict__ qscale,
                                          const float *__restrict__ vscale, const float *__restrict__ rope,
                                          const float *__restrict__ sko_k, int T, int H, void *__restrict__ d4)
@@ -136,10 +150,10 @@ __global__ void att_post_backward_kernel(const float *__restrict__ dq, const flo
             const float4 z = make_float4(0, 0, 0, 0);
             cs[r] = ok[r] ? *(const float4 *)(rope + t[r] * 128 + lane * 4) : z;
             qv[r] = ok[r] ? load_half4(q + t[r] * Q + off[r]) : z;
-            gq[r] = ok[r] ? *(const float4 *)(dq + t[r] * Q + off[r]) : z;
-            gk[r] = ok[r] ? *(const float4 *)(dk + t[r] * Q + off[r]) : z;
+            gq[r] = ok[r] ? load_grad4<GT>(dq + t[r] * Q + off[r]) : z;
+            gk[r] = ok[r] ? load_grad4<GT>(dk + t[r] * Q + off[r]) : z;
             vv[r] = ok[r] ? load_half4(v + t[r] * Q + off[r]) : z;
-            gv[r] = ok[r] ? *(const float4 *)(dv + t[r] * Q + off[r]) : z;
+            gv[r] = ok[r] ? load_grad4<GT>(dv + t[r] * Q + off[r]) : z;
             sq[r] = ok[r] ? qscale[t[r] * H + h] : 0.f;
             sv[r] = ok[r] ? vscale[t[r] * H + h] : 0.f;
         }
@@ -164,14 +178,22 @@ __global__ void att_post_backward_kernel(const float *__restrict__ dq, const flo
     }
 }
 
-int att_post_backward(const Ctx &c, const float *dq, const float *dk, const float *dv, const __half *q, const __half *v,
+int att_post_backward(const Ctx &c, const void *dq, const void *dk, const void *dv, bool grads16, const __half *q, const __half *v,
                       const float *qscale, const float *vscale, const float *rope, const float *sko_k, int T, int H, void *d4)
 {
     const int grid = grid_for(c, (long long)T * H);
-    if (c.ft == 0)
-        att_post_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(dq, dk, dv, q, v, qscale, vscale, rope, sko_k, T, H, d4);
+#define TS2_POST_BWD(FT_, GT_)                                                                                                         \
+    att_post_backward_kernel<FT_, GT_><<<grid, THREADS, 0, c.stream>>>((const GT_ *)dq, (const GT_ *)dk, (const GT_ *)dv, q, v, qscale, \
+                                                                       vscale, rope, sko_k, T, H, d4)
+    if (c.ft == 0 && grads16)
+        TS2_POST_BWD(0, __half);
+    else if (c.ft == 0)
+        TS2_POST_BWD(0, float);
+    else if (grads16)
+        TS2_POST_BWD(1, __half);
     else
-        att_post_backward_kernel<1><<<grid, THREADS, 0, c.stream>>>(dq, dk, dv, q, v, qscale, vscale, rope, sko_k, T, H, d4);
+        TS2_POST_BWD(1, float);
+#undef TS2_POST_BWD
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
@@ -294,9 +316,10 @@ int attention_forward(const Ctx &c, const __half *q, const __half *k, const __ha
 
 int attention_backward(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
                        const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                       int T, int H, float slope, float *dq, float *dk, float *dv)
+                       int T, int H, float slope, void *dq, void *dk, void *dv, bool grads16)
 {
-    return attention_backward_tc(c, q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H, slope, dq, dk, dv);
+    return attention_backward_tc(c, q, k, v, dout, lse, dscale, span_start, span_finish, rev_first, rev_last, T, H, slope, dq, dk, dv,
+                                 grads16);
 }
 
 } // namespace ts2

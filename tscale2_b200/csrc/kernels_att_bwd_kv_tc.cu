@@ -33,10 +33,12 @@ struct AttBwdKvParams {
     float slope;
     const int *rev_first, *rev_last;
     const float4 *meta; // [H][Tpad]: {-lse, -dscale * c2, span start, span length} per node
-    float *dk, *dv;     // fp32 [T][128 H]
+    void *dk, *dv;      // fp32 or fp16 [T][128 H]
     int32_t *status;
 };
 
+// OUT16: the gradients are written as fp16 (what the engine feeds its next kernel with) instead of fp32
+template <bool OUT16>
 __global__ void __launch_bounds__(KV_THREADS, 1)
     att_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
@@ -247,6 +249,38 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
             ok = mbar_wait(all_done, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
+        if constexpr (OUT16) {
+            // fp16: parts 0, 1 take the two 64-column halves of dK, parts 2, 3 those of dV: 32 rows x 128 bytes per warp
+            const int which = part >> 1, hc = part & 1;
+            uint8_t *blk = smem + KV_STAGE_OFF + (warp - 4) * 4096, *srow = blk + lane * 128;
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t r[32];
+                if (n > 0 && ok) {
+                    tmem_ld32((which ? tDV : tDK) + lane_addr + hc * 64 + cc * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        r[i] = 0u;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                  h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                  h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                  h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                    *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) =
+                        make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(which ? (const void *)&tmDV : (const void *)&tmDK, smem_u32(blk), col0 + hc * 64, r0 + quarter * 32);
+                bulk_commit();
+            }
+        } else
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
             uint32_t r[32];
@@ -281,11 +315,13 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
 }
 
 int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float4 *meta,
-                             int Tpad, const int *rev_first, const int *rev_last, int T, int H, float slope, float *dk, float *dv)
+                             int Tpad, const int *rev_first, const int *rev_last, int T, int H, float slope, void *dk, void *dv,
+                             bool out16)
 {
     static bool configured[16] = {};
     if (!configured[c.device & 15]) {
-        TS2_CUDA(cudaFuncSetAttribute(att_bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
+        TS2_CUDA(cudaFuncSetAttribute(att_bwd_kv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
+        TS2_CUDA(cudaFuncSetAttribute(att_bwd_kv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
         configured[c.device & 15] = true;
     }
     const int Q = H * TC_HD;
@@ -299,10 +335,10 @@ int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, con
         return rc;
     if ((rc = make_tensor_map(&tDO, dout, 2, Q, T, Q, TC_BN)) != TS2_OK)
         return rc;
-    // outputs: boxes of 32 fp32 columns x 32 rows
-    if ((rc = make_tensor_map(&tDK, dk, 4, Q, T, Q, 32)) != TS2_OK)
+    // outputs: boxes of 128 bytes (32 fp32 or 64 fp16 columns) x 32 rows
+    if ((rc = make_tensor_map(&tDK, dk, out16 ? 2 : 4, Q, T, Q, 32)) != TS2_OK)
         return rc;
-    if ((rc = make_tensor_map(&tDV, dv, 4, Q, T, Q, 32)) != TS2_OK)
+    if ((rc = make_tensor_map(&tDV, dv, out16 ? 2 : 4, Q, T, Q, 32)) != TS2_OK)
         return rc;
     AttBwdKvParams p;
     p.T = T;
@@ -318,7 +354,10 @@ int attention_backward_kv_tc(const Ctx &c, const __half *q, const __half *k, con
     if (!p.status)
         return fail(TS2_ERR_CUDA, "attention: no device status word");
     dim3 grid((unsigned)ceil_div(T, TC_BM), (unsigned)H);
-    att_bwd_kv_tc_kernel<<<grid, KV_THREADS, KV_SMEM, c.stream>>>(tK, tV, tQ, tDO, tDK, tDV, p);
+    if (out16)
+        att_bwd_kv_tc_kernel<true><<<grid, KV_THREADS, KV_SMEM, c.stream>>>(tK, tV, tQ, tDO, tDK, tDV, p);
+    else
+        att_bwd_kv_tc_kernel<false><<<grid, KV_THREADS, KV_SMEM, c.stream>>>(tK, tV, tQ, tDO, tDK, tDV, p);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

@@ -25,7 +25,7 @@ struct AttBwdParams {
     float slope;
     const int *span_start, *span_finish;
     const float *lse, *dscale;
-    float *out; // dq: fp32 [T][128 H]
+    void *out; // dq: fp32 or fp16 [T][128 H]
     int32_t *status;
 };
 
@@ -59,6 +59,8 @@ __global__ void att_pack_meta_kernel(const float *__restrict__ lse, const float 
     meta[idx] = m;
 }
 
+// OUT16: dQ is written as fp16 (what the engine feeds its next kernel with) instead of fp32
+template <bool OUT16>
 __global__ void __launch_bounds__(BW_THREADS, 1)
     att_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
                       const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
@@ -280,6 +282,35 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         // c ^ (r & 7)), and one TMA store: direct stores would write 16 bytes into each of 32 different lines per
         // instruction.  Rows past T are clipped by the TMA unit.
         uint8_t *blk = smem + L::A1_OFF + b * Q_BYTES + ((warp - 4) & 7) * 4096, *srow = blk + lane * 128;
+        if constexpr (OUT16) { // this warp's 64 columns as fp16: one block of 32 rows x 128 bytes, one store
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t r[32];
+                if (k > 0 && ok) {
+                    tmem_ld32(tACC + (2 * half + cc) * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        r[i] = 0u;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                  h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                  h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                  h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                    *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) =
+                        make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&tmOut, smem_u32(blk), col0 + half * 64, r0 + b * TC_BM + quarter * 32);
+                bulk_commit();
+            }
+        } else
 #pragma unroll 1
         for (int c = 2 * half; c < 2 * half + 2; ++c) {
             uint32_t r[32];
@@ -316,12 +347,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
 }
 
 // a1 = Q, a2 = dO (resident), b1 = K, b2 = V (streamed)
-static int launch_bwd_dq(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p)
+static int launch_bwd_dq(const Ctx &c, const __half *a1, const __half *a2, const __half *b1, const __half *b2, const AttBwdParams &p,
+                         bool out16)
 {
-    auto kern = att_bwd_dq_tc_kernel;
+    auto kern = out16 ? att_bwd_dq_tc_kernel<true> : att_bwd_dq_tc_kernel<false>;
     static bool configured[16] = {};
     if (!configured[c.device & 15]) {
-        TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout::SMEM));
+        TS2_CUDA(cudaFuncSetAttribute(att_bwd_dq_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout::SMEM));
+        TS2_CUDA(cudaFuncSetAttribute(att_bwd_dq_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdLayout::SMEM));
         configured[c.device & 15] = true;
     }
     const int Q = p.H * TC_HD;
@@ -335,7 +368,7 @@ static int launch_bwd_dq(const Ctx &c, const __half *a1, const __half *a2, const
         return rc;
     if ((rc = make_tensor_map(&tB2, b2, 2, Q, p.T, Q, TC_BN)) != TS2_OK)
         return rc;
-    if ((rc = make_tensor_map(&tOut, p.out, 4, Q, p.T, Q, 32)) != TS2_OK) // boxes of 32 fp32 columns x 32 rows
+    if ((rc = make_tensor_map(&tOut, p.out, out16 ? 2 : 4, Q, p.T, Q, 32)) != TS2_OK) // boxes of 128 bytes x 32 rows
         return rc;
     dim3 grid((unsigned)ceil_div(p.T, BW_ROWS), (unsigned)p.H);
     kern<<<grid, BW_THREADS, BwdLayout::SMEM, c.stream>>>(tA1, tA2, tB1, tB2, tOut, p);
@@ -368,7 +401,7 @@ static int meta_buffer(int device, size_t bytes, float4 **out)
 
 int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const __half *v, const __half *dout, const float *lse,
                           const float *dscale, const int *span_start, const int *span_finish, const int *rev_first, const int *rev_last,
-                          int T, int H, float slope, float *dq, float *dk, float *dv)
+                          int T, int H, float slope, void *dq, void *dk, void *dv, bool grads16)
 {
     AttBwdParams p;
     p.T = T;
@@ -393,10 +426,10 @@ int attention_backward_tc(const Ctx &c, const __half *q, const __half *k, const 
         TS2_CHECK_LAUNCH();
     }
     p.out = dq;
-    if ((rc = launch_bwd_dq(c, q, dout, k, v, p)) != TS2_OK)
+    if ((rc = launch_bwd_dq(c, q, dout, k, v, p, grads16)) != TS2_OK)
         return rc;
     // dK and dV from one kernel that shares S and the streamed tiles (kernels_att_bwd_kv_tc.cu)
-    return attention_backward_kv_tc(c, q, k, v, dout, meta, Tpad, rev_first, rev_last, T, H, slope, dk, dv);
+    return attention_backward_kv_tc(c, q, k, v, dout, meta, Tpad, rev_first, rev_last, T, H, slope, dk, dv, grads16);
 }
 
 } // namespace ts2

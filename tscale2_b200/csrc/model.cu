@@ -115,7 +115,8 @@ struct ts2_model {
     int chunk = 0;
     __half *drg = nullptr, *dout = nullptr;
     void *dcat = nullptr;
-    float *dscale = nullptr, *dq = nullptr, *dk = nullptr, *dv = nullptr;
+    float *dscale = nullptr;
+    __half *dq = nullptr, *dk = nullptr, *dv = nullptr; // attention gradients, fp16 between the attention core and its post-kernel
     float *rope = nullptr;
     // mixture-of-experts scratch shared by the layers
     int E = 0, K = 0, X = 0, epad = 0, moe_rows = 0;
@@ -855,8 +856,8 @@ int backward(ts2_model *m)
         if (ly.type == TS2_LAYER_ATT) {
             M_TRY(att_gate_backward(c, m->drg, ly.cat16, ly.o, T, W, m->dcat, m->dout, m->dscale));
             M_TRY(attention_backward(c, ly.q, ly.k, ly.v, m->dout, ly.lse, m->dscale, b.span_start[ly.att_type], b.span_finish[ly.att_type],
-                                     b.rev_first[ly.att_type], b.rev_last[ly.att_type], T, H, ly.slope, m->dq, m->dk, m->dv));
-            M_TRY(att_post_backward(c, m->dq, m->dk, m->dv, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
+                                     b.rev_first[ly.att_type], b.rev_last[ly.att_type], T, H, ly.slope, m->dq, m->dk, m->dv, true));
+            M_TRY(att_post_backward(c, m->dq, m->dk, m->dv, true, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
                                     m->dcat));
         } else {
             M_TRY(ffn_act_backward(c, m->drg, ly.cat16, ly.cat16, 2 * W, ly.wscale, T, W, m->dcat));
