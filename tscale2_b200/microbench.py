@@ -4,6 +4,7 @@ shapes of BASELINE config 2 (backward GEMM microbench) or any other shape, and t
     python -m tscale2_b200.microbench --op dx --prec fp8 --M 16384 --N 4096 --K 4096
     python -m tscale2_b200.microbench --op dw --prec int8 --M 4096 --N 4096 --K 16384   # dW[M][N], K tokens
     python -m tscale2_b200.microbench --op config2
+    python -m tscale2_b200.microbench --op att --T 16384 --heads 12 --variant 3      # attention forward + backward
 
 Times with CUDA events around each launch on the launching stream (ts2_set_kernel_timing); operands are
 random bytes of the operand format (no NaN codes), larger than L2 for the config-2 shapes.  One JSON line
@@ -60,9 +61,49 @@ def time_gemm(lib, op, prec_name, M, N, K, iters, warmup=3):
             else "C[M][N] = A[M][K] . B[N][K]^T"}
 
 
+def time_attention(lib, T, heads, variant, iters, warmup=2, doc=1024):
+    """Forward and backward attention core over documents of `doc` tokens with a causal window of the same length.
+    The times include the entry points' host work (span upload, reverse ranges): the kernels' own times are what a
+    profiler run of this command shows."""
+    import time
+    rng = np.random.default_rng(1)
+    Q = heads * 128
+    q, k, v, do = (DeviceBuffer.from_numpy(rng.standard_normal((T, Q)).astype(np.float16)) for _ in range(4))
+    o, lse, dsc = DeviceBuffer(T * Q * 2), DeviceBuffer(T * heads * 4), DeviceBuffer.from_numpy(np.zeros((T, heads), np.float32))
+    gb = 2 if variant == 3 else 4
+    dq, dk, dv = (DeviceBuffer(T * Q * gb) for _ in range(3))
+    t = np.arange(T)
+    start = np.maximum((t // doc) * doc, t - doc).astype(np.int32)
+    finish = (t - 1).astype(np.int32)
+    none = finish < start
+    start[none], finish[none] = 0, -1
+    ip = lambda a: a.ctypes.data_as(C.c_void_p)
+
+    def fwd():
+        check(lib.ts2_attention_forward(0, None, min(variant, 2), q.ptr, k.ptr, v.ptr, ip(start), ip(finish), T, heads, 0.0, o.ptr, lse.ptr))
+
+    def bwd():
+        check(lib.ts2_attention_backward(0, None, variant, q.ptr, k.ptr, v.ptr, do.ptr, lse.ptr, dsc.ptr, ip(start), ip(finish), T, heads,
+                                         0.0, dq.ptr, dk.ptr, dv.ptr))
+    out = {"op": "att", "T": T, "heads": heads, "variant": variant, "doc": doc}
+    for name, f in (("forward", fwd), ("backward", bwd)):
+        for _ in range(warmup):
+            f()
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            f()
+        sync()
+        out[name + "_ms_incl_host"] = (time.perf_counter() - t0) * 1e3 / iters
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="config2", choices=["dx", "tn", "dw", "config2"])
+    ap.add_argument("--op", default="config2", choices=["dx", "tn", "dw", "config2", "att"])
+    ap.add_argument("--T", type=int, default=16384)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--variant", type=int, default=3, choices=[0, 1, 2, 3])
     ap.add_argument("--prec", default="fp8", choices=sorted(PREC))
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=4096)
@@ -71,7 +112,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     lib = capi.load_library()
-    if args.op == "config2":
+    if args.op == "att":
+        print(json.dumps(time_attention(lib, args.T, args.heads, args.variant, args.iters, args.warmup)))
+    elif args.op == "config2":
         # BASELINE config 2: T = 16384 tokens, 4096 x 4096 weights: dX = dY.W^T (M=T, N=in, K=out), dW = X^T.dY (K = T)
         for prec in ("fp8", "int8", "f16"):
             print(json.dumps(time_gemm(lib, "dx", prec, 16384, 4096, 4096, args.iters, args.warmup)), flush=True)
