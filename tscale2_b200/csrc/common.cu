@@ -1,7 +1,9 @@
 // Library-wide state: last error, launch counter, per-device status word.
 #include "common.cuh"
 #include <cstdarg>
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace ts2 {
 
@@ -44,6 +46,21 @@ int sm_count(int device)
         c = v;
     }
     return c;
+}
+
+int resident_blocks(int device, const void *kernel, int threads)
+{
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, int> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find({kernel, threads * 16 + (device & 15)});
+    if (it != cache.end())
+        return it->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1)
+        n = 1;
+    cache[{kernel, threads * 16 + (device & 15)}] = n;
+    return n;
 }
 
 int32_t *device_status_word(int device)

@@ -39,6 +39,8 @@ int fail(int code, const char *fmt, ...);
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count(int device);
+// blocks of `threads` threads (no dynamic shared memory) of this kernel that one SM holds at once (>= 1)
+int resident_blocks(int device, const void *kernel, int threads);
 
 // A word in device memory that kernels OR error bits into instead of trapping
 // or spinning forever; read by the host after synchronizing.

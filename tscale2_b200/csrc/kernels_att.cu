@@ -21,6 +21,17 @@ static int grid_for(const Ctx &c, long long warp_items)
     return (int)std::max<long long>(1, std::min(blocks, cap));
 }
 
+// for the grid-stride kernels that carry most of the bytes: exactly the blocks that are resident at once.  With a
+// fixed 8 blocks per SM a kernel that fits 5 (48 registers) ran a second, partly filled wave at a fraction of the
+// bandwidth.
+template <typename K>
+static int grid_for(const Ctx &c, K kernel, long long warp_items)
+{
+    long long blocks = ceil_div(warp_items, WARPS);
+    long long cap = (long long)sm_count(c.device) * resident_blocks(c.device, (const void *)kernel, THREADS);
+    return (int)std::max<long long>(1, std::min(blocks, cap));
+}
+
 #define WARP_BATCH_LOOP(total, R)                                                             \
     const int lane = threadIdx.x & 31;                                                        \
     const unsigned wstride = gridDim.x * WARPS, total_items = (unsigned)(total);             \
@@ -105,7 +116,7 @@ __global__ void att_post_forward_kernel(const __half *__restrict__ qkvg, const f
 int att_post_forward(const Ctx &c, const __half *qkvg, const float *rope, int T, int H, __half *q, __half *k, __half *v, float *qscale,
                      float *vscale)
 {
-    att_post_forward_kernel<<<grid_for(c, (long long)T * H), THREADS, 0, c.stream>>>(qkvg, rope, T, H, q, k, v, qscale, vscale);
+    att_post_forward_kernel<<<grid_for(c, att_post_forward_kernel, (long long)T * H), THREADS, 0, c.stream>>>(qkvg, rope, T, H, q, k, v, qscale, vscale);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
@@ -181,10 +192,10 @@ __global__ void att_post_backward_kernel(const GT *__restrict__ dq, const GT *__
 int att_post_backward(const Ctx &c, const void *dq, const void *dk, const void *dv, bool grads16, const __half *q, const __half *v,
                       const float *qscale, const float *vscale, const float *rope, const float *sko_k, int T, int H, void *d4)
 {
-    const int grid = grid_for(c, (long long)T * H);
-#define TS2_POST_BWD(FT_, GT_)                                                                                                         \
-    att_post_backward_kernel<FT_, GT_><<<grid, THREADS, 0, c.stream>>>((const GT_ *)dq, (const GT_ *)dk, (const GT_ *)dv, q, v, qscale, \
-                                                                       vscale, rope, sko_k, T, H, d4)
+#define TS2_POST_BWD(FT_, GT_)                                                                                          \
+    att_post_backward_kernel<FT_, GT_><<<grid_for(c, att_post_backward_kernel<FT_, GT_>, (long long)T * H), THREADS, 0, \
+                                         c.stream>>>((const GT_ *)dq, (const GT_ *)dk, (const GT_ *)dv, q, v, qscale, vscale, \
+                                                     rope, sko_k, T, H, d4)
     if (c.ft == 0 && grads16)
         TS2_POST_BWD(0, __half);
     else if (c.ft == 0)

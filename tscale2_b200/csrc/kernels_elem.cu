@@ -18,6 +18,17 @@ static int grid_for(const Ctx &c, long long warp_items)
     return (int)std::max<long long>(1, std::min(blocks, cap));
 }
 
+// for the grid-stride kernels that carry most of the bytes: exactly the blocks that are resident at once.  With a
+// fixed 8 blocks per SM a kernel that fits 5 (48 registers) ran a second, partly filled wave at a fraction of the
+// bandwidth.
+template <typename K>
+static int grid_for(const Ctx &c, K kernel, long long warp_items)
+{
+    long long blocks = ceil_div(warp_items, WARPS);
+    long long cap = (long long)sm_count(c.device) * resident_blocks(c.device, (const void *)kernel, THREADS);
+    return (int)std::max<long long>(1, std::min(blocks, cap));
+}
+
 // R items per warp and iteration: all loads of the R items are issued before any of them is
 // consumed, which keeps enough bytes in flight per SM to approach HBM bandwidth
 #define WARP_BATCH_LOOP(total, R)                                                                          \
@@ -122,7 +133,8 @@ __global__ void tilenorm_forward_kernel(const float *__restrict__ x, int T, int 
 
 int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, __half *n16)
 {
-    const int grid = grid_for(c, (long long)T * (D / TILE));
+    const int grid = c.ft == 0 ? grid_for(c, tilenorm_forward_kernel<0>, (long long)T * (D / TILE))
+                               : grid_for(c, tilenorm_forward_kernel<1>, (long long)T * (D / TILE));
     if (c.ft == 0)
         tilenorm_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
     else
@@ -189,7 +201,7 @@ __global__ void tilenorm_backward_kernel(const float *__restrict__ x, const floa
 int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float *dyn, float dn_alpha, int T, int D, float *g, bool add,
                       unsigned *absmax)
 {
-    tilenorm_backward_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(x, dn, dyn, dn_alpha, T, D, g, add ? 1 : 0,
+    tilenorm_backward_kernel<<<grid_for(c, tilenorm_backward_kernel, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(x, dn, dyn, dn_alpha, T, D, g, add ? 1 : 0,
                                                                                           absmax);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
@@ -234,7 +246,8 @@ int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, vo
               float *fscale)
 {
     const size_t n4 = n / 4;
-    const int grid = (int)std::min<size_t>(ceil_div(n4, THREADS), (size_t)sm_count(c.device) * 8);
+    const int per_sm = resident_blocks(c.device, c.ft == 0 ? (const void *)cast_grad_kernel<0> : (const void *)cast_grad_kernel<1>, THREADS);
+    const int grid = (int)std::min<size_t>(ceil_div(n4, THREADS), (size_t)sm_count(c.device) * per_sm);
     if (c.ft == 0)
         cast_grad_kernel<0><<<grid, THREADS, 0, c.stream>>>(g, n4, absmax, g_fast, ginv, f_static, sko, fscale);
     else
@@ -292,7 +305,8 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
 int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, int what_ld, const float *wscale, int T, int F,
                      void *d2)
 {
-    const int grid = grid_for(c, (long long)T * (F / TILE));
+    const int grid = c.ft == 0 ? grid_for(c, ffn_act_backward_kernel<0>, (long long)T * (F / TILE))
+                               : grid_for(c, ffn_act_backward_kernel<1>, (long long)T * (F / TILE));
     if (c.ft == 0)
         ffn_act_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, wg, what, what_ld, wscale, T, F, d2);
     else
@@ -336,7 +350,8 @@ __global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const _
 
 int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg)
 {
-    const int grid = grid_for(c, (long long)T * (Q / TILE));
+    const int grid = c.ft == 0 ? grid_for(c, att_gate_forward_kernel<0>, (long long)T * (Q / TILE))
+                               : grid_for(c, att_gate_forward_kernel<1>, (long long)T * (Q / TILE));
     if (c.ft == 0)
         att_gate_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
     else
@@ -389,7 +404,8 @@ __global__ void att_gate_backward_kernel(const __half *__restrict__ drg, const _
 int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const __half *o, int T, int Q, void *d4, __half *dout,
                       float *dscale)
 {
-    const int grid = grid_for(c, (long long)T * (Q / TILE));
+    const int grid = c.ft == 0 ? grid_for(c, att_gate_backward_kernel<0>, (long long)T * (Q / TILE))
+                               : grid_for(c, att_gate_backward_kernel<1>, (long long)T * (Q / TILE));
     if (c.ft == 0)
         att_gate_backward_kernel<0><<<grid, THREADS, 0, c.stream>>>(drg, qkvg, o, T, Q, d4, dout, dscale);
     else
