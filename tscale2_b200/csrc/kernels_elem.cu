@@ -589,17 +589,22 @@ __global__ void __launch_bounds__(1024, 1)
         if ((tid & 31) == 0)
             red[tid >> 5] = mx;
         __syncthreads();
-        mx = 0.f;
-        for (int i = 0; i < nthr / 32; ++i)
-            mx = fmaxf(mx, red[i]);
+        mx = warp_max((tid & 31) < nthr / 32 ? red[tid & 31] : 0.f); // at most 32 warps: one partial per lane
         __syncthreads();
         float sum0 = 0.f, sum1 = 0.f;
+        // the bias vector (4 bytes per logit, as many bytes as two rows) comes from L2 every row: the loads of the next
+        // vector are issued before this one's arithmetic
+        float4 nb0 = make_float4(0, 0, 0, 0), nb1 = nb0;
+        if (bias && tid < nvec)
+            nb0 = __ldg((const float4 *)(bias + 8 * tid)), nb1 = __ldg((const float4 *)(bias + 8 * tid) + 1);
         for (int i = tid; i < nvec; i += nthr) {
             uint4 raw = row_s4[i];
             __half2 *h = (__half2 *)&raw;
             float bv[8];
             if (bias) {
-                const float4 b0 = __ldg((const float4 *)(bias + 8 * i)), b1 = __ldg((const float4 *)(bias + 8 * i) + 1);
+                const float4 b0 = nb0, b1 = nb1;
+                if (i + nthr < nvec)
+                    nb0 = __ldg((const float4 *)(bias + 8 * (i + nthr))), nb1 = __ldg((const float4 *)(bias + 8 * (i + nthr)) + 1);
                 bv[0] = b0.x, bv[1] = b0.y, bv[2] = b0.z, bv[3] = b0.w, bv[4] = b1.x, bv[5] = b1.y, bv[6] = b1.z, bv[7] = b1.w;
             }
             if (i == (tgt >> 3)) { // the vector that holds the target's logit: keep it before it is overwritten
@@ -625,9 +630,7 @@ __global__ void __launch_bounds__(1024, 1)
         if ((tid & 31) == 0)
             red[tid >> 5] = sum;
         __syncthreads();
-        sum = 0.f;
-        for (int i = 0; i < nthr / 32; ++i)
-            sum += red[i];
+        sum = warp_sum((tid & 31) < nthr / 32 ? red[tid & 31] : 0.f);
         const float inv = 1.f / sum;
         if (tid == 0)
             atomicAdd(logp_sum, (x_tgt_s - mx) * 0.69314718f - logf(sum));

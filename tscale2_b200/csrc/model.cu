@@ -102,6 +102,7 @@ struct ts2_model {
     float *w_flat = nullptr, *avg_flat = nullptr, *grad_flat = nullptr;
     float *skos = nullptr; // [n_mats]
     float *bias = nullptr;
+    bool has_bias = false; // a model created without a bias vector skips the loads (the buffer then holds zeros)
     __half *embed16 = nullptr;
     void *Wf = nullptr;      // [V][D] fast
     __half *WfT16 = nullptr; // [D][V]
@@ -470,6 +471,7 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         TS2_CUDA(cudaMemcpyAsync(mt.w, mats[i].data, (size_t)mt.x * mt.y * 4, cudaMemcpyHostToDevice, m->stream));
     }
     M_TRY(dalloc(m, &m->bias, m->V));
+    m->has_bias = bias != nullptr;
     if (bias)
         TS2_CUDA(cudaMemcpyAsync(m->bias, bias, (size_t)m->V * 4, cudaMemcpyHostToDevice, m->stream));
     else
@@ -723,7 +725,7 @@ int final_layer(ts2_model *m, bool backward)
         e.dyn_scale = m->mats[1].sko;
         e.out_kind = TS2_OUT_F16;
         M_TRY(gemm_tn(m, m->kind, rows, V, D, (const uint8_t *)m->nF_fast + (size_t)r0 * D * fs, D, m->Wf, D, m->logits, V, e));
-        M_TRY(softmax_ce(c, m->logits, rows, V, m->bias, m->batch.target + r0, gscale, m->logp, backward));
+        M_TRY(softmax_ce(c, m->logits, rows, V, m->has_bias ? m->bias : nullptr, m->batch.target + r0, gscale, m->logp, backward));
         if (!backward)
             continue;
         // dnF = g . Wf * sqrt(1/D)   (MulBackwardWithAccum, cpu_transformer.cpp:163)
