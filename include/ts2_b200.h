@@ -189,9 +189,35 @@ int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, 
  * ts2_set_debug_taps before the call; costs one copy per layer). */
 int ts2_set_debug_taps(ts2_model *m, int enable);
 /* raw copy of an internal per-layer buffer after the last step, for tests: "rg", "dcat", "cat16", "n_fast",
- * "n_rows", "logits", "ids", "weights", "slot_of", "token_of", "seg_ptr", "moe_g", "drg" (the caller knows the layout) */
+ * "n_rows", "logits", "ids", "weights", "slot_of", "token_of", "seg_ptr", "moe_g", "drg", "capture" (the caller knows the layout) */
 int ts2_debug_read(ts2_model *m, const char *name, int layer, void *dst, int64_t bytes);
 int ts2_get_state_tap(ts2_model *m, int layer, int gradient, float *dst, int64_t n_floats);
+
+/* Step health (no reference counterpart; the reference's trainer only sees a NaN in the averaged training error,
+ * src/gpt/train/train_ctx.cpp:11-31).  first_bad_step[b], b = 0 .. layer_count, is the number (1 = the first
+ * ts2_backprop of this model) of the first step whose state gradient at layer boundary b held a NaN or an infinity,
+ * 0 if that never happened; the flag rides on the abs-max reduction of the norm-backward kernel, so it costs
+ * nothing per step.  reset clears the flags.  steps_so_far (optional) receives the step counter. */
+int ts2_get_step_health(ts2_model *m, int reset, uint32_t *first_bad_step, int n_boundaries, int64_t *steps_so_far);
+/* training error (mean -log p(target), as ts2_avg_train_err) of the last n ts2_backprop calls, oldest first, n <= 256:
+ * every step's loss can be checked after a timed loop without a device read inside it */
+int ts2_get_loss_history(ts2_model *m, float *out_err, int n);
+/* drops an accumulated, not yet applied gradient: the next ts2_backprop starts from zero (the reference reaches the
+ * same state by applying with a zero rate; used by the repeatability tests) */
+int ts2_discard_gradient(ts2_model *m);
+/* Debug trace (no reference counterpart), off by default.  When enabled, every ts2_backprop records for each
+ * intermediate buffer of the step, in stream order, an order-independent checksum (the sum of its 32-bit words as a
+ * 64-bit integer), the number of non-finite elements and the largest finite magnitude (max_abs, optional; 0 for byte
+ * buffers); one extra read pass per buffer.  Two steps from the same
+ * state must give the same checksums for every buffer (the embedding gradient, summed with float atomics, has no
+ * record).  ts2_get_debug_trace returns the number of records of the last step in *count and fills up to `capacity`
+ * entries; ts2_debug_trace_name gives a record's name ("dq[3]" = buffer dq of layer 3). */
+int ts2_set_debug_trace(ts2_model *m, int enable);
+int ts2_get_debug_trace(ts2_model *m, uint64_t *sums, uint64_t *nonfinite, float *max_abs, int capacity, int *count);
+/* with the trace enabled: the buffer behind the record called record_name (NULL or "": none) is also copied aside
+ * during the step, up to max_bytes, and can be read back with ts2_debug_read(m, "capture", 0, dst, bytes) */
+int ts2_set_debug_capture(ts2_model *m, const char *record_name, int64_t max_bytes);
+const char *ts2_debug_trace_name(ts2_model *m, int index);
 
 /* ------------------------------------------------------------------------- */
 /* data-parallel gradient reduction; replaces TMultiDeviceReducer::AllReduce,

@@ -107,3 +107,32 @@ def test_tcgen05_kernels_match_mma_kernels_at_scale():
         for name, a, b in zip(["o", "lse", "dq", "dk", "dv"], got, ref):
             err = np.abs(a - b).max()
             assert err < 2e-2 * max(1.0, np.abs(b).max() / 4), f"{name}: max abs difference {err} (repeat {rep})"
+
+
+def test_fp16_gradients_saturate_instead_of_overflowing():
+    """The engine's form of the backward kernels writes dQ, dK, dV as fp16.  A key that every later node attends to
+    (the first token of a sequence) collects gradients of tens of thousands once the weights have moved, more than
+    fp16 holds: the store must saturate at +-65504, never write an infinity (which the next kernel's differences
+    would turn into NaN and the step into a NaN loss).  Here dout is scaled until dK and dV pass the fp16 range;
+    entries that stay in range must still agree with the fp32 form."""
+    lib = capi.load_library()
+    T, H = 1024, 2
+    rng = np.random.default_rng(11)
+    q, k, v = (rng.standard_normal((T, 128 * H)).astype(np.float16) for _ in range(3))
+    q[:, :] = np.abs(q)  # aligned queries: the sums over the nodes do not cancel
+    dout = (np.abs(rng.standard_normal((T, 128 * H))) * 2000).astype(np.float16)
+    # every node attends to the first eight keys only: each of them sums the contributions of ~1000 nodes
+    t = np.arange(T)
+    start = np.zeros(T, np.int32)
+    finish = np.minimum(t - 1, 7).astype(np.int32)
+    ref = run_device(lib, 2, q, k, v, dout, start, finish, H, 0.0)
+    got = run_device(lib, 3, q, k, v, dout, start, finish, H, 0.0)
+    overflowed = 0
+    for name, a, b in zip(["dq", "dk", "dv"], got[2:], ref[2:]):
+        assert np.isfinite(a).all(), f"{name}: {np.count_nonzero(~np.isfinite(a))} non-finite fp16 outputs"
+        big = np.abs(b) > 65504
+        overflowed += int(big.sum())
+        assert (np.abs(a[big]) == 65504).all(), name
+        assert (np.sign(a[big]) == np.sign(b[big])).all(), name
+        assert rel_l2(a[~big], b[~big]) < 2e-3, name
+    assert overflowed > 0, "the case no longer drives any gradient past the fp16 range"

@@ -269,6 +269,17 @@ __device__ __forceinline__ void pair_barrier(int q)
     }
 }
 
+// fp32 pair -> packed fp16 pair (lo in the low half), round to nearest even; a magnitude above 65504 saturates to
+// +-65504 instead of becoming an infinity.  Every fp16 store of the library goes through this: one infinity in a
+// gradient (the keys every later node attends to collect gradients of many thousand) turns into NaN at the next
+// difference and then into a NaN loss.  Same single cvt instruction as the plain conversion.
+__device__ __forceinline__ __half2 sat_half2(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return *(__half2 *)&r;
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

@@ -33,7 +33,7 @@ struct Fast<1> {
     static constexpr int SIZE = 2;
     static __device__ __forceinline__ void store4(void *base, size_t idx, float4 v)
     {
-        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        __half2 a = sat_half2(v.x, v.y), b = sat_half2(v.z, v.w);
         *(uint2 *)((__half *)base + idx) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
     }
     static __device__ __forceinline__ void zero4(void *base, size_t idx) { *(uint2 *)((__half *)base + idx) = make_uint2(0u, 0u); }
@@ -53,7 +53,7 @@ __device__ __forceinline__ float4 load_half4(const __half *p)
 }
 __device__ __forceinline__ void store_half4(__half *p, float4 v)
 {
-    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    __half2 a = sat_half2(v.x, v.y), b = sat_half2(v.z, v.w);
     *(uint2 *)p = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
 }
 

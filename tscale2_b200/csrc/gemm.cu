@@ -404,8 +404,8 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                     __syncwarp();
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
-                                h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                        __half2 h0 = sat_half2(v[8 * i], v[8 * i + 1]), h1 = sat_half2(v[8 * i + 2], v[8 * i + 3]),
+                                h2 = sat_half2(v[8 * i + 4], v[8 * i + 5]), h3 = sat_half2(v[8 * i + 6], v[8 * i + 7]);
                         *(uint4 *)(srow + ((i ^ sw) << 4)) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                     }
                     fence_proxy_async();
@@ -543,8 +543,8 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                         for (int i = 0; i < 4; ++i) {
                             uint4 pk;
                             if (p.out_kind == TS2_OUT_F16) {
-                                __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
-                                        h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                                __half2 h0 = sat_half2(v[8 * i], v[8 * i + 1]), h1 = sat_half2(v[8 * i + 2], v[8 * i + 3]),
+                                        h2 = sat_half2(v[8 * i + 4], v[8 * i + 5]), h3 = sat_half2(v[8 * i + 6], v[8 * i + 7]);
                                 pk = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                             } else {
                                 __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]),
@@ -618,8 +618,8 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                     uint4 *dst = (uint4 *)((__half *)Cg + row * p.ldc + col);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]),
-                                h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                        __half2 h0 = sat_half2(v[8 * i], v[8 * i + 1]), h1 = sat_half2(v[8 * i + 2], v[8 * i + 3]),
+                                h2 = sat_half2(v[8 * i + 4], v[8 * i + 5]), h3 = sat_half2(v[8 * i + 6], v[8 * i + 7]);
                         dst[i] = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                     }
                 } else {
@@ -696,7 +696,7 @@ __global__ void reduce_splitk_kernel(const GemmParams p)
             float4 o = *(const float4 *)(p.c_in + row * p.ldc + col);
             *d = make_float4(o.x + s.x, o.y + s.y, o.z + s.z, o.w + s.w);
         } else if (p.out_kind == TS2_OUT_F16) {
-            __half2 a = __floats2half2_rn(s.x, s.y), b = __floats2half2_rn(s.z, s.w);
+            __half2 a = sat_half2(s.x, s.y), b = sat_half2(s.z, s.w);
             *(uint2 *)((__half *)p.C + row * p.ldc + col) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
         } else {
             __nv_bfloat162 a = __floats2bfloat162_rn(s.x, s.y), b = __floats2bfloat162_rn(s.z, s.w);

@@ -28,8 +28,9 @@ int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, _
 
 // g_out = (add ? g_in : 0) + tilenorm_bwd(x, dn * (*dyn))   (NormalizeStateBackward, cpu_util.cpp:102-134;
 // BackpropLayerNormalize, gpu_layer_norm.cuh:89-115).  absmax: running max |g_out| as float bits.
+// health (optional): set to step_no by the first call whose g_out holds a NaN or an infinity (0 = never happened).
 int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float *dyn, float dn_alpha, int T, int D, float *g, bool add,
-                      unsigned *absmax);
+                      unsigned *absmax, unsigned *health = nullptr, unsigned step_no = 0);
 
 // g_fast = g * mult, mult = largest power of two with max|g| * mult <= target; ginv = 1/mult;
 // fscale = f_static * (*sko) * ginv   (ScaleGrad / ComputeGradMult, gpu_grad_scale.cuh:33-62)
@@ -48,6 +49,10 @@ int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, i
 // dgate -> d4[:, 3Q:4Q] (fast), do (fp16) and dScale[t][h] = sum do*o  (BackpropLoLU + ComputeDScale)
 int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const __half *o, int T, int Q, void *d4, __half *dout,
                       float *dscale);
+
+// debug trace: out[0] += sum of the buffer's 32-bit words (as a 64-bit integer), out[1] += its non-finite elements,
+// out[2] = max(out[2], fp32 bits of the largest finite magnitude)   (kind 0: words only, 1: fp32, 2: fp16)
+int checksum(const Ctx &c, const void *p, size_t bytes, int kind, unsigned long long *out);
 
 // softmax cross-entropy over base-2 logits (SoftMax, cpu_transformer.cpp:12-37; gradient :146-159):
 // logits fp16 [rows][V] are replaced by (onehot - p) * gscale; logp_sum += log p(target) (natural log).

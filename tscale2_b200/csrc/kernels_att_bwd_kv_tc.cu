@@ -195,7 +195,11 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
         const float ds = att_dot_scale_tc(), c2 = ds * 0.693147f, slope = p.slope;
         bool ok = true;
         for (int j = 0; j < n; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag));
+            // s_full says the products are done; the tile's per-node records came with the same stage by a bulk copy, and
+            // the threads that read them observe that stage's barrier themselves (it has long completed: the issuer
+            // waited for it before the products), which is what orders the copy's writes before these reads
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag) &&
+                                             mbar_wait(st_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1, abort_flag));
             if (!ok)
                 break;
             tc_fence_after();
@@ -223,7 +227,7 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
                     w2[e] = w;
                     g2[e] = w * fmaf(__uint_as_float(rp[i + e]), c2, m.y);
                 }
-                const __half2 hv = __floats2half2_rn(w2[0], w2[1]), hk = __floats2half2_rn(g2[0], g2[1]);
+                const __half2 hv = sat_half2(w2[0], w2[1]), hk = sat_half2(g2[0], g2[1]);
                 gv[i >> 1] = *(const uint32_t *)&hv;
                 gk[i >> 1] = *(const uint32_t *)&hk;
             }
@@ -266,10 +270,10 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                                  h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                                  h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                                  h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                    const __half2 h0 = sat_half2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                  h1 = sat_half2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                  h2 = sat_half2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                  h3 = sat_half2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
                     *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) =
                         make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
                 }

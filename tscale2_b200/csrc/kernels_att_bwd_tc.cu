@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                 uint32_t packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const __half2 hv = __floats2half2_rn(g[2 * i], g[2 * i + 1]);
+                    const __half2 hv = sat_half2(g[2 * i], g[2 * i + 1]);
                     packed[i] = *(const uint32_t *)&hv;
                 }
                 tmem_st8(tDP + q16 * 8, packed);
@@ -296,10 +296,10 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                                  h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                                  h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                                  h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                    const __half2 h0 = sat_half2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                  h1 = sat_half2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                  h2 = sat_half2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                  h3 = sat_half2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
                     *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) =
                         make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
                 }

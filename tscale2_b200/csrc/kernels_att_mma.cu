@@ -52,7 +52,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 }
 __device__ __forceinline__ uint32_t pack_half2(float a, float b)
 {
-    __half2 h = __floats2half2_rn(a, b);
+    __half2 h = sat_half2(a, b);
     return *(uint32_t *)&h;
 }
 
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
         __half *dst = o + (size_t)t * Q + h * HD + (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < 16; ++n)
-            *(__half2 *)(dst + n * 8) = __floats2half2_rn(acc[n][2 * rr] * inv, acc[n][2 * rr + 1] * inv);
+            *(__half2 *)(dst + n * 8) = sat_half2(acc[n][2 * rr] * inv, acc[n][2 * rr + 1] * inv);
         if ((lane & 3) == 0)
             lse[(size_t)t * H + h] = m[rr] + log2f(l[rr]);
     }

@@ -288,8 +288,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
                 uint8_t *prow = smem + Q_BYTES + 4 * KV_BYTES + row * 128;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    __half2 h0 = __floats2half2_rn(s[8 * c], s[8 * c + 1]), h1 = __floats2half2_rn(s[8 * c + 2], s[8 * c + 3]),
-                            h2 = __floats2half2_rn(s[8 * c + 4], s[8 * c + 5]), h3 = __floats2half2_rn(s[8 * c + 6], s[8 * c + 7]);
+                    __half2 h0 = sat_half2(s[8 * c], s[8 * c + 1]), h1 = sat_half2(s[8 * c + 2], s[8 * c + 3]),
+                            h2 = sat_half2(s[8 * c + 4], s[8 * c + 5]), h3 = sat_half2(s[8 * c + 6], s[8 * c + 7]);
                     *(uint4 *)(prow + (((half * 4 + c) ^ (row & 7)) << 4)) =
                         make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
                 }
@@ -328,10 +328,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
-                        h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
-                        h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
-                        h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+                __half2 h0 = sat_half2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
+                        h1 = sat_half2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
+                        h2 = sat_half2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
+                        h3 = sat_half2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
                 *(uint4 *)(srow + (((cc * 4 + i) ^ (lane & 7)) << 4)) = make_uint4(*(uint32_t *)&h0, *(uint32_t *)&h1, *(uint32_t *)&h2, *(uint32_t *)&h3);
             }
         }

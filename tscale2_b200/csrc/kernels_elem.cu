@@ -144,7 +144,8 @@ int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, _
 }
 
 __global__ void tilenorm_backward_kernel(const float *__restrict__ x, const float *__restrict__ dn, const float *__restrict__ dyn,
-                                         float dn_alpha, int T, int D, float *__restrict__ g, int add, unsigned *__restrict__ absmax)
+                                         float dn_alpha, int T, int D, float *__restrict__ g, int add, unsigned *__restrict__ absmax,
+                                         unsigned *__restrict__ health, unsigned step_no)
 {
     const int tiles = D / TILE;
     const float a = dn_alpha * (dyn ? __ldg(dyn) : 1.f);
@@ -180,6 +181,9 @@ __global__ void tilenorm_backward_kernel(const float *__restrict__ x, const floa
             res = make_float4(o[r].x + res.x, o[r].y + res.y, o[r].z + res.z, o[r].w + res.w);
             *(float4 *)(g + idx[r]) = res;
             local_max = fmaxf(local_max, fmaxf(fmaxf(fabsf(res.x), fabsf(res.y)), fmaxf(fabsf(res.z), fabsf(res.w))));
+            // fmaxf drops a NaN operand: a NaN anywhere in the row piece turns the running maximum into inf instead
+            if (!(res.x == res.x && res.y == res.y && res.z == res.z && res.w == res.w))
+                local_max = INFINITY;
         }
     }
     if (absmax) {
@@ -194,15 +198,17 @@ __global__ void tilenorm_backward_kernel(const float *__restrict__ x, const floa
                 m = fmaxf(m, block_max[i]);
             if (m == m && m < 3.0e38f) // NaN / inf never become the scale reference
                 atomicMax(absmax, __float_as_uint(m));
+            else if (health)
+                atomicCAS(health, 0u, step_no); // the first step at which this boundary's gradient was not finite
         }
     }
 }
 
 int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float *dyn, float dn_alpha, int T, int D, float *g, bool add,
-                      unsigned *absmax)
+                      unsigned *absmax, unsigned *health, unsigned step_no)
 {
-    tilenorm_backward_kernel<<<grid_for(c, tilenorm_backward_kernel, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(x, dn, dyn, dn_alpha, T, D, g, add ? 1 : 0,
-                                                                                          absmax);
+    tilenorm_backward_kernel<<<grid_for(c, tilenorm_backward_kernel, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(
+        x, dn, dyn, dn_alpha, T, D, g, add ? 1 : 0, absmax, health, step_no);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
@@ -486,7 +492,7 @@ __global__ void __launch_bounds__(512, 2)
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 - mx));
                 sum0 += e0;
                 sum1 += e1;
-                h[j] = __floats2half2_rn(e0, e1);
+                h[j] = sat_half2(e0, e1);
             }
             row_s4[i] = raw;
         }
@@ -509,7 +515,7 @@ __global__ void __launch_bounds__(512, 2)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 e = __half22float2(h[j]);
-                    h[j] = __floats2half2_rn(fmaf(e.x, ninv, trel == 2 * j ? gscale : 0.f), fmaf(e.y, ninv, trel == 2 * j + 1 ? gscale : 0.f));
+                    h[j] = sat_half2(fmaf(e.x, ninv, trel == 2 * j ? gscale : 0.f), fmaf(e.y, ninv, trel == 2 * j + 1 ? gscale : 0.f));
                 }
                 src[i] = raw;
             }
@@ -622,7 +628,7 @@ __global__ void __launch_bounds__(1024, 1)
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 - mx));
                 sum0 += e0;
                 sum1 += e1;
-                h[j] = __floats2half2_rn(e0, e1);
+                h[j] = sat_half2(e0, e1);
             }
             row_s4[i] = raw;
         }
@@ -649,7 +655,7 @@ __global__ void __launch_bounds__(1024, 1)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 e = __half22float2(h[j]);
-                    h[j] = __floats2half2_rn(e.x * ninv, e.y * ninv);
+                    h[j] = sat_half2(e.x * ninv, e.y * ninv);
                 }
                 if (i == (tgt >> 3)) {
                     const int kk = tgt & 7;
@@ -676,6 +682,58 @@ __global__ void __launch_bounds__(1024, 1)
         if (abort_s)
             atomicOr(status, TS2_STATUS_WAIT_TIMEOUT);
     }
+}
+
+// ---------------------------------------------------------------------------------
+// Debug trace: order-independent checksum (sum of the 32-bit words as a 64-bit integer, so equal buffers give equal
+// sums whatever the thread order), the number of non-finite elements and the largest finite magnitude of a buffer.
+// kind 0: raw words, 1: fp32, 2: fp16 pairs.  out[0] += sum, out[1] += non-finite count, out[2] = max(out[2], bits
+// of the largest finite |x| as fp32).
+__global__ void checksum_kernel(const uint32_t *__restrict__ p, size_t nwords, int kind, unsigned long long *__restrict__ out)
+{
+    unsigned long long sum = 0, bad = 0;
+    float mx = 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nwords; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t w = p[i];
+        sum += w;
+        if (kind == 1) {
+            if ((w & 0x7f800000u) == 0x7f800000u)
+                ++bad;
+            else
+                mx = fmaxf(mx, fabsf(__uint_as_float(w)));
+        } else if (kind == 2) {
+            const float2 f = __half22float2(*(const __half2 *)&w);
+            if ((w & 0x7c00u) == 0x7c00u)
+                ++bad;
+            else
+                mx = fmaxf(mx, fabsf(f.x));
+            if ((w & 0x7c000000u) == 0x7c000000u)
+                ++bad;
+            else
+                mx = fmaxf(mx, fabsf(f.y));
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        bad += __shfl_xor_sync(0xffffffffu, bad, o);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(out, sum);
+        if (bad)
+            atomicAdd(out + 1, bad);
+        if (mx > 0.f)
+            atomicMax(out + 2, (unsigned long long)__float_as_uint(mx));
+    }
+}
+
+int checksum(const Ctx &c, const void *p, size_t bytes, int kind, unsigned long long *out)
+{
+    const size_t nwords = bytes / 4;
+    const int grid = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(nwords, 256 * 8), (size_t)sm_count(c.device) * 8));
+    checksum_kernel<<<grid, 256, 0, c.stream>>>((const uint32_t *)p, nwords, kind, out);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
 }
 
 int softmax_ce(const Ctx &c, __half *logits, int rows, int V, const float *bias, const int *target, float gscale, float *logp_sum,

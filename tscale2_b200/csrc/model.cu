@@ -138,6 +138,21 @@ struct ts2_model {
     bool reduce_in_backward = false; // this backward pass is followed by apply(): all-reduce every layer's gradient as soon as it is complete
     bool debug_taps = false;
     float *grad_taps = nullptr;
+    // step health: health[b] = number of the first step whose state gradient at layer boundary b held a NaN or an
+    // infinity (0: never); the training error of the last LOSS_RING steps (sum of log p, one slot per step)
+    static constexpr int LOSS_RING = 256;
+    unsigned *health = nullptr; // [L + 1]
+    float *logp_ring = nullptr; // [LOSS_RING]
+    int ring_targets[LOSS_RING] = {};
+    unsigned step_no = 0;       // steps (ts2_backprop calls) so far
+    // debug trace: checksum + non-finite count of every intermediate buffer of the step (off by default)
+    static constexpr int TRACE_MAX = 1024;
+    bool trace_on = false;
+    unsigned long long *trace_dev = nullptr; // [TRACE_MAX][4]: checksum, non-finite count, max |x| bits, unused
+    std::vector<std::string> trace_names;
+    std::string capture_name; // trace record whose buffer is also copied aside ("dk[18]"), for ts2_debug_read("capture")
+    void *capture_buf = nullptr;
+    size_t capture_cap = 0, capture_bytes = 0;
     float last_ms = 0;
     bool timing_valid = false;
     int last_targets = 0;
@@ -583,7 +598,11 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     M_TRY(dalloc(m, &m->absmax, L + 2));
     M_TRY(dalloc(m, &m->ginv, 4));
     m->fscale = m->ginv + 1;
-    m->logp = m->ginv + 2;
+    M_TRY(dalloc(m, &m->health, L + 1));
+    TS2_CUDA(cudaMemsetAsync(m->health, 0, (L + 1) * 4, m->stream));
+    M_TRY(dalloc(m, &m->logp_ring, ts2_model::LOSS_RING + 1)); // the last slot serves ts2_forward_score
+    TS2_CUDA(cudaMemsetAsync(m->logp_ring, 0, (ts2_model::LOSS_RING + 1) * 4, m->stream));
+    m->logp = m->logp_ring;
     m->opt_scratch_stride = (size_t)m->max_rows * 4 + 16;
     M_TRY(dalloc(m, &m->opt_scratch, m->opt_scratch_stride * ts2_model::OPT_LANES));
     // batch
@@ -637,17 +656,36 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     return TS2_OK;
 }
 
+// debug trace record (no-op unless enabled): checksum and non-finite count of a buffer as the stream sees it here
+enum { TR_RAW = 0, TR_F32 = 1, TR_F16 = 2 };
+int trace(ts2_model *m, const char *name, int layer, const void *p, size_t bytes, int kind)
+{
+    if (!m->trace_on || (int)m->trace_names.size() >= ts2_model::TRACE_MAX)
+        return TS2_OK;
+    const size_t idx = m->trace_names.size();
+    m->trace_names.push_back(layer >= 0 ? std::string(name) + "[" + std::to_string(layer) + "]" : std::string(name));
+    if (!m->capture_name.empty() && m->trace_names.back() == m->capture_name && bytes <= m->capture_cap) {
+        TS2_CUDA(cudaMemcpyAsync(m->capture_buf, p, bytes, cudaMemcpyDeviceToDevice, m->stream));
+        m->capture_bytes = bytes;
+    }
+    return checksum(ctx_of(m), p, bytes, kind, m->trace_dev + 4 * idx);
+}
+#define TRACE(name, layer, p, bytes, kind) M_TRY(trace(m, name, layer, p, bytes, kind))
+
 // ---- forward -------------------------------------------------------------------------
 int forward(ts2_model *m)
 {
     Ctx c = ctx_of(m);
     const int T = m->batch.node_count, D = m->D, H = m->H;
     const BatchDev &b = m->batch;
+    const size_t fsz = fast_size(m);
     M_TRY(embed_forward(c, m->embed16, m->mats[0].sko, b.label_arr, b.label_ptr, T, D, m->states[0]));
+    TRACE("state", 0, m->states[0], (size_t)T * D * 4, TR_F32);
     for (int l = 0; l < m->L; ++l) {
         Layer &ly = m->layers[l];
         const int W = ly.wide, C = ly.ncat * W;
         M_TRY(tilenorm_forward(c, m->states[l], T, D, ly.n_fast, nullptr));
+        TRACE("n_fast", l, ly.n_fast, (size_t)T * D * fsz, fsz == 2 ? TR_F16 : TR_RAW);
         if (ly.type == TS2_LAYER_MOE) {
             // TMoELayer::ComputeForward, layer_moe.cu:459-486, on expert-sorted rows
             const int E = m->E, K = m->K, X = m->X, rows = (K * T + 127) / 128 * 128 + 128 * E;
@@ -672,6 +710,7 @@ int forward(ts2_model *m)
             e2.out_kind = TS2_OUT_F32;
             M_TRY(gemm_rows_grouped(m, ly, rows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
             M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+            TRACE("state", l + 1, m->states[l + 1], (size_t)T * D * 4, TR_F32);
             continue;
         }
         // [Q|K|V|Gate] or [wide|gate] = n . Wcat^T * sqrt(1/D)   (MulForward, cpu_util.cpp:7-27)
@@ -691,11 +730,20 @@ int forward(ts2_model *m)
             e1.act_f16 = m->ft != 0;
         }
         M_TRY(gemm_tn(m, m->kind, T, C, D, ly.n_fast, D, ly.Wcat, D, ly.cat16, C, e1));
+        TRACE("cat16", l, ly.cat16, (size_t)T * C * 2, TR_F16);
         if (ly.type == TS2_LAYER_ATT) {
             M_TRY(att_post_forward(c, ly.cat16, m->rope, T, H, ly.q, ly.k, ly.v, ly.qscale, ly.vscale));
+            TRACE("q", l, ly.q, (size_t)T * W * 2, TR_F16);
+            TRACE("k", l, ly.k, (size_t)T * W * 2, TR_F16);
+            TRACE("v", l, ly.v, (size_t)T * W * 2, TR_F16);
             M_TRY(attention_forward(c, ly.q, ly.k, ly.v, b.span_start[ly.att_type], b.span_finish[ly.att_type], T, H, ly.slope, ly.o, ly.lse));
+            TRACE("att_o", l, ly.o, (size_t)T * W * 2, TR_F16);
+            TRACE("att_lse", l, ly.lse, (size_t)T * H * 4, TR_F32);
             M_TRY(att_gate_forward(c, ly.cat16, ly.o, T, W, ly.rg));
+        } else {
+            TRACE("wscale", l, ly.wscale, (size_t)T * (W / 128) * 4, TR_F32);
         }
+        TRACE("rg", l, ly.rg, (size_t)T * W * fsz, fsz == 2 ? TR_F16 : TR_RAW);
         // state_out = state_in + rg . Wc^T * sqrt(1/wide) with Wc = q * sko / 32
         Epilogue e2;
         e2.alpha = sqrtf(1.0f / W) / (m->s_act * 32.f);
@@ -703,8 +751,10 @@ int forward(ts2_model *m)
         e2.out_kind = TS2_OUT_F32_ADD;
         e2.c_in = m->states[l];
         M_TRY(gemm_tn(m, m->kind, T, D, W, ly.rg, W, ly.Wc, W, m->states[l + 1], D, e2));
+        TRACE("state", l + 1, m->states[l + 1], (size_t)T * D * 4, TR_F32);
     }
     M_TRY(tilenorm_forward(c, m->states[m->L], T, D, m->nF_fast, m->nF16));
+    TRACE("nF16", -1, m->nF16, (size_t)T * D * 2, TR_F16);
     return TS2_OK;
 }
 
@@ -725,15 +775,18 @@ int final_layer(ts2_model *m, bool backward)
         e.dyn_scale = m->mats[1].sko;
         e.out_kind = TS2_OUT_F16;
         M_TRY(gemm_tn(m, m->kind, rows, V, D, (const uint8_t *)m->nF_fast + (size_t)r0 * D * fs, D, m->Wf, D, m->logits, V, e));
+        TRACE("logits", r0 / m->chunk, m->logits, (size_t)rows * V * 2, TR_F16);
         M_TRY(softmax_ce(c, m->logits, rows, V, m->has_bias ? m->bias : nullptr, m->batch.target + r0, gscale, m->logp, backward));
         if (!backward)
             continue;
+        TRACE("dlogits", r0 / m->chunk, m->logits, (size_t)rows * V * 2, TR_F16);
         // dnF = g . Wf * sqrt(1/D)   (MulBackwardWithAccum, cpu_transformer.cpp:163)
         Epilogue ex;
         ex.alpha = sqrtf(1.0f / D) / 32.f * gs / gscale;
         ex.dyn_scale = m->mats[1].sko;
         ex.out_kind = TS2_OUT_F32;
         M_TRY(gemm_tn(m, KIND_F16, rows, D, V, m->logits, V, m->WfT16, V, m->dn + (size_t)r0 * D, D, ex));
+        TRACE("dnF", r0 / m->chunk, m->dn + (size_t)r0 * D, (size_t)rows * D * 4, TR_F32);
         if (tune_final) {
             // dWf += g^T . nF   (SumRankOne, cpu_transformer.cpp:168)
             Epilogue ew;
@@ -742,6 +795,8 @@ int final_layer(ts2_model *m, bool backward)
             M_TRY(gemm_dw(m, KIND_F16, V, D, rows, m->logits, V, m->nF16 + (size_t)r0 * D, D, m->mats[1].grad, ew));
         }
     }
+    if (backward && tune_final)
+        TRACE("dW_final", -1, m->mats[1].grad, (size_t)V * D * 4, TR_F32);
     return TS2_OK;
 }
 
@@ -779,8 +834,10 @@ int backward(ts2_model *m)
     TS2_CUDA(cudaMemsetAsync(m->absmax, 0, (L + 2) * 4, m->stream));
     M_TRY(final_layer(m, true));
     M_TRY(reduce_matrices(m, 1, 2));
-    M_TRY(tilenorm_backward(c, m->states[L], m->dn, nullptr, 1.f, T, D, m->g, false, m->absmax + L));
+    M_TRY(tilenorm_backward(c, m->states[L], m->dn, nullptr, 1.f, T, D, m->g, false, m->absmax + L, m->health + L, m->step_no));
+    TRACE("g", L, m->g, (size_t)T * D * 4, TR_F32);
     M_TRY(tap_gradient(m, L));
+    const size_t fsz = fast_size(m);
     for (int l = L - 1; l >= 0; --l) {
         Layer &ly = m->layers[l];
         const int W = ly.wide, C = ly.ncat * W;
@@ -834,7 +891,8 @@ int backward(ts2_model *m)
                                      m->mats[ly.mat0 + 1].grad, (int64_t)X * D, e5));
             }
             M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
-            M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
+            M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l, m->health + l, m->step_no));
+            TRACE("g", l, m->g, (size_t)T * D * 4, TR_F32);
             M_TRY(tap_gradient(m, l));
             continue;
         }
@@ -846,7 +904,9 @@ int backward(ts2_model *m)
         Epilogue e3;
         e3.alpha = 1.f / (32.f * sqrtf((float)D));
         e3.out_kind = TS2_OUT_F16;
+        TRACE("g_fast", l, m->g_fast, (size_t)T * D * fsz, fsz == 2 ? TR_F16 : TR_RAW);
         M_TRY(gemm_tn(m, m->kind, T, W, D, m->g_fast, D, ly.WcT, D, m->drg, W, e3));
+        TRACE("drg", l, m->drg, (size_t)T * W * 2, TR_F16);
         if (tune_layers) {
             // dWc = g^T . rg   (SumRankOne)
             Epilogue e6;
@@ -854,21 +914,29 @@ int backward(ts2_model *m)
             e6.dyn_scale = m->ginv;
             e6.out_kind = TS2_OUT_F32_ADD;
             M_TRY(gemm_dw(m, m->kind, D, W, T, m->g_fast, D, ly.rg, W, mc.grad, e6));
+            TRACE("dW_c", l, mc.grad, (size_t)D * W * 4, TR_F32);
         }
         if (ly.type == TS2_LAYER_ATT) {
             M_TRY(att_gate_backward(c, m->drg, ly.cat16, ly.o, T, W, m->dcat, m->dout, m->dscale));
+            TRACE("dout", l, m->dout, (size_t)T * W * 2, TR_F16);
+            TRACE("dscale", l, m->dscale, (size_t)T * H * 4, TR_F32);
             M_TRY(attention_backward(c, ly.q, ly.k, ly.v, m->dout, ly.lse, m->dscale, b.span_start[ly.att_type], b.span_finish[ly.att_type],
                                      b.rev_first[ly.att_type], b.rev_last[ly.att_type], T, H, ly.slope, m->dq, m->dk, m->dv, true));
+            TRACE("dq", l, m->dq, (size_t)T * W * 2, TR_F16);
+            TRACE("dk", l, m->dk, (size_t)T * W * 2, TR_F16);
+            TRACE("dv", l, m->dv, (size_t)T * W * 2, TR_F16);
             M_TRY(att_post_backward(c, m->dq, m->dk, m->dv, true, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
                                     m->dcat));
         } else {
             M_TRY(ffn_act_backward(c, m->drg, ly.cat16, ly.cat16, 2 * W, ly.wscale, T, W, m->dcat));
         }
+        TRACE("dcat", l, m->dcat, (size_t)T * C * fsz, fsz == 2 ? TR_F16 : TR_RAW);
         // dn (scale-free) = dcat . (q_cat/32) * sqrt(1/D)
         Epilogue e4;
         e4.alpha = sqrtf(1.0f / D) / 32.f;
         e4.out_kind = TS2_OUT_F32;
         M_TRY(gemm_tn(m, m->kind, T, D, C, m->dcat, C, ly.WcatT, C, m->dn, D, e4));
+        TRACE("dn", l, m->dn, (size_t)T * D * 4, TR_F32);
         if (tune_layers) {
             // dWcat = dcat^T . n * fscale, rows of matrices that are followed by a normalisation divided by sko
             Epilogue e5;
@@ -877,9 +945,11 @@ int backward(ts2_model *m)
             e5.row_scale = ly.bwd_row;
             e5.out_kind = TS2_OUT_F32_ADD;
             M_TRY(gemm_dw(m, m->kind, C, D, T, m->dcat, C, ly.n_fast, D, m->mats[ly.mat0].grad, e5));
+            TRACE("dW_cat", l, m->mats[ly.mat0].grad, (size_t)C * D * 4, TR_F32);
         }
         M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
-        M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l));
+        M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l, m->health + l, m->step_no));
+        TRACE("g", l, m->g, (size_t)T * D * 4, TR_F32);
         M_TRY(tap_gradient(m, l));
     }
     if (!(m->descr.flags & TS2_MPF_DISABLE_TUNE_EMBED))
@@ -1177,6 +1247,13 @@ int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model)
         return mfail(m, fail(TS2_ERR_INVALID_ARG, "ts2_backprop before ts2_set_batch"));
     TS2_CUDA(cudaSetDevice(m->device));
     TS2_CUDA(cudaEventRecord(m->ev_start, m->stream));
+    ++m->step_no;
+    m->logp = m->logp_ring + m->step_no % ts2_model::LOSS_RING; // final_layer() clears and fills this step's slot
+    m->ring_targets[m->step_no % ts2_model::LOSS_RING] = m->batch.target_count;
+    if (m->trace_on) {
+        m->trace_names.clear();
+        TS2_CUDA(cudaMemsetAsync(m->trace_dev, 0, (size_t)ts2_model::TRACE_MAX * 32, m->stream));
+    }
     if (!m->grads_dirty)
         TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, m->total_params * 4, m->stream));
     M_TRY(forward(m));
@@ -1217,11 +1294,21 @@ int ts2_forward_score(ts2_model *m, float *out_score)
     if (m->batch.node_count <= 0)
         return mfail(m, fail(TS2_ERR_INVALID_ARG, "ts2_forward_score before ts2_set_batch"));
     TS2_CUDA(cudaSetDevice(m->device));
-    M_TRY(forward(m));
-    M_TRY(final_layer(m, false));
+    const bool tr = m->trace_on;
+    m->trace_on = false;
+    float *const step_slot = m->logp;
+    m->logp = m->logp_ring + ts2_model::LOSS_RING; // the last training step's slot stays readable
+    int rc = forward(m);
+    if (rc == TS2_OK)
+        rc = final_layer(m, false);
+    float *const score_slot = m->logp;
+    m->logp = step_slot;
+    m->trace_on = tr;
+    if (rc != TS2_OK)
+        return rc;
     M_TRY(wait_stream(m));
     float s = 0;
-    TS2_CUDA(cudaMemcpy(&s, m->logp, 4, cudaMemcpyDeviceToHost));
+    TS2_CUDA(cudaMemcpy(&s, score_slot, 4, cudaMemcpyDeviceToHost));
     *out_score = m->batch.target_count ? s / m->batch.target_count : 0.f;
     return TS2_OK;
 }
@@ -1366,11 +1453,106 @@ int ts2_debug_read(ts2_model *m, const char *name, int layer, void *dst, int64_t
                       : n == "seg_ptr" ? (const void *)ly.seg_ptr : n == "slot_of" ? (const void *)ly.slot_of
                       : n == "ids" ? (const void *)ly.ids : n == "weights" ? (const void *)ly.weights
                       : n == "cat16" ? (const void *)ly.cat16 : n == "n_fast" ? ly.n_fast : n == "n_rows" ? ly.n_rows
-                      : n == "logits" ? (const void *)ly.logits : n == "moe_g" ? m->moe_g : n == "drg" ? (const void *)m->drg : nullptr;
+                      : n == "logits" ? (const void *)ly.logits : n == "moe_g" ? m->moe_g : n == "drg" ? (const void *)m->drg
+                      : n == "capture" && (size_t)bytes <= m->capture_bytes ? m->capture_buf : nullptr;
     if (!src)
         return fail(TS2_ERR_INVALID_ARG, "ts2_debug_read: unknown or absent buffer '%s'", name);
     TS2_CUDA(cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost));
     return TS2_OK;
+}
+
+int ts2_discard_gradient(ts2_model *m)
+{
+    if (!m)
+        return fail(TS2_ERR_INVALID_ARG, "null model");
+    m->grads_dirty = false; // the next ts2_backprop clears the flat gradient before it accumulates
+    return TS2_OK;
+}
+
+int ts2_get_step_health(ts2_model *m, int reset, uint32_t *first_bad_step, int n_boundaries, int64_t *steps_so_far)
+{
+    if (!m || !first_bad_step || n_boundaries != m->L + 1)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_get_step_health: pass layer_count + 1 entries");
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    TS2_CUDA(cudaMemcpy(first_bad_step, m->health, (size_t)(m->L + 1) * 4, cudaMemcpyDeviceToHost));
+    if (reset)
+        TS2_CUDA(cudaMemset(m->health, 0, (size_t)(m->L + 1) * 4));
+    if (steps_so_far)
+        *steps_so_far = m->step_no;
+    return TS2_OK;
+}
+
+int ts2_get_loss_history(ts2_model *m, float *out_err, int n)
+{
+    if (!m || !out_err || n < 0 || n > ts2_model::LOSS_RING || (unsigned)n > m->step_no)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_get_loss_history: n must be in [0, min(%d, steps so far)]", ts2_model::LOSS_RING);
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    float ring[ts2_model::LOSS_RING];
+    TS2_CUDA(cudaMemcpy(ring, m->logp_ring, sizeof(ring), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; ++i) { // oldest first
+        const unsigned step = m->step_no - (unsigned)(n - 1 - i), slot = step % ts2_model::LOSS_RING;
+        out_err[i] = m->ring_targets[slot] ? -ring[slot] / m->ring_targets[slot] : 0.f;
+    }
+    return TS2_OK;
+}
+
+int ts2_set_debug_trace(ts2_model *m, int enable)
+{
+    if (!m)
+        return fail(TS2_ERR_INVALID_ARG, "null model");
+    TS2_CUDA(cudaSetDevice(m->device));
+    if (enable && !m->trace_dev)
+        M_TRY(dalloc(m, &m->trace_dev, (size_t)ts2_model::TRACE_MAX * 4));
+    m->trace_on = enable != 0;
+    if (!enable)
+        m->trace_names.clear();
+    return TS2_OK;
+}
+
+int ts2_set_debug_capture(ts2_model *m, const char *record_name, int64_t max_bytes)
+{
+    if (!m || max_bytes < 0)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_set_debug_capture");
+    TS2_CUDA(cudaSetDevice(m->device));
+    m->capture_name = record_name ? record_name : "";
+    m->capture_bytes = 0;
+    if (!m->capture_name.empty() && (size_t)max_bytes > m->capture_cap) {
+        M_TRY(dalloc(m, (uint8_t **)&m->capture_buf, (size_t)max_bytes)); // an earlier, smaller buffer stays with the model
+        m->capture_cap = (size_t)max_bytes;
+    }
+    return TS2_OK;
+}
+
+int ts2_get_debug_trace(ts2_model *m, uint64_t *sums, uint64_t *nonfinite, float *max_abs, int capacity, int *count)
+{
+    if (!m || !count || capacity < 0 || (capacity && (!sums || !nonfinite)))
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_debug_trace");
+    const int n = (int)m->trace_names.size();
+    *count = n;
+    if (!capacity || !n)
+        return TS2_OK;
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    std::vector<unsigned long long> host((size_t)n * 4);
+    TS2_CUDA(cudaMemcpy(host.data(), m->trace_dev, host.size() * 8, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < std::min(n, capacity); ++i) {
+        sums[i] = host[4 * i];
+        nonfinite[i] = host[4 * i + 1];
+        if (max_abs) {
+            const uint32_t bits = (uint32_t)host[4 * i + 2];
+            memcpy(max_abs + i, &bits, 4);
+        }
+    }
+    return TS2_OK;
+}
+
+const char *ts2_debug_trace_name(ts2_model *m, int index)
+{
+    if (!m || index < 0 || index >= (int)m->trace_names.size())
+        return "";
+    return m->trace_names[index].c_str();
 }
 
 int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES])

@@ -109,6 +109,47 @@ class Model:
         self._check(self.lib.ts2_get_state_tap(self.h, layer, int(gradient), out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
         return out
 
+    def step_health(self, reset=False):
+        """(first_bad_step per layer boundary, steps so far): 0 = the state gradient at that boundary was finite in
+        every step since the last reset."""
+        n = len(self.spec.layers) + 1
+        out = np.zeros(n, np.uint32)
+        steps = C.c_int64()
+        self._check(self.lib.ts2_get_step_health(self.h, int(reset), out.ctypes.data_as(C.POINTER(C.c_uint32)), n, C.byref(steps)))
+        return out, steps.value
+
+    def loss_history(self, n):
+        out = np.zeros(n, np.float32)
+        self._check(self.lib.ts2_get_loss_history(self.h, out.ctypes.data_as(C.POINTER(C.c_float)), n))
+        return out
+
+    def discard_gradient(self):
+        self._check(self.lib.ts2_discard_gradient(self.h))
+
+    def set_debug_trace(self, enable=True):
+        self._check(self.lib.ts2_set_debug_trace(self.h, int(enable)))
+
+    def get_debug_trace(self):
+        """[(name, checksum, non-finite count, largest finite magnitude)] of the last step, in stream order."""
+        n = C.c_int()
+        self._check(self.lib.ts2_get_debug_trace(self.h, None, None, None, 0, C.byref(n)))
+        sums = np.zeros(max(n.value, 1), np.uint64)
+        bad = np.zeros(max(n.value, 1), np.uint64)
+        mx = np.zeros(max(n.value, 1), np.float32)
+        self._check(self.lib.ts2_get_debug_trace(self.h, sums.ctypes.data_as(C.POINTER(C.c_uint64)),
+                                                 bad.ctypes.data_as(C.POINTER(C.c_uint64)),
+                                                 mx.ctypes.data_as(C.POINTER(C.c_float)), n.value, C.byref(n)))
+        return [(self.lib.ts2_debug_trace_name(self.h, i).decode(), int(sums[i]), int(bad[i]), float(mx[i]))
+                for i in range(n.value)]
+
+    def set_debug_capture(self, record_name, max_bytes):
+        self._check(self.lib.ts2_set_debug_capture(self.h, record_name.encode() if record_name else None, max_bytes))
+
+    def debug_read(self, name, layer, shape, dtype):
+        out = np.empty(shape, dtype)
+        self._check(self.lib.ts2_debug_read(self.h, name.encode(), layer, out.ctypes.data, out.nbytes))
+        return out
+
     def comm_init(self, rank, world, id_bytes):
         buf = (C.c_uint8 * capi.COMM_ID_BYTES).from_buffer_copy(id_bytes)
         self._check(self.lib.ts2_comm_init(self.h, rank, world, buf))
