@@ -145,6 +145,17 @@ def run_cpu_reference(w, steps, warmup):
                        f"{w_name(w)} model, 1 fragment of {n_tok} tokens per step, OpenMP over rows"), n_tok, sec
 
 
+def check_steps(model, n, arm):
+    """A step that produced a non-finite loss or gradient did not do the work it is timed for: no number."""
+    losses = model.loss_history(min(n, 256))
+    first_bad, steps = model.step_health(reset=True)
+    if not np.isfinite(losses).all() or first_bad.any():
+        i = int(np.flatnonzero(~np.isfinite(losses))[0]) if not np.isfinite(losses).all() else None
+        raise SystemExit(f"bench: {arm}: non-finite step: first bad loss at timed step {None if i is None else i + 1} of {n}; "
+                         f"first step (since model creation, now at {steps}) with a non-finite state gradient per layer boundary: "
+                         f"{first_bad.tolist()}; refusing to report a throughput")
+
+
 def w_name(w):
     for k, v in WORKLOADS.items():
         if v is w:
@@ -177,9 +188,13 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        cb, n_tok, sec = run_cpu_reference(w, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        ran_steps, ran_warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+        cb, n_tok, sec = run_cpu_reference(w, ran_steps, ran_warmup)
+        config = dict(config, sample_tokens_per_step=n_tok, sample="one fragment of the workload's model per step, see cpu_baseline.sample")
+        # steps / warmup are the ones this arm ran (each is ~10-20 s of scalar CPU work), not the ones asked for
         line = {"impl": "reference", "metric": "train tokens/s (fwd+bwd)", "value": cb["value"], "unit": "tokens/s",
-                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+                "n_gpus": args.gpus, "steps": ran_steps, "warmup": ran_warmup, "steps_requested": args.steps,
+                "warmup_requested": args.warmup, "ms_per_step": sec * 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -234,6 +249,9 @@ def main():
     launches = model.launch_count()
     barrier()
     clocks = sampler.stop()
+    # every step of the timed region is checked afterwards (no device read inside it): the per-step training error
+    # from the engine's loss ring, and the per-layer-boundary flags the norm-backward kernel raises on a NaN / infinity
+    check_steps(model, args.steps, "device-timed arm")
     gemm_bytes = model.get_kernel_bytes()
     gemm_ms, gemm_n, gemm_flops = model.get_kernel_timing(reset=True)
     model.set_kernel_timing(False)
@@ -245,17 +263,20 @@ def main():
         model.avg_train_err()
     barrier()
     loss = 0.0
+    e2e_losses = []
     model.timer_begin()  # events on the engine's stream: copies, kernels and the idle gaps between steps
     for i in range(args.steps):
         model.set_batch(batches[i % len(batches)])
         model.backprop(train_step, apply=True)
         loss = model.avg_train_err()  # device -> host read, waits for the step
+        e2e_losses.append(loss)
     e2e_ms = model.timer_end()
     barrier()
-
-    if not np.isfinite(loss):
-        # a step that produced a non-finite loss did not do the work it is timed for: no number
-        raise SystemExit(f"bench: training loss is {loss} after the timed steps; refusing to report a throughput")
+    if not np.isfinite(e2e_losses).all():
+        bad = int(np.flatnonzero(~np.isfinite(e2e_losses))[0])
+        raise SystemExit(f"bench: end-to-end arm: training loss is {e2e_losses[bad]} at timed step {bad + 1}; "
+                         "refusing to report a throughput")
+    check_steps(model, args.steps, "end-to-end arm")
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -297,7 +318,8 @@ def main():
             "vs_baseline": None, "dtype": "e4m3" if args.precision == "fp8" else "f16", "data": "synthetic", "config": config,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
-                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_max / args.steps, "last_loss": loss},
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_max / args.steps, "last_loss": loss,
+                    "losses_checked": len(e2e_losses)},
             "gpu_launches": int(launches), "roofline": roofline}
     if world == 1 and not args.no_cpu_baseline:
         cb, _, _ = run_cpu_reference(w, 1, 0)
