@@ -153,8 +153,6 @@ const char *ts2_last_error(const ts2_model *m); /* m may be NULL: last create er
 /* IModelInstance::GetNodes + Init(INIT_BACKPROP), src/gpt/compute/model.h:32-35;
  * TSinlgeComputeContext::Init, src/gpt/compute/gpu_transformer.cu:526-566 */
 int ts2_set_batch(ts2_model *m, const ts2_batch_nodes *nodes);
-/* same, with the batch already in pinned host memory prepared by the caller
- * for repeated steps (no semantic difference) */
 
 /* IModel::Backprop, src/gpt/compute/model.h:53 — asynchronous: enqueues the
  * forward pass, the backward pass and (TS2_GRADIENT_APPLY) the gradient
@@ -306,9 +304,16 @@ int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int
  * before any stream capture.  All calls share the one array and it keeps whatever the last call
  * left there (nothing needs to start at zero: each partial tile is fully rewritten before it is
  * read), so two calls that overlap on the GPU — different streams, or different host threads —
- * race; serialise them on one stream.  out_kind: TS2_OUT_F32 or TS2_OUT_F32_ADD. */
+ * race; serialise them on one stream.  A bounded wait that gives up inside its kernels is reported by the next
+ * ts2_dev_sync / ts2_wait as TS2_ERR_DEVICE_STATUS, like everywhere else.  out_kind: TS2_OUT_F32 or TS2_OUT_F32_ADD. */
 int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
                         const void *dY, const void *X, void *dW, float alpha);
+/* Self-test of that entry point's error path (no counterpart in the reference).  Its kernels report a bounded wait
+ * that ran out in a status word of their own, a static device variable, because the library's ordinary status word is
+ * cudaMalloc'ed on first use; ts2_dev_sync and ts2_wait read and clear both words.  This call makes a wait run out
+ * the allowed way (one CTA, a barrier nothing arrives at, under a second) against that word and returns what
+ * ts2_dev_sync then reports: TS2_ERR_DEVICE_STATUS is the expected result and the context stays usable. */
+int ts2_selftest_wait_limit_noalloc(int device);
 
 /* Grouped forms of the two contractions for expert-sorted rows (the reference's grouped mma.sync
  * GEMMs with GridZ = experts, src/gpt/compute/moe_matmul.cuh:255-291).  Rows are sorted by expert and each

@@ -79,3 +79,19 @@ def test_host_batch_matches_reference_span_rule():
     assert (s[k], f[k]) == (10, 14)
     assert np.array_equal(b.label_arr[:3], b.target_id[:0].astype(np.uint32).tolist() + list(b.label_arr[:3]))
     assert b.label_arr.max() <= spec.vocab and b.label_arr.min() >= 1
+
+
+def test_reference_side_adapter_compiles_against_the_reference_headers():
+    """tscale2_b200/adapter/b200_model.cpp is the IModel / IModelInstance a maintainer adds to the trainer.  Where the
+    reference's sources are present it must pass a syntax check against their own model.h (all pure virtuals
+    overridden with the right signatures)."""
+    import shutil
+    import subprocess
+    ref = os.environ.get("TS2_REFERENCE", "/root/reference")
+    if not os.path.exists(os.path.join(ref, "src", "gpt", "compute", "model.h")) or not shutil.which("g++"):
+        pytest.skip("reference sources or g++ not present on this machine")
+    cmd = ["g++", "-std=c++17", "-march=x86-64-v3", "-w", "-fsyntax-only", "-include", "util/pch.h", "-I" + os.path.join(ref, "src"),
+           "-I/usr/local/cuda/include", "-I" + os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tscale2_b200", "adapter", "b200_model.cpp")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]

@@ -120,6 +120,7 @@ def _declare(lib):
         "ts2_get_kernel_bytes": (i32, [vp, P(C.c_double)]),
         "ts2_device_count": (i32, []),
         "ts2_selftest_wait_limit": (i32, [i32]),
+        "ts2_selftest_wait_limit_noalloc": (i32, [i32]),
         "ts2_dev_alloc": (i32, [i32, C.c_size_t, P(vp)]),
         "ts2_dev_free": (i32, [i32, vp]),
         "ts2_dev_upload": (i32, [i32, vp, vp, C.c_size_t]),

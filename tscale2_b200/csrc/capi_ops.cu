@@ -111,16 +111,7 @@ int ts2_dev_sync(int device)
 {
     TS2_CUDA(cudaSetDevice(device));
     TS2_CUDA(cudaDeviceSynchronize());
-    int32_t *w = device_status_word(device);
-    if (w) {
-        int32_t v = 0;
-        TS2_CUDA(cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost));
-        if (v) {
-            cudaMemset(w, 0, sizeof(v));
-            return fail(TS2_ERR_DEVICE_STATUS, "device status word = 0x%x (bit0: a bounded wait in a kernel timed out)", v);
-        }
-    }
-    return TS2_OK;
+    return collect_device_status(device);
 }
 
 // One CTA waits, with the library's bounded wait, on an mbarrier nothing ever arrives at: the wait gives up after its

@@ -83,4 +83,22 @@ int32_t *device_status_word(int device)
     return w;
 }
 
+int collect_device_status(int device)
+{
+    int32_t *words[2] = {device_status_word(device), static_status_word_if_ready(device)};
+    int32_t seen[2] = {0, 0};
+    for (int i = 0; i < 2; ++i) {
+        if (!words[i])
+            continue;
+        TS2_CUDA(cudaMemcpy(&seen[i], words[i], sizeof(int32_t), cudaMemcpyDeviceToHost));
+        if (seen[i])
+            cudaMemset(words[i], 0, sizeof(int32_t));
+    }
+    if (seen[0] | seen[1])
+        return fail(TS2_ERR_DEVICE_STATUS,
+                    "device status word = 0x%x%s (bit0: a bounded wait in a kernel timed out, bit1: a kernel refused its arguments)",
+                    seen[0] | seen[1], seen[1] ? " (raised by ts2_gemm_dw_noalloc)" : "");
+    return TS2_OK;
+}
+
 } // namespace ts2

@@ -47,6 +47,12 @@ int resident_blocks(int device, const void *kernel, int threads);
 int32_t *device_status_word(int device);
 #define TS2_STATUS_WAIT_TIMEOUT 1
 #define TS2_STATUS_BAD_ARG 2
+// the word ts2_gemm_dw_noalloc's kernels use instead (a static __device__ variable: that entry point may not call
+// cudaMalloc, which device_status_word() does on first use); null until that entry point has run on the device
+int32_t *static_status_word_if_ready(int device);
+// After the caller has synchronized: reads both status words of the device, clears the ones that were set and
+// returns TS2_OK or TS2_ERR_DEVICE_STATUS (with the message set).  Allocates nothing.
+int collect_device_status(int device);
 
 // ---- device side -------------------------------------------------------------
 #ifdef __CUDACC__

@@ -1069,6 +1069,50 @@ struct StaticScratch {
 static StaticScratch g_static[16];
 static std::mutex g_static_mu;
 
+// set-up, once per device, with that device current: in host code the array's name is only a handle; the address a
+// kernel can use comes from cudaGetSymbolAddress
+static int static_setup(int device, StaticScratch *out)
+{
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    StaticScratch &slot = g_static[device];
+    if (!slot.ready) {
+        void *p = nullptr, *q = nullptr;
+        TS2_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        TS2_CUDA(cudaGetSymbolAddress(&q, g_static_status));
+        slot.scratch = (float *)p;
+        slot.status = (int32_t *)q;
+        slot.ready = true;
+    }
+    *out = slot;
+    return TS2_OK;
+}
+
+// one CTA waits, with the library's bounded wait, on a barrier nothing arrives at, gives up after the limit and
+// raises the time-out bit of the given status word (the way a contraction kernel reports a wait that ran out)
+__global__ void static_status_selftest_kernel(int32_t *status)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_s;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_s = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(smem_u32(&bar), 0, &abort_s))
+        atomicOr(status, TS2_STATUS_WAIT_TIMEOUT);
+}
+
+// The status word of the no-allocation entry point on this device, or null while that entry point has not run
+// there (then nothing can have been OR-ed into it).  Never allocates and never triggers the symbol look-up.
+int32_t *static_status_word_if_ready(int device)
+{
+    if (device < 0 || device >= 16)
+        return nullptr;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    return g_static[device].ready ? g_static[device].status : nullptr;
+}
+
 } // namespace ts2
 
 using namespace ts2;
@@ -1093,21 +1137,9 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
         return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_noalloc: device %d out of range", device);
     TS2_CUDA(cudaSetDevice(device));
     StaticScratch st;
-    {
-        // set-up, once per device, with that device current: in host code the array's name is only a
-        // handle; the address a kernel can use comes from cudaGetSymbolAddress
-        std::lock_guard<std::mutex> lk(g_static_mu);
-        StaticScratch &slot = g_static[device];
-        if (!slot.ready) {
-            void *p = nullptr, *q = nullptr;
-            TS2_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-            TS2_CUDA(cudaGetSymbolAddress(&q, g_static_status));
-            slot.scratch = (float *)p;
-            slot.status = (int32_t *)q;
-            slot.ready = true;
-        }
-        st = slot;
-    }
+    int rc = static_setup(device, &st);
+    if (rc != TS2_OK)
+        return rc;
     const Plan pl = make_plan(device, kind, true, out_dim, in_dim, T);
     const size_t need = pl.splits > 1 ? (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float) : 0;
     if (need > STATIC_SCRATCH_BYTES)
@@ -1117,7 +1149,6 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
                     need, STATIC_SCRATCH_BYTES);
     const int es = elem_size(kind), bk = STAGE_ROW_BYTES / es;
     CUtensorMap tmA, tmB;
-    int rc;
     if ((rc = make_tmap(&tmA, dY, es, out_dim, T, out_dim, bk)) != TS2_OK)
         return rc;
     if ((rc = make_tmap(&tmB, X, es, in_dim, T, in_dim, bk)) != TS2_OK)
@@ -1168,4 +1199,21 @@ extern "C" int ts2_gemm_dw_noalloc(int device, void *stream, int prec, int out_k
     if (rc == TS2_ERR_UNSUPPORTED)
         return fail(rc, "ts2_gemm_dw_noalloc: unsupported configuration");
     return rc;
+}
+
+// Self-test of the status path of ts2_gemm_dw_noalloc: the same bounded wait as ts2_selftest_wait_limit, reported
+// through the static status word that entry point's kernels use.  Allocates nothing.
+extern "C" int ts2_selftest_wait_limit_noalloc(int device)
+{
+    if (device < 0 || device >= 16)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_selftest_wait_limit_noalloc: device %d out of range", device);
+    TS2_CUDA(cudaSetDevice(device));
+    StaticScratch st;
+    int rc = static_setup(device, &st);
+    if (rc != TS2_OK)
+        return rc;
+    static_status_selftest_kernel<<<1, 32>>>(st.status);
+    TS2_CHECK_LAUNCH();
+    TS2_CUDA(cudaDeviceSynchronize());
+    return collect_device_status(device);
 }

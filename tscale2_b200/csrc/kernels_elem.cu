@@ -674,6 +674,9 @@ __global__ void __launch_bounds__(1024, 1)
                 bulk_commit();
             }
         } else {
+            // the sum pass wrote e back into this buffer through the generic proxy and the next bulk copy into it goes
+            // through the async proxy: order them (the gradient path above has the same fence before its store)
+            fence_proxy_async();
             __syncthreads(); // red[] and x_tgt_s are reused by the next row
         }
     }

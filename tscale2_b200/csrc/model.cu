@@ -1094,14 +1094,7 @@ int wait_stream(ts2_model *m)
     }
     if (e != cudaSuccess)
         return fail(TS2_ERR_CUDA, "stream failed: %s", cudaGetErrorString(e));
-    int32_t *w = device_status_word(m->device);
-    int32_t v = 0;
-    TS2_CUDA(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
-    if (v) {
-        cudaMemset(w, 0, 4);
-        return fail(TS2_ERR_DEVICE_STATUS, "device status word = 0x%x (bit0: a bounded wait in a kernel timed out)", v);
-    }
-    return TS2_OK;
+    return collect_device_status(m->device);
 }
 
 } // namespace
