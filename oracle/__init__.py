@@ -73,7 +73,23 @@ class Oracle:
 
     # -- whole step -------------------------------------------------------------------------
     def backprop(self, spec: host.ModelSpec, mats, batch: host.Batch, weight_quant, bias=None,
-                 want_states=False):
+                 want_states=False, engine_rounding=False):
+        """engine_rounding: also round the contractions' activation / gradient operands to e4m3 where the B200
+        engine's fp8 pipeline does (ts2o_set_activation_quant), instead of keeping them fp32."""
+        self.lib.ts2o_set_activation_quant(1 if engine_rounding else 0)
+        try:
+            return self._backprop(spec, mats, batch, weight_quant, bias, want_states)
+        finally:
+            self.lib.ts2o_set_activation_quant(0)
+
+    def round_e4m3(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros_like(x)
+        self.lib.ts2o_round_e4m3.argtypes = [_fp, C.c_int64, _fp]
+        self.lib.ts2o_round_e4m3(_f(x), x.size, _f(out))
+        return out
+
+    def _backprop(self, spec, mats, batch, weight_quant, bias, want_states):
         descr, keep = spec.to_c()
         views = host.matrix_views(mats)
         grads = [np.zeros_like(m) for m in mats]

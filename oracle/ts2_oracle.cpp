@@ -181,11 +181,64 @@ void QuantizeMatrix(const float *w, int64_t xSize, int64_t ySize, int quant, boo
 }
 
 // ---------------------------------------------------------------------------
+// Engine-faithful activation rounding (ts2o_set_activation_quant).  The reference's CPU path keeps every activation
+// and gradient in fp32; its GPU path, like the B200 engine, hands them to the fp8 contractions as e4m3 bytes
+// (TNormStateFloat / TFastGradientFloat = e4m3, cfg_precision.h:28-35).  With this mode on, the drivers below round
+// the same four operand tensors at the same points and scales as the engine: the normalized state and the gated
+// activation at 16 (the engine's s_act), the state gradient entering a layer at the power of two that brings its
+// largest magnitude just under 128 (ScaleGrad / ComputeGradMult, gpu_grad_scale.cuh:33-62), and the gradients of the
+// first contraction's outputs in the engine's scale-free units.  The rounding is the OCP e4m3 conversion the hardware
+// does (cvt.rn.satfinite: nearest even, subnormals down to 2^-9, magnitudes from 448 up saturate), not the weight
+// encoder above.  What is left between the engine and this mode is fp16 rounding of intermediates and the fast
+// exponentials; what is left between this mode and the fp32 mode is the format itself.
+int g_actQuant = 0;
+
+float RoundE4M3(float x)
+{
+    if (!(x == x))
+        return x;
+    float a = fabsf(x);
+    if (a >= 448.f)
+        return copysignf(448.f, x);
+    int e;
+    frexpf(a, &e);           // a = m * 2^e, m in [0.5, 1): the leading bit has weight 2^(e - 1)
+    e = std::max(e - 1, -6); // below 2^-6 the spacing stays that of the smallest normal binade
+    float q = ldexpf(1.f, e - 3);
+    return copysignf(nearbyintf(a / q) * q, x); // default rounding mode: to nearest, ties to even
+}
+
+void QuantizeInPlace(Mat *m, float scale)
+{
+    if (!g_actQuant)
+        return;
+    const float inv = 1.f / scale;
+    for (float &v : m->v)
+        v = RoundE4M3(v * scale) * inv;
+}
+
+// the engine's grad_mult: largest power of two that keeps max |g| * mult <= 128
+float GradMult(const Mat &g)
+{
+    float m = 0;
+    for (float v : g.v)
+        if (fabsf(v) > m && fabsf(v) < 3.0e38f)
+            m = fabsf(v);
+    if (!(m > 0))
+        return 1;
+    float e = floorf(log2f(128.f / m));
+    e = std::min(std::max(e, -100.f), 100.f);
+    return exp2f(e);
+}
+
+const float kActScale = 16.f;
+
+// ---------------------------------------------------------------------------
 // model
 
 struct Matrix {
     int64_t x = 0, y = 0;
     Mat data, dataNoScale; // what GetData / GetDataNoScale return
+    float sko = 1;         // matrix scale of TQuantizedMatrix::Convert
     float *gradOut = nullptr;
 };
 
@@ -224,10 +277,12 @@ struct Dims {
 void FfnRecompute(const Dims &d, Matrix *mm, const Mat &prevState, Mat &normState, Mat &wide, Mat &wideNorm, Mat &gate, Mat &rg)
 {
     normState = prim::NormalizeState(prevState, d.dim / kStateNormTile);
+    QuantizeInPlace(&normState, kActScale);
     wide = prim::MulForward(normState, mm[0].data);
     wideNorm = prim::NormalizeState(wide, d.ffnDim / 128);
     gate = prim::MulForward(normState, mm[1].dataNoScale);
     prim::LoLU(gate, wideNorm, &rg);
+    QuantizeInPlace(&rg, kActScale);
 }
 
 void FfnForward(const Dims &d, Matrix *mm, const Mat &prevState, Mat *state)
@@ -244,10 +299,21 @@ void FfnBackward(const Dims &d, Matrix *mm, bool update, const Mat &prevState, M
     FfnRecompute(d, mm, prevState, normState, wide, wideNorm, gate, rg);
     Mat dNormState(normState.rows, normState.cols);
     Mat drg(rg.rows, rg.cols);
-    MatmulBackprop(mm[2], false, rg, *grad, update, &drg);
+    // the contractions see the state gradient as e4m3 at the step's power-of-two scale; the residual path keeps fp32
+    Mat gFast = *grad;
+    const float gradMult = g_actQuant ? GradMult(*grad) : 1.f;
+    QuantizeInPlace(&gFast, gradMult);
+    MatmulBackprop(mm[2], false, rg, gFast, update, &drg);
     Mat dgate, dwide;
     prim::BackpropLoLU(gate, wideNorm, drg, &dgate, &dwide);
     prim::NormalizeStateBackward(wide, d.ffnDim / 128, dwide, &dwide);
+    {
+        // engine units: true gradient = stored value * fscale, fscale = sqrt(dim / ffnDim) * sko_contract / gradMult;
+        // the expansion is used scale-free there (a normalisation follows it), so its gradient carries its matrix scale
+        const float fscale = sqrtf((float)d.dim / (float)d.ffnDim) * mm[2].sko / gradMult;
+        QuantizeInPlace(&dwide, mm[0].sko / fscale);
+        QuantizeInPlace(&dgate, 1.f / fscale);
+    }
     MatmulBackprop(mm[0], false, normState, dwide, update, &dNormState);
     MatmulBackprop(mm[1], true, normState, dgate, update, &dNormState);
     Mat dState;
@@ -264,6 +330,7 @@ struct AttFwd {
 void AttRecompute(const Dims &d, Matrix *mm, const Common &c, float slope, int attType, const Mat &prevState, AttFwd &f)
 {
     f.normState = prim::NormalizeState(prevState, d.dim / kStateNormTile);
+    QuantizeInPlace(&f.normState, kActScale);
     f.comp.Init(d.headCount, d.qDim, d.ttDim, slope);
     f.qSrc = prim::MulForward(f.normState, mm[0].data);
     f.kSrc = prim::MulForward(f.normState, mm[1].data);
@@ -276,6 +343,7 @@ void AttRecompute(const Dims &d, Matrix *mm, const Common &c, float slope, int a
     prim::ApplyRope(c.rope, 1, &f.k);
     f.comp.ComputeValLookup(f.q, f.k, f.v, c.att[attType], &f.valLookup);
     prim::LoLU(f.gate, f.valLookup, &f.rg);
+    QuantizeInPlace(&f.rg, kActScale);
 }
 
 void AttForward(const Dims &d, Matrix *mm, const Common &c, float slope, int attType, const Mat &prevState, Mat *state)
@@ -292,7 +360,10 @@ void AttBackward(const Dims &d, Matrix *mm, bool update, const Common &c, float 
     AttRecompute(d, mm, c, slope, attType, prevState, f);
     Mat dNormState(f.normState.rows, f.normState.cols);
     Mat drg(f.rg.rows, f.rg.cols);
-    MatmulBackprop(mm[4], false, f.rg, *grad, update, &drg);
+    Mat gFast = *grad;
+    const float gradMult = g_actQuant ? GradMult(*grad) : 1.f;
+    QuantizeInPlace(&gFast, gradMult);
+    MatmulBackprop(mm[4], false, f.rg, gFast, update, &drg);
     Mat dgate, dValLookup;
     prim::BackpropLoLU(f.gate, f.valLookup, drg, &dgate, &dValLookup);
     Mat dScale;
@@ -304,6 +375,15 @@ void AttBackward(const Dims &d, Matrix *mm, bool update, const Common &c, float 
     prim::ApplyRope(c.rope, -1, &dK);
     prim::NormalizeStateBackward(f.qSrc, d.headCount, dQ, &dQ);
     prim::NormalizeStateBackward(f.vSrc, d.headCount, dV, &dV);
+    {
+        // engine units (see FfnBackward): Q and V are used scale-free there, K's matrix scale is folded into its
+        // gradient so that the four-way dX contraction reads scale-free weights throughout
+        const float fscale = sqrtf((float)d.dim / (float)(d.ttDim * d.headCount)) * mm[4].sko / gradMult;
+        QuantizeInPlace(&dQ, mm[0].sko / fscale);
+        QuantizeInPlace(&dK, mm[1].sko / fscale);
+        QuantizeInPlace(&dV, mm[2].sko / fscale);
+        QuantizeInPlace(&dgate, 1.f / fscale);
+    }
     MatmulBackprop(mm[0], false, f.normState, dQ, update, &dNormState);
     MatmulBackprop(mm[1], false, f.normState, dK, update, &dNormState);
     MatmulBackprop(mm[2], false, f.normState, dV, update, &dNormState);
@@ -476,6 +556,14 @@ extern "C" {
 
 const char *ts2o_backend(void) { return prim::BackendName(); }
 
+void ts2o_set_activation_quant(int mode) { g_actQuant = mode; }
+
+void ts2o_round_e4m3(const float *src, int64_t n, float *dst)
+{
+    for (int64_t i = 0; i < n; ++i)
+        dst[i] = RoundE4M3(src[i]);
+}
+
 int ts2o_quantize_matrix(const float *w, int64_t x_size, int64_t y_size, int quant, int no_scale, void *q_out, float *deq_out,
                          float *sko_out)
 {
@@ -533,7 +621,7 @@ int ts2o_backprop(const ts2_model_descr *descr, const ts2_matrix_view *mats, int
         int q = (weight_quant == TS2O_QUANT_NONE) ? TS2O_QUANT_NONE : (i == 0 ? TS2O_QUANT_HALF : weight_quant);
         m.data.resize((int)m.y, (int)m.x);
         m.dataNoScale.resize((int)m.y, (int)m.x);
-        QuantizeMatrix(mats[i].data, m.x, m.y, q, false, nullptr, m.data.v.data(), nullptr);
+        QuantizeMatrix(mats[i].data, m.x, m.y, q, false, nullptr, m.data.v.data(), &m.sko);
         QuantizeMatrix(mats[i].data, m.x, m.y, q, true, nullptr, m.dataNoScale.v.data(), nullptr);
         m.gradOut = (out && out->grads) ? out->grads[i] : nullptr;
     }
@@ -583,7 +671,9 @@ int ts2o_backprop(const ts2_model_descr *descr, const ts2_matrix_view *mats, int
             MoeForward(d, lm, states[l], &states[l + 1]);
     }
     Mat finalNorm = prim::NormalizeState(states[L], d.dim / kStateNormTile);
-    Mat pred = prim::MulForward(finalNorm, mm[1].data);
+    Mat finalNormFast = finalNorm; // the engine's logits contraction reads e4m3, its final-layer dW contraction fp16
+    QuantizeInPlace(&finalNormFast, kActScale);
+    Mat pred = prim::MulForward(finalNormFast, mm[1].data);
     for (float &x : pred.v)
         x *= FinalLayerMult();
     // SoftMax, cpu_transformer.cpp:12-37

@@ -26,6 +26,15 @@ typedef struct ts2o_outputs {
 
 const char *ts2o_backend(void);
 
+/* 0 (default): activations and gradients stay fp32, the reference's CPU path.  1: the four operand tensors of the
+ * layer contractions (normalized state, gated activation, state gradient, first-contraction output gradients) are
+ * rounded to e4m3 at the points and scales the B200 engine's fp8 pipeline rounds them (dense ATT / FFN layers; the
+ * reference's GPU path does the same with TNormStateFloat / TFastGradientFloat = e4m3, cfg_precision.h:28-35).
+ * Used to separate the engine's own error from the error of the number format.  Process-wide switch. */
+void ts2o_set_activation_quant(int mode);
+/* the rounding that mode applies: fp32 -> nearest e4m3 value (ties to even, subnormals, saturation at 448) */
+void ts2o_round_e4m3(const float *src, int64_t n, float *dst);
+
 /* one forward + backward of TComputeContext::ComputeBackprop
  * (src/gpt/compute/cpu_transformer.cpp:128-198) */
 int ts2o_backprop(const ts2_model_descr *descr, const ts2_matrix_view *mats, int n_mats, const float *bias,

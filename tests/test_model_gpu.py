@@ -26,24 +26,16 @@ def rel_l2(a, b):
     return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
 
 
-def _save_report(name, text):
-    import os
-    d = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(d):
-        with open(os.path.join(d, name), "w") as f:
-            f.write(text + "\n")
-
-
 def c1_spec(precision, slope=0.0, width=128):
     s = host.ModelSpec(dim=256, head_count=4, ffn_tiles=8, vocab=4096, attention_widths=[width], precision=precision)
     return s.add_blocks(2, alibi_slope=slope)
 
 
-def run_both(oracle_port, spec, n_frag, seq, wseed=1234, bseed=4321):
+def run_both(oracle_port, spec, n_frag, seq, wseed=1234, bseed=4321, engine_rounding=False):
     mats = host.init_weights(spec, wseed)
     batch = host.synthetic_batch(spec, n_frag, seq, bseed)
     quant = oracle.QUANT_E4M3 if spec.precision == capi.PREC_FP8 else oracle.QUANT_HALF
-    ref = oracle_port.backprop(spec, mats, batch, quant, want_states=True)
+    ref = oracle_port.backprop(spec, mats, batch, quant, want_states=True, engine_rounding=engine_rounding)
     model = Model(spec, mats, batch.node_count)
     model.set_debug_taps(True)
     model.set_batch(batch)
@@ -68,9 +60,33 @@ def test_c1_step_matches_oracle(oracle_port, precision, tol):
         report.append((name, rel_l2(g, r)))
     text = "\n".join(f"{n:24s} {e:.3e}" for n, e in report)
     print(text)
-    _save_report(f"parity_c1_{'fp8' if precision == capi.PREC_FP8 else 'f16'}.txt", text)
     assert abs(-model.avg_train_err() - ref["score"]) < (2e-3 if precision == capi.PREC_F16 else 2e-2), text
     bad = [(n, e) for n, e in report if not e < tol]
+    assert not bad, text
+
+
+@pytest.mark.parametrize("slope,width,n_frag,seq", [(0.0, 128, 4, 128), (0.5, 48, 3, 100)])
+def test_fp8_step_matches_the_oracle_with_engine_rounding(oracle_port, slope, width, n_frag, seq):
+    """Separates the engine's own error from the error of the e4m3 format.  The oracle rounds the four operand tensors
+    of the layer contractions (normalized state, gated activation, state gradient, gradients of the first
+    contraction's outputs) to e4m3 at the same points and scales as the engine and keeps everything else fp32; what
+    is left between the two is the engine's fp16 intermediates, its one-instruction tanh / exp2 and the order of
+    summation.  Measured on BASELINE config 1: weight gradients 1e-3 .. 4e-3, states / state gradients <= 3e-3; the
+    bound asserted is 6e-3.  (Against the fp32 oracle the same engine is 3e-2 .. 8e-2 off: that is the format.)"""
+    spec = c1_spec(capi.PREC_FP8, slope=slope, width=width)
+    model, batch, ref = run_both(oracle_port, spec, n_frag, seq, engine_rounding=True)
+    T, L = batch.node_count, len(spec.layers)
+    report = []
+    for l in range(L + 1):
+        report.append((f"state[{l}]", rel_l2(model.get_state_tap(l, False, T), ref["states"][l])))
+    for l in range(L, -1, -1):
+        report.append((f"state_grad[{l}]", rel_l2(model.get_state_tap(l, True, T), ref["state_grads"][l])))
+    for name, g, r in zip(spec.matrix_names(), model.get_gradients(), ref["grads"]):
+        report.append((name, rel_l2(g, r)))
+    text = "\n".join(f"{n:24s} {e:.3e}" for n, e in report)
+    print(text)
+    assert abs(-model.avg_train_err() - ref["score"]) < 2e-3, text
+    bad = [(n, e) for n, e in report if not e < 6e-3]
     assert not bad, text
 
 
