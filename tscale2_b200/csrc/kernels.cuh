@@ -141,4 +141,35 @@ int convert_block(const Ctx &c, const float *w, int64_t x, int64_t y, int quant,
                   const float *sko, bool transposed_as_half);
 int fill_vector(const Ctx &c, float *dst, int n, float value, const float *dyn, bool reciprocal_dyn);
 
+// ---- flat, sharded optimizer + requantiser (kernels_opt.cu) -------------------------
+// the part [a, b) (elements inside the matrix, multiples of 4) of one matrix that a rank owns
+struct OptSeg {
+    long long flat_off; // element offset of the matrix in the flat weight / momentum / gradient buffers
+    long long a, b;
+    int x, y;
+    int row0, nrows; // rows that intersect [a, b)
+    int grow0;       // global row number of the matrix's row 0
+    int item0;       // work items (rows) of the segments before this one
+    int mat;         // matrix index
+    int qsize;       // bytes per quantized element (1: e4m3, 2: fp16)
+    uint8_t *qbase;  // row-major quantized copy of the matrix
+    float sparsity;
+};
+struct OptMat {
+    long long x, y;
+    int row_disp_size, grow0;
+    float *row_disp, *sum_weight;
+};
+int opt_row_sum2(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const float *grad, float *rowsum);
+int opt_disp(const Ctx &c, const OptMat *mats, int n_mats, const float *rowsum, float disp_decay, float *row_scale);
+// step == nullptr: no update, only the per-row sums of squares of the weights
+int opt_update(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const float *grad, const float *row_scale,
+               const ts2_training_step *step, float *avg, float *w, double *roww2);
+int opt_sko(const Ctx &c, const OptMat *mats, int n_mats, const double *roww2, float *skos);
+int opt_quantize(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const float *w, const float *skos);
+// copy / transposed copy of quantized values; dst or dstT may be null
+int qcopy_block(const Ctx &c, const void *src, int64_t x, int64_t y, int64_t ld_src, int elem_size, void *dst, int64_t ld, void *dstT,
+                int64_t ldT, bool transposed_as_half);
+int layer_scales(const Ctx &c, float *fwd_col, float *bwd_row, int W, int ncat, bool is_att, float a, const float *skos);
+
 } // namespace ts2
