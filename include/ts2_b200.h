@@ -220,8 +220,23 @@ const char *ts2_debug_trace_name(ts2_model *m, int index);
 /* ------------------------------------------------------------------------- */
 /* data-parallel gradient reduction; replaces TMultiDeviceReducer::AllReduce,
  * src/lib/cuda/multi_device_buf.cu:193-265, called from
- * TAgpuCudaModelMatrix::ApplyGradientImpl, src/gpt/matrix/agpu_cuda.cuh:484-500.
- * One process per GPU; rank 0 creates the 128-byte id and the host shares it. */
+ * TAgpuCudaModelMatrix::ApplyGradientImpl, src/gpt/matrix/agpu_cuda.cuh:484-500, by reduce-scatter -> sharded
+ * optimizer -> all-gather of the quantized weights (NCCL).  One process per GPU; rank 0 creates the 128-byte id and
+ * the host shares it.  world_size must divide 256.  After ts2_comm_init the fp32 master weights and momentum of a rank
+ * are current only in the parts it owns; ts2_get_params / ts2_set_params bring them up to date first with an
+ * all-gather, so every rank must make those calls together (in the same order), like ts2_backprop.  The gradient tap
+ * (TS2_PARAM_GRADIENT) after an applied step holds the summed gradient in the rank's own parts and the rank's local
+ * gradient elsewhere. */
+/* Layout of the data-parallel exchange, computable without a device.  The engine keeps weights, momentum and gradient
+ * in flat fp32 buffers: the matrices in the order above, grouped into buckets (embedding; final layer; one per layer)
+ * whose lengths are padded to a multiple of 1024 elements.  With world_size ranks, rank r owns elements
+ * [bucket_offset[b] + r * bucket_elems[b] / world_size, + bucket_elems[b] / world_size) of every bucket b: a step
+ * reduce-scatters each bucket's gradient onto those parts (as soon as the backward pass has written the bucket),
+ * every rank runs the optimizer and the requantiser on its parts only (per-row sums of squares are completed by a
+ * small all-reduce), and the quantized bytes are all-gathered.  Returns the number of buckets; fills up to
+ * max_buckets entries of the bucket arrays and, if matrix_offset is given, the n_mats matrix offsets (elements). */
+int ts2_dp_layout(const ts2_model_descr *descr, int64_t *matrix_offset, int n_mats, int64_t *bucket_offset, int64_t *bucket_elems,
+                  int32_t *bucket_first_matrix, int max_buckets);
 #define TS2_COMM_ID_BYTES 128
 int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES]);
 int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_COMM_ID_BYTES]);

@@ -1,5 +1,9 @@
-"""Run by test_dp_gpu.py under torchrun, one process per GPU: three applied steps on different batches per rank;
-with the gradient summed over the ranks every rank must end with bit-identical weights."""
+"""Run by test_dp_gpu.py under torchrun, one process per GPU.  Data parallel = reduce-scatter of the gradient buckets
+during the backward pass, optimizer and requantiser on each rank's parts, all-gather of the quantized weights:
+  * after one applied step the weights equal those of ONE process that accumulates the ranks' batches and applies once
+    (the sum of two gradients is exact in either order; the embedding gradient is summed with float atomics: 1e-6);
+  * after more steps, one of them accumulated and not applied, every rank still holds bit-identical weights, momentum
+    and quantized weights, and the loss is finite."""
 import os
 import sys
 
@@ -19,25 +23,46 @@ def main():
     spec = host.ModelSpec(dim=256, head_count=2, ffn_tiles=8, vocab=4096, attention_widths=[256],
                           precision=capi.PREC_FP8).add_blocks(3)
     mats = host.init_weights(spec, 3)
-    batch = host.synthetic_batch(spec, 8, 256, 100 + rank)
-    model = Model(spec, mats, batch.node_count, device=local)
+    batches = [host.synthetic_batch(spec, 8, 256, 100 + r) for r in range(world)]
+    model = Model(spec, mats, batches[0].node_count, device=local)
     ids = [comm_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ids, src=0)
     model.comm_init(rank, world, ids[0])
-    model.set_batch(batch)
-    # one accumulated (not applied) step first: the sum over ranks must cover it too
-    model.backprop(host.training_step(rate=0.01, iteration=0), apply=False)
+    model.set_batch(batches[rank])
+    step0 = host.training_step(rate=0.01, iteration=0)
+    model.backprop(step0, apply=True)
+    w_dp = model.get_weights()  # collective: brings the other ranks' parts of the fp32 master weights in
+    problems = []
+    if rank == 0:
+        single = Model(spec, mats, batches[0].node_count, device=local)
+        for r in range(world):
+            single.set_batch(batches[r])
+            single.backprop(step0, apply=(r == world - 1))
+        for name, a, b in zip(spec.matrix_names(), w_dp, single.get_weights()):
+            tol = 1e-6 if name == "embed" else 0.0
+            d = float(np.abs(a.astype(np.float64) - b).max())
+            if d > tol * float(np.abs(b).max()):
+                problems.append(f"{name}: data-parallel step differs from the accumulated single-process step by {d}")
+        single.close()
+    # one accumulated (not applied) step, then applied ones: the exchange must cover the accumulated gradient too
+    model.backprop(host.training_step(rate=0.01, iteration=1), apply=False)
     for i in range(3):
-        model.backprop(host.training_step(rate=0.01, iteration=i), apply=True)
+        model.backprop(host.training_step(rate=0.01, iteration=2 + i), apply=True)
     model.wait()
-    sums = torch.tensor([float(np.abs(x.astype(np.float64)).sum()) for x in model.get_weights()], dtype=torch.float64)
+    sums = [float(np.abs(x.astype(np.float64)).sum()) for x in model.get_weights()]
+    sums += [float(np.abs(x.astype(np.float64)).sum()) for x in model.get_momentum()]
+    sums += [float(model.get_fast_weights(i)[0].astype(np.float64).sum()) for i in (0, 1, 2, 6, 7, 9)]
+    sums = torch.tensor(sums, dtype=torch.float64)
     gathered = [torch.zeros_like(sums) for _ in range(world)]
     dist.all_gather(gathered, sums)
     err = model.avg_train_err()
-    ok = all(bool((g == gathered[0]).all()) for g in gathered) and np.isfinite(err)
+    if not all(bool((g == gathered[0]).all()) for g in gathered):
+        problems.append("weights, momentum or quantized weights differ between ranks")
+    if not np.isfinite(err):
+        problems.append(f"loss {err} is not finite")
     dist.destroy_process_group()
-    if not ok:
-        raise SystemExit(f"rank {rank}: weights differ between ranks or loss {err} is not finite")
+    if problems:
+        raise SystemExit(f"rank {rank}: " + "; ".join(problems))
 
 
 if __name__ == "__main__":

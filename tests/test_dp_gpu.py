@@ -1,5 +1,6 @@
-"""Data-parallel step on two GPUs through NCCL (per-layer all-reduce queued during the backward pass): the ranks
-must stay bit-identical.  Needs two GPUs; skipped otherwise."""
+"""Data-parallel step on two GPUs through NCCL (reduce-scatter per bucket queued during the backward pass, optimizer
+on each rank's parts, all-gather of the quantized weights): equal to one process with the summed gradient, and the
+ranks stay bit-identical (tests/dp_two_ranks.py).  Needs two GPUs; skipped otherwise."""
 import os
 import subprocess
 import sys

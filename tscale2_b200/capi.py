@@ -109,6 +109,7 @@ def _declare(lib):
         "ts2_get_debug_trace": (i32, [vp, P(C.c_uint64), P(C.c_uint64), P(f32), i32, P(i32)]),
         "ts2_set_debug_capture": (i32, [vp, C.c_char_p, i64]),
         "ts2_debug_trace_name": (C.c_char_p, [vp, i32]),
+        "ts2_dp_layout": (i32, [P(ModelDescr), P(i64), i32, P(i64), P(i64), P(C.c_int32), i32]),
         "ts2_comm_unique_id": (i32, [P(C.c_uint8)]),
         "ts2_comm_init": (i32, [vp, i32, i32, P(C.c_uint8)]),
         "ts2_launch_count": (i64, [vp, i32]),

@@ -115,30 +115,6 @@ int moe_router_backward(const Ctx &c, const float *dmoe_part, int tiles, const i
                         int k, int E, int ld, void *dl);
 
 // ---- kernels_opt.cu ----------------------------------------------------------------
-// MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel (agpu_cuda.cu:32-134), one matrix.
-struct OptMatrix {
-    float *w, *avg_grad;
-    const float *grad;
-    int64_t x, y;
-    float *row_disp;
-    int row_disp_size;
-    float *sum_weight;
-    float sparsity;
-    float *row_sum2;  // scratch [y]
-    float *row_scale; // scratch [y]
-    float *w_sum2;    // scratch [y] (sum of squares of the new weights per row)
-};
-int apply_gradient(const Ctx &c, const OptMatrix &m, const ts2_training_step &step);
-// ConvertMatrixKernel (agpu_cuda.cuh:63-101) with the reference's CPU encoders
-// (sse_utils.h:56-78,161-204): q = enc(w * 32 / sko) into dst[y][ld] and, if dstT, the transposed copy
-// dstT[x][ldT] (optionally widened to fp16); sko written to *sko_out; scratch holds y doubles.
-int requantize(const Ctx &c, const float *w, int64_t x, int64_t y, int quant /*0 e4m3, 1 fp16*/, void *dst, int64_t ld, void *dstT,
-               int64_t ldT, float *sko_out, float *scratch_y_doubles, bool transposed_as_half);
-// the two halves of requantize: the matrix scale of a whole matrix, and the conversion of a block of its rows
-// with a given scale (expert blocks of a mixture-of-experts matrix share the matrix scale)
-int matrix_sko(const Ctx &c, const float *w, int64_t x, int64_t y, float *sko_out, float *scratch_y_doubles);
-int convert_block(const Ctx &c, const float *w, int64_t x, int64_t y, int quant, void *dst, int64_t ld, void *dstT, int64_t ldT,
-                  const float *sko, bool transposed_as_half);
 int fill_vector(const Ctx &c, float *dst, int n, float value, const float *dyn, bool reciprocal_dyn);
 
 // ---- flat, sharded optimizer + requantiser (kernels_opt.cu) -------------------------

@@ -66,6 +66,18 @@ struct Layer {
     float *weights = nullptr, *weight_of = nullptr;
 };
 
+// A bucket is a run of matrices that is contiguous in the flat buffers: the embedding, the final layer, one per layer.
+// It is the unit of the data-parallel exchange: its gradient is reduce-scattered as soon as the backward pass has
+// written it, every rank updates and requantises one contiguous 1 / world part of it, and the quantized bytes are
+// all-gathered.  Its length is padded to a multiple of BUCKET_PAD elements so that it divides evenly.
+static constexpr size_t BUCKET_PAD = 1024;
+struct Bucket {
+    size_t off = 0, elems = 0; // element offset / padded length in the flat buffers
+    int mat0 = 0, mat1 = 0;    // matrices [mat0, mat1)
+    int qsize = 1;             // bytes per quantized element
+    uint8_t *qflat = nullptr;  // row-major quantized copies of the bucket's matrices, in flat order (elems * qsize bytes)
+};
+
 struct BatchDev {
     uint32_t *label_arr = nullptr, *label_ptr = nullptr;
     int *target = nullptr;
@@ -87,12 +99,18 @@ struct ts2_model {
     int kind = KIND_E4M3;
     float s_act = 16.f;
     cudaStream_t stream = nullptr, comm_stream = nullptr;
-    // The optimizer and the requantiser are hundreds of small launches, one chain per matrix; the chains of different
-    // layers are independent and run on OPT_LANES streams forked from / joined to the main stream by events
-    static constexpr int OPT_LANES = 8;
-    cudaStream_t opt_stream[OPT_LANES] = {};
-    cudaEvent_t ev_opt_fork = nullptr, ev_opt_join[OPT_LANES] = {};
-    std::vector<int> mat_lane; // lane of every matrix: a layer's matrices share one (its scale vectors depend on all of them)
+    // flat, sharded optimizer (kernels_opt.cu): buckets, per-row vectors over all matrices, segment tables for the
+    // whole model (requantisation at creation / ts2_set_params) and for this rank's parts (training steps)
+    std::vector<Bucket> buckets;
+    std::vector<int> mat_bucket, mat_grow0;
+    size_t flat_elems = 0;
+    int n_rows_total = 0;
+    float *rowsum = nullptr, *row_scale = nullptr; // [n_rows_total]
+    double *roww2 = nullptr;                       // [n_rows_total]
+    OptMat *d_optmats = nullptr;
+    OptSeg *d_segs_full = nullptr, *d_segs_shard = nullptr;
+    int nseg_full = 0, nitems_full = 0, nseg_shard = 0, nitems_shard = 0;
+    bool master_stale = false; // data parallel: the fp32 weights / momentum outside this rank's parts are out of date
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr, ev_grads = nullptr, ev_reduced = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
     std::string error;
     std::vector<void *> allocs;
@@ -128,8 +146,6 @@ struct ts2_model {
     float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
-    float *opt_scratch = nullptr; // per lane: row_sum2 | row_scale | doubles
-    size_t opt_scratch_stride = 0;
     int64_t max_rows = 0;
     BatchDev batch;
     void *pinned = nullptr;
@@ -344,88 +360,137 @@ void shapes_of(const ts2_model_descr *d, std::vector<std::pair<int64_t, int64_t>
     }
 }
 
-// ---- requantisation of every matrix + the scale vectors derived from the matrix scales ----
-// optimizer lanes: every lane stream waits for what the main stream has queued so far ...
-int opt_fork(ts2_model *m)
+// Layout of the flat parameter buffers: the matrices in C-ABI order, grouped into buckets (embedding, final layer, one
+// per layer), every bucket padded to BUCKET_PAD elements
+void layout_buckets(const ts2_model_descr *d, const std::vector<std::pair<int64_t, int64_t>> &shapes, std::vector<Bucket> *buckets,
+                    std::vector<size_t> *mat_off, std::vector<int> *mat_bucket)
 {
-    TS2_CUDA(cudaEventRecord(m->ev_opt_fork, m->stream));
-    for (int i = 0; i < ts2_model::OPT_LANES; ++i)
-        TS2_CUDA(cudaStreamWaitEvent(m->opt_stream[i], m->ev_opt_fork, 0));
-    return TS2_OK;
-}
-// ... and the main stream waits for all lanes
-int opt_join(ts2_model *m)
-{
-    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
-        TS2_CUDA(cudaEventRecord(m->ev_opt_join[i], m->opt_stream[i]));
-        TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_opt_join[i], 0));
+    const int n_mats = (int)shapes.size();
+    std::vector<int> first = {0, 1};
+    int mi = 2;
+    for (int l = 0; l < d->layer_count; ++l) {
+        first.push_back(mi);
+        mi += layer_matrix_count(d->layers[l].layer_type);
     }
-    return TS2_OK;
-}
-// stream and scratch (doubles behind the two float vectors) of a matrix's lane
-static Ctx lane_ctx(ts2_model *m, int mat, float **scratch)
-{
-    Ctx c = ctx_of(m);
-    const int lane = m->mat_lane[mat];
-    c.stream = m->opt_stream[lane];
-    *scratch = m->opt_scratch + lane * m->opt_scratch_stride + 2 * m->max_rows;
-    return c;
+    first.push_back(n_mats);
+    buckets->assign(first.size() - 1, Bucket());
+    mat_off->assign(n_mats, 0);
+    mat_bucket->assign(n_mats, 0);
+    size_t off = 0;
+    for (size_t b = 0; b + 1 < first.size(); ++b) {
+        Bucket &bk = (*buckets)[b];
+        bk.mat0 = first[b];
+        bk.mat1 = first[b + 1];
+        bk.off = off;
+        for (int i = bk.mat0; i < bk.mat1; ++i) {
+            (*mat_off)[i] = off;
+            (*mat_bucket)[i] = (int)b;
+            off += (size_t)shapes[i].first * shapes[i].second;
+        }
+        off = (off + BUCKET_PAD - 1) / BUCKET_PAD * BUCKET_PAD;
+        bk.elems = off - bk.off;
+    }
 }
 
-// between opt_fork and opt_join
-int requantize_all(ts2_model *m)
+// ---- optimizer + requantisation over the flat buffers -------------------------------------------------------
+// the parts of the matrices that rank `rank` of `world` owns: one contiguous 1 / world part of every bucket
+void build_segments(const ts2_model *m, int world, int rank, std::vector<OptSeg> *segs, int *nitems)
 {
+    segs->clear();
+    int items = 0;
+    for (const Bucket &bk : m->buckets) {
+        const size_t part = bk.elems / world, lo = bk.off + part * rank, hi = lo + part;
+        for (int i = bk.mat0; i < bk.mat1; ++i) {
+            const Matrix &mt = m->mats[i];
+            const size_t m_lo = mt.offset, m_hi = mt.offset + (size_t)mt.x * mt.y;
+            const size_t a = std::max(lo, m_lo), b = std::min(hi, m_hi);
+            if (b <= a)
+                continue;
+            OptSeg sg;
+            sg.flat_off = (long long)mt.offset;
+            sg.a = (long long)(a - m_lo);
+            sg.b = (long long)(b - m_lo);
+            sg.x = (int)mt.x;
+            sg.y = (int)mt.y;
+            sg.row0 = (int)(sg.a / mt.x);
+            sg.nrows = (int)((sg.b - 1) / mt.x) - sg.row0 + 1;
+            sg.grow0 = m->mat_grow0[i];
+            sg.item0 = items;
+            sg.mat = i;
+            sg.qsize = bk.qsize;
+            sg.qbase = bk.qflat + (mt.offset - bk.off) * bk.qsize;
+            sg.sparsity = mt.sparsity;
+            items += sg.nrows;
+            segs->push_back(sg);
+        }
+    }
+    *nitems = items;
+}
+
+int upload_segments(ts2_model *m, const std::vector<OptSeg> &segs, OptSeg **dst)
+{
+    if (!*dst)
+        M_TRY(dalloc(m, dst, m->mats.size() + 2 * m->buckets.size() + 4)); // a part cuts at most two matrices more per bucket
+    TS2_CUDA(cudaMemcpyAsync(*dst, segs.data(), segs.size() * sizeof(OptSeg), cudaMemcpyHostToDevice, m->stream));
+    TS2_CUDA(cudaStreamSynchronize(m->stream)); // the host vector may go away
+    return TS2_OK;
+}
+
+#define M_NCCL(expr)                                                                              \
+    do {                                                                                          \
+        ncclResult_t _r = (expr);                                                                 \
+        if (_r != ncclSuccess)                                                                    \
+            return mfail(m, fail(TS2_ERR_COMM, "%s failed: %s", #expr, ncclGetErrorString(_r))); \
+    } while (0)
+
+// transposed copies, per-expert layouts and scale vectors from the row-major quantized matrices and their scales
+int post_quantize(ts2_model *m)
+{
+    Ctx c = ctx_of(m);
     const int D = m->D;
-    float *scratch = nullptr;
-    Ctx c = lane_ctx(m, 0, &scratch);
-    // embedding: always fp16 (TEmbedFloat, cfg_precision.h:62)
-    M_TRY(requantize(c, m->mats[0].w, D, m->mats[0].y, 1, m->embed16, D, nullptr, 0, m->mats[0].sko, scratch, false));
-    // final layer: fast copy for the logits, fp16 transposed copy of the same quantized values for dX
-    c = lane_ctx(m, 1, &scratch);
-    M_TRY(requantize(c, m->mats[1].w, D, m->V, m->ft, m->Wf, D, m->WfT16, m->V, m->mats[1].sko, scratch, m->ft == 0));
     const size_t fs = fast_size(m);
+    // final layer: fp16 transposed copy of the same quantized values for the dX contraction
+    M_TRY(qcopy_block(c, m->Wf, D, m->V, D, (int)fs, nullptr, 0, m->WfT16, m->V, m->ft == 0));
     const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
     for (Layer &ly : m->layers) {
         const int W = ly.wide, n = ly.ncat;
-        c = lane_ctx(m, ly.mat0, &scratch);
+        const Bucket &bk = m->buckets[m->mat_bucket[ly.mat0]];
+        auto qsrc = [&](int mat) { return bk.qflat + (m->mats[mat].offset - bk.off) * fs; };
         if (ly.type == TS2_LAYER_MOE) {
+            // the flat order keeps each matrix whole ([E X][D] expand, gate; [E D][X] contract); the contractions want
+            // the blocks of one expert together: Wcat [E][2X][D], WcatT [E][D][2X], Wc [E][D][X], WcT [E][X][D]
             const int E = m->E, X = m->X;
-            Matrix &me = m->mats[ly.mat0], &mg = m->mats[ly.mat0 + 1], &mc = m->mats[ly.mat0 + 2], &ms = m->mats[ly.mat0 + 3];
-            M_TRY(matrix_sko(c, me.w, D, (int64_t)E * X, me.sko, scratch));
-            M_TRY(matrix_sko(c, mg.w, D, (int64_t)E * X, mg.sko, scratch));
-            M_TRY(matrix_sko(c, mc.w, X, (int64_t)E * D, mc.sko, scratch));
             for (int e = 0; e < E; ++e) {
                 uint8_t *cat = (uint8_t *)ly.Wcat + (size_t)e * 2 * X * D * fs, *catT = (uint8_t *)ly.WcatT + (size_t)e * D * 2 * X * fs;
-                M_TRY(convert_block(c, me.w + (size_t)e * X * D, D, X, m->ft, cat, D, catT, 2 * X, me.sko, false));
-                M_TRY(convert_block(c, mg.w + (size_t)e * X * D, D, X, m->ft, cat + (size_t)X * D * fs, D, catT + (size_t)X * fs, 2 * X,
-                                    mg.sko, false));
-                M_TRY(convert_block(c, mc.w + (size_t)e * D * X, X, D, m->ft, (uint8_t *)ly.Wc + (size_t)e * D * X * fs, X,
-                                    (uint8_t *)ly.WcT + (size_t)e * X * D * fs, D, mc.sko, false));
+                M_TRY(qcopy_block(c, qsrc(ly.mat0) + (size_t)e * X * D * fs, D, X, D, (int)fs, cat, D, catT, 2 * X, false));
+                M_TRY(qcopy_block(c, qsrc(ly.mat0 + 1) + (size_t)e * X * D * fs, D, X, D, (int)fs, cat + (size_t)X * D * fs, D,
+                                  catT + (size_t)X * fs, 2 * X, false));
+                M_TRY(qcopy_block(c, qsrc(ly.mat0 + 2) + (size_t)e * D * X * fs, X, D, X, (int)fs, (uint8_t *)ly.Wc + (size_t)e * D * X * fs, X,
+                                  (uint8_t *)ly.WcT + (size_t)e * X * D * fs, D, false));
             }
-            M_TRY(requantize(c, ms.w, D, E, m->ft, ly.Wsel, D, ly.WselT, m->epad, ms.sko, scratch, false));
+            M_TRY(qcopy_block(c, qsrc(ly.mat0 + 3), D, E, D, (int)fs, ly.Wsel, D, ly.WselT, m->epad, false));
             M_TRY(fill_vector(c, ly.fwd_col, 2 * X, a, nullptr, false));
-            M_TRY(fill_vector(c, ly.bwd_row_e, X, 1.f, me.sko, true));
+            M_TRY(fill_vector(c, ly.bwd_row_e, X, 1.f, m->mats[ly.mat0].sko, true));
             continue;
         }
-        for (int j = 0; j < n; ++j) {
-            Matrix &mt = m->mats[ly.mat0 + j];
-            M_TRY(requantize(c, mt.w, D, W, m->ft, (uint8_t *)ly.Wcat + (size_t)j * W * D * fs, D, (uint8_t *)ly.WcatT + (size_t)j * W * fs,
-                             (int64_t)n * W, mt.sko, scratch, false));
-        }
-        Matrix &mc = m->mats[ly.mat0 + n];
-        M_TRY(requantize(c, mc.w, W, D, m->ft, ly.Wc, W, ly.WcT, D, mc.sko, scratch, false));
-        // forward column scales: matrices followed by a normalisation (Q, V, Expand) and the gates use the
-        // unit-RMS matrix q/32 (GetDataNoScale); K carries its matrix scale
-        M_TRY(fill_vector(c, ly.fwd_col, n * W, a, nullptr, false));
-        M_TRY(fill_vector(c, ly.bwd_row, n * W, 1.f, nullptr, false));
-        if (ly.type == TS2_LAYER_ATT) {
-            M_TRY(fill_vector(c, ly.fwd_col + W, W, a, m->mats[ly.mat0 + 1].sko, false));
-            for (int j = 0; j < 3; ++j) // dW rows of Q, K, V are divided by their matrix scale
-                M_TRY(fill_vector(c, ly.bwd_row + j * W, W, 1.f, m->mats[ly.mat0 + j].sko, true));
-        } else {
-            M_TRY(fill_vector(c, ly.bwd_row, W, 1.f, m->mats[ly.mat0].sko, true));
-        }
+        // the concatenated block [n W][D] transposes in one pass: its row blocks become the column blocks of WcatT
+        M_TRY(qcopy_block(c, ly.Wcat, D, (int64_t)n * W, D, (int)fs, nullptr, 0, ly.WcatT, (int64_t)n * W, false));
+        M_TRY(qcopy_block(c, ly.Wc, W, D, W, (int)fs, nullptr, 0, ly.WcT, D, false));
+        // forward column scales: matrices followed by a normalisation (Q, V, Expand) and the gates use the unit-RMS
+        // matrix q/32 (GetDataNoScale), K carries its matrix scale; dW rows of Q, K, V / Expand are divided by theirs
+        M_TRY(layer_scales(c, ly.fwd_col, ly.bwd_row, W, n, ly.type == TS2_LAYER_ATT, a, m->skos + ly.mat0));
     }
+    return TS2_OK;
+}
+
+// Requantisation of the whole model on this rank alone (creation, ts2_set_params): matrix scales, quantized copies
+int requantize_all(ts2_model *m)
+{
+    Ctx c = ctx_of(m);
+    M_TRY(opt_update(c, m->d_segs_full, m->nseg_full, m->nitems_full, nullptr, nullptr, nullptr, nullptr, m->w_flat, m->roww2));
+    M_TRY(opt_sko(c, m->d_optmats, (int)m->mats.size(), m->roww2, m->skos));
+    M_TRY(opt_quantize(c, m->d_segs_full, m->nseg_full, m->nitems_full, m->w_flat, m->skos));
+    M_TRY(post_quantize(m));
     return TS2_OK;
 }
 
@@ -454,7 +519,14 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     if ((int)shapes.size() != n_mats)
         return fail(TS2_ERR_INVALID_ARG, "expected %d matrices, got %d", (int)shapes.size(), n_mats);
     m->mats.resize(n_mats);
-    size_t off = 0;
+    std::vector<size_t> mat_off;
+    layout_buckets(&d, shapes, &m->buckets, &mat_off, &m->mat_bucket);
+    m->buckets[0].qsize = 2; // the embedding is always fp16 (TEmbedFloat, cfg_precision.h:62)
+    for (size_t b = 1; b < m->buckets.size(); ++b)
+        m->buckets[b].qsize = (int)fs;
+    m->mat_grow0.assign(n_mats, 0);
+    size_t params = 0;
+    int rows = 0;
     for (int i = 0; i < n_mats; ++i) {
         if (!mats[i].data || mats[i].x_size != shapes[i].first || mats[i].y_size != shapes[i].second)
             return fail(TS2_ERR_INVALID_ARG, "matrix %d: expected [%lld][%lld], got [%lld][%lld]", i, (long long)shapes[i].second,
@@ -463,17 +535,34 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         mt.x = shapes[i].first;
         mt.y = shapes[i].second;
         mt.row_disp_size = (i < 2) ? (int)mt.y : 1; // per-row dispersion for embedding and final layer (model_params.cpp:150-151)
-        mt.offset = off;
-        off += (size_t)mt.x * mt.y;
+        mt.offset = mat_off[i];
+        params += (size_t)mt.x * mt.y;
+        m->mat_grow0[i] = rows;
+        rows += (int)mt.y;
         m->max_rows = std::max(m->max_rows, mt.y);
     }
-    m->total_params = off;
+    const size_t off = m->buckets.back().off + m->buckets.back().elems;
+    m->total_params = params;
+    m->flat_elems = off;
+    m->n_rows_total = rows;
     M_TRY(dalloc(m, &m->w_flat, off));
     M_TRY(dalloc(m, &m->avg_flat, off));
     M_TRY(dalloc(m, &m->grad_flat, off));
     M_TRY(dalloc(m, &m->skos, n_mats));
+    M_TRY(dalloc(m, &m->rowsum, (size_t)rows));
+    M_TRY(dalloc(m, &m->row_scale, (size_t)rows));
+    M_TRY(dalloc(m, &m->roww2, (size_t)rows));
+    TS2_CUDA(cudaMemsetAsync(m->w_flat, 0, off * 4, m->stream));
     TS2_CUDA(cudaMemsetAsync(m->avg_flat, 0, off * 4, m->stream));
     TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, off * 4, m->stream));
+    for (Bucket &bk : m->buckets) {
+        M_TRY(dalloc(m, &bk.qflat, bk.elems * bk.qsize));
+        TS2_CUDA(cudaMemsetAsync(bk.qflat, 0, bk.elems * bk.qsize, m->stream));
+    }
+    auto qptr = [&](int mat) {
+        const Bucket &bk = m->buckets[m->mat_bucket[mat]];
+        return bk.qflat + (m->mats[mat].offset - bk.off) * bk.qsize;
+    };
     for (int i = 0; i < n_mats; ++i) {
         Matrix &mt = m->mats[i];
         mt.w = m->w_flat + mt.offset;
@@ -492,9 +581,10 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     else
         TS2_CUDA(cudaMemsetAsync(m->bias, 0, (size_t)m->V * 4, m->stream));
 
-    // quantized weights
-    M_TRY(dalloc(m, &m->embed16, (size_t)d.label_count * D));
-    M_TRY(dalloc(m, (uint8_t **)&m->Wf, (size_t)m->V * D * fs));
+    // quantized weights: the row-major copies of the embedding, the final layer and the dense layers' matrices are
+    // the buckets' quantized buffers themselves (the requantiser and the data-parallel all-gather write them in place)
+    m->embed16 = (__half *)qptr(0);
+    m->Wf = qptr(1);
     M_TRY(dalloc(m, &m->WfT16, (size_t)m->V * D));
     m->layers.resize(L);
     int mi = 2;
@@ -541,9 +631,9 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         max_wide = std::max(max_wide, ly.wide);
         max_cat = std::max(max_cat, ly.ncat * ly.wide);
         const size_t W = ly.wide, C = (size_t)ly.ncat * ly.wide;
-        M_TRY(dalloc(m, (uint8_t **)&ly.Wcat, C * D * fs));
+        ly.Wcat = qptr(ly.mat0); // the ncat matrices are consecutive in the flat order: together they are [C][D]
+        ly.Wc = qptr(ly.mat0 + ly.ncat);
         M_TRY(dalloc(m, (uint8_t **)&ly.WcatT, C * D * fs));
-        M_TRY(dalloc(m, (uint8_t **)&ly.Wc, W * D * fs));
         M_TRY(dalloc(m, (uint8_t **)&ly.WcT, W * D * fs));
         M_TRY(dalloc(m, &ly.fwd_col, C));
         M_TRY(dalloc(m, &ly.bwd_row, C));
@@ -603,8 +693,6 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     M_TRY(dalloc(m, &m->logp_ring, ts2_model::LOSS_RING + 1)); // the last slot serves ts2_forward_score
     TS2_CUDA(cudaMemsetAsync(m->logp_ring, 0, (ts2_model::LOSS_RING + 1) * 4, m->stream));
     m->logp = m->logp_ring;
-    m->opt_scratch_stride = (size_t)m->max_rows * 4 + 16;
-    M_TRY(dalloc(m, &m->opt_scratch, m->opt_scratch_stride * ts2_model::OPT_LANES));
     // batch
     BatchDev &b = m->batch;
     b.label_cap = (size_t)T * 4;
@@ -642,16 +730,30 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
 
     Ctx c = ctx_of(m);
     M_TRY(fill_rope(c, m->rope, T));
-    m->mat_lane.assign(m->mats.size(), 0);
-    m->mat_lane[1] = 1 % ts2_model::OPT_LANES;
-    for (size_t l = 0; l < m->layers.size(); ++l) {
-        const size_t end = l + 1 < m->layers.size() ? (size_t)m->layers[l + 1].mat0 : m->mats.size();
-        for (size_t i = m->layers[l].mat0; i < end; ++i)
-            m->mat_lane[i] = (int)((l + 2) % ts2_model::OPT_LANES);
+    // tables of the flat optimizer
+    {
+        std::vector<OptMat> om(n_mats);
+        for (int i = 0; i < n_mats; ++i) {
+            om[i].x = m->mats[i].x;
+            om[i].y = m->mats[i].y;
+            om[i].row_disp_size = m->mats[i].row_disp_size;
+            om[i].grow0 = m->mat_grow0[i];
+            om[i].row_disp = m->mats[i].row_disp;
+            om[i].sum_weight = m->mats[i].sum_weight;
+        }
+        M_TRY(dalloc(m, &m->d_optmats, (size_t)n_mats));
+        TS2_CUDA(cudaMemcpyAsync(m->d_optmats, om.data(), om.size() * sizeof(OptMat), cudaMemcpyHostToDevice, m->stream));
+        TS2_CUDA(cudaStreamSynchronize(m->stream));
+        std::vector<OptSeg> segs;
+        build_segments(m, 1, 0, &segs, &m->nitems_full);
+        m->nseg_full = (int)segs.size();
+        M_TRY(upload_segments(m, segs, &m->d_segs_full));
+        // without data parallelism this rank's parts are everything
+        m->d_segs_shard = m->d_segs_full;
+        m->nseg_shard = m->nseg_full;
+        m->nitems_shard = m->nitems_full;
     }
-    M_TRY(opt_fork(m));
     M_TRY(requantize_all(m));
-    M_TRY(opt_join(m));
     TS2_CUDA(cudaStreamSynchronize(m->stream));
     return TS2_OK;
 }
@@ -809,19 +911,19 @@ int tap_gradient(ts2_model *m, int boundary)
     return TS2_OK;
 }
 
-// data-parallel sum of the gradients of matrices [m0, m1) (contiguous in the flat buffer) on the communication
-// stream, ordered after what the main stream has queued so far; the backward pass goes on meanwhile
-static int reduce_matrices(ts2_model *m, int m0, int m1)
+// data-parallel sum of the gradient of the bucket that starts at matrix m0, on the communication stream, ordered
+// after what the main stream has queued so far; the backward pass goes on meanwhile.  Reduce-scatter: every rank
+// receives the sum for the 1 / world part of the bucket it will update (in place: the part sits where it was).
+static int reduce_matrices(ts2_model *m, int m0, int)
 {
     if (!m->reduce_in_backward)
         return TS2_OK;
-    const size_t off = m->mats[m0].offset;
-    const size_t end = m1 < (int)m->mats.size() ? m->mats[m1].offset : m->total_params;
+    const Bucket &bk = m->buckets[m->mat_bucket[m0]];
+    const size_t part = bk.elems / m->world;
     TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
     TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
-    ncclResult_t r = ncclAllReduce(m->grad_flat + off, m->grad_flat + off, end - off, ncclFloat, ncclSum, m->comm, m->comm_stream);
-    if (r != ncclSuccess)
-        return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+    M_NCCL(ncclReduceScatter(m->grad_flat + bk.off, m->grad_flat + bk.off + part * m->rank, part, ncclFloat, ncclSum, m->comm,
+                             m->comm_stream));
     return TS2_OK;
 }
 
@@ -958,44 +1060,72 @@ int backward(ts2_model *m)
     return TS2_OK;
 }
 
+// Optimizer + requantisation of this rank's parts (everything without data parallelism).  Per-row sums of squares
+// of gradient and weights go to vectors over all rows of all matrices; with data parallelism those vectors are summed
+// over the ranks (1 MB and 2 MB), which completes the rows a part boundary cuts and gives every rank the matrix-level
+// sums; the quantized bytes are then all-gathered (a quarter of the fp32 bytes an all-reduce design moves twice).
 int apply(ts2_model *m, const ts2_training_step *step)
 {
-    if (m->comm && m->world > 1) {
-        // data-parallel sum of the gradient: queued per layer on the communication stream during the backward pass
-        // (reduce_matrices), so that only the last pieces are still in flight here
-        if (!m->reduce_in_backward) {
-            TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
-            TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
-            ncclResult_t r = ncclAllReduce(m->grad_flat, m->grad_flat, m->total_params, ncclFloat, ncclSum, m->comm, m->comm_stream);
-            if (r != ncclSuccess)
-                return mfail(m, fail(TS2_ERR_COMM, "ncclAllReduce failed: %s", ncclGetErrorString(r)));
+    Ctx c = ctx_of(m);
+    const bool dp = m->comm && m->world > 1;
+    const int n_mats = (int)m->mats.size();
+    if (dp) {
+        if (!m->reduce_in_backward) { // gradients accumulated by calls that did not apply: exchange them now
+            m->reduce_in_backward = true;
+            for (const Bucket &bk : m->buckets)
+                M_TRY(reduce_matrices(m, bk.mat0, bk.mat1));
+            m->reduce_in_backward = false;
         }
         TS2_CUDA(cudaEventRecord(m->ev_reduced, m->comm_stream));
         TS2_CUDA(cudaStreamWaitEvent(m->stream, m->ev_reduced, 0));
+        TS2_CUDA(cudaMemsetAsync(m->rowsum, 0, (size_t)m->n_rows_total * 4, m->stream));
+        TS2_CUDA(cudaMemsetAsync(m->roww2, 0, (size_t)m->n_rows_total * 8, m->stream));
     }
-    M_TRY(opt_fork(m));
-    for (size_t mi = 0; mi < m->mats.size(); ++mi) {
-        Matrix &mt = m->mats[mi];
-        float *lane_doubles = nullptr;
-        Ctx c = lane_ctx(m, (int)mi, &lane_doubles);
-        float *lane_scratch = lane_doubles - 2 * m->max_rows;
-        OptMatrix o;
-        o.w = mt.w;
-        o.avg_grad = mt.avg;
-        o.grad = mt.grad;
-        o.x = mt.x;
-        o.y = mt.y;
-        o.row_disp = mt.row_disp;
-        o.row_disp_size = mt.row_disp_size;
-        o.sum_weight = mt.sum_weight;
-        o.sparsity = mt.sparsity;
-        o.row_sum2 = lane_scratch;
-        o.row_scale = lane_scratch + m->max_rows;
-        o.w_sum2 = nullptr;
-        M_TRY(apply_gradient(c, o, *step));
+    M_TRY(opt_row_sum2(c, m->d_segs_shard, m->nseg_shard, m->nitems_shard, m->grad_flat, m->rowsum));
+    if (dp)
+        M_NCCL(ncclAllReduce(m->rowsum, m->rowsum, (size_t)m->n_rows_total, ncclFloat, ncclSum, m->comm, m->stream));
+    M_TRY(opt_disp(c, m->d_optmats, n_mats, m->rowsum, step->disp_decay, m->row_scale));
+    M_TRY(opt_update(c, m->d_segs_shard, m->nseg_shard, m->nitems_shard, m->grad_flat, m->row_scale, step, m->avg_flat, m->w_flat,
+                     m->roww2));
+    if (dp)
+        M_NCCL(ncclAllReduce(m->roww2, m->roww2, (size_t)m->n_rows_total, ncclDouble, ncclSum, m->comm, m->stream));
+    M_TRY(opt_sko(c, m->d_optmats, n_mats, m->roww2, m->skos));
+    M_TRY(opt_quantize(c, m->d_segs_shard, m->nseg_shard, m->nitems_shard, m->w_flat, m->skos));
+    if (dp) {
+        M_NCCL(ncclGroupStart());
+        for (const Bucket &bk : m->buckets) {
+            const size_t part = bk.elems / m->world * bk.qsize;
+            ncclResult_t r = ncclAllGather(bk.qflat + part * m->rank, bk.qflat, part, ncclUint8, m->comm, m->stream);
+            if (r != ncclSuccess) {
+                ncclGroupEnd();
+                return mfail(m, fail(TS2_ERR_COMM, "ncclAllGather failed: %s", ncclGetErrorString(r)));
+            }
+        }
+        M_NCCL(ncclGroupEnd());
+        m->master_stale = true;
     }
-    M_TRY(requantize_all(m));
-    M_TRY(opt_join(m));
+    M_TRY(post_quantize(m));
+    return TS2_OK;
+}
+
+// data parallel: brings the fp32 weights and momentum of the other ranks' parts up to date (all ranks must call)
+int sync_master(ts2_model *m)
+{
+    if (!m->master_stale)
+        return TS2_OK;
+    M_NCCL(ncclGroupStart());
+    for (const Bucket &bk : m->buckets) {
+        const size_t part = bk.elems / m->world;
+        for (float *flat : {m->w_flat, m->avg_flat}) {
+            ncclResult_t r = ncclAllGather(flat + bk.off + part * m->rank, flat + bk.off, part, ncclFloat, m->comm, m->stream);
+            if (r != ncclSuccess) {
+                ncclGroupEnd();
+                return mfail(m, fail(TS2_ERR_COMM, "ncclAllGather failed: %s", ncclGetErrorString(r)));
+            }
+        }
+    }
+    M_NCCL(ncclGroupEnd());
+    m->master_stale = false;
     return TS2_OK;
 }
 
@@ -1155,11 +1285,6 @@ int ts2_create(const ts2_model_descr *descr, const ts2_matrix_view *mats, int n_
     m->max_nodes = (max_nodes + 127) / 128 * 128;
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking);
-    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
-        cudaStreamCreateWithFlags(&m->opt_stream[i], cudaStreamNonBlocking);
-        cudaEventCreateWithFlags(&m->ev_opt_join[i], cudaEventDisableTiming);
-    }
-    cudaEventCreateWithFlags(&m->ev_opt_fork, cudaEventDisableTiming);
     cudaEventCreate(&m->ev_start);
     cudaEventCreate(&m->ev_stop);
     cudaEventCreate(&m->ev_t0);
@@ -1203,14 +1328,6 @@ void ts2_destroy(ts2_model *m)
         cudaStreamDestroy(m->stream);
     if (m->comm_stream)
         cudaStreamDestroy(m->comm_stream);
-    for (int i = 0; i < ts2_model::OPT_LANES; ++i) {
-        if (m->opt_stream[i])
-            cudaStreamDestroy(m->opt_stream[i]);
-        if (m->ev_opt_join[i])
-            cudaEventDestroy(m->ev_opt_join[i]);
-    }
-    if (m->ev_opt_fork)
-        cudaEventDestroy(m->ev_opt_fork);
     delete m;
 }
 
@@ -1248,7 +1365,7 @@ int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model)
         TS2_CUDA(cudaMemsetAsync(m->trace_dev, 0, (size_t)ts2_model::TRACE_MAX * 32, m->stream));
     }
     if (!m->grads_dirty)
-        TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, m->total_params * 4, m->stream));
+        TS2_CUDA(cudaMemsetAsync(m->grad_flat, 0, m->flat_elems * 4, m->stream));
     M_TRY(forward(m));
     // an accumulated gradient of earlier calls sits in the same buffer: the per-layer sums below then cover it too
     m->reduce_in_backward = add_to_model == TS2_GRADIENT_APPLY && m->comm && m->world > 1;
@@ -1259,7 +1376,7 @@ int ts2_backprop(ts2_model *m, const ts2_training_step *step, int add_to_model)
     m->grads_dirty = true;
     m->last_targets = m->batch.target_count;
     if (add_to_model == TS2_GRADIENT_APPLY) {
-        m->reduce_in_backward = m->comm && m->world > 1; // tells apply() that the sums are already queued
+        m->reduce_in_backward = m->comm && m->world > 1; // tells apply() that the exchanges are already queued
         const int arc = apply(m, step);
         m->reduce_in_backward = false;
         if (arc != TS2_OK)
@@ -1323,6 +1440,8 @@ int ts2_get_params(ts2_model *m, int what, ts2_matrix_view *mats_out, int n_mats
     if (!m || !mats_out || n_mats != (int)m->mats.size())
         return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_get_params");
     TS2_CUDA(cudaSetDevice(m->device));
+    if (what != TS2_PARAM_GRADIENT)
+        M_TRY(sync_master(m));
     M_TRY(wait_stream(m));
     for (int i = 0; i < n_mats; ++i) {
         Matrix &mt = m->mats[i];
@@ -1341,6 +1460,7 @@ int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_ma
     if (!m || !mats || n_mats != (int)m->mats.size() || what == TS2_PARAM_GRADIENT)
         return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_set_params");
     TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(sync_master(m)); // a partial update must land on current values
     M_TRY(wait_stream(m));
     for (int i = 0; i < n_mats; ++i) {
         Matrix &mt = m->mats[i];
@@ -1351,9 +1471,7 @@ int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_ma
         TS2_CUDA(cudaMemcpy(what == TS2_PARAM_WEIGHTS ? mt.w : mt.avg, mats[i].data, (size_t)mt.x * mt.y * 4, cudaMemcpyHostToDevice));
     }
     if (what == TS2_PARAM_WEIGHTS) {
-        M_TRY(opt_fork(m));
         M_TRY(requantize_all(m));
-        M_TRY(opt_join(m));
         M_TRY(wait_stream(m));
     }
     return TS2_OK;
@@ -1548,6 +1666,35 @@ const char *ts2_debug_trace_name(ts2_model *m, int index)
     return m->trace_names[index].c_str();
 }
 
+int ts2_dp_layout(const ts2_model_descr *descr, int64_t *matrix_offset, int n_mats, int64_t *bucket_offset, int64_t *bucket_elems,
+                  int32_t *bucket_first_matrix, int max_buckets)
+{
+    int rc = validate(descr);
+    if (rc != TS2_OK)
+        return rc;
+    std::vector<std::pair<int64_t, int64_t>> shapes;
+    shapes_of(descr, &shapes);
+    std::vector<Bucket> buckets;
+    std::vector<size_t> mat_off;
+    std::vector<int> mat_bucket;
+    layout_buckets(descr, shapes, &buckets, &mat_off, &mat_bucket);
+    if (matrix_offset) {
+        if (n_mats != (int)shapes.size())
+            return fail(TS2_ERR_INVALID_ARG, "ts2_dp_layout: expected %d matrices, got %d", (int)shapes.size(), n_mats);
+        for (int i = 0; i < n_mats; ++i)
+            matrix_offset[i] = (int64_t)mat_off[i];
+    }
+    for (int b = 0; b < std::min((int)buckets.size(), max_buckets); ++b) {
+        if (bucket_offset)
+            bucket_offset[b] = (int64_t)buckets[b].off;
+        if (bucket_elems)
+            bucket_elems[b] = (int64_t)buckets[b].elems;
+        if (bucket_first_matrix)
+            bucket_first_matrix[b] = buckets[b].mat0;
+    }
+    return (int)buckets.size();
+}
+
 int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES])
 {
     static_assert(sizeof(ncclUniqueId) <= TS2_COMM_ID_BYTES, "id buffer too small");
@@ -1573,13 +1720,31 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
     m->world = world_size;
     if (world_size == 1)
         return TS2_OK;
+    if (BUCKET_PAD % (4 * (size_t)world_size))
+        return fail(TS2_ERR_UNSUPPORTED, "world size %d: every rank's part of a bucket must be a multiple of 4 elements (world sizes that divide %zu)",
+                    world_size, BUCKET_PAD / 4);
     ncclUniqueId u;
     memcpy(&u, id, sizeof(u));
-    ncclResult_t r = ncclCommInitRank(&m->comm, world_size, u, rank);
+    // The exchanges run beside the backward pass, whose contractions are persistent kernels sized to every SM: keep the
+    // communication kernels to a few CTAs (TS2_NCCL_MAX_CTAS, default 8; the volume per step is small against NVLink)
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    int max_ctas = 8;
+    if (const char *e = getenv("TS2_NCCL_MAX_CTAS"))
+        max_ctas = atoi(e);
+    if (max_ctas > 0) {
+        cfg.maxCTAs = max_ctas;
+        cfg.minCTAs = std::min(cfg.maxCTAs, 1);
+    }
+    ncclResult_t r = ncclCommInitRankConfig(&m->comm, world_size, u, rank, &cfg);
     if (r != ncclSuccess) {
         m->comm = nullptr;
-        return mfail(m, fail(TS2_ERR_COMM, "ncclCommInitRank failed: %s", ncclGetErrorString(r)));
+        return mfail(m, fail(TS2_ERR_COMM, "ncclCommInitRankConfig failed: %s", ncclGetErrorString(r)));
     }
+    std::vector<OptSeg> segs;
+    build_segments(m, world_size, rank, &segs, &m->nitems_shard);
+    m->nseg_shard = (int)segs.size();
+    m->d_segs_shard = nullptr;
+    M_TRY(upload_segments(m, segs, &m->d_segs_shard));
     return TS2_OK;
 }
 

@@ -92,6 +92,23 @@ class ModelSpec:
         return d, arr
 
 
+def dp_layout(spec: ModelSpec):
+    """(matrix_offset, bucket_offset, bucket_elems, bucket_first_matrix) of the engine's flat parameter buffers
+    (ts2_dp_layout): what a data-parallel rank owns is bucket_elems / world elements of every bucket."""
+    lib = capi.load_library()
+    descr, keep = spec.to_c()
+    n = len(spec.matrix_shapes())
+    nb = 2 + len(spec.layers)
+    mo, bo, be = np.zeros(n, np.int64), np.zeros(nb, np.int64), np.zeros(nb, np.int64)
+    bf = np.zeros(nb, np.int32)
+    p64 = C.POINTER(C.c_int64)
+    rc = lib.ts2_dp_layout(C.byref(descr), mo.ctypes.data_as(p64), n, bo.ctypes.data_as(p64), be.ctypes.data_as(p64),
+                           bf.ctypes.data_as(C.POINTER(C.c_int32)), nb)
+    if rc != nb:
+        raise capi.Ts2Error(rc, lib.ts2_last_error(None).decode())
+    return mo, bo, be, bf
+
+
 def init_weights(spec: ModelSpec, seed: int, std: float = 0.02, select_std: float = None) -> List[np.ndarray]:
     """fp32 master weights ~ N(0, std) from numpy's default_rng(seed)."""
     rng = np.random.default_rng(seed)
