@@ -22,6 +22,7 @@
 #include "fast_types.cuh"
 #include <cuda.h>
 #include <vector>
+#include <type_traits>
 #include <mutex>
 
 namespace ts2 {
@@ -45,6 +46,9 @@ struct GemmParams {
     int out_kind;
     float *workspace;
     int32_t *status;
+    // dynamic unit scheduler: {next unit, finished CTAs}, both zero between launches (the last CTA to finish resets
+    // them); null: unit i of CTA b is b + i * gridDim.x
+    int *sched = nullptr;
     // grouped forms (mixture-of-experts): 0 none; 1 every 128-row M tile belongs to one group (tile_group[m_tile],
     // negative: skip) and reads B rows [group * group_rows_b + n]; 2 the K range of a unit is the row segment of
     // its group (group_kptr[g] .. group_kptr[g+1], multiples of the K block) and C moves by c_group_stride per group
@@ -182,6 +186,14 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                    tempty0 = smem_u32(bars + 2 * STAGES + 2), drain = smem_u32(bars + 2 * STAGES + 4);
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 5);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    // Unit ring: the producer draws the CTA's next unit (from a global counter, so that a CTA that starts late or runs
+    // beside another kernel simply takes fewer units) and hands its number to the MMA thread and the epilogue warps
+    // through RING shared-memory slots: rfull (1 arrival: the producer), rempty (the MMA thread + every epilogue warp).
+    constexpr int RING = 8;
+    constexpr int EPI_WARPS = GATED ? 16 : 8;
+    uint64_t *rbars = (uint64_t *)(smem + L::BAR_OFFSET + 256);
+    const uint32_t rfull0 = smem_u32(rbars), rempty0 = smem_u32(rbars + RING);
+    volatile int *unit_ring = (volatile int *)(rbars + 2 * RING);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -189,9 +201,13 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
+        for (int s = 0; s < RING; ++s) {
+            mbar_init(rfull0 + 8 * s, 1);
+            mbar_init(rempty0 + 8 * s, 1 + EPI_WARPS);
+        }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, GATED ? 16 : 8); // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * a, EPI_WARPS); // one arrival per epilogue warp
         }
         mbar_init(drain, 1);
         *abort_flag = 0;
@@ -218,7 +234,38 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
             uint32_t phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            int rslot = 0, seq = 0;
+            uint32_t rphase = 0;
+            // Two instances of the loop, so that the number drawn from the counter is not merged with the static one
+            // right after the draw: the atomic takes about a microsecond to answer, and its result must not be touched
+            // before the top of the next iteration, a whole unit's copies later.
+            auto producer_loop = [&](auto dynamic_tag) {
+            constexpr bool DYNAMIC = decltype(dynamic_tag)::value;
+            auto draw = [&]() -> int {
+                if constexpr (DYNAMIC) {
+                    int v;
+                    asm volatile("atom.global.add.s32 %0, [%1], 1;" : "=r"(v) : "l"(p.sched) : "memory");
+                    return v;
+                } else {
+                    return (int)blockIdx.x + (seq++) * (int)gridDim.x;
+                }
+            };
+            int next_u = draw();
+            while (ok) {
+                const int u = next_u;
+                if (!mbar_wait(rempty0 + 8 * rslot, rphase ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                unit_ring[rslot] = u < units ? u : -1;
+                mbar_arrive(rfull0 + 8 * rslot); // release: the slot's number is visible to whoever sees the arrival
+                if (++rslot == RING) {
+                    rslot = 0;
+                    rphase ^= 1;
+                }
+                if (u >= units)
+                    break;
+                next_u = draw(); // the counter's latency hides behind this unit's copies
                 Unit un;
                 if (!decode_unit(p, u, BN, un))
                     continue;
@@ -256,6 +303,11 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                     }
                 }
             }
+            };
+            if (p.sched)
+                producer_loop(std::true_type());
+            else
+                producer_loop(std::false_type());
             if (!ok) {
                 // abort path: wait (bounded) for the copies still in flight before the CTA gives its
                 // shared memory back.  The last min(issued, STAGES) stages may have pending copies.
@@ -271,6 +323,12 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                     }
                 }
             }
+            // every CTA passes here exactly once, after its last draw: the last one leaves the counters at zero for the
+            // next launch that uses them
+            if (p.sched && atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+                p.sched[0] = 0;
+                p.sched[1] = 0;
+            }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
@@ -278,7 +336,19 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            int rslot = 0;
+            uint32_t rphase = 0;
+            while (ok) {
+                if (!mbar_wait(rfull0 + 8 * rslot, rphase, abort_flag))
+                    break;
+                const int u = unit_ring[rslot];
+                mbar_arrive(rempty0 + 8 * rslot);
+                if (++rslot == RING) {
+                    rslot = 0;
+                    rphase ^= 1;
+                }
+                if (u < 0)
+                    break;
                 Unit un;
                 if (!decode_unit(p, u, BN, un))
                     continue;
@@ -343,7 +413,21 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
         const int c_begin = half * (CHUNKS / 2), c_end = c_begin + CHUNKS / 2;
         uint8_t *const stg_warp = smem + L::STAGING_OFFSET + (warp - 2) * 4096;
         const bool out16 = p.out_kind == TS2_OUT_F16 || p.out_kind == TS2_OUT_BF16;
-        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        int rslot = 0;
+        uint32_t rphase = 0;
+        for (;;) {
+            if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + 8 * rslot, rphase, abort_flag)))
+                break;
+            const int u = unit_ring[rslot];
+            __syncwarp(); // every lane has read the slot before the warp gives it back
+            if (lane == 0)
+                mbar_arrive(rempty0 + 8 * rslot);
+            if (++rslot == RING) {
+                rslot = 0;
+                rphase ^= 1;
+            }
+            if (u < 0)
+                break;
             Unit un;
             if (!decode_unit(p, u, BN, un))
                 continue;
@@ -813,6 +897,32 @@ size_t gemm_workspace_bytes(int device, int kind, bool mn, int64_t M, int64_t N,
     return (size_t)pl.m_tiles * pl.n_tiles * pl.splits * BM * pl.bn * sizeof(float);
 }
 
+// Counters of the dynamic unit scheduler: SCHED_SLOTS pairs {next unit, finished CTAs} per device, zero between
+// launches (the kernel's last CTA resets its pair).  Launches take the pairs in turn, so two launches share one only
+// if SCHED_SLOTS others were issued between them while the first is still running.
+static constexpr int SCHED_SLOTS = 1024;
+static int *sched_counters(int device)
+{
+    static int *base[16] = {};
+    static std::mutex mu;
+    static std::atomic<unsigned> serial{0};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        int *&b = base[device & 15];
+        if (!b) {
+            if (cudaMalloc(&b, SCHED_SLOTS * 2 * sizeof(int)) != cudaSuccess) {
+                b = nullptr;
+                return nullptr;
+            }
+            cudaMemset(b, 0, SCHED_SLOTS * 2 * sizeof(int));
+        }
+    }
+    return base[device & 15] + 2 * (serial.fetch_add(1, std::memory_order_relaxed) % SCHED_SLOTS);
+}
+
+static std::atomic<int> g_reserved_sms{0};
+void gemm_reserve_sms(int n) { g_reserved_sms.store(std::max(0, n), std::memory_order_relaxed); }
+
 // ---- timing ----------------------------------------------------------------------
 static std::mutex g_time_mu;
 static bool g_time_on = false;
@@ -889,7 +999,10 @@ static int launch(const GemmArgs &a, const Plan &pl, const CUtensorMap &tmA, con
         TS2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL));
         configured[a.device & 15] = true;
     }
-    kern<<<pl.grid, GATED ? NUM_THREADS_GATED : NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, tmC, p);
+    // SMs left to kernels that run beside this one (the data-parallel exchange): a persistent CTA that finds its SM
+    // taken starts only when another CTA of the grid has finished all of its units, which can double the launch's time
+    const int grid = std::max(1, std::min(pl.grid, sm_count(a.device) - g_reserved_sms.load(std::memory_order_relaxed)));
+    kern<<<grid, GATED ? NUM_THREADS_GATED : NUM_THREADS, SmemLayout<BN>::TOTAL, a.stream>>>(tmA, tmB, tmC, p);
     TS2_CHECK_LAUNCH();
     if (pl.splits > 1) {
         const long long total = (long long)pl.m_tiles * pl.n_tiles * BM * BN / 4;
@@ -975,6 +1088,13 @@ int gemm(const GemmArgs &a)
     p.status = device_status_word(a.device);
     if (!p.status)
         return fail(TS2_ERR_CUDA, "gemm: no device status word");
+    // Units are assigned statically by default (CTA b takes units b, b + grid, ...).  Drawing them from a global counter
+    // (TS2_GEMM_DYNAMIC_UNITS=1) keeps a CTA that starts late, because a communication kernel holds its SM, from
+    // stretching the launch, but measured 6 - 10 % slower on the contractions of a whole step, more than it saves.
+    static const bool dynamic_units = getenv("TS2_GEMM_DYNAMIC_UNITS") != nullptr;
+    p.sched = dynamic_units ? sched_counters(a.device) : nullptr;
+    if (dynamic_units && !p.sched)
+        return fail(TS2_ERR_CUDA, "gemm: no scheduler counters");
     p.group_mode = a.group_mode;
     p.groups = a.groups;
     p.tile_group = a.tile_group;

@@ -65,6 +65,9 @@ int gemm(const GemmArgs &a);
 // out-of-range elements read as zero
 int make_tensor_map(::CUtensorMap_st *tm, const void *base, int es, int64_t inner, int64_t rows, int64_t ld, int box_rows);
 
+// SMs the contraction's persistent grid leaves free (for communication kernels that run beside it); process-wide
+void gemm_reserve_sms(int n);
+
 // accumulated device time of the contraction kernel (enabled by gemm_timing_enable)
 void gemm_timing_enable(bool on);
 void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *flops_total, double *bytes_total = nullptr);

@@ -1725,10 +1725,13 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
                     world_size, BUCKET_PAD / 4);
     ncclUniqueId u;
     memcpy(&u, id, sizeof(u));
-    // The exchanges run beside the backward pass, whose contractions are persistent kernels sized to every SM: keep the
-    // communication kernels to a few CTAs (TS2_NCCL_MAX_CTAS, default 8; the volume per step is small against NVLink)
+    // The exchanges run beside the backward pass, whose contractions are persistent kernels sized to every SM, and a
+    // communication CTA does not fit beside a contraction CTA (shared memory).  Measured on two B200s (step time against
+    // one GPU's on the same box): a cap of 4 CTAs +5.1 %, 8 +2.8 %, 16 +2.1 %, 32 +0.9 %, NCCL's own choice +1.5 %: short
+    // exchanges on many SMs disturb the contractions less than long ones on few, so the default is no cap
+    // (TS2_NCCL_MAX_CTAS sets one).
     ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
-    int max_ctas = 8;
+    int max_ctas = 0;
     if (const char *e = getenv("TS2_NCCL_MAX_CTAS"))
         max_ctas = atoi(e);
     if (max_ctas > 0) {
@@ -1740,6 +1743,9 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
         m->comm = nullptr;
         return mfail(m, fail(TS2_ERR_COMM, "ncclCommInitRankConfig failed: %s", ncclGetErrorString(r)));
     }
+    // Leaving SMs free for the exchanges instead (TS2_GEMM_RESERVE_SMS, default 0) measured slower: +7 % with 8 SMs.
+    if (const char *e = getenv("TS2_GEMM_RESERVE_SMS"))
+        gemm_reserve_sms(atoi(e));
     std::vector<OptSeg> segs;
     build_segments(m, world_size, rank, &segs, &m->nitems_shard);
     m->nseg_shard = (int)segs.size();
