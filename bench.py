@@ -39,8 +39,6 @@ WORKLOADS = {
 }
 
 
-# average DRAM bytes per contraction launch from one ncu capture of a whole step (see profiles/)
-NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH = {("c3_dense12_d768", "fp8"): 533793211}
 
 
 def make_spec(w, precision):
@@ -145,6 +143,137 @@ def run_cpu_reference(w, steps, warmup):
                        f"{w_name(w)} model, 1 fragment of {n_tok} tokens per step, OpenMP over rows"), n_tok, sec
 
 
+def measure_cublaslt_fp8(seconds=1.5):
+    """Dense e4m3 x e4m3 -> bf16 rate of the vendor library on this GPU (torch._scaled_mm, 8192^3): best of 10 launches
+    (burst) and back to back for `seconds` (sustained, power-capped).  MEASURED_PEAKS.json has no fp8 figure; this one is
+    reported beside the 2 x bf16 working peak, it is not the denominator of roofline.frac."""
+    import torch
+    try:
+        n = 8192
+        a = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device="cuda")
+        f = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(seconds * 1e3 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        return {"burst": flops / best / 1e9, "sustained": flops * reps / e0.elapsed_time(e1) / 1e9, "how": "torch._scaled_mm e4m3 8192^3 -> bf16"}
+    except Exception as e:  # an absent or changed private API must not cost the bench line
+        return {"unavailable": str(e)[:200]}
+
+
+def run_c2_gemm(args):
+    """BASELINE.json configs[1], the backward-GEMM microbench: X int8 [16384 x 4096] with per-row scales ~U(0.01, 0.1),
+    W int8 [4096 x 4096] with per-column scales, dY e4m3 [16384 x 4096] ~ N(0,1); dX = dY . W^T and dW = X^T . dY, fp32
+    accumulate, bf16 output, one GPU.  A mixed fp8 x int8 MMA does not exist, so two variants are timed:
+      fp8 : X and W converted to e4m3, dY e4m3;
+      int8: X and W as they are, dY quantized to int8 (per row for dX, per column for dW).
+    Scales that lie along the contraction (W's column scales for dX, X's row scales for dW) cannot be applied in an
+    epilogue; they are folded into dY when it is (re)quantized, once, outside the timed region; the scales across the
+    output (the int8 row / column scales of dY) are applied in the epilogue.  Every launch is timed with CUDA events on
+    its stream; operands + output of a launch are 208 - 224 MB (> L2).  A few output rows are checked against float64."""
+    import ctypes as C
+    import ml_dtypes
+    from tscale2_b200.device import DeviceBuffer, check, sync
+    lib = capi.load_library()
+    T, n_in, n_out = 16384, 4096, 4096
+    rng = np.random.default_rng(1)
+    Xq = rng.integers(-127, 128, (T, n_in), dtype=np.int8)
+    sx = rng.uniform(0.01, 0.1, T).astype(np.float32)
+    Wq = np.random.default_rng(2).integers(-127, 128, (n_in, n_out), dtype=np.int8)
+    sw = np.random.default_rng(2).uniform(0.01, 0.1, n_out).astype(np.float32)
+    dY = np.random.default_rng(3).standard_normal((T, n_out)).astype(np.float32)
+    e4 = ml_dtypes.float8_e4m3fn
+    dY_e4 = dY.astype(e4)
+    dYf = dY_e4.astype(np.float32)
+    dY_x = dYf * sw[None, :]   # operand of dX: W's column scales folded in
+    dY_w = dYf * sx[:, None]   # operand of dW: X's row scales folded in
+    variants = {}
+    # fp8
+    variants["fp8"] = dict(prec=capi.PREC_FP8, dx_a=dY_x.astype(e4), dx_b=Wq.astype(np.float32).astype(e4), dx_row=None,
+                           dw_a=Xq.astype(np.float32).astype(e4), dw_b=dY_w.astype(e4), dw_col=None)
+    # int8: per-row quantization of dY for dX, per-column for dW
+    r = np.abs(dY_x).max(1) / 127
+    c = np.abs(dY_w).max(0) / 127
+    variants["int8"] = dict(prec=capi.PREC_INT8, dx_a=np.rint(dY_x / r[:, None]).astype(np.int8), dx_b=Wq, dx_row=r.astype(np.float32),
+                            dw_a=Xq, dw_b=np.rint(dY_w / c[None, :]).astype(np.int8), dw_col=c.astype(np.float32))
+    peaks, peak_src = measured_peaks()
+    out = {}
+    sample = np.arange(0, T, T // 8)[:8]
+    for name, v in variants.items():
+        A, B = DeviceBuffer.from_numpy(v["dx_a"]), DeviceBuffer.from_numpy(v["dx_b"])
+        DX = DeviceBuffer(T * n_in * 2)
+        ROW = DeviceBuffer.from_numpy(v["dx_row"]) if v["dx_row"] is not None else None
+        A2, B2 = DeviceBuffer.from_numpy(v["dw_a"]), DeviceBuffer.from_numpy(v["dw_b"])
+        DW = DeviceBuffer(n_in * n_out * 2)
+        COL = DeviceBuffer.from_numpy(v["dw_col"]) if v["dw_col"] is not None else None
+
+        def dx():
+            check(lib.ts2_gemm_tn(0, None, v["prec"], capi.OUT_BF16, T, n_in, n_out, A.ptr, n_out, B.ptr, n_out, DX.ptr, n_in, 1.0,
+                                  ROW.ptr if ROW else None, None))
+
+        def dw():  # dW[in][out] = X^T . dY: the entry point's "dY" operand is X, its "X" operand is dY
+            check(lib.ts2_gemm_dw_scaled(0, None, v["prec"], capi.OUT_BF16, T, n_out, n_in, A2.ptr, B2.ptr, DW.ptr, 1.0, None,
+                                         COL.ptr if COL else None, None, 0))
+        res = {}
+        for op, f in (("dx", dx), ("dw", dw)):
+            for _ in range(max(args.warmup, 3)):
+                f()
+            sync()
+            check(lib.ts2_set_kernel_timing(None, 1))
+            lib.ts2_get_kernel_timing(None, 1, None, None, None)
+            for _ in range(args.steps):
+                f()
+            sync()
+            ms, n, fl = C.c_double(), C.c_int64(), C.c_double()
+            check(lib.ts2_get_kernel_timing(None, 1, C.byref(ms), C.byref(n), C.byref(fl)))
+            check(lib.ts2_set_kernel_timing(None, 0))
+            res[op] = {"ms": ms.value / n.value, "tflops": fl.value / ms.value / 1e9, "launches": n.value}
+        # correctness of what was timed, on a sample of rows, against float64 of the same quantized operands
+        got = DX.download((T, n_in), ml_dtypes.bfloat16).astype(np.float64)[sample]
+        a64 = v["dx_a"].astype(np.float64)[sample] * (v["dx_row"][sample, None] if v["dx_row"] is not None else 1.0)
+        want = a64 @ v["dx_b"].astype(np.float64).T
+        res["dx"]["rel_l2_vs_float64"] = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        got = DW.download((n_in, n_out), ml_dtypes.bfloat16).astype(np.float64)[sample]
+        want = v["dw_a"].astype(np.float64)[:, sample].T @ (v["dw_b"].astype(np.float64) * (v["dw_col"][None, :] if v["dw_col"] is not None else 1.0))
+        res["dw"]["rel_l2_vs_float64"] = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        assert res["dx"]["rel_l2_vs_float64"] < 5e-3 and res["dw"]["rel_l2_vs_float64"] < 5e-3, res  # bf16 output rounding
+        out[name] = res
+    flops = 2.0 * T * n_in * n_out
+    f8 = out["fp8"]
+    both_ms = f8["dx"]["ms"] + f8["dw"]["ms"]
+    achieved = 2 * flops / both_ms / 1e9
+    peak = 2.0 * peaks["bf16_tflops"]
+    vendor = measure_cublaslt_fp8()
+    line = {"metric": "bwd GEMM TFLOP/s (dX + dW)", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": both_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3", "data": "synthetic",
+            "config": {"workload": "c2_gemm", "tokens": T, "in": n_in, "out": n_out, "variant": "fp8 (headline); int8 under variants",
+                       "l2": "operands and output of one launch are 208-224 MB, larger than L2"},
+            "variants": out,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "kernel": "gemm_kernel (tcgen05), isolated launches", "fp8_cublaslt_tflops": vendor,
+                         "peak_source": f"2 x bf16_tflops (burst: isolated launches) of MEASURED_PEAKS.json ({peak_src}); nominal dense fp8 is 4500"},
+            "gpu_launches": int(2 * 2 * args.steps)}
+    print(json.dumps(line))
+
+
 def check_steps(model, n, arm):
     """A step that produced a non-finite loss or gradient did not do the work it is timed for: no number."""
     losses = model.loss_history(min(n, 256))
@@ -169,10 +298,16 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_dense12_d768", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3_dense12_d768", choices=sorted(WORKLOADS) + ["c2_gemm"])
     ap.add_argument("--precision", default="fp8", choices=["fp8", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload == "c2_gemm":
+        if args.impl == "reference" or args.gpus != 1:
+            print(json.dumps({"impl": args.impl, "unavailable": "c2_gemm is a one-GPU kernel microbench of this library"}))
+            return
+        run_c2_gemm(args)
+        return
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -253,6 +388,7 @@ def main():
     # from the engine's loss ring, and the per-layer-boundary flags the norm-backward kernel raises on a NaN / infinity
     check_steps(model, args.steps, "device-timed arm")
     gemm_bytes = model.get_kernel_bytes()
+    gemm_classes = model.get_kernel_timing_by_class()
     gemm_ms, gemm_n, gemm_flops = model.get_kernel_timing(reset=True)
     model.set_kernel_timing(False)
 
@@ -302,17 +438,28 @@ def main():
     else:
         peak = peaks["bf16_tflops_sustained"]
         peak_note = f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src})"
-    # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of the 183 contraction launches of one step
-    # of this workload, averaged (ncu capture summarised in profiles/gemm_dram_traffic_c3_dense12_d768_step.md);
-    # the algorithmic bytes next to it are counted by the library at launch time over the timed region
-    traffic = NCU_GEMM_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.precision))
+    # DRAM traffic per launch is not measured in this run (it needs ncu): null; profiles/ holds small-case captures with
+    # dram__bytes next to the algorithmic bytes.  The algorithmic bytes here are counted by the library at launch time.
+    traffic = None
+    by_class = {}
+    for name, (c_ms, c_n, c_fl) in gemm_classes.items():
+        if c_n:
+            by_class[name] = {"tflops": c_fl / c_ms / 1e9, "ms_per_step": c_ms / args.steps, "launches_per_step": c_n / args.steps}
+    # the target of the north star is stated on the backward contractions of the layers alone (dX + dW, operand format)
+    bw_ms = gemm_classes["dx"][0] + gemm_classes["dw"][0]
+    bw_fl = gemm_classes["dx"][2] + gemm_classes["dw"][2]
+    backward = {"tflops": bw_fl / bw_ms / 1e9, "frac": bw_fl / bw_ms / 1e9 / peak, "ms_per_step": bw_ms / args.steps} if bw_ms > 0 else None
+    vendor_fp8 = measure_cublaslt_fp8() if (args.precision == "fp8" and world == 1) else None
+    if vendor_fp8 and backward and "sustained" in vendor_fp8:
+        backward["frac_of_cublaslt_fp8_sustained"] = backward["tflops"] / vendor_fp8["sustained"]
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": (achieved / peak) if achieved else None, "traffic": traffic,
                 "algorithmic_bytes_per_launch": gemm_bytes / gemm_n if gemm_n else None,
                 "hbm_gbs_algorithmic": gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else None,
                 "hbm_peak_gbs": peaks.get("hbm_gbs"), "kernel": "gemm_kernel (tcgen05)",
                 "launches_per_step": gemm_n / args.steps, "share_of_step": gemm_ms / ms_max, "peak_source": peak_note,
-                "step_flops_per_token": fpt, "step_tflops": value / world * fpt / 1e12}
+                "step_flops_per_token": fpt, "step_tflops": value / world * fpt / 1e12,
+                "by_class": by_class, "backward_gemm": backward, "fp8_cublaslt_tflops": vendor_fp8}
     line = {"metric": "train tokens/s (fwd+bwd)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e4m3" if args.precision == "fp8" else "f16", "data": "synthetic", "config": config,

@@ -255,6 +255,15 @@ int ts2_timer_end(ts2_model *m, float *ms);
  * when profiling is enabled (adds a pair of events per launch) */
 int ts2_set_kernel_timing(ts2_model *m, int enable);
 int ts2_get_kernel_timing(ts2_model *m, int reset, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total);
+/* the same totals for one class of launches (read before a resetting ts2_get_kernel_timing): 0 operator-level calls,
+ * 1 forward contractions of the layers, 2 their dX contractions, 3 their dW contractions, 4 the final layer's three
+ * (logits, dX and dW in fp16).  No reference counterpart (measurement). */
+#define TS2_GEMM_CLASS_OTHER 0
+#define TS2_GEMM_CLASS_FORWARD 1
+#define TS2_GEMM_CLASS_DX 2
+#define TS2_GEMM_CLASS_DW 3
+#define TS2_GEMM_CLASS_FINAL 4
+int ts2_get_kernel_timing_class(ts2_model *m, int cls, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total);
 /* algorithmic bytes (both operands once, output once, residual input once) of the contraction launches timed
  * since the last reset; read it before ts2_get_kernel_timing(reset = 1).  No reference counterpart (measurement). */
 int ts2_get_kernel_bytes(ts2_model *m, double *gemm_bytes_total);
@@ -308,6 +317,12 @@ size_t ts2_gemm_dw_workspace_bytes(int64_t T, int64_t in_dim, int64_t out_dim);
 int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
                 const void *dY, const void *X, void *dW, float alpha, void *workspace, size_t workspace_bytes);
 
+/* ts2_gemm_dw with the per-row / per-column fp32 factors of the epilogue (row_scale[out_dim], col_scale[in_dim], either may
+ * be NULL): the dW side of the reference's scaled stores (TStoreScaled, src/lib/cuda/cuda_matmul.cuh). */
+int ts2_gemm_dw_scaled(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                       const void *dY, const void *X, void *dW, float alpha, const float *row_scale, const float *col_scale,
+                       void *workspace, size_t workspace_bytes);
+
 /* The same contraction as ts2_gemm_dw for callers that must not allocate device memory — a host
  * whose own pools took all of it at start-up, or a loop that cannot afford cudaMalloc's device-wide
  * synchronisation.  (No counterpart in the reference: its kernels get scratch from the trainer's
@@ -342,6 +357,29 @@ int ts2_gemm_tn_grouped(int device, void *stream, int prec, int out_kind, int64_
                         const void *B, void *C, float alpha, int groups, const int32_t *tile_group);
 int ts2_gemm_dw_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t in_dim, int64_t out_dim,
                         const void *dY, const void *X, void *dW, float alpha, int groups, const int32_t *seg_ptr);
+
+/* The bandwidth-bound gradient kernels, one call each (device pointers), exported for operator-level parity tests.
+ *  - ts2_op_tilenorm_backward: g = (add ? g : 0) + NormalizeStateBackward(x, dn * (*dyn_scale or 1)) over 128-wide tiles
+ *    (src/gpt/compute/cpu_util.cpp:102-134; BackpropLayerNormalize, src/gpt/compute/gpu_layer_norm.cuh:89-115), and the
+ *    running maximum of |g| as float bits (absmax_bits, optional; the caller zeroes it);
+ *  - ts2_op_cast_grad: g_fast = g * 2^k in the operand format (e4m3 bytes or fp16), 2^k the largest power of two with
+ *    max|g| * 2^k <= 128 taken from *absmax_bits, *ginv = 2^-k (ScaleGrad / ComputeGradMult,
+ *    src/gpt/compute/gpu_grad_scale.cuh:33-62);
+ *  - ts2_op_ffn_act_backward: wide_gate fp16 [T][2F] = [tile-normalized wide | gate], wscale [T][F/128] the tiles' norm
+ *    factors, drg fp16 [T][F] -> d_wide_gate [T][2F] = [d wide | d gate] in the operand format (BackpropLoLU +
+ *    NormalizeStateBackward of the wide vector, src/gpt/compute/layer_ffn.cu:232-236; BackpropRowTileNormalizeLoLU,
+ *    src/gpt/compute/gpu_lolu.cuh:108-173);
+ *  - ts2_op_att_gate_backward: qkvg fp16 [T][4Q] (gate in columns [3Q, 4Q)), o fp16 [T][Q], drg fp16 [T][Q] ->
+ *    d4[:, 3Q:4Q] = d gate (operand format, row pitch 4Q), dout fp16 [T][Q], dscale[T][Q/128] = sum(dout * o) per head
+ *    (BackpropLoLUdScale, src/gpt/compute/gpu_lolu.cuh:72-106). */
+int ts2_op_tilenorm_backward(int device, void *stream, const float *x, const float *dn, const float *dyn_scale, int T, int D,
+                             float *g, int add, uint32_t *absmax_bits);
+int ts2_op_cast_grad(int device, void *stream, int prec, const float *g, int64_t n, const uint32_t *absmax_bits, void *g_fast,
+                     float *ginv);
+int ts2_op_ffn_act_backward(int device, void *stream, int prec, const void *drg, const void *wide_gate, const float *wscale, int T,
+                            int F, void *d_wide_gate);
+int ts2_op_att_gate_backward(int device, void *stream, int prec, const void *drg, const void *qkvg, const void *o, int T, int Q,
+                             void *d4, void *dout, float *dscale);
 
 /* Expert selection of a mixture-of-experts layer (CpuMoe, src/gpt/compute/layer_moe.cu:287-328;
  * MoeCalcSampleExpertLists, src/gpt/compute/moe_kernels.cu:54-104): the `selected` largest logits per

@@ -119,6 +119,8 @@ def _declare(lib):
         "ts2_set_kernel_timing": (i32, [vp, i32]),
         "ts2_get_kernel_timing": (i32, [vp, i32, P(C.c_double), P(i64), P(C.c_double)]),
         "ts2_get_kernel_bytes": (i32, [vp, P(C.c_double)]),
+        "ts2_get_kernel_timing_class": (i32, [vp, i32, P(C.c_double), P(i64), P(C.c_double)]),
+        "ts2_gemm_dw_scaled": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, vp, vp, C.c_size_t]),
         "ts2_device_count": (i32, []),
         "ts2_selftest_wait_limit": (i32, [i32]),
         "ts2_selftest_wait_limit_noalloc": (i32, [i32]),
@@ -135,6 +137,10 @@ def _declare(lib):
         "ts2_gemm_tn_grouped": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, i32, vp]),
         "ts2_gemm_dw_grouped": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, i32, vp]),
         "ts2_moe_route": (i32, [i32, vp, i32, i32, i32, vp, vp]),
+        "ts2_op_tilenorm_backward": (i32, [i32, vp, vp, vp, vp, i32, i32, vp, i32, vp]),
+        "ts2_op_cast_grad": (i32, [i32, vp, i32, vp, i64, vp, vp, vp]),
+        "ts2_op_ffn_act_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp]),
+        "ts2_op_att_gate_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp, vp, vp]),
         "ts2_attention_forward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp]),
         "ts2_attention_backward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),

@@ -211,6 +211,28 @@ int ts2_gemm_dw(int device, void *stream, int prec, int out_kind, int64_t T, int
     return gemm(a);
 }
 
+int ts2_gemm_dw_scaled(int device, void *stream, int prec, int out_kind, int64_t T, int64_t in_dim, int64_t out_dim,
+                       const void *dY, const void *X, void *dW, float alpha, const float *row_scale, const float *col_scale,
+                       void *workspace, size_t workspace_bytes)
+{
+    GemmArgs a;
+    a.device = device;
+    a.stream = (cudaStream_t)stream;
+    a.kind = kind_of(prec);
+    if (a.kind < 0)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_gemm_dw_scaled: unknown precision %d", prec);
+    a.mn_major = true;
+    a.M = out_dim, a.N = in_dim, a.K = T;
+    a.A = dY, a.lda = out_dim, a.B = X, a.ldb = in_dim, a.C = dW, a.ldc = in_dim;
+    a.epi.alpha = alpha;
+    a.epi.row_scale = row_scale;
+    a.epi.col_scale = col_scale;
+    a.epi.out_kind = out_kind;
+    a.workspace = workspace;
+    a.workspace_bytes = workspace_bytes;
+    return gemm(a);
+}
+
 // grouped contractions of the mixture-of-experts layers (device pointers; tables on the device)
 int ts2_gemm_tn_grouped(int device, void *stream, int prec, int out_kind, int64_t rows, int64_t N, int64_t K, const void *A,
                         const void *B, void *C, float alpha, int groups, const int32_t *tile_group)
@@ -276,6 +298,55 @@ int ts2_moe_route(int device, const float *logits, int T, int expert_count, int 
     cudaFree(dw);
     cudaFree(di);
     return rc;
+}
+
+// ---- the bandwidth-bound gradient kernels, one call each (device pointers) ----------------------------------------
+static Ctx op_ctx(int device, void *stream, int prec)
+{
+    Ctx c;
+    c.device = device;
+    c.stream = (cudaStream_t)stream;
+    c.ft = prec == TS2_PREC_FP8 ? 0 : 1;
+    c.s_act = c.ft == 0 ? 16.f : 1.f;
+    return c;
+}
+
+int ts2_op_tilenorm_backward(int device, void *stream, const float *x, const float *dn, const float *dyn_scale, int T, int D,
+                             float *g, int add, uint32_t *absmax_bits)
+{
+    if (!x || !dn || !g || T <= 0 || D <= 0 || D % 128)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_tilenorm_backward: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    return tilenorm_backward(op_ctx(device, stream, TS2_PREC_F16), x, dn, dyn_scale, 1.f, T, D, g, add != 0, absmax_bits);
+}
+
+int ts2_op_cast_grad(int device, void *stream, int prec, const float *g, int64_t n, const uint32_t *absmax_bits, void *g_fast,
+                     float *ginv)
+{
+    if (!g || !absmax_bits || !g_fast || !ginv || n <= 0 || n % 4 || (prec != TS2_PREC_FP8 && prec != TS2_PREC_F16))
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_cast_grad: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    return cast_grad(op_ctx(device, stream, prec), g, (size_t)n, absmax_bits, g_fast, ginv, 1.f, nullptr, nullptr);
+}
+
+int ts2_op_ffn_act_backward(int device, void *stream, int prec, const void *drg, const void *wide_gate, const float *wscale, int T,
+                            int F, void *d_wide_gate)
+{
+    if (!drg || !wide_gate || !wscale || !d_wide_gate || T <= 0 || F <= 0 || F % 128 || (prec != TS2_PREC_FP8 && prec != TS2_PREC_F16))
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_ffn_act_backward: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    return ffn_act_backward(op_ctx(device, stream, prec), (const __half *)drg, (const __half *)wide_gate, (const __half *)wide_gate,
+                            2 * F, wscale, T, F, d_wide_gate);
+}
+
+int ts2_op_att_gate_backward(int device, void *stream, int prec, const void *drg, const void *qkvg, const void *o, int T, int Q,
+                             void *d4, void *dout, float *dscale)
+{
+    if (!drg || !qkvg || !o || !d4 || !dout || !dscale || T <= 0 || Q <= 0 || Q % 128 || (prec != TS2_PREC_FP8 && prec != TS2_PREC_F16))
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_att_gate_backward: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    return att_gate_backward(op_ctx(device, stream, prec), (const __half *)drg, (const __half *)qkvg, (const __half *)o, T, Q, d4,
+                             (__half *)dout, dscale);
 }
 
 // attention core on device arrays; span_start / span_finish are host arrays of T ints

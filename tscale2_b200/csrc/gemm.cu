@@ -929,7 +929,10 @@ static bool g_time_on = false;
 struct TimedLaunch {
     cudaEvent_t a, b;
     double flops, bytes;
+    int tag;
 };
+static double g_tag_ms[GEMM_TAGS] = {}, g_tag_flops[GEMM_TAGS] = {};
+static long long g_tag_launches[GEMM_TAGS] = {};
 static std::vector<TimedLaunch> g_timed;
 static std::vector<cudaEvent_t> g_event_pool;
 static double g_ms_total = 0, g_flops_total = 0, g_bytes_total = 0;
@@ -951,6 +954,10 @@ static void timing_collect_locked()
                 g_flops_total += t.flops;
                 g_bytes_total += t.bytes;
                 ++g_timed_launches;
+                const int tag = t.tag >= 0 && t.tag < GEMM_TAGS ? t.tag : 0;
+                g_tag_ms[tag] += ms;
+                g_tag_flops[tag] += t.flops;
+                ++g_tag_launches[tag];
             }
         }
         g_event_pool.push_back(t.a);
@@ -974,7 +981,24 @@ void gemm_timing_get(bool reset, double *ms_total, long long *launches, double *
     if (reset) {
         g_ms_total = g_flops_total = g_bytes_total = 0;
         g_timed_launches = 0;
+        for (int i = 0; i < GEMM_TAGS; ++i) {
+            g_tag_ms[i] = g_tag_flops[i] = 0;
+            g_tag_launches[i] = 0;
+        }
     }
+}
+
+void gemm_timing_get_tag(int tag, double *ms_total, long long *launches, double *flops_total)
+{
+    std::lock_guard<std::mutex> lk(g_time_mu);
+    timing_collect_locked();
+    const int t = tag >= 0 && tag < GEMM_TAGS ? tag : 0;
+    if (ms_total)
+        *ms_total = g_tag_ms[t];
+    if (launches)
+        *launches = g_tag_launches[t];
+    if (flops_total)
+        *flops_total = g_tag_flops[t];
 }
 
 static cudaEvent_t pooled_event()
@@ -1164,7 +1188,7 @@ int gemm(const GemmArgs &a)
         // algorithmic bytes: both operands once, the output once, the residual input of the accumulate form once
         const double mn = (double)a.M * (double)a.N;
         const double bytes = ((double)a.M + (double)a.N) * (double)a.K * es + mn * out_es + (a.epi.out_kind == TS2_OUT_F32_ADD ? mn * 4 : 0);
-        g_timed.push_back({ea, eb, 2.0 * mn * (double)a.K, bytes});
+        g_timed.push_back({ea, eb, 2.0 * mn * (double)a.K, bytes, a.tag});
     }
     return rc;
 }

@@ -52,6 +52,7 @@ struct GemmArgs {
     int group_rows_b = 0;
     const int *group_kptr = nullptr; // device, groups + 1 row offsets (multiples of 128)
     int64_t c_group_stride = 0;      // elements of C between groups (mode 2)
+    int tag = 0;               // class of the launch for the timing statistics (GEMM_TAG_*)
     void *workspace = nullptr; // split-K partial tiles (fp32); needed when gemm_splits() > 1
     size_t workspace_bytes = 0;
 };
@@ -67,6 +68,11 @@ int make_tensor_map(::CUtensorMap_st *tm, const void *base, int es, int64_t inne
 
 // SMs the contraction's persistent grid leaves free (for communication kernels that run beside it); process-wide
 void gemm_reserve_sms(int n);
+
+// classes of launches the timing statistics keep apart: other (operator-level calls), forward, dX and dW of the layers
+// in the engine's operand format, and the final layer's three contractions (logits in the operand format, dX and dW fp16)
+enum { GEMM_TAG_OTHER = 0, GEMM_TAG_FWD = 1, GEMM_TAG_DX = 2, GEMM_TAG_DW = 3, GEMM_TAG_FINAL = 4, GEMM_TAGS = 5 };
+void gemm_timing_get_tag(int tag, double *ms_total, long long *launches, double *flops_total);
 
 // accumulated device time of the contraction kernel (enabled by gemm_timing_enable)
 void gemm_timing_enable(bool on);

@@ -152,6 +152,7 @@ struct ts2_model {
     size_t pinned_bytes = 0;
     bool grads_dirty = false; // the flat gradient holds an accumulated, not yet applied gradient
     bool reduce_in_backward = false; // this backward pass is followed by apply(): all-reduce every layer's gradient as soon as it is complete
+    int gemm_tag = 0; // class of the contractions being queued (timing statistics)
     bool debug_taps = false;
     float *grad_taps = nullptr;
     // step health: health[b] = number of the first step whose state gradient at layer boundary b held a NaN or an
@@ -232,6 +233,7 @@ int gemm_tn(ts2_model *m, int kind, int64_t M, int64_t N, int64_t K, const void 
     a.M = M, a.N = N, a.K = K;
     a.A = A, a.lda = lda, a.B = B, a.ldb = ldb, a.C = C, a.ldc = ldc;
     a.epi = epi;
+    a.tag = m->gemm_tag;
     a.workspace = m->workspace;
     a.workspace_bytes = m->workspace_bytes;
     return gemm(a);
@@ -249,6 +251,7 @@ int gemm_dw(ts2_model *m, int kind, int64_t Mo, int64_t Ni, int64_t T, const voi
     a.M = Mo, a.N = Ni, a.K = T;
     a.A = dY, a.lda = ldy, a.B = X, a.ldb = ldx, a.C = dW, a.ldc = Ni;
     a.epi = epi;
+    a.tag = m->gemm_tag == GEMM_TAG_FINAL ? GEMM_TAG_FINAL : GEMM_TAG_DW;
     a.workspace = m->workspace;
     a.workspace_bytes = m->workspace_bytes;
     return gemm(a);
@@ -266,6 +269,7 @@ int gemm_rows_grouped(ts2_model *m, const Layer &ly, int64_t rows, int64_t N, in
     a.M = rows, a.N = N, a.K = K;
     a.A = A, a.lda = lda, a.B = B, a.ldb = ldb, a.C = C, a.ldc = ldc;
     a.epi = epi;
+    a.tag = m->gemm_tag;
     a.group_mode = 1;
     a.groups = m->E;
     a.tile_group = ly.tile_group;
@@ -285,6 +289,7 @@ int gemm_k_grouped(ts2_model *m, const Layer &ly, int64_t Mo, int64_t Ni, int64_
     a.M = Mo, a.N = Ni, a.K = rows;
     a.A = dY, a.lda = ldy, a.B = X, a.ldb = ldx, a.C = dW, a.ldc = Ni;
     a.epi = epi;
+    a.tag = GEMM_TAG_DW;
     a.group_mode = 2;
     a.groups = m->E;
     a.group_kptr = ly.seg_ptr;
@@ -781,6 +786,7 @@ int forward(ts2_model *m)
     const int T = m->batch.node_count, D = m->D, H = m->H;
     const BatchDev &b = m->batch;
     const size_t fsz = fast_size(m);
+    m->gemm_tag = GEMM_TAG_FWD;
     M_TRY(embed_forward(c, m->embed16, m->mats[0].sko, b.label_arr, b.label_ptr, T, D, m->states[0]));
     TRACE("state", 0, m->states[0], (size_t)T * D * 4, TR_F32);
     for (int l = 0; l < m->L; ++l) {
@@ -869,6 +875,7 @@ int final_layer(ts2_model *m, bool backward)
     const float gscale = 1024.f;                           // keeps p ~ 1/V inside the fp16 normal range
     const float gs = (1.f / LOG2F) * LOG2F;                // CalcFinalLayerMult() * LOG2, cpu_transformer.cpp:159
     const bool tune_final = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_FINAL_LAYER);
+    m->gemm_tag = GEMM_TAG_FINAL;
     TS2_CUDA(cudaMemsetAsync(m->logp, 0, 4, m->stream));
     for (int r0 = 0; r0 < T; r0 += m->chunk) {
         const int rows = std::min(m->chunk, T - r0);
@@ -935,6 +942,7 @@ int backward(ts2_model *m)
     const bool tune_layers = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_LAYERS);
     TS2_CUDA(cudaMemsetAsync(m->absmax, 0, (L + 2) * 4, m->stream));
     M_TRY(final_layer(m, true));
+    m->gemm_tag = GEMM_TAG_DX;
     M_TRY(reduce_matrices(m, 1, 2));
     M_TRY(tilenorm_backward(c, m->states[L], m->dn, nullptr, 1.f, T, D, m->g, false, m->absmax + L, m->health + L, m->step_no));
     TRACE("g", L, m->g, (size_t)T * D * 4, TR_F32);
@@ -1799,6 +1807,17 @@ int ts2_set_kernel_timing(ts2_model *, int enable)
 int ts2_get_kernel_bytes(ts2_model *, double *gemm_bytes_total)
 {
     gemm_timing_get(false, nullptr, nullptr, nullptr, gemm_bytes_total);
+    return TS2_OK;
+}
+
+int ts2_get_kernel_timing_class(ts2_model *, int cls, double *gemm_ms_total, int64_t *gemm_launches, double *gemm_flops_total)
+{
+    if (cls < 0 || cls >= GEMM_TAGS)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_get_kernel_timing_class: class %d outside [0, %d)", cls, (int)GEMM_TAGS);
+    long long n = 0;
+    gemm_timing_get_tag(cls, gemm_ms_total, &n, gemm_flops_total);
+    if (gemm_launches)
+        *gemm_launches = n;
     return TS2_OK;
 }
 

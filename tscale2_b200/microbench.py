@@ -5,6 +5,7 @@ shapes of BASELINE config 2 (backward GEMM microbench) or any other shape, and t
     python -m tscale2_b200.microbench --op dw --prec int8 --M 4096 --N 4096 --K 16384   # dW[M][N], K tokens
     python -m tscale2_b200.microbench --op config2
     python -m tscale2_b200.microbench --op att --T 16384 --heads 12 --variant 3      # attention forward + backward
+    python -m tscale2_b200.microbench --op step --blocks 1 --T 65536 --iters 2       # training steps of a short model
 
 Times with CUDA events around each launch on the launching stream (ts2_set_kernel_timing); operands are
 random bytes of the operand format (no NaN codes), larger than L2 for the config-2 shapes.  One JSON line
@@ -98,9 +99,31 @@ def time_attention(lib, T, heads, variant, iters, warmup=2, doc=1024):
     return out
 
 
+def time_steps(blocks, T, seq, iters, prec_name, dim=768, heads=12, ffn_tiles=24, vocab=50304):
+    """Applied training steps of a model with the headline benchmark's layer shapes but only `blocks` blocks: every
+    kernel of the step runs at full width on a few GB of device memory, which is what a profiler capture wants."""
+    from . import host
+    from .model import Model
+    spec = host.ModelSpec(dim=dim, head_count=heads, ffn_tiles=ffn_tiles, vocab=vocab, attention_widths=[seq],
+                          precision=PREC[prec_name][0]).add_blocks(blocks)
+    model = Model(spec, host.init_weights(spec, 1000), T)
+    model.set_batch(host.synthetic_batch(spec, T // seq, seq, 1000))
+    step = host.training_step(rate=0.01, iteration=10)
+    model.backprop(step, apply=True)
+    model.wait()
+    model.timer_begin()
+    for _ in range(iters):
+        model.backprop(step, apply=True)
+    ms = model.timer_end()
+    return {"op": "step", "blocks": blocks, "T": T, "seq": seq, "prec": prec_name, "ms_per_step": ms / iters,
+            "loss": model.avg_train_err(), "launches": model.launch_count()}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="config2", choices=["dx", "tn", "dw", "config2", "att"])
+    ap.add_argument("--op", default="config2", choices=["dx", "tn", "dw", "config2", "att", "step"])
+    ap.add_argument("--blocks", type=int, default=1)
+    ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--T", type=int, default=16384)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--variant", type=int, default=3, choices=[0, 1, 2, 3])
@@ -112,7 +135,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     lib = capi.load_library()
-    if args.op == "att":
+    if args.op == "step":
+        print(json.dumps(time_steps(args.blocks, args.T, args.seq, args.iters, args.prec if args.prec != "int8" else "fp8")))
+    elif args.op == "att":
         print(json.dumps(time_attention(lib, args.T, args.heads, args.variant, args.iters, args.warmup)))
     elif args.op == "config2":
         # BASELINE config 2: T = 16384 tokens, 4096 x 4096 weights: dX = dY.W^T (M=T, N=in, K=out), dW = X^T.dY (K = T)

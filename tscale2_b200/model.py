@@ -175,6 +175,16 @@ class Model:
         self._check(self.lib.ts2_get_kernel_timing(self.h, int(reset), C.byref(ms), C.byref(n), C.byref(fl)))
         return ms.value, n.value, fl.value
 
+    def get_kernel_timing_by_class(self):
+        """{class: (ms, launches, flops)} of the contraction launches timed since the last reset (read before a
+        resetting get_kernel_timing): forward, dx, dw of the layers, the final layer's three, other."""
+        out = {}
+        for cls, name in enumerate(("other", "forward", "dx", "dw", "final")):
+            ms, n, fl = C.c_double(), C.c_int64(), C.c_double()
+            self._check(self.lib.ts2_get_kernel_timing_class(self.h, cls, C.byref(ms), C.byref(n), C.byref(fl)))
+            out[name] = (ms.value, n.value, fl.value)
+        return out
+
     def get_kernel_bytes(self):
         """Algorithmic bytes of the contraction launches timed since the last reset (read before a resetting
         get_kernel_timing)."""
