@@ -215,7 +215,8 @@ def run_c2_gemm(args):
                             dw_a=Xq, dw_b=np.rint(dY_w / c[None, :]).astype(np.int8), dw_col=c.astype(np.float32))
     peaks, peak_src = measured_peaks()
     out = {}
-    sample = np.arange(0, T, T // 8)[:8]
+    sample = np.arange(0, T, T // 8)[:8]          # rows of dX checked against float64
+    sample_w = np.arange(0, n_in, n_in // 8)[:8]  # rows of dW
     for name, v in variants.items():
         A, B = DeviceBuffer.from_numpy(v["dx_a"]), DeviceBuffer.from_numpy(v["dx_b"])
         DX = DeviceBuffer(T * n_in * 2)
@@ -250,8 +251,8 @@ def run_c2_gemm(args):
         a64 = v["dx_a"].astype(np.float64)[sample] * (v["dx_row"][sample, None] if v["dx_row"] is not None else 1.0)
         want = a64 @ v["dx_b"].astype(np.float64).T
         res["dx"]["rel_l2_vs_float64"] = float(np.linalg.norm(got - want) / np.linalg.norm(want))
-        got = DW.download((n_in, n_out), ml_dtypes.bfloat16).astype(np.float64)[sample]
-        want = v["dw_a"].astype(np.float64)[:, sample].T @ (v["dw_b"].astype(np.float64) * (v["dw_col"][None, :] if v["dw_col"] is not None else 1.0))
+        got = DW.download((n_in, n_out), ml_dtypes.bfloat16).astype(np.float64)[sample_w]
+        want = v["dw_a"].astype(np.float64)[:, sample_w].T @ (v["dw_b"].astype(np.float64) * (v["dw_col"][None, :] if v["dw_col"] is not None else 1.0))
         res["dw"]["rel_l2_vs_float64"] = float(np.linalg.norm(got - want) / np.linalg.norm(want))
         assert res["dx"]["rel_l2_vs_float64"] < 5e-3 and res["dw"]["rel_l2_vs_float64"] < 5e-3, res  # bf16 output rounding
         out[name] = res
@@ -299,7 +300,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3_dense12_d768", choices=sorted(WORKLOADS) + ["c2_gemm"])
-    ap.add_argument("--precision", default="fp8", choices=["fp8", "f16"])
+    ap.add_argument("--precision", default="fp8", choices=["fp8", "f16", "int8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload == "c2_gemm":
@@ -346,7 +347,7 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    precision = capi.PREC_FP8 if args.precision == "fp8" else capi.PREC_F16
+    precision = {"fp8": capi.PREC_FP8, "f16": capi.PREC_F16, "int8": capi.PREC_INT8}[args.precision]
     spec = make_spec(w, precision)
     # same weights on every rank; router weights N(0, 1) for the mixture-of-experts workload (BASELINE.json configs[3])
     mats = host.init_weights(spec, 1000, select_std=1.0 if "experts" in w else None)
@@ -432,9 +433,9 @@ def main():
     fpt, bwd_fpt = flops_per_token(w)
     # dominant kernel: the tcgen05 contraction (all forward, dX and dW launches of the step)
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
-    if args.precision == "fp8":
+    if args.precision in ("fp8", "int8"):
         peak = 2.0 * peaks["bf16_tflops_sustained"]
-        peak_note = f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src}); no fp8 peak is measured there"
+        peak_note = f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src}); no fp8 / int8 peak is measured there"
     else:
         peak = peaks["bf16_tflops_sustained"]
         peak_note = f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src})"
@@ -462,7 +463,7 @@ def main():
                 "by_class": by_class, "backward_gemm": backward, "fp8_cublaslt_tflops": vendor_fp8}
     line = {"metric": "train tokens/s (fwd+bwd)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "e4m3" if args.precision == "fp8" else "f16", "data": "synthetic", "config": config,
+            "vs_baseline": None, "dtype": {"fp8": "e4m3", "f16": "f16", "int8": "int8 (dW contractions fp16)"}[args.precision], "data": "synthetic", "config": config,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_max / args.steps, "last_loss": loss,

@@ -59,7 +59,8 @@ extern "C" {
  * in src/gpt/compute/cfg_precision.h:18-46 */
 #define TS2_PREC_FP8 0  /* e4m3 operands, fp32 accumulate (reference "fp8 matmul" block) */
 #define TS2_PREC_F16 1  /* fp16 operands, fp32 accumulate (reference "fp16 matmul" block) */
-#define TS2_PREC_INT8 2 /* int8 operands, int32 accumulate (op-level GEMM only) */
+#define TS2_PREC_INT8 2 /* int8 operands, int32 accumulate (reference "int8 matmul" block, its default); the engine
+                         * runs forward and dX contractions in int8 with per-row gradient scales, dW in fp16 */
 
 /* ts2_backprop add_to_model; EAddToModel, src/gpt/matrix/base_host.h:20-23 */
 #define TS2_GRADIENT_ACCUMULATE 0
@@ -92,7 +93,7 @@ typedef struct ts2_model_descr {
     int32_t layer_count;
     const ts2_layer_params *layers;
     uint64_t flags;
-    int32_t precision; /* TS2_PREC_FP8 or TS2_PREC_F16 */
+    int32_t precision; /* TS2_PREC_FP8, TS2_PREC_F16 or TS2_PREC_INT8 (dense layers only) */
     int32_t reserved;
 } ts2_model_descr;
 
@@ -380,6 +381,13 @@ int ts2_op_ffn_act_backward(int device, void *stream, int prec, const void *drg,
                             int F, void *d_wide_gate);
 int ts2_op_att_gate_backward(int device, void *stream, int prec, const void *drg, const void *qkvg, const void *o, int T, int Q,
                              void *d4, void *dout, float *dscale);
+/* Row quantization of the int8 pipeline's gradient operands (NormalizeVecsRowMaxKernel with TCudaRngLCG,
+ * src/gpt/compute/row_scale.cuh:12-43, src/lib/cuda/cuda_util.cuh:538-559): x fp32 [T][D] on the device, D a multiple
+ * of 128; row_scale[t] = max|x[t]| / 127; q[t][d] = the int8 nearest (ties to even, saturating) to
+ * x[t][d] / row_scale[t] + u - 0.5, u in [0, 1) drawn for row t by lane h = d mod 32 as its (d / 32 + 1)-th number from
+ * state = bits(x[t][h]) * 0x398bf183 + bits(x[t][0]) * 0x1affc3df + t * 0x9023a049, state = state * 0x448e3079 +
+ * 0xc484ef10, u = state * 2^-32.  Bit-exact with that definition. */
+int ts2_op_rowquant_i8(int device, void *stream, const float *x, int T, int D, int8_t *q, float *row_scale);
 
 /* Expert selection of a mixture-of-experts layer (CpuMoe, src/gpt/compute/layer_moe.cu:287-328;
  * MoeCalcSampleExpertLists, src/gpt/compute/moe_kernels.cu:54-104): the `selected` largest logits per

@@ -74,9 +74,10 @@ class Oracle:
     # -- whole step -------------------------------------------------------------------------
     def backprop(self, spec: host.ModelSpec, mats, batch: host.Batch, weight_quant, bias=None,
                  want_states=False, engine_rounding=False):
-        """engine_rounding: also round the contractions' activation / gradient operands to e4m3 where the B200
-        engine's fp8 pipeline does (ts2o_set_activation_quant), instead of keeping them fp32."""
-        self.lib.ts2o_set_activation_quant(1 if engine_rounding else 0)
+        """engine_rounding: also round the contractions' activation / gradient operands where the B200 engine's fp8
+        pipeline (e4m3) or, with int8 weights, its int8 pipeline does (ts2o_set_activation_quant), instead of keeping
+        them fp32."""
+        self.lib.ts2o_set_activation_quant((2 if weight_quant == QUANT_I8 else 1) if engine_rounding else 0)
         try:
             return self._backprop(spec, mats, batch, weight_quant, bias, want_states)
         finally:
@@ -88,6 +89,15 @@ class Oracle:
         self.lib.ts2o_round_e4m3.argtypes = [_fp, C.c_int64, _fp]
         self.lib.ts2o_round_e4m3(_f(x), x.size, _f(out))
         return out
+
+    def rowquant_i8(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        T, D = x.shape
+        q = np.zeros((T, D), np.int8)
+        scale = np.zeros(T, np.float32)
+        self.lib.ts2o_rowquant_i8.argtypes = [_fp, C.c_int, C.c_int, C.c_void_p, _fp]
+        self.lib.ts2o_rowquant_i8(_f(x), T, D, q.ctypes.data_as(C.c_void_p), _f(scale))
+        return q, scale
 
     def _backprop(self, spec, mats, batch, weight_quant, bias, want_states):
         descr, keep = spec.to_c()

@@ -207,13 +207,43 @@ float RoundE4M3(float x)
     return copysignf(nearbyintf(a / q) * q, x); // default rounding mode: to nearest, ties to even
 }
 
-void QuantizeInPlace(Mat *m, float scale)
+// mode 1: e4m3 at `scale`; mode 2 (the engine's int8 pipeline): int8, nearest even, saturating, at `scale_i8`
+void QuantizeInPlace(Mat *m, float scale, float scale_i8 = 0)
 {
     if (!g_actQuant)
         return;
+    if (g_actQuant == 2) {
+        if (scale_i8 == 0)
+            return;
+        for (float &v : m->v)
+            v = (float)FloatToI8(v * scale_i8) / scale_i8;
+        return;
+    }
     const float inv = 1.f / scale;
     for (float &v : m->v)
         v = RoundE4M3(v * scale) * inv;
+}
+
+// mode 2: the gradient operand of a dX contraction, quantized per token row to int8 with scale max|row| / 127.  A row
+// may consist of several blocks, each in its own units (factor[i]): the maximum is taken over the scaled row.  Nearest
+// rounding here; the engine rounds stochastically (same variance class, different draws).
+void RowQuantI8Joint(const std::vector<Mat *> &parts, const std::vector<float> &factor)
+{
+    const int T = parts[0]->rows;
+    for (int t = 0; t < T; ++t) {
+        float mx = 0;
+        for (size_t i = 0; i < parts.size(); ++i)
+            for (int x = 0; x < parts[i]->cols; ++x)
+                mx = fmaxf(mx, fabsf(parts[i]->row(t)[x] * factor[i]));
+        if (mx == 0)
+            continue;
+        const float scale = mx / 127;
+        for (size_t i = 0; i < parts.size(); ++i)
+            for (int x = 0; x < parts[i]->cols; ++x) {
+                float &v = parts[i]->row(t)[x];
+                v = (float)FloatToI8(v * factor[i] / scale) * scale / factor[i];
+            }
+    }
 }
 
 // the engine's grad_mult: largest power of two that keeps max |g| * mult <= 128
@@ -230,7 +260,8 @@ float GradMult(const Mat &g)
     return exp2f(e);
 }
 
-const float kActScale = 16.f;
+const float kActScale = 16.f;    // e4m3 pipeline
+const float kActScaleI8 = 24.f;  // int8 pipeline (STATE_VEC_SCALE = 1 / 24, cfg_precision.h:72)
 
 // ---------------------------------------------------------------------------
 // model
@@ -254,12 +285,14 @@ void StoreDelta(Matrix &m, const Mat &delta)
         memcpy(m.gradOut, delta.v.data(), sizeof(float) * delta.v.size());
 }
 
-void MatmulBackprop(Matrix &m, bool noScale, const Mat &src, const Mat &dstGrad, bool update, Mat *srcGrad)
+// dstGradDelta: the gradient the weight-gradient product reads, where it differs from the one the dX product reads
+// (int8 pipeline: dX from the row-quantized gradient, dW from the unquantized one)
+void MatmulBackprop(Matrix &m, bool noScale, const Mat &src, const Mat &dstGrad, bool update, Mat *srcGrad, const Mat *dstGradDelta = nullptr)
 {
     prim::MulBackwardWithAccum(srcGrad, noScale ? m.dataNoScale : m.data, dstGrad);
     if (update) {
         Mat delta;
-        prim::SumRankOne(src, &delta, dstGrad);
+        prim::SumRankOne(src, &delta, dstGradDelta ? *dstGradDelta : dstGrad);
         StoreDelta(m, delta);
     }
 }
@@ -277,12 +310,12 @@ struct Dims {
 void FfnRecompute(const Dims &d, Matrix *mm, const Mat &prevState, Mat &normState, Mat &wide, Mat &wideNorm, Mat &gate, Mat &rg)
 {
     normState = prim::NormalizeState(prevState, d.dim / kStateNormTile);
-    QuantizeInPlace(&normState, kActScale);
+    QuantizeInPlace(&normState, kActScale, kActScaleI8);
     wide = prim::MulForward(normState, mm[0].data);
     wideNorm = prim::NormalizeState(wide, d.ffnDim / 128);
     gate = prim::MulForward(normState, mm[1].dataNoScale);
     prim::LoLU(gate, wideNorm, &rg);
-    QuantizeInPlace(&rg, kActScale);
+    QuantizeInPlace(&rg, kActScale, kActScaleI8);
 }
 
 void FfnForward(const Dims &d, Matrix *mm, const Mat &prevState, Mat *state)
@@ -303,19 +336,24 @@ void FfnBackward(const Dims &d, Matrix *mm, bool update, const Mat &prevState, M
     Mat gFast = *grad;
     const float gradMult = g_actQuant ? GradMult(*grad) : 1.f;
     QuantizeInPlace(&gFast, gradMult);
-    MatmulBackprop(mm[2], false, rg, gFast, update, &drg);
+    if (g_actQuant == 2)
+        RowQuantI8Joint({&gFast}, {1.f});
+    MatmulBackprop(mm[2], false, rg, gFast, update, &drg, g_actQuant == 2 ? grad : nullptr);
     Mat dgate, dwide;
     prim::BackpropLoLU(gate, wideNorm, drg, &dgate, &dwide);
     prim::NormalizeStateBackward(wide, d.ffnDim / 128, dwide, &dwide);
+    Mat dwideFull = dwide, dgateFull = dgate;
     {
         // engine units: true gradient = stored value * fscale, fscale = sqrt(dim / ffnDim) * sko_contract / gradMult;
         // the expansion is used scale-free there (a normalisation follows it), so its gradient carries its matrix scale
         const float fscale = sqrtf((float)d.dim / (float)d.ffnDim) * mm[2].sko / gradMult;
         QuantizeInPlace(&dwide, mm[0].sko / fscale);
         QuantizeInPlace(&dgate, 1.f / fscale);
+        if (g_actQuant == 2)
+            RowQuantI8Joint({&dwide, &dgate}, {mm[0].sko / fscale, 1.f / fscale});
     }
-    MatmulBackprop(mm[0], false, normState, dwide, update, &dNormState);
-    MatmulBackprop(mm[1], true, normState, dgate, update, &dNormState);
+    MatmulBackprop(mm[0], false, normState, dwide, update, &dNormState, g_actQuant == 2 ? &dwideFull : nullptr);
+    MatmulBackprop(mm[1], true, normState, dgate, update, &dNormState, g_actQuant == 2 ? &dgateFull : nullptr);
     Mat dState;
     prim::NormalizeStateBackward(prevState, d.dim / kStateNormTile, dNormState, &dState);
     AddInto(grad, dState);
@@ -330,7 +368,7 @@ struct AttFwd {
 void AttRecompute(const Dims &d, Matrix *mm, const Common &c, float slope, int attType, const Mat &prevState, AttFwd &f)
 {
     f.normState = prim::NormalizeState(prevState, d.dim / kStateNormTile);
-    QuantizeInPlace(&f.normState, kActScale);
+    QuantizeInPlace(&f.normState, kActScale, kActScaleI8);
     f.comp.Init(d.headCount, d.qDim, d.ttDim, slope);
     f.qSrc = prim::MulForward(f.normState, mm[0].data);
     f.kSrc = prim::MulForward(f.normState, mm[1].data);
@@ -343,7 +381,7 @@ void AttRecompute(const Dims &d, Matrix *mm, const Common &c, float slope, int a
     prim::ApplyRope(c.rope, 1, &f.k);
     f.comp.ComputeValLookup(f.q, f.k, f.v, c.att[attType], &f.valLookup);
     prim::LoLU(f.gate, f.valLookup, &f.rg);
-    QuantizeInPlace(&f.rg, kActScale);
+    QuantizeInPlace(&f.rg, kActScale, kActScaleI8);
 }
 
 void AttForward(const Dims &d, Matrix *mm, const Common &c, float slope, int attType, const Mat &prevState, Mat *state)
@@ -363,7 +401,9 @@ void AttBackward(const Dims &d, Matrix *mm, bool update, const Common &c, float 
     Mat gFast = *grad;
     const float gradMult = g_actQuant ? GradMult(*grad) : 1.f;
     QuantizeInPlace(&gFast, gradMult);
-    MatmulBackprop(mm[4], false, f.rg, gFast, update, &drg);
+    if (g_actQuant == 2)
+        RowQuantI8Joint({&gFast}, {1.f});
+    MatmulBackprop(mm[4], false, f.rg, gFast, update, &drg, g_actQuant == 2 ? grad : nullptr);
     Mat dgate, dValLookup;
     prim::BackpropLoLU(f.gate, f.valLookup, drg, &dgate, &dValLookup);
     Mat dScale;
@@ -384,10 +424,16 @@ void AttBackward(const Dims &d, Matrix *mm, bool update, const Common &c, float 
         QuantizeInPlace(&dV, mm[2].sko / fscale);
         QuantizeInPlace(&dgate, 1.f / fscale);
     }
-    MatmulBackprop(mm[0], false, f.normState, dQ, update, &dNormState);
-    MatmulBackprop(mm[1], false, f.normState, dK, update, &dNormState);
-    MatmulBackprop(mm[2], false, f.normState, dV, update, &dNormState);
-    MatmulBackprop(mm[3], true, f.normState, dgate, update, &dNormState);
+    Mat dQFull = dQ, dKFull = dK, dVFull = dV, dgateFull = dgate;
+    if (g_actQuant == 2) {
+        const float fscale = sqrtf((float)d.dim / (float)(d.ttDim * d.headCount)) * mm[4].sko / gradMult;
+        RowQuantI8Joint({&dQ, &dK, &dV, &dgate}, {mm[0].sko / fscale, mm[1].sko / fscale, mm[2].sko / fscale, 1.f / fscale});
+    }
+    const bool sep = g_actQuant == 2;
+    MatmulBackprop(mm[0], false, f.normState, dQ, update, &dNormState, sep ? &dQFull : nullptr);
+    MatmulBackprop(mm[1], false, f.normState, dK, update, &dNormState, sep ? &dKFull : nullptr);
+    MatmulBackprop(mm[2], false, f.normState, dV, update, &dNormState, sep ? &dVFull : nullptr);
+    MatmulBackprop(mm[3], true, f.normState, dgate, update, &dNormState, sep ? &dgateFull : nullptr);
     Mat dState;
     prim::NormalizeStateBackward(prevState, d.dim / kStateNormTile, dNormState, &dState);
     AddInto(grad, dState);
@@ -558,6 +604,39 @@ const char *ts2o_backend(void) { return prim::BackendName(); }
 
 void ts2o_set_activation_quant(int mode) { g_actQuant = mode; }
 
+// NormalizeVecsRowMaxKernel (src/gpt/compute/row_scale.cuh:12-43) with TCudaRngLCG (src/lib/cuda/cuda_util.cuh:538-559)
+// for an int8 destination: the warp of the kernel becomes a loop over its 32 lanes.  The GPU code contracts
+// buf * mult + u into one fused multiply-add (nvcc's default), then subtracts 0.5; fmaf states that here.
+void ts2o_rowquant_i8(const float *x, int T, int D, int8_t *q, float *row_scale)
+{
+    for (int t = 0; t < T; ++t) {
+        const float *buf = x + (size_t)t * D;
+        float maxVal = 0;
+        for (int d = 0; d < D; ++d)
+            maxVal = fmaxf(maxVal, fabsf(buf[d]));
+        float discrScale = 0;
+        if (maxVal > 0) {
+            discrScale = maxVal / 127; // GetMaxDiscrScale(maxVal, (i8 *)0), cuda_util.cuh:371-374
+            float mult = 1 / discrScale;
+            for (int h = 0; h < 32; ++h) {
+                uint32_t a, b0;
+                memcpy(&a, &buf[h], 4);
+                memcpy(&b0, &buf[0], 4);
+                uint32_t state = a * 0x398bf183u + b0 * 0x1affc3dfu + (uint32_t)t * 0x9023a049u;
+                for (int d = h; d < D; d += 32) {
+                    state = state * 0x448e3079u + 0xc484ef10u;
+                    float u = state * (1.0f / float(1ll << 32));
+                    q[(size_t)t * D + d] = FloatToI8(fmaf(buf[d], mult, u) - 0.5f); // cvt.rni.sat.s8.f32
+                }
+            }
+        } else {
+            for (int d = 0; d < D; ++d)
+                q[(size_t)t * D + d] = 0;
+        }
+        row_scale[t] = discrScale;
+    }
+}
+
 void ts2o_round_e4m3(const float *src, int64_t n, float *dst)
 {
     for (int64_t i = 0; i < n; ++i)
@@ -672,7 +751,7 @@ int ts2o_backprop(const ts2_model_descr *descr, const ts2_matrix_view *mats, int
     }
     Mat finalNorm = prim::NormalizeState(states[L], d.dim / kStateNormTile);
     Mat finalNormFast = finalNorm; // the engine's logits contraction reads e4m3, its final-layer dW contraction fp16
-    QuantizeInPlace(&finalNormFast, kActScale);
+    QuantizeInPlace(&finalNormFast, kActScale, kActScaleI8);
     Mat pred = prim::MulForward(finalNormFast, mm[1].data);
     for (float &x : pred.v)
         x *= FinalLayerMult();

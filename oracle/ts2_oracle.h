@@ -30,8 +30,13 @@ const char *ts2o_backend(void);
  * layer contractions (normalized state, gated activation, state gradient, first-contraction output gradients) are
  * rounded to e4m3 at the points and scales the B200 engine's fp8 pipeline rounds them (dense ATT / FFN layers; the
  * reference's GPU path does the same with TNormStateFloat / TFastGradientFloat = e4m3, cfg_precision.h:28-35).
- * Used to separate the engine's own error from the error of the number format.  Process-wide switch. */
+ * 2: the same for the engine's int8 pipeline: normalized state and gated activation as int8 at 24 x their value, the
+ * gradient operand of every dX product quantized per token row to int8 (nearest), the dW products from the unquantized
+ * gradients.  Used to separate the engine's own error from the error of the number format.  Process-wide switch. */
 void ts2o_set_activation_quant(int mode);
+/* row quantization to int8 with stochastic rounding, the operand form of the reference's int8 backward contractions
+ * (NormalizeVecsRowMaxKernel, src/gpt/compute/row_scale.cuh:12-43) */
+void ts2o_rowquant_i8(const float *x, int T, int D, int8_t *q, float *row_scale);
 /* the rounding that mode applies: fp32 -> nearest e4m3 value (ties to even, subnormals, saturation at 448) */
 void ts2o_round_e4m3(const float *src, int64_t n, float *dst);
 

@@ -102,3 +102,23 @@ def test_attention_gate_backward(oracle_port):
     assert rel_l2(dout, dval) < 2e-3
     want_ds = (dval * o.astype(np.float32)).reshape(T, H, 128).sum(-1)
     assert rel_l2(DS.download((T, H), np.float32), want_ds) < 2e-3
+
+
+@pytest.mark.parametrize("T,D", [(64, 256), (300, 768), (33, 6144)])
+def test_row_quantization_is_bit_exact_with_the_reference_generator(oracle_port, T, D):
+    """int8 row quantization with the reference's linear congruential generator: same bytes and scales as the oracle's
+    restatement of NormalizeVecsRowMaxKernel on the same fp32 rows (rows of very different magnitude, a zero row)."""
+    lib = capi.load_library()
+    rng = np.random.default_rng(T + D)
+    x = (rng.standard_normal((T, D)) * np.exp(rng.uniform(-8, 8, (T, 1)))).astype(np.float32)
+    x[3] = 0
+    X, Q, S = DeviceBuffer.from_numpy(x), DeviceBuffer(T * D), DeviceBuffer(T * 4)
+    check(lib.ts2_op_rowquant_i8(0, None, X.ptr, T, D, Q.ptr, S.ptr))
+    sync()
+    q_ref, s_ref = oracle_port.rowquant_i8(x)
+    assert np.array_equal(S.download(T, np.float32), s_ref)
+    q = Q.download((T, D), np.int8)
+    assert np.array_equal(q, q_ref), f"{np.count_nonzero(q != q_ref)} of {q.size} bytes differ"
+    # unbiased: the mean of the dequantized rows is the mean of the rows to well within a rounding step
+    nz = s_ref > 0
+    assert np.abs((q[nz] * s_ref[nz, None] - x[nz]).mean(1)).max() < 0.1 * s_ref[nz].max()

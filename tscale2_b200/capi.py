@@ -141,6 +141,7 @@ def _declare(lib):
         "ts2_op_cast_grad": (i32, [i32, vp, i32, vp, i64, vp, vp, vp]),
         "ts2_op_ffn_act_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp]),
         "ts2_op_att_gate_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp, vp, vp]),
+        "ts2_op_rowquant_i8": (i32, [i32, vp, vp, i32, i32, vp, vp]),
         "ts2_attention_forward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp]),
         "ts2_attention_backward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),

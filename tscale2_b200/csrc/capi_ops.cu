@@ -306,8 +306,8 @@ static Ctx op_ctx(int device, void *stream, int prec)
     Ctx c;
     c.device = device;
     c.stream = (cudaStream_t)stream;
-    c.ft = prec == TS2_PREC_FP8 ? 0 : 1;
-    c.s_act = c.ft == 0 ? 16.f : 1.f;
+    c.ft = prec == TS2_PREC_FP8 ? 0 : prec == TS2_PREC_F16 ? 1 : 2;
+    c.s_act = c.ft == 0 ? 16.f : c.ft == 1 ? 1.f : 24.f;
     return c;
 }
 
@@ -347,6 +347,14 @@ int ts2_op_att_gate_backward(int device, void *stream, int prec, const void *drg
     TS2_CUDA(cudaSetDevice(device));
     return att_gate_backward(op_ctx(device, stream, prec), (const __half *)drg, (const __half *)qkvg, (const __half *)o, T, Q, d4,
                              (__half *)dout, dscale);
+}
+
+int ts2_op_rowquant_i8(int device, void *stream, const float *x, int T, int D, int8_t *q, float *row_scale)
+{
+    if (!x || !q || !row_scale || T <= 0 || D <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_rowquant_i8: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    return rowquant_grad(op_ctx(device, stream, TS2_PREC_INT8), x, T, D, nullptr, q, row_scale, nullptr, nullptr, 1.f, nullptr, nullptr);
 }
 
 // attention core on device arrays; span_start / span_finish are host arrays of T ints

@@ -45,6 +45,28 @@ struct Fast<1> {
     }
 };
 
+// int8, round to nearest even, saturating (CvtToI8, src/lib/cuda/cuda_util.cuh:61-66)
+__device__ __forceinline__ uint32_t sat_i8(float x)
+{
+    int32_t r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return (uint32_t)r & 0xffu;
+}
+template <>
+struct Fast<2> {
+    static constexpr int SIZE = 1;
+    static __device__ __forceinline__ void store4(void *base, size_t idx, float4 v)
+    {
+        *(uint32_t *)((uint8_t *)base + idx) = sat_i8(v.x) | (sat_i8(v.y) << 8) | (sat_i8(v.z) << 16) | (sat_i8(v.w) << 24);
+    }
+    static __device__ __forceinline__ void zero4(void *base, size_t idx) { *(uint32_t *)((uint8_t *)base + idx) = 0u; }
+    static __device__ __forceinline__ float4 load4(const void *base, size_t idx)
+    {
+        const char4 raw = *(const char4 *)((const uint8_t *)base + idx);
+        return make_float4((float)raw.x, (float)raw.y, (float)raw.z, (float)raw.w);
+    }
+};
+
 __device__ __forceinline__ float4 load_half4(const __half *p)
 {
     uint2 raw = *(const uint2 *)p;
@@ -81,7 +103,7 @@ __device__ __forceinline__ float lolu_mult(float gate)
 template <int FT>
 __device__ __forceinline__ float lolu_mult_ft(float gate)
 {
-    if (FT == 0) {
+    if (FT == 0) { // FT 1 (fp16) and 2 (int8, steps of 1/24 of the rms) keep the exact form
         float th;
         asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(gate));
         return fmaf(th, 0.5f, 0.5f);

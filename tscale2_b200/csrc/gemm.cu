@@ -66,7 +66,7 @@ struct GemmParams {
     long long act_ld = 0;
     float *act_scale = nullptr;
     float act_mult = 1.f;
-    int act_f16 = 0;
+    int act_kind = 0; // format of act_out: 0 e4m3, 1 fp16, 2 int8
 };
 
 struct Unit {
@@ -466,17 +466,18 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                     uint32_t r[32];
                     tmem_ld32(taddr + chunk * 32, r);
                     tmem_ld_wait();
+                    auto acc = [&](int i) { return (MMA == 2) ? (float)(int)r[i] : __uint_as_float(r[i]); };
                     if (p.col_scale) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 cs = __ldg((const float4 *)(p.col_scale + col) + i);
-                            v[4 * i] = __uint_as_float(r[4 * i]) * rs * cs.x, v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * rs * cs.y;
-                            v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * rs * cs.z, v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * rs * cs.w;
+                            v[4 * i] = acc(4 * i) * rs * cs.x, v[4 * i + 1] = acc(4 * i + 1) * rs * cs.y;
+                            v[4 * i + 2] = acc(4 * i + 2) * rs * cs.z, v[4 * i + 3] = acc(4 * i + 3) * rs * cs.w;
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            v[i] = __uint_as_float(r[i]) * rs;
+                            v[i] = acc(i) * rs;
                     }
                 };
                 // 32 fp16 columns -> the warp's staging block -> TMA store (rows >= M, columns >= N clipped)
@@ -528,7 +529,14 @@ __global__ void __launch_bounds__(GATED ? NUM_THREADS_GATED : NUM_THREADS, 1)
                 stage_store16(gv, gcol);
                 if (row < p.M) {
                     const size_t aidx = (size_t)row * p.act_ld + wcol;
-                    if (p.act_f16) {
+                    if (p.act_kind == 2) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            Fast<2>::store4(p.act_out, aidx + 4 * i,
+                                            make_float4(lolu_mult(gv[4 * i]) * wv[4 * i] * p.act_mult, lolu_mult(gv[4 * i + 1]) * wv[4 * i + 1] * p.act_mult,
+                                                        lolu_mult(gv[4 * i + 2]) * wv[4 * i + 2] * p.act_mult,
+                                                        lolu_mult(gv[4 * i + 3]) * wv[4 * i + 3] * p.act_mult));
+                    } else if (p.act_kind == 1) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             Fast<1>::store4(p.act_out, aidx + 4 * i,
@@ -1057,9 +1065,10 @@ int gemm(const GemmArgs &a)
     if (a.group_mode == 2 && (!a.mn_major || !a.group_kptr || a.groups <= 0))
         return fail(TS2_ERR_INVALID_ARG, "gemm: bad K-grouped arguments");
     const bool paired = a.epi.pair_stride != 0;
-    if (paired && (a.mn_major || a.group_mode || a.kind == KIND_I8 || a.epi.out_kind != TS2_OUT_F16 || a.N != 2 * a.epi.pair_stride ||
+    if (paired && (a.mn_major || a.group_mode || a.epi.out_kind != TS2_OUT_F16 || a.N != 2 * a.epi.pair_stride ||
                    a.epi.pair_stride % 128 || !a.epi.act_out || !a.epi.act_scale || a.epi.act_ld < a.epi.pair_stride ||
-                   (a.epi.act_ld * (a.epi.act_f16 ? 2 : 1)) % 16 || ((uintptr_t)a.epi.act_out & 15)))
+                   a.epi.act_kind < 0 || a.epi.act_kind > 2 || (a.epi.act_ld * (a.epi.act_kind == 1 ? 2 : 1)) % 16 ||
+                   ((uintptr_t)a.epi.act_out & 15)))
         return fail(TS2_ERR_INVALID_ARG, "gemm: bad gated-activation arguments");
     Plan pl = make_plan(a.device, a.kind, a.mn_major, a.M, a.N, a.K, a.group_mode, a.groups);
     if (paired) { // one tile = 128 wide + 128 gate columns, never split along K (the epilogue needs whole sums)
@@ -1131,7 +1140,7 @@ int gemm(const GemmArgs &a)
     p.act_ld = a.epi.act_ld;
     p.act_scale = a.epi.act_scale;
     p.act_mult = a.epi.act_mult;
-    p.act_f16 = a.epi.act_f16 ? 1 : 0;
+    p.act_kind = a.epi.act_kind;
     // coalesced TMA-store epilogue (the accumulate form adds its residual input first; split units go to the workspace;
     // per-group C offsets of mode 2 are not expressible as one 2-D map)
     CUtensorMap tmC = tmA;
@@ -1165,6 +1174,8 @@ int gemm(const GemmArgs &a)
             rc = launch<256, 1, 0, false, true>(a, pl, tmA, tmB, tmC, p);
         else if (es == 2 && mma == 1)
             rc = launch<256, 2, 1, false, true>(a, pl, tmA, tmB, tmC, p);
+        else if (es == 1 && mma == 2)
+            rc = launch<256, 1, 2, false, true>(a, pl, tmA, tmB, tmC, p);
     } else {
     TS2_GEMM_CASE(256, 1, 0, false)
     TS2_GEMM_CASE(128, 1, 0, false)

@@ -21,13 +21,13 @@ struct Epilogue {
     // and "gate" rows [pair_stride, 2 pair_stride), N = 2 pair_stride.  A tile covers 128 columns of each, and the
     // epilogue applies the 128-wide tile normalisation to the wide half, stores the normalised wide and the raw gate
     // values as fp16 in C (same columns as the plain form), the tile scale in act_scale[M][pair_stride / 128] and
-    // act_mult * sigmoid(2 gate) * normalised wide in act_out[M][act_ld] (e4m3 bytes, or fp16 when act_f16).
+    // act_mult * sigmoid(2 gate) * normalised wide in act_out[M][act_ld] (act_kind 0: e4m3 bytes, 1: fp16, 2: int8).
     int64_t pair_stride = 0;
     void *act_out = nullptr;
     int64_t act_ld = 0;
     float *act_scale = nullptr;
     float act_mult = 1.f;
-    bool act_f16 = false;
+    int act_kind = 0;
 };
 
 struct GemmArgs {

@@ -12,7 +12,7 @@ constexpr int TILE = 128; // STATE_NORM_TILE / MM_TILE / head dim of the referen
 struct Ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
-    int ft = 0;         // 0 e4m3, 1 fp16
+    int ft = 0;         // 0 e4m3, 1 fp16, 2 int8
     float s_act = 16.f; // quantization scale of normalized activations (1 for fp16)
 };
 
@@ -36,6 +36,16 @@ int tilenorm_backward(const Ctx &c, const float *x, const float *dn, const float
 // fscale = f_static * (*sko) * ginv   (ScaleGrad / ComputeGradMult, gpu_grad_scale.cuh:33-62)
 int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, void *g_fast, float *ginv, float f_static, const float *sko,
               float *fscale);
+
+// int8 pipeline: row quantization with the reference's stochastic rounding (NormalizeVecsRowMaxKernel,
+// row_scale.cuh:12-43): q[t][d] int8, row_scale[t] = max|x[t]| / 127.
+//  rowquant_grad: x = g * 2^k (2^k from the running abs-max as in cast_grad; also writes ginv, fscale and, optionally,
+//                 x as fp16 for the fp16 dW contraction);  rowquant_half: x = an fp16 tensor as it is.
+int rowquant_grad(const Ctx &c, const float *g, int T, int D, const unsigned *absmax, int8_t *q, float *row_scale, __half *g16, float *ginv,
+                  float f_static, const float *sko, float *fscale);
+int rowquant_half(const Ctx &c, const __half *x, int T, int D, int8_t *q, float *row_scale);
+// int8 values widened to fp16 (exact), n a multiple of 4
+int i8_to_half(const Ctx &c, const void *src, size_t n, __half *dst);
 
 // FFN activation (LoLU + tile-norm of the wide vector), TFFLayer::ComputeForward layer_ffn.cu:190-211.
 // wg: [T][2F] fp16 = [wide | gate]; what: normalized wide fp16 [T][F]; wscale [T][F/128]; rg fast [T][F]
@@ -127,7 +137,8 @@ struct OptSeg {
     int grow0;       // global row number of the matrix's row 0
     int item0;       // work items (rows) of the segments before this one
     int mat;         // matrix index
-    int qsize;       // bytes per quantized element (1: e4m3, 2: fp16)
+    int qsize;       // bytes per quantized element
+    int qkind;       // its format: 0 e4m3, 1 fp16, 2 int8
     uint8_t *qbase;  // row-major quantized copy of the matrix
     float sparsity;
 };
@@ -143,9 +154,9 @@ int opt_update(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const flo
                const ts2_training_step *step, float *avg, float *w, double *roww2);
 int opt_sko(const Ctx &c, const OptMat *mats, int n_mats, const double *roww2, float *skos);
 int opt_quantize(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const float *w, const float *skos);
-// copy / transposed copy of quantized values; dst or dstT may be null
+// copy / transposed copy of quantized values; dst or dstT may be null; transposed_as_half: 0 no, 1 e4m3 -> fp16, 2 int8 -> fp16
 int qcopy_block(const Ctx &c, const void *src, int64_t x, int64_t y, int64_t ld_src, int elem_size, void *dst, int64_t ld, void *dstT,
-                int64_t ldT, bool transposed_as_half);
+                int64_t ldT, int transposed_as_half);
 int layer_scales(const Ctx &c, float *fwd_col, float *bwd_row, int W, int ncat, bool is_att, float a, const float *skos);
 
 } // namespace ts2

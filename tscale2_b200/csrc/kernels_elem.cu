@@ -133,12 +133,15 @@ __global__ void tilenorm_forward_kernel(const float *__restrict__ x, int T, int 
 
 int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, __half *n16)
 {
-    const int grid = c.ft == 0 ? grid_for(c, tilenorm_forward_kernel<0>, (long long)T * (D / TILE))
-                               : grid_for(c, tilenorm_forward_kernel<1>, (long long)T * (D / TILE));
+    const int grid = c.ft == 0   ? grid_for(c, tilenorm_forward_kernel<0>, (long long)T * (D / TILE))
+                     : c.ft == 1 ? grid_for(c, tilenorm_forward_kernel<1>, (long long)T * (D / TILE))
+                                 : grid_for(c, tilenorm_forward_kernel<2>, (long long)T * (D / TILE));
     if (c.ft == 0)
         tilenorm_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
-    else
+    else if (c.ft == 1)
         tilenorm_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
+    else
+        tilenorm_forward_kernel<2><<<grid, THREADS, 0, c.stream>>>(x, T, D, c.s_act, n_fast, n16);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }
@@ -263,6 +266,133 @@ int cast_grad(const Ctx &c, const float *g, size_t n, const unsigned *absmax, vo
 }
 
 // ---------------------------------------------------------------------------------
+// Row quantization to int8 with the reference's stochastic rounding (NormalizeVecsRowMaxKernel,
+// src/gpt/compute/row_scale.cuh:12-43, TCudaRngLCG, src/lib/cuda/cuda_util.cuh:538-559): one warp per row;
+// scale = max|x| / 127; lane h owns the elements h, h + 32, h + 64, ... and draws one uniform number per element, in
+// that order, from a linear congruential generator seeded with (bits of x[h], bits of x[0], row); q = round to
+// nearest even, saturating, of x / scale + u - 0.5.  x = src * mult, mult a power of two (so the scaling is exact).
+// The quantized row goes through a shared-memory row so that it leaves in 16-byte pieces.  Optionally also writes x as
+// fp16 (the operand of the fp16 dW contraction).  SRC: float or __half.
+struct RowQuantLCG {
+    uint32_t state;
+    __device__ RowQuantLCG(uint32_t a, uint32_t b, uint32_t c) { state = a * 0x398bf183u + b * 0x1affc3dfu + c * 0x9023a049u; }
+    __device__ float uniform()
+    {
+        state = state * 0x448e3079u + 0xc484ef10u;
+        return (float)state * (1.0f / 4294967296.0f);
+    }
+};
+
+template <typename SRC>
+__device__ __forceinline__ float rq_load(const SRC *p, size_t i);
+template <>
+__device__ __forceinline__ float rq_load<float>(const float *p, size_t i)
+{
+    return p[i];
+}
+template <>
+__device__ __forceinline__ float rq_load<__half>(const __half *p, size_t i)
+{
+    return __half2float(p[i]);
+}
+
+template <typename SRC>
+__global__ void rowquant_i8_kernel(const SRC *__restrict__ src, int T, int D, const unsigned *__restrict__ absmax, float target,
+                                   int8_t *__restrict__ q, float *__restrict__ row_scale, __half *__restrict__ x16,
+                                   float *__restrict__ ginv, float f_static, const float *__restrict__ sko, float *__restrict__ fscale)
+{
+    extern __shared__ int8_t rq_rows[]; // [WARPS][D]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const float mult = absmax ? grad_mult(*absmax, target) : 1.f;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && ginv) {
+        *ginv = 1.f / mult;
+        if (fscale)
+            *fscale = f_static * (sko ? *sko : 1.f) / mult;
+    }
+    int8_t *row_s = rq_rows + (size_t)wid * D;
+    for (int t = blockIdx.x * WARPS + wid; t < T; t += gridDim.x * WARPS) {
+        const SRC *row = src + (size_t)t * D;
+        float mx = 0.f;
+        for (int d = lane; d < D; d += 32)
+            mx = fmaxf(mx, fabsf(rq_load<SRC>(row, d) * mult));
+        mx = warp_max(mx);
+        float scale = 0.f;
+        if (mx > 0.f) {
+            scale = mx / 127;
+            const float inv = 1 / scale;
+            RowQuantLCG rng(__float_as_uint(rq_load<SRC>(row, lane) * mult), __float_as_uint(rq_load<SRC>(row, 0) * mult), (uint32_t)t);
+            for (int d = lane; d < D; d += 32) {
+                const float x = rq_load<SRC>(row, d) * mult;
+                row_s[d] = (int8_t)sat_i8(__fsub_rn(__fmaf_rn(x, inv, rng.uniform()), 0.5f));
+                if (x16)
+                    x16[(size_t)t * D + d] = __float2half_rn(x);
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) {
+                row_s[d] = 0;
+                if (x16)
+                    x16[(size_t)t * D + d] = __float2half_rn(0.f);
+            }
+        }
+        __syncwarp();
+        for (int i = lane; i < D / 16; i += 32)
+            *(uint4 *)(q + (size_t)t * D + 16 * i) = *(const uint4 *)(row_s + 16 * i);
+        if (lane == 0)
+            row_scale[t] = scale;
+        __syncwarp();
+    }
+}
+
+template <typename SRC>
+static int rowquant_launch(const Ctx &c, const SRC *src, int T, int D, const unsigned *absmax, int8_t *q, float *row_scale, __half *x16,
+                           float *ginv, float f_static, const float *sko, float *fscale)
+{
+    if (D % 128 || D > 16384)
+        return fail(TS2_ERR_INVALID_ARG, "rowquant: row length %d must be a multiple of 128 up to 16384", D);
+    auto kern = rowquant_i8_kernel<SRC>;
+    const size_t smem = (size_t)WARPS * D;
+    static bool configured[16] = {};
+    if (smem > 48 * 1024 && !configured[c.device & 15]) {
+        TS2_CUDA(cudaFuncSetAttribute(rowquant_i8_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * 16384));
+        TS2_CUDA(cudaFuncSetAttribute(rowquant_i8_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * 16384));
+        configured[c.device & 15] = true;
+    }
+    const int grid = (int)std::max<long long>(1, std::min<long long>(ceil_div(T, WARPS), (long long)sm_count(c.device) * 4));
+    kern<<<grid, THREADS, smem, c.stream>>>(src, T, D, absmax, 128.f, q, row_scale, x16, ginv, f_static, sko, fscale);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+int rowquant_grad(const Ctx &c, const float *g, int T, int D, const unsigned *absmax, int8_t *q, float *row_scale, __half *g16, float *ginv,
+                  float f_static, const float *sko, float *fscale)
+{
+    return rowquant_launch<float>(c, g, T, D, absmax, q, row_scale, g16, ginv, f_static, sko, fscale);
+}
+
+int rowquant_half(const Ctx &c, const __half *x, int T, int D, int8_t *q, float *row_scale)
+{
+    return rowquant_launch<__half>(c, x, T, D, nullptr, q, row_scale, nullptr, nullptr, 1.f, nullptr, nullptr);
+}
+
+__global__ void i8_to_half_kernel(const char4 *__restrict__ src, size_t n4, uint2 *__restrict__ dst)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const char4 v = src[i];
+        const __half2 a = __floats2half2_rn((float)v.x, (float)v.y), b = __floats2half2_rn((float)v.z, (float)v.w);
+        dst[i] = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
+    }
+}
+
+int i8_to_half(const Ctx &c, const void *src, size_t n, __half *dst)
+{
+    const size_t n4 = n / 4;
+    const int grid = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(n4, 256 * 4), (size_t)sm_count(c.device) * 8));
+    i8_to_half_kernel<<<grid, 256, 0, c.stream>>>((const char4 *)src, n4, (uint2 *)dst);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------
 // (the forward FFN activation lives in the contraction's gated epilogue, gemm.cu)
 template <int FT>
 __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __half *__restrict__ wg, const __half *__restrict__ what,
@@ -356,12 +486,15 @@ __global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const _
 
 int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg)
 {
-    const int grid = c.ft == 0 ? grid_for(c, att_gate_forward_kernel<0>, (long long)T * (Q / TILE))
-                               : grid_for(c, att_gate_forward_kernel<1>, (long long)T * (Q / TILE));
+    const int grid = c.ft == 0   ? grid_for(c, att_gate_forward_kernel<0>, (long long)T * (Q / TILE))
+                     : c.ft == 1 ? grid_for(c, att_gate_forward_kernel<1>, (long long)T * (Q / TILE))
+                                 : grid_for(c, att_gate_forward_kernel<2>, (long long)T * (Q / TILE));
     if (c.ft == 0)
         att_gate_forward_kernel<0><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
-    else
+    else if (c.ft == 1)
         att_gate_forward_kernel<1><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
+    else
+        att_gate_forward_kernel<2><<<grid, THREADS, 0, c.stream>>>(qkvg, o, T, Q, c.s_act, rg);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

@@ -214,7 +214,9 @@ __global__ void opt_quant_kernel(const OptSeg *__restrict__ segs, int nseg, int 
         uint8_t *dst = sg.qbase + (size_t)r * sg.x * sg.qsize;
         for (int i = c0 / 4 + lane; i < c1 / 4; i += 32) {
             const float4 v = scale4(src[i], mult);
-            if (sg.qsize == 1) {
+            if (sg.qkind == 2) { // int8: nearest even, saturating (PackFloatToInt8, src/gpt/model_params/sse_utils.h:56-78)
+                *(uint32_t *)(dst + 4 * (size_t)i) = sat_i8(v.x) | (sat_i8(v.y) << 8) | (sat_i8(v.z) << 16) | (sat_i8(v.w) << 24);
+            } else if (sg.qkind == 0) {
                 const uint32_t pk = (uint32_t)encode_e4m3_weight(v.x) | ((uint32_t)encode_e4m3_weight(v.y) << 8) |
                                     ((uint32_t)encode_e4m3_weight(v.z) << 16) | ((uint32_t)encode_e4m3_weight(v.w) << 24);
                 *(uint32_t *)(dst + 4 * (size_t)i) = pk;
@@ -280,13 +282,14 @@ int opt_quantize(const Ctx &c, const OptSeg *segs, int nseg, int nitems, const f
 }
 
 // Copy of a block of already quantized values (ES bytes per element) into another row-major place and / or its
-// transpose: 32x32 tiles, both sides coalesced.  TH: the transposed copy holds the e4m3 value widened to fp16.
-template <int ES, bool TH>
+// transpose: 32x32 tiles, both sides coalesced.  TH: the transposed copy holds the value widened to fp16 (1: from e4m3,
+// 2: from int8), 0: copied as it is.
+template <int ES, int TH>
 __global__ void qcopy_kernel(const void *__restrict__ src, long long x, long long y, long long ld_src, void *__restrict__ dst,
                              long long ld, void *__restrict__ dstT, long long ldT)
 {
     using QT = typename std::conditional<ES == 1, uint8_t, uint16_t>::type;
-    using TT = typename std::conditional<TH, uint16_t, QT>::type;
+    using TT = typename std::conditional<TH != 0, uint16_t, QT>::type;
     __shared__ QT tile[32][33];
     const long long x0 = (long long)blockIdx.x * 32, y0 = (long long)blockIdx.y * 32;
     for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -306,9 +309,11 @@ __global__ void qcopy_kernel(const void *__restrict__ src, long long x, long lon
         const long long xx = x0 + r, yy = y0 + threadIdx.x;
         if (xx < x && yy < y) {
             const QT qv = tile[threadIdx.x][r];
-            if constexpr (TH && ES == 1) {
+            if constexpr (TH == 1 && ES == 1) {
                 __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)qv, __NV_E4M3);
                 ((uint16_t *)dstT)[xx * ldT + yy] = h2.x;
+            } else if constexpr (TH == 2 && ES == 1) {
+                ((uint16_t *)dstT)[xx * ldT + yy] = __half_as_ushort(__float2half_rn((float)(int8_t)qv));
             } else {
                 ((TT *)dstT)[xx * ldT + yy] = qv;
             }
@@ -317,15 +322,17 @@ __global__ void qcopy_kernel(const void *__restrict__ src, long long x, long lon
 }
 
 int qcopy_block(const Ctx &c, const void *src, int64_t x, int64_t y, int64_t ld_src, int elem_size, void *dst, int64_t ld, void *dstT,
-                int64_t ldT, bool transposed_as_half)
+                int64_t ldT, int transposed_as_half)
 {
     dim3 g((unsigned)ceil_div(x, 32), (unsigned)ceil_div(y, 32)), b(32, 8);
-    if (elem_size == 1 && transposed_as_half)
-        qcopy_kernel<1, true><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
+    if (elem_size == 1 && transposed_as_half == 1)
+        qcopy_kernel<1, 1><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
+    else if (elem_size == 1 && transposed_as_half == 2)
+        qcopy_kernel<1, 2><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
     else if (elem_size == 1)
-        qcopy_kernel<1, false><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
+        qcopy_kernel<1, 0><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
     else
-        qcopy_kernel<2, false><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
+        qcopy_kernel<2, 0><<<g, b, 0, c.stream>>>(src, x, y, ld_src, dst, ld, dstT, ldT);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

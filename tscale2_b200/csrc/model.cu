@@ -136,6 +136,11 @@ struct ts2_model {
     void *dcat = nullptr;
     float *dscale = nullptr;
     __half *dq = nullptr, *dk = nullptr, *dv = nullptr; // attention gradients, fp16 between the attention core and its post-kernel
+    // int8 pipeline: the gradient operands of the dX contractions are row-quantized int8 (+ one fp32 scale per row), the
+    // dW contractions read fp16: the state gradient and the first-contraction output gradients as fp16, and the int8
+    // activations widened to fp16
+    __half *g16 = nullptr, *dcat16 = nullptr, *x16 = nullptr;
+    float *g_rs = nullptr, *dcat_rs = nullptr;
     float *rope = nullptr;
     // mixture-of-experts scratch shared by the layers
     int E = 0, K = 0, X = 0, epad = 0, moe_rows = 0;
@@ -219,7 +224,7 @@ Ctx ctx_of(ts2_model *m)
     return c;
 }
 
-size_t fast_size(const ts2_model *m) { return m->ft == 0 ? 1 : 2; }
+size_t fast_size(const ts2_model *m) { return m->ft == 1 ? 2 : 1; }
 
 // C = epilogue(A[M][K] . B[N][K]^T), K contiguous in both
 int gemm_tn(ts2_model *m, int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
@@ -309,11 +314,13 @@ int validate(const ts2_model_descr *d)
         return fail(TS2_ERR_INVALID_ARG, "bad head / ffn / layer counts");
     if (d->label_count <= 0 || d->output_token_count <= 0 || d->output_token_count % 32)
         return fail(TS2_ERR_INVALID_ARG, "label_count must be positive and output_token_count a positive multiple of 32");
-    if (d->precision != TS2_PREC_FP8 && d->precision != TS2_PREC_F16)
-        return fail(TS2_ERR_UNSUPPORTED, "precision must be TS2_PREC_FP8 or TS2_PREC_F16");
+    if (d->precision != TS2_PREC_FP8 && d->precision != TS2_PREC_F16 && d->precision != TS2_PREC_INT8)
+        return fail(TS2_ERR_UNSUPPORTED, "precision must be TS2_PREC_FP8, TS2_PREC_F16 or TS2_PREC_INT8");
     for (int l = 0; l < d->layer_count; ++l) {
         int t = d->layers[l].layer_type;
         if (t == TS2_LAYER_MOE) {
+            if (d->precision == TS2_PREC_INT8)
+                return fail(TS2_ERR_UNSUPPORTED, "layer %d: mixture-of-experts layers are not available with TS2_PREC_INT8", l);
             if (d->moe_expert_count < 1 || d->moe_expert_count > 128 || d->moe_selected < 1 || d->moe_selected > 8 ||
                 d->moe_selected > d->moe_expert_count || d->expert_dim <= 0 || d->expert_dim % 128)
                 return fail(TS2_ERR_UNSUPPORTED,
@@ -423,6 +430,7 @@ void build_segments(const ts2_model *m, int world, int rank, std::vector<OptSeg>
             sg.item0 = items;
             sg.mat = i;
             sg.qsize = bk.qsize;
+            sg.qkind = bk.qsize == 2 ? 1 : (m->ft == 2 ? 2 : 0);
             sg.qbase = bk.qflat + (mt.offset - bk.off) * bk.qsize;
             sg.sparsity = mt.sparsity;
             items += sg.nrows;
@@ -455,7 +463,7 @@ int post_quantize(ts2_model *m)
     const int D = m->D;
     const size_t fs = fast_size(m);
     // final layer: fp16 transposed copy of the same quantized values for the dX contraction
-    M_TRY(qcopy_block(c, m->Wf, D, m->V, D, (int)fs, nullptr, 0, m->WfT16, m->V, m->ft == 0));
+    M_TRY(qcopy_block(c, m->Wf, D, m->V, D, (int)fs, nullptr, 0, m->WfT16, m->V, m->ft == 0 ? 1 : m->ft == 2 ? 2 : 0));
     const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
     for (Layer &ly : m->layers) {
         const int W = ly.wide, n = ly.ncat;
@@ -467,20 +475,20 @@ int post_quantize(ts2_model *m)
             const int E = m->E, X = m->X;
             for (int e = 0; e < E; ++e) {
                 uint8_t *cat = (uint8_t *)ly.Wcat + (size_t)e * 2 * X * D * fs, *catT = (uint8_t *)ly.WcatT + (size_t)e * D * 2 * X * fs;
-                M_TRY(qcopy_block(c, qsrc(ly.mat0) + (size_t)e * X * D * fs, D, X, D, (int)fs, cat, D, catT, 2 * X, false));
+                M_TRY(qcopy_block(c, qsrc(ly.mat0) + (size_t)e * X * D * fs, D, X, D, (int)fs, cat, D, catT, 2 * X, 0));
                 M_TRY(qcopy_block(c, qsrc(ly.mat0 + 1) + (size_t)e * X * D * fs, D, X, D, (int)fs, cat + (size_t)X * D * fs, D,
-                                  catT + (size_t)X * fs, 2 * X, false));
+                                  catT + (size_t)X * fs, 2 * X, 0));
                 M_TRY(qcopy_block(c, qsrc(ly.mat0 + 2) + (size_t)e * D * X * fs, X, D, X, (int)fs, (uint8_t *)ly.Wc + (size_t)e * D * X * fs, X,
-                                  (uint8_t *)ly.WcT + (size_t)e * X * D * fs, D, false));
+                                  (uint8_t *)ly.WcT + (size_t)e * X * D * fs, D, 0));
             }
-            M_TRY(qcopy_block(c, qsrc(ly.mat0 + 3), D, E, D, (int)fs, ly.Wsel, D, ly.WselT, m->epad, false));
+            M_TRY(qcopy_block(c, qsrc(ly.mat0 + 3), D, E, D, (int)fs, ly.Wsel, D, ly.WselT, m->epad, 0));
             M_TRY(fill_vector(c, ly.fwd_col, 2 * X, a, nullptr, false));
             M_TRY(fill_vector(c, ly.bwd_row_e, X, 1.f, m->mats[ly.mat0].sko, true));
             continue;
         }
         // the concatenated block [n W][D] transposes in one pass: its row blocks become the column blocks of WcatT
-        M_TRY(qcopy_block(c, ly.Wcat, D, (int64_t)n * W, D, (int)fs, nullptr, 0, ly.WcatT, (int64_t)n * W, false));
-        M_TRY(qcopy_block(c, ly.Wc, W, D, W, (int)fs, nullptr, 0, ly.WcT, D, false));
+        M_TRY(qcopy_block(c, ly.Wcat, D, (int64_t)n * W, D, (int)fs, nullptr, 0, ly.WcatT, (int64_t)n * W, 0));
+        M_TRY(qcopy_block(c, ly.Wc, W, D, W, (int)fs, nullptr, 0, ly.WcT, D, 0));
         // forward column scales: matrices followed by a normalisation (Q, V, Expand) and the gates use the unit-RMS
         // matrix q/32 (GetDataNoScale), K carries its matrix scale; dW rows of Q, K, V / Expand are divided by theirs
         M_TRY(layer_scales(c, ly.fwd_col, ly.bwd_row, W, n, ly.type == TS2_LAYER_ATT, a, m->skos + ly.mat0));
@@ -508,9 +516,11 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     m->F = 128 * d.ffn_tiles;
     m->V = d.output_token_count;
     m->L = d.layer_count;
-    m->ft = d.precision == TS2_PREC_FP8 ? 0 : 1;
-    m->kind = m->ft == 0 ? KIND_E4M3 : KIND_F16;
-    m->s_act = m->ft == 0 ? 16.f : 1.f;
+    // operand format of the contractions: e4m3 with activations at 16 x their unit-rms value; fp16; int8 with activations at
+    // 24 x (the reference's STATE_VEC_SCALE / FFN_VEC_SCALE / V_VEC_SCALE = 1 / 24, cfg_precision.h:72-77)
+    m->ft = d.precision == TS2_PREC_FP8 ? 0 : d.precision == TS2_PREC_F16 ? 1 : 2;
+    m->kind = m->ft == 0 ? KIND_E4M3 : m->ft == 1 ? KIND_F16 : KIND_I8;
+    m->s_act = m->ft == 0 ? 16.f : m->ft == 1 ? 1.f : 24.f;
     m->E = d.moe_expert_count;
     m->K = d.moe_selected;
     m->X = d.expert_dim;
@@ -685,6 +695,13 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     M_TRY(dalloc(m, &m->drg, drg_elems));
     M_TRY(dalloc(m, &m->dout, (size_t)T * m->Q));
     M_TRY(dalloc(m, (uint8_t **)&m->dcat, dcat_elems * fs));
+    if (m->ft == 2) {
+        M_TRY(dalloc(m, &m->g16, (size_t)T * D));
+        M_TRY(dalloc(m, &m->dcat16, dcat_elems));
+        M_TRY(dalloc(m, &m->x16, (size_t)T * std::max(max_wide, D)));
+        M_TRY(dalloc(m, &m->g_rs, (size_t)T));
+        M_TRY(dalloc(m, &m->dcat_rs, (size_t)T));
+    }
     M_TRY(dalloc(m, &m->dscale, (size_t)T * m->H));
     M_TRY(dalloc(m, &m->dq, (size_t)T * m->Q));
     M_TRY(dalloc(m, &m->dk, (size_t)T * m->Q));
@@ -723,8 +740,10 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     for (Layer &ly : m->layers) {
         if (ly.type == TS2_LAYER_MOE)
             continue; // the grouped contractions never split K
-        ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, (int64_t)ly.ncat * ly.wide, D, T));
-        ws = std::max(ws, gemm_workspace_bytes(m->device, m->kind, true, D, ly.wide, T));
+        for (int kind : {m->kind, (int)KIND_F16}) { // the int8 pipeline runs its dW contractions in fp16
+            ws = std::max(ws, gemm_workspace_bytes(m->device, kind, true, (int64_t)ly.ncat * ly.wide, D, T));
+            ws = std::max(ws, gemm_workspace_bytes(m->device, kind, true, D, ly.wide, T));
+        }
     }
     ws = std::max(ws, gemm_workspace_bytes(m->device, KIND_F16, true, m->V, D, m->chunk));
     ws = std::max(ws, gemm_workspace_bytes(m->device, KIND_F16, true, m->V, D, 128));
@@ -835,7 +854,7 @@ int forward(ts2_model *m)
             e1.act_ld = W;
             e1.act_scale = ly.wscale;
             e1.act_mult = m->s_act;
-            e1.act_f16 = m->ft != 0;
+            e1.act_kind = m->ft;
         }
         M_TRY(gemm_tn(m, m->kind, T, C, D, ly.n_fast, D, ly.Wcat, D, ly.cat16, C, e1));
         TRACE("cat16", l, ly.cat16, (size_t)T * C * 2, TR_F16);
@@ -934,6 +953,74 @@ static int reduce_matrices(ts2_model *m, int m0, int)
     return TS2_OK;
 }
 
+// Backward pass of one dense layer in the int8 pipeline (the reference's default build: FWD / BWD_MATMUL_TYPE =
+// MATMUL_INT8, cfg_precision.h:21-26).  Same chain as the e4m3 / fp16 pipelines with these differences:
+//  * the gradient operand of each dX contraction is quantized per row to int8 with the reference's stochastic rounding
+//    (NormalizeVecsRowMaxKernel, row_scale.cuh:12-43) and its row scale is applied in the contraction's epilogue
+//    (Int8MatMulKernelRowScale, src/lib/cuda/cuda_i8.cuh:200-260);
+//  * the dW contractions run in fp16 on the unquantized gradients and the int8 activations widened to fp16: their
+//    contraction index is the token, so a per-token scale cannot leave through the epilogue; the reference sorts the
+//    tokens by scale and rescales its int32 accumulator every 128 tokens (cuda_i8.cuh:264-320), which has no cheap
+//    form on a TMEM accumulator; fp16 operands are more exact than that and cost the tensor rate of that third;
+//  * the element-wise gradient kernels are the fp16 pipeline's.
+int backward_dense_int8(ts2_model *m, int l)
+{
+    Ctx c = ctx_of(m), c16 = c;
+    c16.ft = 1;
+    const int T = m->batch.node_count, D = m->D, H = m->H;
+    const BatchDev &b = m->batch;
+    const bool tune_layers = !(m->descr.flags & TS2_MPF_DISABLE_TUNE_LAYERS);
+    Layer &ly = m->layers[l];
+    const int W = ly.wide, C = ly.ncat * W;
+    Matrix &mc = m->mats[ly.mat0 + ly.ncat];
+    M_TRY(rowquant_grad(c, m->g, T, D, m->absmax + l + 1, (int8_t *)m->g_fast, m->g_rs, m->g16, m->ginv, sqrtf((float)D / (float)W), mc.sko,
+                        m->fscale));
+    TRACE("g_fast", l, m->g_fast, (size_t)T * D, TR_RAW);
+    Epilogue e3;
+    e3.alpha = 1.f / (32.f * sqrtf((float)D));
+    e3.row_scale = m->g_rs;
+    e3.out_kind = TS2_OUT_F16;
+    M_TRY(gemm_tn(m, KIND_I8, T, W, D, m->g_fast, D, ly.WcT, D, m->drg, W, e3));
+    TRACE("drg", l, m->drg, (size_t)T * W * 2, TR_F16);
+    if (tune_layers) {
+        M_TRY(i8_to_half(c, ly.rg, (size_t)T * W, m->x16));
+        Epilogue e6;
+        e6.alpha = 1.f / m->s_act;
+        e6.dyn_scale = m->ginv;
+        e6.out_kind = TS2_OUT_F32_ADD;
+        M_TRY(gemm_dw(m, KIND_F16, D, W, T, m->g16, D, m->x16, W, mc.grad, e6));
+        TRACE("dW_c", l, mc.grad, (size_t)D * W * 4, TR_F32);
+    }
+    if (ly.type == TS2_LAYER_ATT) {
+        M_TRY(att_gate_backward(c16, m->drg, ly.cat16, ly.o, T, W, m->dcat16, m->dout, m->dscale));
+        M_TRY(attention_backward(c, ly.q, ly.k, ly.v, m->dout, ly.lse, m->dscale, b.span_start[ly.att_type], b.span_finish[ly.att_type],
+                                 b.rev_first[ly.att_type], b.rev_last[ly.att_type], T, H, ly.slope, m->dq, m->dk, m->dv, true));
+        M_TRY(att_post_backward(c16, m->dq, m->dk, m->dv, true, ly.q, ly.v, ly.qscale, ly.vscale, m->rope, m->mats[ly.mat0 + 1].sko, T, H,
+                                m->dcat16));
+    } else {
+        M_TRY(ffn_act_backward(c16, m->drg, ly.cat16, ly.cat16, 2 * W, ly.wscale, T, W, m->dcat16));
+    }
+    TRACE("dcat16", l, m->dcat16, (size_t)T * C * 2, TR_F16);
+    M_TRY(rowquant_half(c, m->dcat16, T, C, (int8_t *)m->dcat, m->dcat_rs));
+    Epilogue e4;
+    e4.alpha = sqrtf(1.0f / D) / 32.f;
+    e4.row_scale = m->dcat_rs;
+    e4.out_kind = TS2_OUT_F32;
+    M_TRY(gemm_tn(m, KIND_I8, T, D, C, m->dcat, C, ly.WcatT, C, m->dn, D, e4));
+    TRACE("dn", l, m->dn, (size_t)T * D * 4, TR_F32);
+    if (tune_layers) {
+        M_TRY(i8_to_half(c, ly.n_fast, (size_t)T * D, m->x16));
+        Epilogue e5;
+        e5.alpha = 1.f / m->s_act;
+        e5.dyn_scale = m->fscale;
+        e5.row_scale = ly.bwd_row;
+        e5.out_kind = TS2_OUT_F32_ADD;
+        M_TRY(gemm_dw(m, KIND_F16, C, D, T, m->dcat16, C, m->x16, D, m->mats[ly.mat0].grad, e5));
+        TRACE("dW_cat", l, m->mats[ly.mat0].grad, (size_t)C * D * 4, TR_F32);
+    }
+    return TS2_OK;
+}
+
 int backward(ts2_model *m)
 {
     Ctx c = ctx_of(m);
@@ -1006,6 +1093,9 @@ int backward(ts2_model *m)
             M_TRY(tap_gradient(m, l));
             continue;
         }
+        if (m->ft == 2) {
+            M_TRY(backward_dense_int8(m, l));
+        } else {
         // g_fast = g * 2^k; fscale = sqrt(D/W) * sko_c / 2^k turns the scale-free intermediate gradients
         // below into true ones
         M_TRY(cast_grad(c, m->g, (size_t)T * D, m->absmax + l + 1, m->g_fast, m->ginv, sqrtf((float)D / (float)W), mc.sko, m->fscale));
@@ -1056,6 +1146,7 @@ int backward(ts2_model *m)
             e5.out_kind = TS2_OUT_F32_ADD;
             M_TRY(gemm_dw(m, m->kind, C, D, T, m->dcat, C, ly.n_fast, D, m->mats[ly.mat0].grad, e5));
             TRACE("dW_cat", l, m->mats[ly.mat0].grad, (size_t)C * D * 4, TR_F32);
+        }
         }
         M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
         M_TRY(tilenorm_backward(c, m->states[l], m->dn, m->fscale, 1.f, T, D, m->g, true, m->absmax + l, m->health + l, m->step_no));
