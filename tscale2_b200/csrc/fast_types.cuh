@@ -111,6 +111,33 @@ __device__ __forceinline__ float lolu_mult_ft(float gate)
     return lolu_mult(gate);
 }
 
+// Packed fp16 arithmetic for the e4m3 pipeline's element-wise kernels.  Those kernels were bound by instruction issue,
+// not by memory (about 190 warp instructions per 128 elements: three fp16 -> fp32 conversions, one MUFU and an
+// fp32 -> e4m3 conversion per element): in packed fp16 one instruction serves two elements, the exponential included,
+// and the result converts to two e4m3 bytes in one step.  fp16 carries 11 bits, the e4m3 results 4.
+__device__ __forceinline__ __half2 h2_from_bits(uint32_t w) { return *(const __half2 *)&w; }
+__device__ __forceinline__ uint32_t bits_from_h2(__half2 v) { return *(const uint32_t *)&v; }
+__device__ __forceinline__ __half2 tanh_h2(__half2 v)
+{
+    uint32_t r;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(r) : "r"(bits_from_h2(v)));
+    return h2_from_bits(r);
+}
+// sigmoid(2 g) = 0.5 + 0.5 tanh(g) for two gates
+__device__ __forceinline__ __half2 lolu_mult_h2(__half2 gate)
+{
+    const __half2 half = __float2half2_rn(0.5f);
+    return __hfma2(tanh_h2(gate), half, half);
+}
+// two fp16 -> two e4m3 bytes (low element in the low byte), nearest even, saturating (an infinity becomes 448)
+__device__ __forceinline__ uint32_t e4m3x2_from_h2(__half2 v)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(bits_from_h2(v)));
+    return r;
+}
+__device__ __forceinline__ uint32_t e4m3x4_from_h2(__half2 lo, __half2 hi) { return e4m3x2_from_h2(lo) | (e4m3x2_from_h2(hi) << 16); }
+
 // scale of one 128-wide tile: sqrt(128 / sum of squares), 0 for an all-zero tile
 __device__ __forceinline__ float tile_scale(float sum2) { return sum2 == 0.f ? 0.f : 11.3137085f * rsqrtf(sum2); }
 

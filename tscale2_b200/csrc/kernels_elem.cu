@@ -438,9 +438,64 @@ __global__ void ffn_act_backward_kernel(const __half *__restrict__ drg, const __
     }
 }
 
+// The e4m3 pipeline's form of the kernel above in packed fp16 (see fast_types.cuh): same loads and stores, a third of
+// the instructions.  The sum over the tile is accumulated in fp32.
+__global__ void ffn_act_backward_e4m3_kernel(const __half *__restrict__ drg, const __half *__restrict__ wg, const __half *__restrict__ what,
+                                             int what_ld, const float *__restrict__ wscale, int T, int F, uint8_t *__restrict__ d2)
+{
+    const int tiles = F / TILE;
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
+    {
+        uint2 g[R], gate[R], wn[R];
+        float scale[R];
+        size_t t[R];
+        int off[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            const int tile = ok[r] ? (int)(item % tiles) : 0;
+            off[r] = tile * TILE + lane * 4;
+            const uint2 z = make_uint2(0u, 0u);
+            g[r] = ok[r] ? *(const uint2 *)(drg + t[r] * F + off[r]) : z;
+            gate[r] = ok[r] ? *(const uint2 *)(wg + t[r] * 2 * F + F + off[r]) : z;
+            wn[r] = ok[r] ? *(const uint2 *)(what + t[r] * what_ld + off[r]) : z;
+            scale[r] = ok[r] ? wscale[t[r] * tiles + tile] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const __half2 one = __float2half2_rn(1.f), two = __float2half2_rn(2.f);
+            const __half2 g0 = h2_from_bits(g[r].x), g1 = h2_from_bits(g[r].y), w0 = h2_from_bits(wn[r].x), w1 = h2_from_bits(wn[r].y);
+            const __half2 m0 = lolu_mult_h2(h2_from_bits(gate[r].x)), m1 = lolu_mult_h2(h2_from_bits(gate[r].y));
+            // d gate = g wn m (1 - m) 2: the bounded factors first, the gradient last
+            const __half2 dg0 = __hmul2(g0, __hmul2(w0, __hmul2(__hmul2(m0, two), __hsub2(one, m0))));
+            const __half2 dg1 = __hmul2(g1, __hmul2(w1, __hmul2(__hmul2(m1, two), __hsub2(one, m1))));
+            const __half2 dw0 = __hmul2(g0, m0), dw1 = __hmul2(g1, m1); // gradient of the normalized wide values
+            // tile-norm backward expressed with the normalized vector: scale * (d - wn * (wn . d) / 128)
+            const float2 p0 = __half22float2(__hmul2(w0, dw0)), p1 = __half22float2(__hmul2(w1, dw1));
+            const float proj = warp_sum((p0.x + p0.y) + (p1.x + p1.y)) * (1.f / 128);
+            const __half2 nproj = __float2half2_rn(-proj), sc = __float2half2_rn(scale[r]);
+            const __half2 dx0 = __hmul2(sc, __hfma2(w0, nproj, dw0)), dx1 = __hmul2(sc, __hfma2(w1, nproj, dw1));
+            *(uint32_t *)(d2 + t[r] * 2 * F + off[r]) = e4m3x4_from_h2(dx0, dx1);
+            *(uint32_t *)(d2 + t[r] * 2 * F + F + off[r]) = e4m3x4_from_h2(dg0, dg1);
+        }
+    }
+}
+
 int ffn_act_backward(const Ctx &c, const __half *drg, const __half *wg, const __half *what, int what_ld, const float *wscale, int T, int F,
                      void *d2)
 {
+    if (c.ft == 0) {
+        ffn_act_backward_e4m3_kernel<<<grid_for(c, ffn_act_backward_e4m3_kernel, (long long)T * (F / TILE)), THREADS, 0, c.stream>>>(
+            drg, wg, what, what_ld, wscale, T, F, (uint8_t *)d2);
+        TS2_CHECK_LAUNCH();
+        return TS2_OK;
+    }
     const int grid = c.ft == 0 ? grid_for(c, ffn_act_backward_kernel<0>, (long long)T * (F / TILE))
                                : grid_for(c, ffn_act_backward_kernel<1>, (long long)T * (F / TILE));
     if (c.ft == 0)
@@ -484,8 +539,47 @@ __global__ void att_gate_forward_kernel(const __half *__restrict__ qkvg, const _
     }
 }
 
+__global__ void att_gate_forward_e4m3_kernel(const __half *__restrict__ qkvg, const __half *__restrict__ o, int T, int Q, float s_act,
+                                             uint8_t *__restrict__ rg)
+{
+    const int tiles = Q / TILE;
+    constexpr int R = 4;
+    const __half2 sa = __float2half2_rn(s_act);
+    WARP_BATCH_LOOP((long long)T * tiles, R)
+    {
+        uint2 gate[R], ov[R];
+        size_t t[R];
+        int off[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            off[r] = (ok[r] ? (int)(item % tiles) : 0) * TILE + lane * 4;
+            const uint2 z = make_uint2(0u, 0u);
+            gate[r] = ok[r] ? *(const uint2 *)(qkvg + t[r] * 4 * Q + 3 * Q + off[r]) : z;
+            ov[r] = ok[r] ? *(const uint2 *)(o + t[r] * Q + off[r]) : z;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const __half2 r0 = __hmul2(__hmul2(lolu_mult_h2(h2_from_bits(gate[r].x)), h2_from_bits(ov[r].x)), sa);
+            const __half2 r1 = __hmul2(__hmul2(lolu_mult_h2(h2_from_bits(gate[r].y)), h2_from_bits(ov[r].y)), sa);
+            *(uint32_t *)(rg + t[r] * Q + off[r]) = e4m3x4_from_h2(r0, r1);
+        }
+    }
+}
+
 int att_gate_forward(const Ctx &c, const __half *qkvg, const __half *o, int T, int Q, void *rg)
 {
+    if (c.ft == 0) {
+        att_gate_forward_e4m3_kernel<<<grid_for(c, att_gate_forward_e4m3_kernel, (long long)T * (Q / TILE)), THREADS, 0, c.stream>>>(
+            qkvg, o, T, Q, c.s_act, (uint8_t *)rg);
+        TS2_CHECK_LAUNCH();
+        return TS2_OK;
+    }
     const int grid = c.ft == 0   ? grid_for(c, att_gate_forward_kernel<0>, (long long)T * (Q / TILE))
                      : c.ft == 1 ? grid_for(c, att_gate_forward_kernel<1>, (long long)T * (Q / TILE))
                                  : grid_for(c, att_gate_forward_kernel<2>, (long long)T * (Q / TILE));
@@ -540,9 +634,60 @@ __global__ void att_gate_backward_kernel(const __half *__restrict__ drg, const _
     }
 }
 
+__global__ void att_gate_backward_e4m3_kernel(const __half *__restrict__ drg, const __half *__restrict__ qkvg, const __half *__restrict__ o,
+                                              int T, int Q, uint8_t *__restrict__ d4, __half *__restrict__ dout, float *__restrict__ dscale)
+{
+    const int tiles = Q / TILE; // = heads
+    constexpr int R = 2;
+    WARP_BATCH_LOOP((long long)T * tiles, R)
+    {
+        uint2 g[R], gate[R], ov[R];
+        size_t t[R];
+        int h[R];
+        bool ok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned item = base + r * wstride;
+            ok[r] = item < total_items;
+            t[r] = ok[r] ? item / tiles : 0;
+            h[r] = ok[r] ? (int)(item % tiles) : 0;
+            const int off = h[r] * TILE + lane * 4;
+            const uint2 z = make_uint2(0u, 0u);
+            g[r] = ok[r] ? *(const uint2 *)(drg + t[r] * Q + off) : z;
+            gate[r] = ok[r] ? *(const uint2 *)(qkvg + t[r] * 4 * Q + 3 * Q + off) : z;
+            ov[r] = ok[r] ? *(const uint2 *)(o + t[r] * Q + off) : z;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (!ok[r])
+                continue;
+            const int off = h[r] * TILE + lane * 4;
+            const __half2 one = __float2half2_rn(1.f), two = __float2half2_rn(2.f);
+            const __half2 g0 = h2_from_bits(g[r].x), g1 = h2_from_bits(g[r].y), o0 = h2_from_bits(ov[r].x), o1 = h2_from_bits(ov[r].y);
+            const __half2 m0 = lolu_mult_h2(h2_from_bits(gate[r].x)), m1 = lolu_mult_h2(h2_from_bits(gate[r].y));
+            const __half2 dg0 = __hmul2(g0, __hmul2(o0, __hmul2(__hmul2(m0, two), __hsub2(one, m0))));
+            const __half2 dg1 = __hmul2(g1, __hmul2(o1, __hmul2(__hmul2(m1, two), __hsub2(one, m1))));
+            const __half2 do0 = __hmul2(g0, m0), do1 = __hmul2(g1, m1);
+            *(uint32_t *)(d4 + t[r] * 4 * Q + 3 * Q + off) = e4m3x4_from_h2(dg0, dg1);
+            *(uint2 *)(dout + t[r] * Q + off) = make_uint2(bits_from_h2(do0), bits_from_h2(do1));
+            // dscale from the fp16 values the attention kernels will read
+            const float2 a0 = __half22float2(do0), a1 = __half22float2(do1), b0 = __half22float2(o0), b1 = __half22float2(o1);
+            const float ds = warp_sum(fmaf(a0.x, b0.x, a0.y * b0.y) + fmaf(a1.x, b1.x, a1.y * b1.y));
+            if (lane == 0)
+                dscale[t[r] * tiles + h[r]] = ds;
+        }
+    }
+}
+
 int att_gate_backward(const Ctx &c, const __half *drg, const __half *qkvg, const __half *o, int T, int Q, void *d4, __half *dout,
                       float *dscale)
 {
+    if (c.ft == 0) {
+        att_gate_backward_e4m3_kernel<<<grid_for(c, att_gate_backward_e4m3_kernel, (long long)T * (Q / TILE)), THREADS, 0, c.stream>>>(
+            drg, qkvg, o, T, Q, (uint8_t *)d4, dout, dscale);
+        TS2_CHECK_LAUNCH();
+        return TS2_OK;
+    }
     const int grid = c.ft == 0 ? grid_for(c, att_gate_backward_kernel<0>, (long long)T * (Q / TILE))
                                : grid_for(c, att_gate_backward_kernel<1>, (long long)T * (Q / TILE));
     if (c.ft == 0)
