@@ -526,6 +526,8 @@ void MoeRecompute(const Dims &d, Matrix *mm, const Mat &prevState, MoeFwd &f)
 {
     int moeDim = d.expertCount * d.expertDim;
     f.normState = prim::NormalizeState(prevState, d.dim / kStateNormTile);
+    if (g_actQuant == 1)
+        QuantizeInPlace(&f.normState, kActScale);
     f.wide = prim::MulForward(f.normState, mm[0].data);
     f.wideNorm = prim::NormalizeState(f.wide, moeDim / 128);
     f.gate = prim::MulForward(f.normState, mm[1].dataNoScale);
@@ -540,6 +542,8 @@ void MoeRecompute(const Dims &d, Matrix *mm, const Mat &prevState, MoeFwd &f)
             for (int x = e * expertSize; x < (e + 1) * expertSize; ++x)
                 f.rg.row(t)[x] *= s;
         }
+    if (g_actQuant == 1) // the engine stores the gated activation with the routing weight folded in
+        QuantizeInPlace(&f.rg, kActScale);
 }
 
 void MoeForward(const Dims &d, Matrix *mm, const Mat &prevState, Mat *state)
@@ -557,11 +561,17 @@ void MoeBackward(const Dims &d, Matrix *mm, bool update, const Mat &prevState, M
     int moeDim = d.expertCount * d.expertDim;
     Mat dNormState(f.normState.rows, f.normState.cols);
     Mat drg(f.rg.rows, f.rg.cols);
+    Mat gFast = *grad;
+    const float gradMult = g_actQuant == 1 ? GradMult(*grad) : 1.f;
+    if (g_actQuant == 1)
+        QuantizeInPlace(&gFast, gradMult);
+    // engine units of the layer's intermediate gradients (see FfnBackward); the contract matrix is [dim][E * expertDim]
+    const float fscale = sqrtf((float)d.dim / (float)moeDim) * mm[2].sko / gradMult;
     { // ContractMatmulBackprop, layer_moe.cu:441-452
-        prim::MulBackwardWithAccum(&drg, FwdContract(mm[2].data, d.expertCount), *grad);
+        prim::MulBackwardWithAccum(&drg, FwdContract(mm[2].data, d.expertCount), gFast);
         if (update) {
             Mat delta;
-            prim::SumRankOne(f.rg, &delta, *grad);
+            prim::SumRankOne(f.rg, &delta, gFast);
             StoreDelta(mm[2], BwdContract(delta, d.expertCount));
         }
     }
@@ -580,10 +590,16 @@ void MoeBackward(const Dims &d, Matrix *mm, bool update, const Mat &prevState, M
             }
     }
     MoeSelectBackward(f.moe, d.expertCount, &dMoe);
+    if (g_actQuant == 1)
+        QuantizeInPlace(&dMoe, 1.f / fscale);
     MatmulBackprop(mm[3], true, f.normState, dMoe, update, &dNormState);
     Mat dgate, dwide;
     prim::BackpropLoLU(f.gate, f.wideNorm, drg, &dgate, &dwide);
     prim::NormalizeStateBackward(f.wide, moeDim / 128, dwide, &dwide);
+    if (g_actQuant == 1) {
+        QuantizeInPlace(&dwide, mm[0].sko / fscale);
+        QuantizeInPlace(&dgate, 1.f / fscale);
+    }
     MatmulBackprop(mm[0], false, f.normState, dwide, update, &dNormState);
     MatmulBackprop(mm[1], true, f.normState, dgate, update, &dNormState);
     Mat dState;

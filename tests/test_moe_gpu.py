@@ -46,29 +46,58 @@ def moe_spec(precision):
     return s.add_blocks(1, attention_type_id=0).add_blocks(1, attention_type_id=1, alibi_slope=0.25, moe=True)
 
 
-# e4m3: this model is tiny (120 nodes, dim 128), so the rounding noise of the format averages over few terms and
-# a router logit within that noise of a tie selects another expert; measured 6e-2 .. 1.1e-1, the router matrix 1.6e-1
-@pytest.mark.parametrize("precision,tol", [(capi.PREC_F16, 5e-3), (capi.PREC_FP8, 2.5e-1)])
-def test_moe_step_matches_oracle(oracle_port, precision, tol):
-    """The model of the golden fixture tiny_moe_e4m3: one ATT+FFN block, one ATT+MoE block (4 experts, 2 selected)."""
+def _moe_run(oracle_port, precision, engine_rounding=False):
     spec = moe_spec(precision)
     mats = host.init_weights(spec, 77, select_std=1.0)
     batch = host.synthetic_batch(spec, 3, 40, 78)
     quant = oracle.QUANT_E4M3 if precision == capi.PREC_FP8 else oracle.QUANT_HALF
-    ref = oracle_port.backprop(spec, mats, batch, quant, want_states=True)
+    ref = oracle_port.backprop(spec, mats, batch, quant, want_states=True, engine_rounding=engine_rounding)
+    return spec, mats, batch, ref
+
+
+def _moe_engine(spec, mats, batch):
     model = Model(spec, mats, batch.node_count)
     model.set_debug_taps(True)
     model.set_batch(batch)
     model.backprop(host.training_step(), apply=False)
     model.wait()
+    return model
+
+
+def test_moe_step_matches_oracle(oracle_port):
+    """The model of the golden fixture tiny_moe_e4m3: one ATT+FFN block, one ATT+MoE block (4 experts, 2 selected), fp16
+    operands: every tensor within 5e-3 of the oracle."""
+    spec, mats, batch, ref = _moe_run(oracle_port, capi.PREC_F16)
+    model = _moe_engine(spec, mats, batch)
     T, L = batch.node_count, len(spec.layers)
     report = [(f"state[{l}]", rel_l2(model.get_state_tap(l, False, T), ref["states"][l])) for l in range(L + 1)]
     report += [(f"state_grad[{l}]", rel_l2(model.get_state_tap(l, True, T), ref["state_grads"][l])) for l in range(L, -1, -1)]
     report += [(n, rel_l2(g, r)) for n, g, r in zip(spec.matrix_names(), model.get_gradients(), ref["grads"])]
     text = "\n".join(f"{n:24s} {e:.3e}" for n, e in report)
     print(text)
-    bad = [(n, e) for n, e in report if not e < tol]
+    bad = [(n, e) for n, e in report if not e < 5e-3]
     assert not bad, text
+
+
+def test_moe_fp8_step_is_as_close_to_fp32_as_the_format_allows(oracle_port):
+    """e4m3 operands on the same model.  The model is tiny (120 nodes, dim 128): the format's rounding noise averages
+    over few terms, and a router logit that the noise moves across a near-tie selects another expert for that node, a
+    discrete change.  So the bar is the format's own: the oracle with the engine's e4m3 rounding inserted (router
+    logits from the rounded normalized state, as in the engine) against the fp32 oracle gives the distance the format
+    causes per tensor, and the engine may be at most 1.5 x that + 1e-2 from the fp32 oracle; the expert choices of
+    engine and rounding oracle are compared through the router matrix gradient."""
+    spec, mats, batch, ref = _moe_run(oracle_port, capi.PREC_FP8)
+    fmt = _moe_run(oracle_port, capi.PREC_FP8, engine_rounding=True)[3]
+    model = _moe_engine(spec, mats, batch)
+    report, bad = [], []
+    for name, g, f, r in zip(spec.matrix_names(), model.get_gradients(), fmt["grads"], ref["grads"]):
+        e_engine, e_format = rel_l2(g, r), rel_l2(f, r)
+        report.append(f"{name:24s} engine-fp32 {e_engine:.3e}   format-fp32 {e_format:.3e}   engine-format {rel_l2(g, f):.3e}")
+        if not e_engine <= 1.5 * e_format + 1e-2:
+            bad.append(name)
+    text = "\n".join(report)
+    print(text)
+    assert not bad, f"further from fp32 than the format explains: {bad}\n{text}"
 
 
 def test_moe_step_applies_and_trains(oracle_port):
