@@ -10,9 +10,10 @@
 // With two S / dP pairs the issuer queues the products of tile j+1 before it waits for the compute warps of tile
 // j, so the tensor pipe works while they compute.  G goes where the thread's own S / dP values were (same lane,
 // own columns); at that time no MMA writes into that 128-column group (the next tile's products go to the other
-// pair, the accumulators are other groups), and the pair is overwritten only after acc_ready of the tile that
-// read it.  20 warps: TMA producer, MMA issuer, 2 idle, 16 compute (four per TMEM lane quarter, 16 of the tile's 64
-// columns each).  Every wait is bounded; a give-up raises the status word.
+// pair, the accumulators are other groups), and the pair is overwritten only after the MMAs that read it are complete
+// (pair_free).  20 warps: TMA producer, two MMA issuers (first products; accumulating products), 1 idle, 16 compute
+// (four per TMEM lane quarter, 16 of the tile's 64 columns each).  Every wait is bounded; a give-up raises the status
+// word.
 #include "att_tc.cuh"
 
 namespace ts2 {
@@ -53,10 +54,12 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
     }
     const uint32_t sK = smem_u32(smem), sV = sK + Q_BYTES, sStage = sK + KV_STAGE_OFF, sMeta = sK + KV_META_OFF;
     uint64_t *bars = (uint64_t *)(smem + KV_BAR_OFF);
-    // res_full, st_full[4], st_empty[4], s_full[2], g_full, acc_ready, all_done
+    // res_full, st_full[4], st_empty[4], s_full[2], pair_free[2], g_full[2], all_done.  Everything that is handed over
+    // once per tile has one barrier per S / dP pair: the next phase of a pair's barrier belongs to the tile two further
+    // on, which cannot start before the waiter of this phase has acted, so a parity test can never miss a phase.
     const uint32_t res_full = smem_u32(bars), st_full0 = smem_u32(bars + 1), st_empty0 = smem_u32(bars + 5), s_full0 = smem_u32(bars + 9),
-                   g_full = smem_u32(bars + 11), acc_ready = smem_u32(bars + 12), all_done = smem_u32(bars + 13);
-    uint32_t *tmem_slot = (uint32_t *)(bars + 14);
+                   pair_free0 = smem_u32(bars + 11), g_full0 = smem_u32(bars + 13), all_done = smem_u32(bars + 15);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 16);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     int *rng = (int *)(tmem_slot + 2);
 
@@ -84,8 +87,10 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
         }
         mbar_init(s_full0, 1);
         mbar_init(s_full0 + 8, 1);
-        mbar_init(g_full, 512);
-        mbar_init(acc_ready, 1);
+        mbar_init(g_full0, 512);
+        mbar_init(g_full0 + 8, 512);
+        mbar_init(pair_free0, 1);
+        mbar_init(pair_free0 + 8, 1);
         mbar_init(all_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -130,13 +135,24 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer --------------------------------
+        // ------------------------------ MMA issuer A: S^T and dP^T ----------------
+        // Two issuing threads on two schedulers.  A thread is held for about as long as the MMAs it issues run, and
+        // while the compute warps are busy its instructions wait for issue slots; with one thread for all four products
+        // of a tile the tensor pipe stood idle for more than half of every tile.  This one runs one tile ahead with the
+        // first products; issuer B (warp 2) follows the compute warps with the accumulating ones.
         if (lane == 0 && n > 0) {
             constexpr uint32_t idesc_s = umma_idesc_f16(TC_BN, false, false);
-            constexpr uint32_t idesc_acc = umma_idesc_f16(TC_HD, false, true);
             const uint64_t dK = umma_smem_desc(sK, 16, 1024), dV = umma_smem_desc(sV, 16, 1024);
-            auto first_products = [&](int jj) { // S^T and dP^T of tile jj into pair jj & 1
+            bool ok = mbar_wait(res_full, 0, abort_flag);
+            for (int jj = 0; jj < n && ok; ++jj) { // S^T and dP^T of tile jj into pair jj & 1
+                // the pair held G of tile jj - 2: the MMAs that read it must be complete before these write there.  A
+                // barrier per pair, so that its next phase cannot complete before this thread has issued tile jj
+                if (jj >= 2 && !mbar_wait(pair_free0 + 8 * (jj & 1), ((jj - 2) >> 1) & 1, abort_flag))
+                    break;
                 const int st = jj % KV_STAGES;
+                if (!mbar_wait(st_full0 + 8 * st, (jj / KV_STAGES) & 1, abort_flag))
+                    break;
+                tc_fence_after();
                 const uint32_t bq = sStage + st * KV_STAGE_BYTES, bd = bq + KV_BYTES;
                 const uint64_t dQ = umma_smem_desc(bq, 16, 1024), dD = umma_smem_desc(bd, 16, 1024);
                 const uint32_t tS = tmem_base + ((jj & 1) ? 384 : 0), tDP = tS + TC_BN;
@@ -146,30 +162,21 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
                 umma_f16_x4(tDP, dV, dD, idesc_s, 0u, 2u, 2u);
                 umma_f16_x4(tDP, dV + (Q_BYTES / 2 >> 4), dD + (KV_BYTES / 2 >> 4), idesc_s, 1u, 2u, 2u);
                 tc_commit(s_full0 + 8 * (jj & 1));
-            };
-            bool ok = mbar_wait(res_full, 0, abort_flag) && mbar_wait(st_full0, 0, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                first_products(0);
             }
-            for (int j = 0; j < n && ok; ++j) {
-                if (j + 1 < n) {
-                    // pair (j + 1) & 1 held G of tile j - 1: the MMAs that read it must be complete before the next
-                    // products write there (they were issued a whole compute phase ago)
-                    if (j > 0 && !mbar_wait(acc_ready, (j - 1) & 1, abort_flag))
-                        break;
-                    if (!mbar_wait(st_full0 + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, abort_flag))
-                        break;
-                    tc_fence_after();
-                    first_products(j + 1);
-                }
-                if (!mbar_wait(g_full, j & 1, abort_flag))
+        }
+    } else if (warp == 2) {
+        // ------------------------------ MMA issuer B: dV and dK -------------------
+        if (lane == 0 && n > 0) {
+            constexpr uint32_t idesc_acc = umma_idesc_f16(TC_HD, false, true);
+            for (int j = 0; j < n; ++j) {
+                const int st = j % KV_STAGES;
+                if (!mbar_wait(g_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag) ||
+                    !mbar_wait(st_full0 + 8 * st, (j / KV_STAGES) & 1, abort_flag))
                     break;
                 tc_fence_after();
                 // dV += Gv . dO, dK += Gk . Q: 4 steps of 16 nodes; G from tensor memory (part kk of the compute warps
                 // left its 16 nodes as 8 columns of fp16 pairs at column 16 kk of the S / dP block), the streamed
                 // tile read MN-major (its 128 columns are the output columns), 16 rows = 2048 bytes per step
-                const int st = j % KV_STAGES;
                 const uint32_t bq = sStage + st * KV_STAGE_BYTES, bd = bq + KV_BYTES;
                 const uint64_t dQm = umma_smem_desc(bq, KV_BYTES / 2, 1024), dDm = umma_smem_desc(bd, KV_BYTES / 2, 1024);
                 const uint32_t tS = tmem_base + ((j & 1) ? 384 : 0), tDP = tS + TC_BN;
@@ -179,11 +186,10 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     umma_f16_ts(tDK, tDP + 16 * kk, dQm + (uint64_t)(kk * 128), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(acc_ready);
+                tc_commit(pair_free0 + 8 * (j & 1));
                 tc_commit(st_empty0 + 8 * st);
                 if (j == n - 1)
-                    tc_commit(all_done); // a barrier of its own for the epilogue: the compute warps do not follow
-                                         // acc_ready tile by tile, so its parity would be ambiguous for them
+                    tc_commit(all_done); // a barrier of its own for the epilogue
             }
         }
     } else if (warp >= 4) {
@@ -236,14 +242,9 @@ __global__ void __launch_bounds__(KV_THREADS, 1)
             tmem_st8(tDP, gk);
             tmem_st_wait();
             tc_fence_before();
-            // g_full counts 512 arrivals per tile; with two S / dP pairs a warp may be done with tile j before a slower
-            // one has arrived for tile j - 1: it arrives only when that phase is complete (which it cannot be
-            // without this thread's own earlier arrival, so the parity test is unambiguous)
-            if (j > 0)
-                ok = __all_sync(0xffffffffu, mbar_wait(g_full, (j - 1) & 1, abort_flag));
-            if (!ok)
-                break;
-            mbar_arrive(g_full);
+            // 512 arrivals per tile on the pair's barrier.  No thread can arrive for tile j + 2 (same barrier) before this
+            // phase is complete: S of tile j + 2 is written only after the MMAs that read this tile's G have finished.
+            mbar_arrive(g_full0 + 8 * (j & 1));
         }
         // epilogue: both accumulators -> fp32 outputs.  A warp's 32 rows x 32 columns go through a 4 KB block of the
         // (now idle) stage area, rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7)),

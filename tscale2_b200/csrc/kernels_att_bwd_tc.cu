@@ -165,6 +165,12 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
             const uint64_t dA1 = umma_smem_desc(sA1 + b * Q_BYTES, 16, 1024), dA2 = umma_smem_desc(sA2 + b * Q_BYTES, 16, 1024);
             const uint32_t s_full = s_full0 + 8 * b, g_full = g_full0 + 8 * b, acc_ready = acc_ready0 + 8 * b;
             bool ok = mbar_wait(res_full, 0, abort_flag);
+            // The two blocks run the same cycle (first products, compute, accumulating product); started together they stay
+            // in step, the tensor pipe idle while both compute and the compute warps idle while both multiply.  Block 1
+            // therefore starts when block 0's first products are done (block 0 then computes), after which the shared
+            // tensor pipe keeps the two out of phase.
+            if (ok && b == 1 && any0)
+                ok = mbar_wait(s_full0, 0, abort_flag);
             int k = 0; // tiles of this block so far
             for (int j = 0; j < n && ok; ++j) {
                 const int st = j % STAGES, tile = u0 + j;
