@@ -178,6 +178,8 @@ int ts2_get_params(ts2_model *m, int what, ts2_matrix_view *mats_out, int n_mats
 int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_mats);
 /* RowDisp / SumWeight of a matrix (TModelMatrix, src/gpt/model_params/model_matrix.h:61-70) */
 int ts2_get_row_disp(ts2_model *m, int index, float *row_disp, int64_t n, float *sum_weight);
+/* the other direction, for resuming from a model file (TModelMatrix::SetRowDisp, model_matrix.h:85-89) */
+int ts2_set_row_disp(ts2_model *m, int index, const float *row_disp, int64_t n, float sum_weight);
 /* quantized weights as the contractions see them: bytes (e4m3) or halves,
  * [y][x], and the per-matrix scale sko (src/gpt/matrix/agpu_cuda.cuh:63-101) */
 int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, float *matrix_scale);

@@ -29,7 +29,7 @@ def build(reference="/root/reference"):
     """Compile the restatement, and the reference-linked variant where the reference tree exists."""
     subprocess.check_call(["make", "-s", "-C", _HERE])
     if os.path.isdir(os.path.join(reference, "src")):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REFERENCE={reference}"])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "ckpt", f"REFERENCE={reference}"])
 
 
 _fp = C.POINTER(C.c_float)

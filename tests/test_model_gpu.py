@@ -211,3 +211,28 @@ def test_many_waves_step_is_finite_and_agrees_between_precisions():
     a, b = np.array(errs[capi.PREC_FP8]), np.array(errs[capi.PREC_F16])
     assert np.isfinite(a).all() and np.isfinite(b).all(), (a, b)
     assert np.abs(a - b).max() < 0.05, (a, b)
+
+
+def test_training_resumes_from_a_model_file(tmp_path):
+    """Three applied steps, save in the reference's file format, load into a new engine: two more steps on both must
+    give the same weights (bit-identical except the embedding, whose gradient is summed with float atomics)."""
+    spec = c1_spec(capi.PREC_FP8)
+    mats = host.init_weights(spec, 21)
+    batches = [host.synthetic_batch(spec, 4, 128, 30 + i) for i in range(5)]
+    a = Model(spec, mats, batches[0].node_count)
+    for i in range(3):
+        a.set_batch(batches[i])
+        a.backprop(host.training_step(rate=0.01, iteration=i), apply=True)
+    path = tmp_path / "model.bin"
+    a.save(str(path))
+    b = Model.from_file(str(path), batches[0].node_count, precision=capi.PREC_FP8)
+    for model in (a, b):
+        for i in range(3, 5):
+            model.set_batch(batches[i])
+            model.backprop(host.training_step(rate=0.01, iteration=i), apply=True)
+    for name, wa, wb in zip(spec.matrix_names(), a.get_weights(), b.get_weights()):
+        if name == "embed":
+            assert np.abs(wa - wb).max() <= 1e-6 * np.abs(wa).max(), name
+        else:
+            assert np.array_equal(wa, wb), name
+    assert abs(a.avg_train_err() - b.avg_train_err()) < 1e-5

@@ -98,6 +98,7 @@ def _declare(lib):
         "ts2_get_params": (i32, [vp, i32, P(MatrixView), i32]),
         "ts2_set_params": (i32, [vp, i32, P(MatrixView), i32]),
         "ts2_get_row_disp": (i32, [vp, i32, P(f32), i64, P(f32)]),
+        "ts2_set_row_disp": (i32, [vp, i32, P(f32), i64, f32]),
         "ts2_get_fast_weights": (i32, [vp, i32, vp, i64, P(f32)]),
         "ts2_set_debug_taps": (i32, [vp, i32]),
         "ts2_debug_read": (i32, [vp, C.c_char_p, i32, vp, i64]),

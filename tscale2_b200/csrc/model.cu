@@ -1592,6 +1592,20 @@ int ts2_get_row_disp(ts2_model *m, int index, float *row_disp, int64_t n, float 
     return TS2_OK;
 }
 
+int ts2_set_row_disp(ts2_model *m, int index, const float *row_disp, int64_t n, float sum_weight)
+{
+    if (!m || index < 0 || index >= (int)m->mats.size() || !row_disp)
+        return fail(TS2_ERR_INVALID_ARG, "bad arguments to ts2_set_row_disp");
+    Matrix &mt = m->mats[index];
+    if (n != mt.row_disp_size)
+        return fail(TS2_ERR_INVALID_ARG, "matrix %d has %d dispersion entries, caller passed %lld", index, mt.row_disp_size, (long long)n);
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    TS2_CUDA(cudaMemcpy(mt.row_disp, row_disp, (size_t)n * 4, cudaMemcpyHostToDevice));
+    TS2_CUDA(cudaMemcpy(mt.sum_weight, &sum_weight, 4, cudaMemcpyHostToDevice));
+    return TS2_OK;
+}
+
 int ts2_get_fast_weights(ts2_model *m, int index, void *dst, int64_t dst_bytes, float *matrix_scale)
 {
     if (!m || index < 0 || index >= (int)m->mats.size() || !dst)

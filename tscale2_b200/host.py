@@ -35,11 +35,12 @@ class ModelSpec:
     precision: int = capi.PREC_FP8
     q_dim: int = 128
     tt_dim: int = 128
+    labels: int = 0  # embedding rows; 0: vocab + 1
 
     @property
     def label_count(self) -> int:
         # GetLabelCount with MPF_DISABLE_NOISE_LABELS: InputTokenCount + 1 (sliding_window.cpp:47-68)
-        return self.vocab + 1
+        return self.labels or self.vocab + 1
 
     def add_blocks(self, n_blocks: int, attention_type_id=0, alibi_slope=0.0, moe=False):
         for _ in range(n_blocks):

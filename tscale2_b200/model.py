@@ -86,6 +86,31 @@ class Model:
     def set_weights(self, mats):
         self._check(self.lib.ts2_set_params(self.h, capi.PARAM_WEIGHTS, host.matrix_views(mats), len(mats)))
 
+    def set_momentum(self, mats):
+        self._check(self.lib.ts2_set_params(self.h, capi.PARAM_MOMENTUM, host.matrix_views(mats), len(mats)))
+
+    def set_row_disp(self, index, row_disp, sum_weight):
+        rd = np.ascontiguousarray(row_disp, np.float32)
+        self._check(self.lib.ts2_set_row_disp(self.h, index, rd.ctypes.data_as(C.POINTER(C.c_float)), rd.size, float(sum_weight)))
+
+    @classmethod
+    def from_file(cls, path, max_nodes, device=0, precision=capi.PREC_FP8):
+        """IModel::SetParams from a model file in the reference's format (tscale2_b200/checkpoint.py): weights,
+        momentum and the dispersion state of every matrix, so that training resumes where the file was written."""
+        from . import checkpoint
+        mf = checkpoint.load(path)
+        mf.spec.precision = precision
+        model = cls(mf.spec, [np.ascontiguousarray(m.weights) for m in mf.matrices], max_nodes, device=device, bias=mf.bias)
+        model.set_momentum([np.ascontiguousarray(m.momentum) for m in mf.matrices])
+        for i, m in enumerate(mf.matrices):
+            model.set_row_disp(i, m.row_disp, m.sum_weight)
+        return model
+
+    def save(self, path, bias=None, **kw):
+        """IModel::GetParams into a model file the reference's tools can load."""
+        from . import checkpoint
+        checkpoint.save(path, checkpoint.from_model(self, bias=bias, **kw))
+
     def get_row_disp(self, index):
         n = self.shapes[index][0] if index < 2 else 1
         rd = np.empty(n, np.float32)
