@@ -154,6 +154,24 @@ const char *ts2_last_error(const ts2_model *m); /* m may be NULL: last create er
 /* IModelInstance::GetNodes + Init(INIT_BACKPROP), src/gpt/compute/model.h:32-35;
  * TSinlgeComputeContext::Init, src/gpt/compute/gpu_transformer.cu:526-566 */
 int ts2_set_batch(ts2_model *m, const ts2_batch_nodes *nodes);
+/* What the reference derives from a batch on the host before a step (span tables of TNodesBatch / GroupAttention,
+ * src/gpt/att/att.h:125-211; TLabelInverseIndex::BuildInverseIndex, src/gpt/compute/gpu_embedding.cuh:38-75) is
+ * derived on the device here: ts2_set_batch copies the arrays as they are and checks only counts and capacities.
+ * Every element is validated on the device; a malformed element (label or target out of range, a node with more than
+ * one span or target, a span outside the batch, a label_ptr / span_ptr that is not a CSR offset array) is replaced by a
+ * harmless one and reported by the next ts2_wait (or any other call that waits) as TS2_ERR_INVALID_ARG /
+ * TS2_ERR_UNSUPPORTED with the first offending element in ts2_last_error; the step that used the batch is then
+ * meaningless but has touched nothing outside its buffers.
+ *
+ * The derived tables of the current batch, for tests (each pointer may be NULL; node_count ints each):
+ * span_start / span_finish: the node's span or (0, -1); rev_first / rev_last: per key the range of nodes that may
+ * attend to it, (node_count, -1) if none - a superset, kernels test each node's own span; target: id or -1. */
+int ts2_get_batch_tables(ts2_model *m, int attention_type, int32_t *span_start, int32_t *span_finish, int32_t *rev_first,
+                         int32_t *rev_last, int32_t *target);
+/* The inverse label index of the current batch: all (label, node) entries sorted by label, the nodes of one label in
+ * the order of label_arr (= node order); bit 31 of a node entry is TS2_LABEL_NEGATIVE of that occurrence.  The
+ * embedding gradient sums a label's nodes in this order, so it does not depend on the schedule. */
+int ts2_get_label_index(ts2_model *m, uint32_t *labels, uint32_t *nodes, int64_t capacity, int64_t *count);
 
 /* IModel::Backprop, src/gpt/compute/model.h:53 — asynchronous: enqueues the
  * forward pass, the backward pass and (TS2_GRADIENT_APPLY) the gradient
@@ -390,6 +408,11 @@ int ts2_op_att_gate_backward(int device, void *stream, int prec, const void *drg
  * state = bits(x[t][h]) * 0x398bf183 + bits(x[t][0]) * 0x1affc3df + t * 0x9023a049, state = state * 0x448e3079 +
  * 0xc484ef10, u = state * 2^-32.  Bit-exact with that definition. */
 int ts2_op_rowquant_i8(int device, void *stream, const float *x, int T, int D, int8_t *q, float *row_scale);
+/* Per key the range of nodes whose span may hold it, computed on the device as ts2_set_batch does (prefix maximum
+ * of the span ends, suffix minimum of the span starts, two binary searches per key).  Host arrays of T ints; nodes
+ * without a span have finish < start.  Any spans are allowed, monotone or not. */
+int ts2_op_attention_reverse_ranges(int device, void *stream, const int32_t *span_start, const int32_t *span_finish, int T,
+                                    int32_t *rev_first, int32_t *rev_last);
 
 /* Expert selection of a mixture-of-experts layer (CpuMoe, src/gpt/compute/layer_moe.cu:287-328;
  * MoeCalcSampleExpertLists, src/gpt/compute/moe_kernels.cu:54-104): the `selected` largest logits per

@@ -97,6 +97,8 @@ def _declare(lib):
         "ts2_avg_train_err": (i32, [vp, P(f32)]),
         "ts2_get_params": (i32, [vp, i32, P(MatrixView), i32]),
         "ts2_set_params": (i32, [vp, i32, P(MatrixView), i32]),
+        "ts2_get_batch_tables": (i32, [vp, i32, vp, vp, vp, vp, vp]),
+        "ts2_get_label_index": (i32, [vp, vp, vp, i64, P(i64)]),
         "ts2_get_row_disp": (i32, [vp, i32, P(f32), i64, P(f32)]),
         "ts2_set_row_disp": (i32, [vp, i32, P(f32), i64, f32]),
         "ts2_get_fast_weights": (i32, [vp, i32, vp, i64, P(f32)]),
@@ -143,6 +145,7 @@ def _declare(lib):
         "ts2_op_ffn_act_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp]),
         "ts2_op_att_gate_backward": (i32, [i32, vp, i32, vp, vp, vp, i32, i32, vp, vp, vp]),
         "ts2_op_rowquant_i8": (i32, [i32, vp, vp, i32, i32, vp, vp]),
+        "ts2_op_attention_reverse_ranges": (i32, [i32, vp, vp, vp, i32, vp, vp]),
         "ts2_attention_forward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp]),
         "ts2_attention_backward": (i32, [i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "ts2_gemm_dw": (i32, [i32, vp, i32, i32, i64, i64, i64, vp, vp, vp, f32, vp, C.c_size_t]),

@@ -7,44 +7,6 @@
 namespace ts2 {
 const char *global_error();
 
-void attention_reverse_ranges(const int *span_start, const int *span_finish, int T, int *rev_first, int *rev_last)
-{
-    for (int to = 0; to < T; ++to) {
-        rev_first[to] = T;
-        rev_last[to] = -1;
-    }
-    bool monotone = true;
-    int ps = 0, pf = -1;
-    for (int t = 0; t < T; ++t) {
-        if (span_finish[t] < span_start[t])
-            continue;
-        if (span_start[t] < ps || span_finish[t] < pf)
-            monotone = false;
-        ps = span_start[t];
-        pf = span_finish[t];
-    }
-    if (monotone) {
-        // starts and finishes never decrease over the nodes that have a span: the nodes attending to a
-        // key are contiguous up to span-less nodes in between
-        int lo = 0, hi = 0;
-        for (int to = 0; to < T; ++to) {
-            while (lo < T && span_finish[lo] < to)
-                ++lo; // first node whose span reaches `to` (span-less nodes have finish -1)
-            if (hi < lo)
-                hi = lo;
-            while (hi < T && (span_finish[hi] < span_start[hi] || span_start[hi] <= to))
-                ++hi; // one past the last node whose span starts at or before `to`
-            rev_first[to] = lo;
-            rev_last[to] = hi - 1;
-        }
-    } else {
-        for (int t = 0; t < T; ++t)
-            for (int to = span_start[t]; to <= span_finish[t]; ++to) {
-                rev_first[to] = std::min(rev_first[to], t);
-                rev_last[to] = std::max(rev_last[to], t);
-            }
-    }
-}
 }
 using namespace ts2;
 
@@ -389,16 +351,17 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
     if (T <= 0 || head_count <= 0 || !q || !k || !v || !dout || !lse || !dscale || !span_start || !span_finish || !dq || !dk || !dv)
         return fail(TS2_ERR_INVALID_ARG, "ts2_attention_backward: bad arguments");
     TS2_CUDA(cudaSetDevice(device));
-    std::vector<int> rev(2 * (size_t)T);
-    attention_reverse_ranges(span_start, span_finish, T, rev.data(), rev.data() + T);
-    int *d = nullptr;
-    TS2_CUDA(cudaMalloc(&d, (size_t)T * 16));
+    int *d = nullptr; // start | finish | rev_first | rev_last | scan scratch (2T)
+    TS2_CUDA(cudaMalloc(&d, (size_t)T * 24));
     TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
     TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
-    TS2_CUDA(cudaMemcpy(d + 2 * (size_t)T, rev.data(), (size_t)T * 8, cudaMemcpyHostToDevice));
     Ctx c;
     c.device = device;
     c.stream = (cudaStream_t)stream;
+    if (int rc0 = batch_reverse_ranges(c, d, d + T, T, d + 4 * (size_t)T, d + 2 * (size_t)T, d + 3 * (size_t)T)) {
+        cudaFree(d);
+        return rc0;
+    }
     const __half *Q = (const __half *)q, *K = (const __half *)k, *V = (const __half *)v, *DO = (const __half *)dout;
     float *fq = (float *)dq, *fk = (float *)dk, *fv = (float *)dv;
     int rc = variant == 2 || variant == 3
@@ -409,6 +372,30 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
                           : attention_backward_rowwise(c, Q, K, V, DO, lse, dscale, d, d + T, d + 2 * T, d + 3 * T, T, head_count,
                                                        alibi_slope, fq, fk, fv);
     cudaStreamSynchronize(c.stream);
+    cudaFree(d);
+    return rc;
+}
+
+int ts2_op_attention_reverse_ranges(int device, void *stream, const int32_t *span_start, const int32_t *span_finish, int T,
+                                    int32_t *rev_first, int32_t *rev_last)
+{
+    if (T <= 0 || !span_start || !span_finish || !rev_first || !rev_last)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_op_attention_reverse_ranges: bad arguments");
+    TS2_CUDA(cudaSetDevice(device));
+    int *d = nullptr;
+    TS2_CUDA(cudaMalloc(&d, (size_t)T * 24));
+    TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
+    TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
+    Ctx c;
+    c.device = device;
+    c.stream = (cudaStream_t)stream;
+    int rc = batch_reverse_ranges(c, d, d + T, T, d + 4 * (size_t)T, d + 2 * (size_t)T, d + 3 * (size_t)T);
+    if (rc == TS2_OK && cudaStreamSynchronize(c.stream) != cudaSuccess)
+        rc = fail(TS2_ERR_CUDA, "ts2_op_attention_reverse_ranges: the stream failed");
+    if (rc == TS2_OK) {
+        cudaMemcpy(rev_first, d + 2 * (size_t)T, (size_t)T * 4, cudaMemcpyDeviceToHost);
+        cudaMemcpy(rev_last, d + 3 * (size_t)T, (size_t)T * 4, cudaMemcpyDeviceToHost);
+    }
     cudaFree(d);
     return rc;
 }

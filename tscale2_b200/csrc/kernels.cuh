@@ -20,8 +20,45 @@ struct Ctx {
 // state0[t] = sum over the node's labels of +-E[label] * (sko/32)   (ComputeEmbedding, cpu_transformer.cpp:66-90)
 int embed_forward(const Ctx &c, const __half *embed, const float *sko, const uint32_t *label_arr, const uint32_t *label_ptr, int T,
                   int D, float *state);
-// dE[label] += +-g[t]   (embedding delta, cpu_transformer.cpp:176-196)
-int embed_backward(const Ctx &c, const float *g, const uint32_t *label_arr, const uint32_t *label_ptr, int T, int D, float *dE);
+
+// ---- kernels_batch.cu: batch preparation on the device -------------------------------
+// codes of the batch status record {code, where, detail, detail}; 0 = the batch was well formed
+enum {
+    BATCH_OK = 0,
+    BATCH_BAD_SPAN_PTR = 1,  // where = node
+    BATCH_MULTI_SPAN = 2,    // where = node, detail = spans
+    BATCH_BAD_SPAN = 3,      // where = node, details = start, finish
+    BATCH_BAD_TARGET = 4,    // where = target entry, details = node, id
+    BATCH_DUP_TARGET = 5,    // where = node
+    BATCH_BAD_LABEL_PTR = 6, // where = node
+    BATCH_BAD_LABEL = 7,     // where = entry of label_arr, details = label, node
+};
+// per-node span tables from the CSR form (at most one span per node), and per key the range [rev_first, rev_last] of
+// nodes that may attend to it ((T, -1) = none; a superset, the kernels test each node's own span).  scan_tmp: 2T ints.
+int batch_span_tables(const Ctx &c, const int *span_ptr, const int *csr_start, const int *csr_finish, int T, int n_spans, int *start,
+                      int *finish, int *scan_tmp, int *rev_first, int *rev_last, int *status);
+int batch_reverse_ranges(const Ctx &c, const int *start, const int *finish, int T, int *scan_tmp, int *rev_first, int *rev_last);
+// target[t] = id of the node's target or -1
+int batch_targets(const Ctx &c, const int *node, const int *id, int n, int T, int V, int *target, int *status);
+// inverse label index (TLabelInverseIndex, gpu_embedding.cuh:10-76): the entries (label, node | sign bit) of the batch
+// sorted by label, nodes of one label in node order
+struct LabelIndex {
+    uint32_t *key[2] = {nullptr, nullptr}, *val[2] = {nullptr, nullptr}; // capacity label_cap each
+    uint32_t *hist = nullptr;                                            // label_index_hist_elems(label_cap)
+    float *partial = nullptr;                                            // label_index_partial_elems(label_cap, D)
+    uint32_t n = 0;
+    int sorted = 0; // which of key[] / val[] holds the sorted entries
+};
+size_t label_index_hist_elems(size_t label_cap);
+size_t label_index_partial_elems(size_t label_cap, int D);
+// validates label_arr / label_ptr in place (bad labels become label 0, label_ptr is clamped to n_labels) and writes the
+// unsorted entries of ix; label_index_sort orders them (a stable radix sort, 8 bits per pass)
+int label_index_entries(const Ctx &c, uint32_t *label_arr, uint32_t *label_ptr, int T, uint32_t n_labels, uint32_t label_count,
+                        LabelIndex &ix, int *status);
+int label_index_sort(const Ctx &c, uint32_t label_count, LabelIndex &ix);
+// dE[label] += sum over the label's nodes, in node order, of +-g[node]   (embedding delta, cpu_transformer.cpp:176-196;
+// BackpropEmbeddings over the inverse index, gpu_embedding.cuh).  One writer per row: no atomics, a fixed order.
+int embed_backward_indexed(const Ctx &c, const float *g, const LabelIndex &ix, int D, float *dE);
 
 // n = tilenorm(x) quantized (NormalizeState with 128-wide tiles, cpu_util.cpp:72-99); n16 optional fp16 copy
 int tilenorm_forward(const Ctx &c, const float *x, int T, int D, void *n_fast, __half *n16);
@@ -105,7 +142,6 @@ int attention_backward_rowwise(const Ctx &c, const __half *q, const __half *k, c
                                const float *dscale, const int *span_start, const int *span_finish, const int *rev_first,
                                const int *rev_last, int T, int H, float slope, float *dq, float *dk, float *dv);
 // host: for every key the range [first, last] of nodes whose span may contain it (a superset; kernels re-check)
-void attention_reverse_ranges(const int *span_start, const int *span_finish, int T, int *rev_first, int *rev_last);
 
 // ---- kernels_moe.cu ----------------------------------------------------------------
 // CpuMoe (layer_moe.cu:287-328): ids[T][k] and weights[T][k] from router logits [T][ld]

@@ -75,30 +75,6 @@ int embed_forward(const Ctx &c, const __half *embed, const float *sko, const uin
     return TS2_OK;
 }
 
-__global__ void embed_backward_kernel(const float *__restrict__ g, const uint32_t *__restrict__ label_arr,
-                                      const uint32_t *__restrict__ label_ptr, int T, int D, float *__restrict__ dE)
-{
-    const int tiles = D / TILE;
-    WARP_ITEM_LOOP((long long)T * tiles)
-    {
-        const int t = (int)(item / tiles), off = (int)(item % tiles) * TILE + lane * 4;
-        const float4 gv = *(const float4 *)(g + (size_t)t * D + off);
-        for (uint32_t k = label_ptr[t]; k < label_ptr[t + 1]; ++k) {
-            uint32_t label = label_arr[k];
-            float w = (label & TS2_LABEL_NEGATIVE) ? -1.f : 1.f;
-            label &= TS2_LABEL_MASK;
-            atomicAdd((float4 *)(dE + (size_t)label * D + off), make_float4(gv.x * w, gv.y * w, gv.z * w, gv.w * w));
-        }
-    }
-}
-
-int embed_backward(const Ctx &c, const float *g, const uint32_t *label_arr, const uint32_t *label_ptr, int T, int D, float *dE)
-{
-    embed_backward_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(g, label_arr, label_ptr, T, D, dE);
-    TS2_CHECK_LAUNCH();
-    return TS2_OK;
-}
-
 // ---------------------------------------------------------------------------------
 template <int FT>
 __global__ void tilenorm_forward_kernel(const float *__restrict__ x, int T, int D, float s_act, void *__restrict__ n_fast,

@@ -79,11 +79,24 @@ struct Bucket {
 };
 
 struct BatchDev {
+    // one host-to-device copy per batch brings the raw CSR arrays into `raw`; label_arr / label_ptr point into it,
+    // everything else is derived on the device (kernels_batch.cu)
+    uint32_t *raw = nullptr;
+    size_t raw_cap = 0; // elements, also the size of one pinned staging slot
     uint32_t *label_arr = nullptr, *label_ptr = nullptr;
+    uint32_t n_labels = 0;
     int *target = nullptr;
     std::vector<int *> span_start, span_finish, rev_first, rev_last;
+    int *scan_tmp = nullptr; // 2 x max_nodes
+    int *status = nullptr;   // {code, where, detail, detail}: the first malformed element seen since it was last reported
+    LabelIndex ix;
+    bool ix_sorted = false;
     size_t label_cap = 0;
     int node_count = 0, target_count = 0;
+    // two pinned staging slots: the next batch is written while the copy of the previous one may still be queued
+    cudaEvent_t slot_ev[2] = {nullptr, nullptr};
+    bool slot_used[2] = {false, false};
+    int next_slot = 0;
 };
 
 } // namespace ts2
@@ -155,6 +168,7 @@ struct ts2_model {
     BatchDev batch;
     void *pinned = nullptr;
     size_t pinned_bytes = 0;
+    int *h_batch_status = nullptr; // pinned copy of batch.status, refreshed by every ts2_set_batch
     bool grads_dirty = false; // the flat gradient holds an accumulated, not yet applied gradient
     bool reduce_in_backward = false; // this backward pass is followed by apply(): all-reduce every layer's gradient as soon as it is complete
     int gemm_tag = 0; // class of the contractions being queued (timing statistics)
@@ -718,10 +732,13 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     // batch
     BatchDev &b = m->batch;
     b.label_cap = (size_t)T * 4;
-    M_TRY(dalloc(m, &b.label_arr, b.label_cap));
-    M_TRY(dalloc(m, &b.label_ptr, (size_t)T + 1));
     M_TRY(dalloc(m, &b.target, (size_t)T));
     const int na = std::max(1, d.attention_type_count);
+    // labels, label_ptr, per attention type span_ptr + starts + finishes, target nodes + ids; each rounded up to 16 bytes
+    b.raw_cap = b.label_cap + ((size_t)T + 4) + (size_t)na * 3 * ((size_t)T + 4) + 2 * ((size_t)T + 4);
+    M_TRY(dalloc(m, &b.raw, b.raw_cap));
+    b.label_arr = b.raw;
+    b.label_ptr = b.raw;
     b.span_start.resize(na);
     b.span_finish.resize(na);
     b.rev_first.resize(na);
@@ -732,8 +749,21 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         M_TRY(dalloc(m, &b.rev_first[a], (size_t)T));
         M_TRY(dalloc(m, &b.rev_last[a], (size_t)T));
     }
-    m->pinned_bytes = (b.label_cap + (size_t)T + 1 + (size_t)T + (size_t)na * 4 * T) * 4;
+    M_TRY(dalloc(m, &b.scan_tmp, 2 * (size_t)T));
+    M_TRY(dalloc(m, &b.status, 4));
+    TS2_CUDA(cudaMemsetAsync(b.status, 0, 16, m->stream));
+    for (int i = 0; i < 2; ++i) {
+        M_TRY(dalloc(m, &b.ix.key[i], b.label_cap));
+        M_TRY(dalloc(m, &b.ix.val[i], b.label_cap));
+    }
+    M_TRY(dalloc(m, &b.ix.hist, label_index_hist_elems(b.label_cap)));
+    M_TRY(dalloc(m, &b.ix.partial, label_index_partial_elems(b.label_cap, D)));
+    m->pinned_bytes = 2 * b.raw_cap * 4 + 16;
     TS2_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes));
+    m->h_batch_status = (int *)((uint32_t *)m->pinned + 2 * b.raw_cap);
+    memset(m->h_batch_status, 0, 16);
+    for (int i = 0; i < 2; ++i)
+        TS2_CUDA(cudaEventCreateWithFlags(&b.slot_ev[i], cudaEventDisableTiming));
 
     // split-K scratch: the largest request of any dW contraction of this model
     size_t ws = 0;
@@ -1154,7 +1184,11 @@ int backward(ts2_model *m)
         M_TRY(tap_gradient(m, l));
     }
     if (!(m->descr.flags & TS2_MPF_DISABLE_TUNE_EMBED))
-        M_TRY(embed_backward(c, m->g, b.label_arr, b.label_ptr, T, D, m->mats[0].grad));
+        if (!m->batch.ix_sorted) {
+            M_TRY(label_index_sort(c, (uint32_t)m->descr.label_count, m->batch.ix));
+            m->batch.ix_sorted = true;
+        }
+        M_TRY(embed_backward_indexed(c, m->g, b.ix, D, m->mats[0].grad));
     M_TRY(reduce_matrices(m, 0, 1));
     return TS2_OK;
 }
@@ -1228,7 +1262,8 @@ int sync_master(ts2_model *m)
     return TS2_OK;
 }
 
-// host side of ts2_set_batch: per-node arrays from the CSR inputs
+// ts2_set_batch: the raw CSR arrays of the batch go to the device in one copy; the per-node tables are derived and
+// every element is validated there (kernels_batch.cu).  The host checks only what it can without a loop over the batch.
 int stage_batch(ts2_model *m, const ts2_batch_nodes *nd)
 {
     const int T = nd->node_count;
@@ -1237,77 +1272,98 @@ int stage_batch(ts2_model *m, const ts2_batch_nodes *nd)
     if (!nd->label_ptr || (nd->label_ptr[T] && !nd->label_arr))
         return fail(TS2_ERR_INVALID_ARG, "null label arrays");
     const size_t n_labels = nd->label_ptr[T];
-    if (n_labels > m->batch.label_cap)
-        return fail(TS2_ERR_TOO_LARGE, "%zu labels exceed the capacity %zu", n_labels, m->batch.label_cap);
-    if (nd->attention_type_count < m->descr.attention_type_count)
-        return fail(TS2_ERR_INVALID_ARG, "batch has %d attention types, the model needs %d", nd->attention_type_count,
-                    m->descr.attention_type_count);
-    for (size_t i = 0; i < n_labels; ++i)
-        if ((nd->label_arr[i] & TS2_LABEL_MASK) >= (uint32_t)m->descr.label_count)
-            return fail(TS2_ERR_INVALID_ARG, "label %u out of range", nd->label_arr[i] & TS2_LABEL_MASK);
-    uint32_t *p = (uint32_t *)m->pinned;
-    uint32_t *h_label_arr = p;
-    p += m->batch.label_cap;
-    uint32_t *h_label_ptr = p;
-    p += (size_t)m->max_nodes + 1;
-    int *h_target = (int *)p;
-    p += m->max_nodes;
-    memcpy(h_label_arr, nd->label_arr, n_labels * 4);
-    memcpy(h_label_ptr, nd->label_ptr, ((size_t)T + 1) * 4);
-    for (int t = 0; t < T; ++t)
-        h_target[t] = -1;
-    for (int i = 0; i < nd->target_count; ++i) {
-        const int node = nd->target_node[i], id = nd->target_id[i];
-        if (node < 0 || node >= T || id < 0 || id >= m->V)
-            return fail(TS2_ERR_INVALID_ARG, "target %d: node %d / id %d out of range", i, node, id);
-        if (h_target[node] >= 0)
-            return fail(TS2_ERR_UNSUPPORTED, "node %d has more than one target", node);
-        h_target[node] = id;
-    }
+    BatchDev &b = m->batch;
+    if (n_labels > b.label_cap)
+        return fail(TS2_ERR_TOO_LARGE, "%zu labels exceed the capacity %zu", n_labels, b.label_cap);
     const int na = m->descr.attention_type_count;
-    std::vector<int *> h_start(na), h_finish(na), h_first(na), h_last(na);
+    if (nd->attention_type_count < na)
+        return fail(TS2_ERR_INVALID_ARG, "batch has %d attention types, the model needs %d", nd->attention_type_count, na);
+    const int n_targets = nd->target_count;
+    if (n_targets < 0 || (n_targets && (!nd->target_node || !nd->target_id)))
+        return fail(TS2_ERR_INVALID_ARG, "bad target arrays");
+    if (n_targets > T)
+        return fail(TS2_ERR_UNSUPPORTED, "%d targets for %d nodes: at most one target per node is supported", n_targets, T);
     for (int a = 0; a < na; ++a) {
-        h_start[a] = (int *)p;
-        p += m->max_nodes;
-        h_finish[a] = (int *)p;
-        p += m->max_nodes;
-        h_first[a] = (int *)p;
-        p += m->max_nodes;
-        h_last[a] = (int *)p;
-        p += m->max_nodes;
         const ts2_attention_info &ai = nd->att[a];
         if (!ai.span_ptr)
             return fail(TS2_ERR_INVALID_ARG, "attention type %d: null span_ptr", a);
-        for (int t = 0; t < T; ++t) {
-            const int n = ai.span_ptr[t + 1] - ai.span_ptr[t];
-            if (n > 1)
-                return fail(TS2_ERR_UNSUPPORTED, "node %d has %d attention spans; at most one is supported", t, n);
-            int s = 0, f = -1;
-            if (n == 1) {
-                s = ai.span_start[ai.span_ptr[t]];
-                f = ai.span_finish[ai.span_ptr[t]];
-                if (s < 0 || f >= T || f < s)
-                    return fail(TS2_ERR_INVALID_ARG, "node %d: span [%d, %d] out of range", t, s, f);
-            }
-            h_start[a][t] = s;
-            h_finish[a][t] = f;
-        }
-        attention_reverse_ranges(h_start[a], h_finish[a], T, h_first[a], h_last[a]);
+        const int n_spans = ai.span_ptr[T];
+        if (n_spans < 0 || (n_spans && (!ai.span_start || !ai.span_finish)))
+            return fail(TS2_ERR_INVALID_ARG, "attention type %d: bad span arrays", a);
+        if (n_spans > T)
+            return fail(TS2_ERR_UNSUPPORTED, "attention type %d: %d spans for %d nodes; at most one span per node is supported", a,
+                        n_spans, T);
     }
-    BatchDev &b = m->batch;
-    cudaStream_t s = m->stream;
-    TS2_CUDA(cudaMemcpyAsync(b.label_arr, h_label_arr, std::max<size_t>(n_labels, 1) * 4, cudaMemcpyHostToDevice, s));
-    TS2_CUDA(cudaMemcpyAsync(b.label_ptr, h_label_ptr, ((size_t)T + 1) * 4, cudaMemcpyHostToDevice, s));
-    TS2_CUDA(cudaMemcpyAsync(b.target, h_target, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    const int slot = b.next_slot;
+    b.next_slot ^= 1;
+    if (b.slot_used[slot])
+        TS2_CUDA(cudaEventSynchronize(b.slot_ev[slot])); // the copy that last read this slot
+    uint32_t *h = (uint32_t *)m->pinned + (size_t)slot * b.raw_cap;
+    size_t used = 0;
+    auto put = [&](const void *src, size_t n) {
+        const size_t at = used;
+        if (n)
+            memcpy(h + at, src, n * 4);
+        used += (n + 3) & ~(size_t)3;
+        return at;
+    };
+    const size_t o_labels = put(nd->label_arr, n_labels), o_label_ptr = put(nd->label_ptr, (size_t)T + 1);
+    std::vector<size_t> o_ptr(na), o_start(na), o_finish(na);
+    std::vector<int> n_spans(na);
     for (int a = 0; a < na; ++a) {
-        TS2_CUDA(cudaMemcpyAsync(b.span_start[a], h_start[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
-        TS2_CUDA(cudaMemcpyAsync(b.span_finish[a], h_finish[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
-        TS2_CUDA(cudaMemcpyAsync(b.rev_first[a], h_first[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
-        TS2_CUDA(cudaMemcpyAsync(b.rev_last[a], h_last[a], (size_t)T * 4, cudaMemcpyHostToDevice, s));
+        const ts2_attention_info &ai = nd->att[a];
+        n_spans[a] = ai.span_ptr[T];
+        o_ptr[a] = put(ai.span_ptr, (size_t)T + 1);
+        o_start[a] = put(ai.span_start, n_spans[a]);
+        o_finish[a] = put(ai.span_finish, n_spans[a]);
     }
+    const size_t o_tnode = put(nd->target_node, n_targets), o_tid = put(nd->target_id, n_targets);
+    cudaStream_t s = m->stream;
+    TS2_CUDA(cudaMemcpyAsync(b.raw, h, used * 4, cudaMemcpyHostToDevice, s));
+    TS2_CUDA(cudaEventRecord(b.slot_ev[slot], s));
+    b.slot_used[slot] = true;
+    Ctx c = ctx_of(m);
+    b.label_arr = b.raw + o_labels;
+    b.label_ptr = b.raw + o_label_ptr;
+    b.n_labels = (uint32_t)n_labels;
+    b.ix_sorted = false;
+    M_TRY(label_index_entries(c, b.label_arr, b.label_ptr, T, b.n_labels, (uint32_t)m->descr.label_count, b.ix, b.status));
+    for (int a = 0; a < na; ++a)
+        M_TRY(batch_span_tables(c, (const int *)b.raw + o_ptr[a], (const int *)b.raw + o_start[a], (const int *)b.raw + o_finish[a], T,
+                                n_spans[a], b.span_start[a], b.span_finish[a], b.scan_tmp, b.rev_first[a], b.rev_last[a], b.status));
+    M_TRY(batch_targets(c, (const int *)b.raw + o_tnode, (const int *)b.raw + o_tid, n_targets, T, m->V, b.target, b.status));
+    TS2_CUDA(cudaMemcpyAsync(m->h_batch_status, b.status, 16, cudaMemcpyDeviceToHost, s));
     b.node_count = T;
-    b.target_count = nd->target_count;
+    b.target_count = n_targets;
     return TS2_OK;
+}
+
+// what the device found wrong with a batch, if anything; clears the record
+int report_batch_status(ts2_model *m)
+{
+    int *h = m->h_batch_status;
+    if (!h || h[0] == BATCH_OK)
+        return TS2_OK;
+    const int code = h[0], where = h[1], d0 = h[2], d1 = h[3];
+    h[0] = BATCH_OK;
+    cudaMemsetAsync(m->batch.status, 0, 16, m->stream);
+    switch (code) {
+    case BATCH_BAD_SPAN_PTR:
+        return fail(TS2_ERR_INVALID_ARG, "batch: span_ptr of node %d is malformed (offset %d, count %d)", where, d0, d1);
+    case BATCH_MULTI_SPAN:
+        return fail(TS2_ERR_UNSUPPORTED, "batch: node %d has %d attention spans; at most one is supported", where, d0);
+    case BATCH_BAD_SPAN:
+        return fail(TS2_ERR_INVALID_ARG, "batch: node %d: span [%d, %d] out of range", where, d0, d1);
+    case BATCH_BAD_TARGET:
+        return fail(TS2_ERR_INVALID_ARG, "batch: target %d: node %d / id %d out of range", where, d0, d1);
+    case BATCH_DUP_TARGET:
+        return fail(TS2_ERR_UNSUPPORTED, "batch: node %d has more than one target", where);
+    case BATCH_BAD_LABEL_PTR:
+        return fail(TS2_ERR_INVALID_ARG, "batch: label_ptr of node %d is malformed (%d, %d)", where, d0, d1);
+    case BATCH_BAD_LABEL:
+        return fail(TS2_ERR_INVALID_ARG, "batch: label %d (entry %d, node %d) out of range", d0, where, d1);
+    }
+    return fail(TS2_ERR_INVALID_ARG, "batch: malformed (code %d)", code);
 }
 
 int wait_stream(ts2_model *m)
@@ -1323,7 +1379,8 @@ int wait_stream(ts2_model *m)
     }
     if (e != cudaSuccess)
         return fail(TS2_ERR_CUDA, "stream failed: %s", cudaGetErrorString(e));
-    return collect_device_status(m->device);
+    M_TRY(collect_device_status(m->device));
+    return report_batch_status(m);
 }
 
 } // namespace
@@ -1572,6 +1629,52 @@ int ts2_set_params(ts2_model *m, int what, const ts2_matrix_view *mats, int n_ma
     if (what == TS2_PARAM_WEIGHTS) {
         M_TRY(requantize_all(m));
         M_TRY(wait_stream(m));
+    }
+    return TS2_OK;
+}
+
+int ts2_get_batch_tables(ts2_model *m, int attention_type, int32_t *span_start, int32_t *span_finish, int32_t *rev_first,
+                         int32_t *rev_last, int32_t *target)
+{
+    if (!m)
+        return TS2_ERR_INVALID_ARG;
+    const BatchDev &b = m->batch;
+    if (b.node_count <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "no batch was set");
+    if (attention_type < 0 || attention_type >= (int)b.span_start.size())
+        return fail(TS2_ERR_INVALID_ARG, "attention type %d out of range", attention_type);
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    const size_t bytes = (size_t)b.node_count * 4;
+    const int a = attention_type;
+    const std::pair<int32_t *, const int *> out[] = {{span_start, b.span_start[a]}, {span_finish, b.span_finish[a]},
+                                                     {rev_first, b.rev_first[a]},   {rev_last, b.rev_last[a]},
+                                                     {target, b.target}};
+    for (const auto &o : out)
+        if (o.first)
+            TS2_CUDA(cudaMemcpy(o.first, o.second, bytes, cudaMemcpyDeviceToHost));
+    return TS2_OK;
+}
+
+int ts2_get_label_index(ts2_model *m, uint32_t *labels, uint32_t *nodes, int64_t capacity, int64_t *count)
+{
+    if (!m || !count)
+        return TS2_ERR_INVALID_ARG;
+    BatchDev &b = m->batch;
+    if (b.node_count <= 0)
+        return fail(TS2_ERR_INVALID_ARG, "no batch was set");
+    *count = b.n_labels;
+    if ((int64_t)b.n_labels > capacity || (b.n_labels && (!labels || !nodes)))
+        return fail(TS2_ERR_TOO_LARGE, "%u entries, capacity %lld", b.n_labels, (long long)capacity);
+    TS2_CUDA(cudaSetDevice(m->device));
+    if (!b.ix_sorted) {
+        M_TRY(label_index_sort(ctx_of(m), (uint32_t)m->descr.label_count, b.ix));
+        b.ix_sorted = true;
+    }
+    M_TRY(wait_stream(m));
+    if (b.n_labels) {
+        TS2_CUDA(cudaMemcpy(labels, b.ix.key[b.ix.sorted], (size_t)b.n_labels * 4, cudaMemcpyDeviceToHost));
+        TS2_CUDA(cudaMemcpy(nodes, b.ix.val[b.ix.sorted], (size_t)b.n_labels * 4, cudaMemcpyDeviceToHost));
     }
     return TS2_OK;
 }

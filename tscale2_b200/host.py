@@ -155,6 +155,20 @@ class Batch:
             self.att.append((start[has].astype(np.int32), finish[has].astype(np.int32), ptr))
         self._build_c()
 
+    @classmethod
+    def from_arrays(cls, node_count, label_arr, label_ptr, target_node, target_id, att) -> "Batch":
+        """A batch from its raw arrays as TBatchNodes holds them (src/gpt/att/nodes_batch.h): any number of labels per
+        node (bit 31 = negative), att = [(span_start, span_finish, span_ptr)] per attention type."""
+        b = object.__new__(cls)
+        b.node_count = int(node_count)
+        b.label_arr = np.ascontiguousarray(label_arr, np.uint32)
+        b.label_ptr = np.ascontiguousarray(label_ptr, np.uint32)
+        b.target_node = np.ascontiguousarray(target_node, np.int32)
+        b.target_id = np.ascontiguousarray(target_id, np.int32)
+        b.att = [tuple(np.ascontiguousarray(x, np.int32) for x in a) for a in att]
+        b._build_c()
+        return b
+
     def _build_c(self):
         ip = C.POINTER(C.c_int32)
         up = C.POINTER(C.c_uint32)

@@ -45,6 +45,7 @@ class Model:
     # IModelInstance::GetNodes + Init
     def set_batch(self, batch: host.Batch):
         self._check(self.lib.ts2_set_batch(self.h, C.byref(batch.c)))
+        self._node_count, self._label_count = batch.node_count, len(batch.label_arr)
 
     # IModel::Backprop
     def backprop(self, step: capi.TrainingStep, apply: bool = True):
@@ -110,6 +111,24 @@ class Model:
         """IModel::GetParams into a model file the reference's tools can load."""
         from . import checkpoint
         checkpoint.save(path, checkpoint.from_model(self, bias=bias, **kw))
+
+    def batch_tables(self, attention_type=0):
+        """The per-node tables the device derived from the current batch: dict of int32 arrays span_start,
+        span_finish, rev_first, rev_last, target."""
+        T = self._node_count
+        out = {k: np.empty(T, np.int32) for k in ("span_start", "span_finish", "rev_first", "rev_last", "target")}
+        self._check(self.lib.ts2_get_batch_tables(self.h, attention_type, *[out[k].ctypes.data for k in
+                                                  ("span_start", "span_finish", "rev_first", "rev_last", "target")]))
+        return out
+
+    def label_index(self):
+        """(labels, nodes, negative) of the inverse label index of the current batch, sorted by label."""
+        cap = max(1, self._label_count)
+        labels, nodes = np.empty(cap, np.uint32), np.empty(cap, np.uint32)
+        n = C.c_int64()
+        self._check(self.lib.ts2_get_label_index(self.h, labels.ctypes.data, nodes.ctypes.data, cap, C.byref(n)))
+        labels, nodes = labels[:n.value], nodes[:n.value]
+        return labels, nodes & np.uint32(0x7fffffff), (nodes >> np.uint32(31)).astype(bool)
 
     def get_row_disp(self, index):
         n = self.shapes[index][0] if index < 2 else 1
