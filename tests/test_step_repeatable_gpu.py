@@ -1,7 +1,7 @@
 """The training step at the size of the headline benchmark (65536 nodes per step) must be repeatable and stay
 finite: from one state, repeated steps give the same checksum for every intermediate buffer and bit-identical
-weight gradients (the embedding gradient is summed with float atomics and is compared to 1e-6), and a run of
-applied steps ends with every loss finite and no non-finite state gradient at any layer boundary.
+weight gradients (the embedding gradient included: it is summed in a fixed order over the inverse label index), and a
+run of applied steps ends with every loss finite and no non-finite state gradient at any layer boundary.
 
 Background: an earlier version wrote the attention gradients as fp16 without saturation; after ~30 applied steps of
 the 12-block model the gradient of a sequence's first key (attended to by every later node) passed 65504, became an
@@ -49,10 +49,7 @@ def test_step_is_repeatable_at_bench_size():
         differing = [a[0] for a, b in zip(ref_trace, trace) if a[:2] != b[:2]]
         assert not differing, f"repeat {rep}: buffers differ between identical steps: {differing[:8]}"
         for name, a, b in zip(spec.matrix_names(), ref_grads, grads):
-            if name == "embed":
-                assert np.abs(a - b).max() <= 1e-6 * max(np.abs(a).max(), 1e-30), name
-            else:
-                assert np.array_equal(a, b), name
+            assert np.array_equal(a, b), name
     model.close()
 
 
