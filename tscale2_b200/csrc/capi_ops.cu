@@ -352,7 +352,7 @@ int ts2_attention_backward(int device, void *stream, int variant, const void *q,
         return fail(TS2_ERR_INVALID_ARG, "ts2_attention_backward: bad arguments");
     TS2_CUDA(cudaSetDevice(device));
     int *d = nullptr; // start | finish | rev_first | rev_last | scan scratch (2T)
-    TS2_CUDA(cudaMalloc(&d, (size_t)T * 24));
+    TS2_CUDA(cudaMalloc(&d, (4 * (size_t)T + batch_scan_tmp_elems(T)) * 4));
     TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
     TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
     Ctx c;
@@ -383,7 +383,7 @@ int ts2_op_attention_reverse_ranges(int device, void *stream, const int32_t *spa
         return fail(TS2_ERR_INVALID_ARG, "ts2_op_attention_reverse_ranges: bad arguments");
     TS2_CUDA(cudaSetDevice(device));
     int *d = nullptr;
-    TS2_CUDA(cudaMalloc(&d, (size_t)T * 24));
+    TS2_CUDA(cudaMalloc(&d, (4 * (size_t)T + batch_scan_tmp_elems(T)) * 4));
     TS2_CUDA(cudaMemcpy(d, span_start, (size_t)T * 4, cudaMemcpyHostToDevice));
     TS2_CUDA(cudaMemcpy(d + T, span_finish, (size_t)T * 4, cudaMemcpyHostToDevice));
     Ctx c;

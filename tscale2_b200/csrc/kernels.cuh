@@ -34,7 +34,9 @@ enum {
     BATCH_BAD_LABEL = 7,     // where = entry of label_arr, details = label, node
 };
 // per-node span tables from the CSR form (at most one span per node), and per key the range [rev_first, rev_last] of
-// nodes that may attend to it ((T, -1) = none; a superset, the kernels test each node's own span).  scan_tmp: 2T ints.
+// nodes that may attend to it ((T, -1) = none; a superset, the kernels test each node's own span).
+// scan_tmp: batch_scan_tmp_elems(T) ints.
+size_t batch_scan_tmp_elems(int T);
 int batch_span_tables(const Ctx &c, const int *span_ptr, const int *csr_start, const int *csr_finish, int T, int n_spans, int *start,
                       int *finish, int *scan_tmp, int *rev_first, int *rev_last, int *status);
 int batch_reverse_ranges(const Ctx &c, const int *start, const int *finish, int T, int *scan_tmp, int *rev_first, int *rev_last);

@@ -56,45 +56,89 @@ __global__ void span_expand_kernel(const int *__restrict__ span_ptr, const int *
     finish[t] = f;
 }
 
-// run_max[t] = max of finish[0..t], suf_min[t] = min of start[t..T) over the nodes that have a span (T where none has).
-// One block: each thread scans a contiguous piece, the pieces are combined through shared memory.
-__global__ void __launch_bounds__(1024) span_scan_kernel(const int *__restrict__ start, const int *__restrict__ finish, int T,
-                                                         int *__restrict__ run_max, int *__restrict__ suf_min)
+// run_max[t] = max of finish[0..t], suf_min[t] = min of start[t..T) over the nodes that have a span (-1 / T where none
+// has).  Two launches over blocks of 1024 nodes: the blocks' own maxima and minima first, then each block scans its
+// nodes starting from what the blocks before (after) it hold.
+__global__ void __launch_bounds__(1024) span_block_reduce_kernel(const int *__restrict__ start, const int *__restrict__ finish, int T,
+                                                                 int *__restrict__ blk_max, int *__restrict__ blk_min)
 {
-    __shared__ int s_max[1024], s_min[1024];
-    const int tid = threadIdx.x, piece = (T + 1023) / 1024;
-    const int t0 = min(T, tid * piece), t1 = min(T, t0 + piece);
+    __shared__ int s_max[32], s_min[32];
+    const int t = blockIdx.x * 1024 + threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int mx = -1, mn = T;
-    for (int t = t0; t < t1; ++t) {
+    if (t < T) {
         const int s = start[t], f = finish[t];
         if (f >= s) {
-            mx = max(mx, f);
-            mn = min(mn, s);
+            mx = f;
+            mn = s;
         }
     }
-    s_max[tid] = mx;
-    s_min[tid] = mn;
+    for (int d = 16; d; d >>= 1) {
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+        mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, d));
+    }
+    if (lane == 0) {
+        s_max[warp] = mx;
+        s_min[warp] = mn;
+    }
     __syncthreads();
-    // inclusive prefix maximum / suffix minimum over the 1024 pieces
-    for (int d = 1; d < 1024; d <<= 1) {
-        const int a = tid >= d ? s_max[tid - d] : -1;
-        const int b = tid + d < 1024 ? s_min[tid + d] : T;
-        __syncthreads();
-        s_max[tid] = max(s_max[tid], a);
-        s_min[tid] = min(s_min[tid], b);
-        __syncthreads();
+    if (warp == 0) {
+        mx = s_max[lane];
+        mn = s_min[lane];
+        for (int d = 16; d; d >>= 1) {
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+            mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, d));
+        }
+        if (lane == 0) {
+            blk_max[blockIdx.x] = mx;
+            blk_min[blockIdx.x] = mn;
+        }
     }
-    mx = tid ? s_max[tid - 1] : -1;
-    for (int t = t0; t < t1; ++t) {
-        if (finish[t] >= start[t])
-            mx = max(mx, finish[t]);
-        run_max[t] = mx;
+}
+
+__global__ void __launch_bounds__(1024) span_scan_kernel(const int *__restrict__ start, const int *__restrict__ finish, int T,
+                                                         const int *__restrict__ blk_max, const int *__restrict__ blk_min,
+                                                         int *__restrict__ run_max, int *__restrict__ suf_min)
+{
+    __shared__ int s_max[32], s_min[32];
+    const int t = blockIdx.x * 1024 + threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int mx = -1, mn = T;
+    if (t < T) {
+        const int s = start[t], f = finish[t];
+        if (f >= s) {
+            mx = f;
+            mn = s;
+        }
     }
-    mn = tid < 1023 ? s_min[tid + 1] : T;
-    for (int t = t1 - 1; t >= t0; --t) {
-        if (finish[t] >= start[t])
-            mn = min(mn, start[t]);
-        suf_min[t] = mn;
+    // inside the warp: inclusive prefix maximum, inclusive suffix minimum
+    for (int d = 1; d < 32; d <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, mx, d), b = __shfl_down_sync(0xffffffffu, mn, d);
+        if (lane >= d)
+            mx = max(mx, a);
+        if (lane + d < 32)
+            mn = min(mn, b);
+    }
+    if (lane == 31)
+        s_max[warp] = mx;
+    if (lane == 0)
+        s_min[warp] = mn;
+    __syncthreads();
+    // what the earlier warps and blocks hold (the later ones for the minimum)
+    int before = -1, after = T;
+    for (int w = 0; w < warp; ++w)
+        before = max(before, s_max[w]);
+    for (int w = warp + 1; w < 32; ++w)
+        after = min(after, s_min[w]);
+    for (int bb = lane; bb < (int)blockIdx.x; bb += 32)
+        before = max(before, blk_max[bb]);
+    for (int bb = blockIdx.x + 1 + lane; bb < (int)gridDim.x; bb += 32)
+        after = min(after, blk_min[bb]);
+    for (int d = 16; d; d >>= 1) {
+        before = max(before, __shfl_xor_sync(0xffffffffu, before, d));
+        after = min(after, __shfl_xor_sync(0xffffffffu, after, d));
+    }
+    if (t < T) {
+        run_max[t] = max(mx, before);
+        suf_min[t] = min(mn, after);
     }
 }
 
@@ -219,30 +263,53 @@ __global__ void __launch_bounds__(BP_THREADS) radix_pass_kernel(const uint32_t *
     }
 }
 
-// exclusive scan of `total` counters in place, one block
-__global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *__restrict__ x, uint32_t total)
+// exclusive scan of `total` counters in place, blocks of 1024: the blocks' sums first, then each block scans its
+// counters on top of the sums of the blocks before it
+__global__ void __launch_bounds__(1024) scan_block_sums_kernel(const uint32_t *__restrict__ x, uint32_t total, uint32_t *__restrict__ blk_sum)
 {
-    __shared__ uint32_t s[1024];
-    const int tid = threadIdx.x;
-    const uint32_t piece = (total + 1023) / 1024;
-    const uint32_t i0 = min(total, tid * piece), i1 = min(total, i0 + piece);
-    uint32_t sum = 0;
-    for (uint32_t i = i0; i < i1; ++i)
-        sum += x[i];
-    s[tid] = sum;
+    __shared__ uint32_t s_sum[32];
+    const uint32_t i = blockIdx.x * 1024 + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t v = i < total ? x[i] : 0;
+    for (int d = 16; d; d >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, d);
+    if (lane == 0)
+        s_sum[warp] = v;
     __syncthreads();
-    for (int d = 1; d < 1024; d <<= 1) {
-        const uint32_t a = tid >= d ? s[tid - d] : 0;
-        __syncthreads();
-        s[tid] += a;
-        __syncthreads();
+    if (warp == 0) {
+        v = s_sum[lane];
+        for (int d = 16; d; d >>= 1)
+            v += __shfl_xor_sync(0xffffffffu, v, d);
+        if (lane == 0)
+            blk_sum[blockIdx.x] = v;
     }
-    uint32_t run = tid ? s[tid - 1] : 0;
-    for (uint32_t i = i0; i < i1; ++i) {
-        const uint32_t v = x[i];
-        x[i] = run;
-        run += v;
+}
+
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t *__restrict__ x, uint32_t total, const uint32_t *__restrict__ blk_sum)
+{
+    __shared__ uint32_t s_sum[32];
+    const uint32_t i = blockIdx.x * 1024 + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t own = i < total ? x[i] : 0;
+    uint32_t v = own;
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d)
+            v += a;
     }
+    if (lane == 31)
+        s_sum[warp] = v;
+    __syncthreads();
+    uint32_t before = 0;
+    for (int w = 0; w < warp; ++w)
+        before += s_sum[w];
+    uint32_t carry = 0;
+    for (uint32_t bb = lane; bb < blockIdx.x; bb += 32)
+        carry += blk_sum[bb];
+    for (int d = 16; d; d >>= 1)
+        carry += __shfl_xor_sync(0xffffffffu, carry, d);
+    if (i < total)
+        x[i] = carry + before + v - own;
 }
 
 // ---- embedding gradient through the inverse index ----------------------------------------
@@ -378,7 +445,11 @@ int batch_span_tables(const Ctx &c, const int *span_ptr, const int *csr_start, c
 
 int batch_reverse_ranges(const Ctx &c, const int *start, const int *finish, int T, int *scan_tmp, int *rev_first, int *rev_last)
 {
-    span_scan_kernel<<<1, 1024, 0, c.stream>>>(start, finish, T, scan_tmp, scan_tmp + T);
+    const int nb = (T + 1023) / 1024;
+    int *blk = scan_tmp + 2 * (size_t)T;
+    span_block_reduce_kernel<<<nb, 1024, 0, c.stream>>>(start, finish, T, blk, blk + nb);
+    TS2_CHECK_LAUNCH();
+    span_scan_kernel<<<nb, 1024, 0, c.stream>>>(start, finish, T, blk, blk + nb, scan_tmp, scan_tmp + T);
     TS2_CHECK_LAUNCH();
     span_reverse_kernel<<<blocks_for(T), BP_THREADS, 0, c.stream>>>(scan_tmp, scan_tmp + T, T, rev_first, rev_last);
     TS2_CHECK_LAUNCH();
@@ -395,9 +466,15 @@ int batch_targets(const Ctx &c, const int *node, const int *id, int n, int T, in
     return TS2_OK;
 }
 
+size_t batch_scan_tmp_elems(int T)
+{
+    return 2 * (size_t)T + 2 * (((size_t)T + 1023) / 1024);
+}
+
 size_t label_index_hist_elems(size_t label_cap)
 {
-    return 256 * ((label_cap + BP_THREADS - 1) / BP_THREADS);
+    const size_t counters = 256 * ((label_cap + BP_THREADS - 1) / BP_THREADS);
+    return counters + (counters + 1023) / 1024; // and the block sums of their scan
 }
 
 size_t label_index_partial_elems(size_t label_cap, int D)
@@ -437,7 +514,10 @@ int label_index_sort(const Ctx &c, uint32_t label_count, LabelIndex &ix)
         radix_pass_kernel<true><<<nblocks, BP_THREADS, 0, c.stream>>>(ix.key[cur], ix.val[cur], ix.n, shift, ix.hist, nblocks, nullptr,
                                                                      nullptr);
         TS2_CHECK_LAUNCH();
-        exclusive_scan_kernel<<<1, 1024, 0, c.stream>>>(ix.hist, 256 * nblocks);
+        const uint32_t total = 256 * nblocks, nb = (total + 1023) / 1024;
+        scan_block_sums_kernel<<<nb, 1024, 0, c.stream>>>(ix.hist, total, ix.hist + total);
+        TS2_CHECK_LAUNCH();
+        exclusive_scan_kernel<<<nb, 1024, 0, c.stream>>>(ix.hist, total, ix.hist + total);
         TS2_CHECK_LAUNCH();
         radix_pass_kernel<false><<<nblocks, BP_THREADS, 0, c.stream>>>(ix.key[cur], ix.val[cur], ix.n, shift, ix.hist, nblocks, ix.key[out],
                                                                       ix.val[out]);

@@ -87,7 +87,7 @@ struct BatchDev {
     uint32_t n_labels = 0;
     int *target = nullptr;
     std::vector<int *> span_start, span_finish, rev_first, rev_last;
-    int *scan_tmp = nullptr; // 2 x max_nodes
+    int *scan_tmp = nullptr; // batch_scan_tmp_elems(max_nodes)
     int *status = nullptr;   // {code, where, detail, detail}: the first malformed element seen since it was last reported
     LabelIndex ix;
     bool ix_sorted = false;
@@ -749,7 +749,7 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         M_TRY(dalloc(m, &b.rev_first[a], (size_t)T));
         M_TRY(dalloc(m, &b.rev_last[a], (size_t)T));
     }
-    M_TRY(dalloc(m, &b.scan_tmp, 2 * (size_t)T));
+    M_TRY(dalloc(m, &b.scan_tmp, batch_scan_tmp_elems(T)));
     M_TRY(dalloc(m, &b.status, 4));
     TS2_CUDA(cudaMemsetAsync(b.status, 0, 16, m->stream));
     for (int i = 0; i < 2; ++i) {
