@@ -30,8 +30,8 @@ WORKLOADS = {
     "c3_dense12_d768": dict(dim=768, heads=12, ffn_tiles=24, vocab=50304, blocks=12, seq=1024, seqs=64),
     # BASELINE.json configs[0], for quick checks
     "c1_dense2_d256": dict(dim=256, heads=4, ffn_tiles=8, vocab=4096, blocks=2, seq=128, seqs=4),
-    # BASELINE.json configs[3]: 12 attention + mixture-of-experts blocks, 32 experts of width 1024, 2 selected;
-    # every rank holds all experts (no expert-parallel exchange)
+    # BASELINE.json configs[3]: 12 attention + mixture-of-experts blocks, 32 experts of width 1024, 2 selected; on more
+    # than one GPU the experts are divided over the ranks (--expert-parallel 0: every rank computes all experts)
     "c4_moe12_d1024": dict(dim=1024, heads=16, ffn_tiles=8, vocab=50304, blocks=12, seq=1024, seqs=32, experts=32, selected=2,
                            expert_dim=1024),
     # BASELINE.json configs[4]: 24 blocks, dim 2048, 16 heads, FFN 8192, 8 sequences of 4096 tokens per GPU
@@ -302,6 +302,8 @@ def main():
     ap.add_argument("--workload", default="c3_dense12_d768", choices=sorted(WORKLOADS) + ["c2_gemm"])
     ap.add_argument("--precision", default="fp8", choices=["fp8", "f16", "int8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--expert-parallel", type=int, default=1, choices=[0, 1],
+                    help="mixture-of-experts workloads on more than one GPU: divide the experts over the ranks")
     args = ap.parse_args()
     if args.workload == "c2_gemm":
         if args.impl == "reference" or args.gpus != 1:
@@ -357,6 +359,9 @@ def main():
         ids = [comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         model.comm_init(rank, world, ids[0])
+        if "experts" in w and args.expert_parallel and w["experts"] % world == 0:
+            model.set_expert_parallel()
+            config["parallelism"] = f"dp{world} x ep{world} (experts divided over the ranks, rows exchanged with ncclSend / ncclRecv)"
 
     def barrier():
         if world > 1:

@@ -261,6 +261,26 @@ int ts2_dp_layout(const ts2_model_descr *descr, int64_t *matrix_offset, int n_ma
 #define TS2_COMM_ID_BYTES 128
 int ts2_comm_unique_id(uint8_t id[TS2_COMM_ID_BYTES]);
 int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_COMM_ID_BYTES]);
+/* Expert parallelism for the mixture-of-experts layers, on top of the data-parallel exchange (after ts2_comm_init, all
+ * ranks, expert_count divisible by the world size): rank r computes experts [r E / N, (r + 1) E / N) for the rows of
+ * ALL ranks.  Each rank sorts its (token, choice) rows by expert as before; per layer the ranks exchange their
+ * per-expert row counts, then the rows themselves travel to the experts' owners and the results back (ncclSend /
+ * ncclRecv blocks in expert order on a communicator of their own); the backward pass sends the state gradient rows
+ * the same way and returns the routing-weight gradients and the input gradients.  The weight gradient of an expert
+ * arises complete on its owner.  The counts are read on the host once per layer and step.  The reference splits
+ * experts over the devices of a device group that all see the same tokens (GetExpertSpan / AllGatherMoe / ReduceMoe,
+ * src/gpt/compute/layer_moe.cu:52-66,170,231); with one process per GPU and different tokens on every rank that becomes
+ * this exchange.  capacity_factor (1 .. world size; 0 = the default 2): a rank can receive up to that many times its own
+ * number of rows; a step that needs more fails on every rank with TS2_ERR_TOO_LARGE. */
+int ts2_set_expert_parallel(ts2_model *m, float capacity_factor);
+/* The plan of one layer's exchange, as every rank computes it from all ranks' per-expert row counts
+ * counts[world_size][expert_count] (host arithmetic only; no device needed).  own_seg[E + 1]: this rank's own
+ * expert-sorted layout (segments padded to 128 rows); x_seg[E + 1], x_valid[E]: the layout of the rows it receives for
+ * its experts; moves: n_out blocks this rank sends then n_in blocks it receives, each {peer, first row in the
+ * sender's own layout (-1 for a remote sender), first row in the owner's layout, rows}; max_x_rows: the largest
+ * received layout of any rank. */
+int ts2_moe_exchange_plan(int world_size, int rank, int expert_count, const int32_t *counts, int32_t *own_seg, int32_t *x_seg,
+                          int32_t *x_valid, int32_t *moves, int max_moves, int32_t *n_out, int32_t *n_in, int32_t *max_x_rows);
 
 /* counters for the bench: kernels of this library launched since the last reset */
 int64_t ts2_launch_count(ts2_model *m, int reset);

@@ -151,7 +151,11 @@ int moe_route(const Ctx &c, const float *logits, int ld, int T, int E, int k, in
 // expert-sorted slot tables (segments padded to 128 rows): seg_ptr[E+1], tile_group[max_rows/128] (-1: unused),
 // slot_of[T*k], token_of[max_rows] (-1: unused), weight_of[max_rows]; scratch: hist and block_base, ceil(T/256)*E ints each
 int moe_build_slots(const Ctx &c, const int *ids, const float *weights, int T, int k, int E, int max_rows, int *hist_scratch,
-                    int *block_base_scratch, int *seg_ptr, int *tile_group, int *slot_of, int *token_of, float *weight_of);
+                    int *block_base_scratch, int *seg_ptr, int *tile_group, int *slot_of, int *token_of, float *weight_of, int *counts = nullptr);
+// expert-parallel row space (rows received for the experts a rank owns): tables from the segment offsets seg[E + 1] and
+// the rows with data valid[E]; zeroing of the padding rows of a received buffer
+int moe_ep_tables(const Ctx &c, const int *seg, const int *valid, int E, int max_rows, int *tile_group, int *token_of);
+int moe_zero_pad_rows(const Ctx &c, void *buf, int row_bytes, const int *seg, const int *valid, int E);
 int moe_gather_rows(const Ctx &c, const void *src, const int *token_of, int rows, int row_bytes, void *dst);
 int moe_act_forward(const Ctx &c, const __half *cat, const int *token_of, const float *weight_of, int rows, int X, __half *what,
                     float *wscale, void *rg);

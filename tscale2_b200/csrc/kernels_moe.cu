@@ -98,7 +98,8 @@ __global__ void moe_count_kernel(const int *__restrict__ ids, int n_pairs, int k
 // seg_ptr[e]: first row of expert e's segment (multiples of 128); block_base[b][e]: first slot of block b in it;
 // tile_group[tile]: expert of each 128-row tile, -1 beyond the used rows; token_of / weight_of reset for all rows
 __global__ void moe_scan_kernel(const int *__restrict__ hist, int n_blocks, int E, int max_rows, int *__restrict__ seg_ptr,
-                                int *__restrict__ block_base, int *__restrict__ tile_group, int *__restrict__ token_of)
+                                int *__restrict__ block_base, int *__restrict__ tile_group, int *__restrict__ token_of,
+                                int *__restrict__ counts)
 {
     __shared__ int total[128], start[129];
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -121,6 +122,9 @@ __global__ void moe_scan_kernel(const int *__restrict__ hist, int n_blocks, int 
     __syncthreads();
     for (int e = threadIdx.x; e <= E; e += blockDim.x)
         seg_ptr[e] = start[e];
+    if (counts)
+        for (int e = threadIdx.x; e < E; e += blockDim.x)
+            counts[e] = total[e];
     for (int i = threadIdx.x; i < n_blocks * E; i += blockDim.x)
         block_base[i] += start[i % E];
     for (int tile = threadIdx.x; tile < max_rows / 128; tile += blockDim.x) {
@@ -155,14 +159,64 @@ __global__ void moe_assign_kernel(const int *__restrict__ ids, const float *__re
 }
 
 int moe_build_slots(const Ctx &c, const int *ids, const float *weights, int T, int k, int E, int max_rows, int *hist_scratch,
-                    int *block_base_scratch, int *seg_ptr, int *tile_group, int *slot_of, int *token_of, float *weight_of)
+                    int *block_base_scratch, int *seg_ptr, int *tile_group, int *slot_of, int *token_of, float *weight_of, int *counts)
 {
     const int n_pairs = T * k, n_blocks = (T + ROUTE_BLOCK - 1) / ROUTE_BLOCK;
     moe_count_kernel<<<n_blocks, 256, E * sizeof(int), c.stream>>>(ids, n_pairs, k, E, hist_scratch);
     TS2_CHECK_LAUNCH();
-    moe_scan_kernel<<<1, 1024, 0, c.stream>>>(hist_scratch, n_blocks, E, max_rows, seg_ptr, block_base_scratch, tile_group, token_of);
+    moe_scan_kernel<<<1, 1024, 0, c.stream>>>(hist_scratch, n_blocks, E, max_rows, seg_ptr, block_base_scratch, tile_group, token_of,
+                                               counts);
     TS2_CHECK_LAUNCH();
     moe_assign_kernel<<<n_blocks, 128, 0, c.stream>>>(ids, weights, n_pairs, k, E, block_base_scratch, slot_of, token_of, weight_of);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Expert-parallel row space: the rows a rank received for the experts it owns.  seg[e] .. seg[e + 1] is expert e's
+// segment (multiples of 128, empty for experts of other ranks), valid[e] of its rows hold data.
+//  tile_group[tile] = expert of each 128-row tile (-1 beyond the used rows); token_of[row] = 0 for a row with data, -1
+//  for padding (the activation kernels only test its sign).
+__global__ void moe_ep_tables_kernel(const int *__restrict__ seg, const int *__restrict__ valid, int E, int max_rows,
+                                     int *__restrict__ tile_group, int *__restrict__ token_of)
+{
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= max_rows)
+        return;
+    int g = -1, used = 0;
+    for (int e = 0; e < E; ++e)
+        if (r >= seg[e] && r < seg[e + 1]) {
+            g = e;
+            used = r - seg[e] < valid[e];
+        }
+    token_of[r] = used ? 0 : -1;
+    if ((r & 127) == 0)
+        tile_group[r >> 7] = g;
+}
+
+int moe_ep_tables(const Ctx &c, const int *seg, const int *valid, int E, int max_rows, int *tile_group, int *token_of)
+{
+    moe_ep_tables_kernel<<<(max_rows + 255) / 256, 256, 0, c.stream>>>(seg, valid, E, max_rows, tile_group, token_of);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
+// zeroes the padding rows of a received buffer (a contraction over an expert's segment reads them)
+__global__ void moe_zero_pad_rows_kernel(uint8_t *__restrict__ buf, int row_bytes, const int *__restrict__ seg, const int *__restrict__ valid)
+{
+    const int e = blockIdx.x;
+    const int r0 = seg[e] + valid[e], r1 = seg[e + 1];
+    const long long chunks = (long long)(r1 - r0) * (row_bytes / 16);
+    uint4 *dst = (uint4 *)(buf + (size_t)r0 * row_bytes);
+    for (long long i = threadIdx.x; i < chunks; i += blockDim.x)
+        dst[i] = make_uint4(0, 0, 0, 0);
+}
+
+int moe_zero_pad_rows(const Ctx &c, void *buf, int row_bytes, const int *seg, const int *valid, int E)
+{
+    if (row_bytes % 16)
+        return fail(TS2_ERR_INVALID_ARG, "moe_zero_pad_rows: row size must be a multiple of 16 bytes");
+    moe_zero_pad_rows_kernel<<<E, 256, 0, c.stream>>>((uint8_t *)buf, row_bytes, seg, valid);
     TS2_CHECK_LAUNCH();
     return TS2_OK;
 }

@@ -36,6 +36,21 @@ struct Matrix {
     size_t offset = 0; // element offset in the flat buffers
 };
 
+// Expert-parallel exchange of one mixture-of-experts layer, computed on the host from every rank's per-expert row counts.
+// Own rows are sorted by expert (segments padded to 128 rows), so the rows for one destination expert are one block.
+struct EpPlan {
+    struct Move {
+        int peer;      // the other rank (this rank: a local copy)
+        int own_row;   // first row in this rank's own expert-sorted layout
+        int x_row;     // first row in the owner's layout
+        int rows;
+    };
+    std::vector<Move> out;  // blocks of own rows that go to the experts' owners (x_row: in the owner's layout)
+    std::vector<Move> in;   // blocks this rank receives for its experts (own_row: in the sender's layout)
+    std::vector<int> x_seg, x_valid; // [E + 1], [E]: segments of the received rows, empty for other ranks' experts
+    int x_rows = 0;                  // rows of the received layout, a multiple of 128
+};
+
 struct Layer {
     int type = 0;
     float slope = 0;
@@ -64,6 +79,11 @@ struct Layer {
     float *logits = nullptr;                // [T][epad]
     int *ids = nullptr, *slot_of = nullptr, *token_of = nullptr, *tile_group = nullptr, *seg_ptr = nullptr;
     float *weights = nullptr, *weight_of = nullptr;
+    // expert parallel: the tables above describe this rank's own (token, choice) rows; the rows the rank computes (received
+    // for the experts it owns) have tables of their own, and a plan of the exchange kept from the forward pass
+    int *x_token_of = nullptr, *x_tile_group = nullptr, *x_seg = nullptr, *x_valid = nullptr;
+    float *x_weight_of = nullptr;
+    EpPlan plan;
 };
 
 // A bucket is a run of matrices that is contiguous in the flat buffers: the embedding, the final layer, one per layer.
@@ -160,6 +180,14 @@ struct ts2_model {
     float *moe_y = nullptr, *dmoe_part = nullptr;
     void *moe_g = nullptr, *moe_dl = nullptr;
     int *moe_hist = nullptr, *moe_base = nullptr;
+    // expert parallel (ts2_set_expert_parallel): rank r owns experts [r E / world, (r + 1) E / world)
+    bool ep = false;
+    int x_cap = 0;                                    // capacity of the received layout in rows
+    void *own_rows = nullptr, *own_g = nullptr;       // staging in this rank's own layout: gathered rows going out
+    float *own_y = nullptr, *own_part = nullptr;      // and results coming back
+    int *cnt_own = nullptr, *cnt_all = nullptr;       // [E], [world][E] row counts per expert
+    int *h_cnt = nullptr;                             // pinned copy of cnt_all
+    ncclComm_t comm_x = nullptr;                      // communicator of the row exchanges (a split of comm)
     unsigned *absmax = nullptr; // [L+2]
     float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
     void *workspace = nullptr;
@@ -224,6 +252,20 @@ int dalloc(ts2_model *m, T **p, size_t count)
     m->allocs.push_back(q);
     *p = (T *)q;
     return TS2_OK;
+}
+
+// replaces a device buffer by a larger one (contents are not kept); the device must be idle
+template <class T>
+int regrow(ts2_model *m, T **p, size_t count)
+{
+    if (*p) {
+        auto it = std::find(m->allocs.begin(), m->allocs.end(), (void *)*p);
+        if (it != m->allocs.end())
+            m->allocs.erase(it);
+        cudaFree((void *)*p);
+        *p = nullptr;
+    }
+    return dalloc(m, p, count);
 }
 
 int layer_matrix_count(int type) { return type == TS2_LAYER_ATT ? 5 : type == TS2_LAYER_FFN ? 3 : type == TS2_LAYER_MOE ? 4 : -1; }
@@ -291,7 +333,7 @@ int gemm_rows_grouped(ts2_model *m, const Layer &ly, int64_t rows, int64_t N, in
     a.tag = m->gemm_tag;
     a.group_mode = 1;
     a.groups = m->E;
-    a.tile_group = ly.tile_group;
+    a.tile_group = m->ep ? ly.x_tile_group : ly.tile_group;
     a.group_rows_b = (int)N;
     return gemm(a);
 }
@@ -311,7 +353,7 @@ int gemm_k_grouped(ts2_model *m, const Layer &ly, int64_t Mo, int64_t Ni, int64_
     a.tag = GEMM_TAG_DW;
     a.group_mode = 2;
     a.groups = m->E;
-    a.group_kptr = ly.seg_ptr;
+    a.group_kptr = m->ep ? ly.x_seg : ly.seg_ptr;
     a.c_group_stride = stride;
     return gemm(a);
 }
@@ -469,6 +511,118 @@ int upload_segments(ts2_model *m, const std::vector<OptSeg> &segs, OptSeg **dst)
         if (_r != ncclSuccess)                                                                    \
             return mfail(m, fail(TS2_ERR_COMM, "%s failed: %s", #expr, ncclGetErrorString(_r))); \
     } while (0)
+
+// ---- expert parallel ------------------------------------------------------------------------------------------
+// The plan of one layer's exchange from all ranks' per-expert row counts cnt[world][E] (pure host arithmetic; every rank
+// computes the same numbers).  Returns the largest received layout over all ranks in *max_x_rows.
+void ep_plan(int world, int rank, int E, const int *cnt, EpPlan *p, int *max_x_rows)
+{
+    const int per = E / world;
+    auto pad = [](int n) { return (n + 127) / 128 * 128; };
+    std::vector<int> own_seg(E + 1, 0), total(E, 0), before(E, 0), owner_seg(E, 0);
+    for (int e = 0; e < E; ++e) {
+        own_seg[e + 1] = own_seg[e] + pad(cnt[rank * E + e]);
+        for (int s = 0; s < world; ++s) {
+            if (s == rank)
+                before[e] = total[e];
+            total[e] += cnt[s * E + e];
+        }
+    }
+    *max_x_rows = 0;
+    for (int o = 0; o < world; ++o) {
+        int pos = 0;
+        for (int e = o * per; e < (o + 1) * per; ++e) {
+            owner_seg[e] = pos;
+            pos += pad(total[e]);
+        }
+        *max_x_rows = std::max(*max_x_rows, pos);
+    }
+    p->out.clear();
+    p->in.clear();
+    p->x_seg.assign(E + 1, 0);
+    p->x_valid.assign(E, 0);
+    int pos = 0;
+    for (int e = 0; e < E; ++e) {
+        const int owner = e / per;
+        p->x_seg[e] = pos;
+        if (cnt[rank * E + e])
+            p->out.push_back({owner, own_seg[e], owner_seg[e] + before[e], cnt[rank * E + e]});
+        if (owner != rank)
+            continue;
+        int off = 0;
+        for (int s = 0; s < world; ++s) {
+            const int n = cnt[s * E + e];
+            if (n)
+                p->in.push_back({s, s == rank ? own_seg[e] : -1, pos + off, n});
+            off += n;
+        }
+        p->x_valid[e] = off;
+        pos += pad(off);
+    }
+    p->x_seg[E] = pos;
+    p->x_rows = pos;
+}
+
+// counts of all ranks -> plan, tables of the received layout.  Waits for the device (the counts come from this step's
+// routing): once per mixture-of-experts layer in the forward pass; the backward pass reuses the plan.
+// The exchanges use a communicator of their own (comm_x) on the compute stream - they are on the critical path anyway -
+// so that they do not queue behind the gradient reduce-scatters of the communication stream.
+int ep_prepare(ts2_model *m, Layer &ly)
+{
+    const int E = m->E, N = m->world;
+    M_NCCL(ncclAllGather(m->cnt_own, m->cnt_all, E, ncclInt32, m->comm_x, m->stream));
+    TS2_CUDA(cudaMemcpyAsync(m->h_cnt, m->cnt_all, (size_t)N * E * 4, cudaMemcpyDeviceToHost, m->stream));
+    TS2_CUDA(cudaStreamSynchronize(m->stream));
+    int max_x = 0;
+    ep_plan(N, m->rank, E, m->h_cnt, &ly.plan, &max_x);
+    if (max_x > m->x_cap) // every rank sees the same counts and takes the same decision
+        return fail(TS2_ERR_TOO_LARGE,
+                    "expert parallel: one rank would receive %d rows, the capacity is %d (ts2_set_expert_parallel with a larger factor)",
+                    max_x, m->x_cap);
+    TS2_CUDA(cudaMemcpyAsync(ly.x_seg, ly.plan.x_seg.data(), (size_t)(E + 1) * 4, cudaMemcpyHostToDevice, m->stream));
+    TS2_CUDA(cudaMemcpyAsync(ly.x_valid, ly.plan.x_valid.data(), (size_t)E * 4, cudaMemcpyHostToDevice, m->stream));
+    if (ly.plan.x_rows)
+        M_TRY(moe_ep_tables(ctx_of(m), ly.x_seg, ly.x_valid, E, ly.plan.x_rows, ly.x_tile_group, ly.x_token_of));
+    return TS2_OK;
+}
+
+// to_owner: rows of `own` (this rank's expert-sorted layout) go to the experts' owners, which place them in `x`
+// (their received layout); otherwise the way back.  Blocks travel in expert order between every pair of ranks, so
+// sends and receives pair up.
+int ep_exchange(ts2_model *m, const Layer &ly, bool to_owner, void *own, void *x, size_t row_bytes, bool zero_pads)
+{
+    const EpPlan &p = ly.plan;
+    cudaStream_t cs = m->stream;
+    uint8_t *o = (uint8_t *)own, *xx = (uint8_t *)x;
+    for (const EpPlan::Move &mv : p.in)
+        if (mv.peer == m->rank) {
+            uint8_t *a = o + (size_t)mv.own_row * row_bytes, *b = xx + (size_t)mv.x_row * row_bytes;
+            TS2_CUDA(cudaMemcpyAsync(to_owner ? b : a, to_owner ? a : b, (size_t)mv.rows * row_bytes, cudaMemcpyDeviceToDevice, cs));
+        }
+    M_NCCL(ncclGroupStart());
+    for (const EpPlan::Move &mv : p.out) {
+        if (mv.peer == m->rank)
+            continue;
+        uint8_t *a = o + (size_t)mv.own_row * row_bytes;
+        if (to_owner)
+            M_NCCL(ncclSend(a, (size_t)mv.rows * row_bytes, ncclUint8, mv.peer, m->comm_x, cs));
+        else
+            M_NCCL(ncclRecv(a, (size_t)mv.rows * row_bytes, ncclUint8, mv.peer, m->comm_x, cs));
+    }
+    for (const EpPlan::Move &mv : p.in) {
+        if (mv.peer == m->rank)
+            continue;
+        uint8_t *b = xx + (size_t)mv.x_row * row_bytes;
+        if (to_owner)
+            M_NCCL(ncclRecv(b, (size_t)mv.rows * row_bytes, ncclUint8, mv.peer, m->comm_x, cs));
+        else
+            M_NCCL(ncclSend(b, (size_t)mv.rows * row_bytes, ncclUint8, mv.peer, m->comm_x, cs));
+    }
+    M_NCCL(ncclGroupEnd());
+    if (to_owner && zero_pads && p.x_rows)
+        M_TRY(moe_zero_pad_rows(ctx_of(m), x, (int)row_bytes, ly.x_seg, ly.x_valid, m->E));
+    return TS2_OK;
+}
 
 // transposed copies, per-expert layouts and scale vectors from the row-major quantized matrices and their scales
 int post_quantize(ts2_model *m)
@@ -853,20 +1007,42 @@ int forward(ts2_model *m)
             M_TRY(gemm_tn(m, m->kind, T, m->epad, D, ly.n_fast, D, ly.Wsel, D, ly.logits, m->epad, es));
             M_TRY(moe_route(c, ly.logits, m->epad, T, E, K, ly.ids, ly.weights));
             M_TRY(moe_build_slots(c, ly.ids, ly.weights, T, K, E, rows, m->moe_hist, m->moe_base, ly.seg_ptr, ly.tile_group, ly.slot_of,
-                                  ly.token_of, ly.weight_of));
-            M_TRY(moe_gather_rows(c, ly.n_fast, ly.token_of, rows, (int)(D * fs), ly.n_rows));
+                                  ly.token_of, ly.weight_of, m->ep ? m->cnt_own : nullptr));
+            // xrows: the rows this rank computes - its own (token, choice) rows, or, expert parallel, the rows of all
+            // ranks for the experts it owns
+            int xrows = rows;
+            const int *x_token_of = ly.token_of;
+            const float *x_weight_of = ly.weight_of;
+            if (m->ep) {
+                M_TRY(moe_gather_rows(c, ly.n_fast, ly.token_of, rows, (int)(D * fs), m->own_rows));
+                M_TRY(ep_prepare(m, ly));
+                xrows = ly.plan.x_rows;
+                x_token_of = ly.x_token_of;
+                x_weight_of = ly.x_weight_of;
+                M_TRY(ep_exchange(m, ly, true, m->own_rows, ly.n_rows, D * fs, true));
+                M_TRY(ep_exchange(m, ly, true, ly.weight_of, ly.x_weight_of, 4, false));
+            } else {
+                M_TRY(moe_gather_rows(c, ly.n_fast, ly.token_of, rows, (int)(D * fs), ly.n_rows));
+            }
             Epilogue e1;
             e1.col_scale = ly.fwd_col;
             e1.out_kind = TS2_OUT_F16;
-            M_TRY(gemm_rows_grouped(m, ly, rows, 2 * X, D, ly.n_rows, D, ly.Wcat, D, ly.cat16, 2 * X, e1));
-            M_TRY(moe_act_forward(c, ly.cat16, ly.token_of, ly.weight_of, rows, X, ly.what, ly.wscale, ly.rg));
             // the contract matrix is [D][E*X] for the CPU path: its dot scale is sqrt(1 / (E*X))
             Epilogue e2;
             e2.alpha = sqrtf(1.0f / ((float)E * X)) / (m->s_act * 32.f);
             e2.dyn_scale = m->mats[ly.mat0 + 2].sko;
             e2.out_kind = TS2_OUT_F32;
-            M_TRY(gemm_rows_grouped(m, ly, rows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
-            M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+            if (xrows) {
+                M_TRY(gemm_rows_grouped(m, ly, xrows, 2 * X, D, ly.n_rows, D, ly.Wcat, D, ly.cat16, 2 * X, e1));
+                M_TRY(moe_act_forward(c, ly.cat16, x_token_of, x_weight_of, xrows, X, ly.what, ly.wscale, ly.rg));
+                M_TRY(gemm_rows_grouped(m, ly, xrows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
+            }
+            const float *y_own = m->moe_y;
+            if (m->ep) {
+                M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 4, false));
+                y_own = m->own_y;
+            }
+            M_TRY(moe_combine(c, y_own, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
             TRACE("state", l + 1, m->states[l + 1], (size_t)T * D * 4, TR_F32);
             continue;
         }
@@ -1073,22 +1249,39 @@ int backward(ts2_model *m)
             // TMoELayer::ComputeBackward, layer_moe.cu:488-537, on expert-sorted rows
             const int E = m->E, K = m->K, X = m->X, rows = (K * T + 127) / 128 * 128 + 128 * E;
             const size_t fs = fast_size(m);
+            if (m->ep) // rows of all ranks meet in one contraction: one power-of-two gradient scale for all of them
+                M_NCCL(ncclAllReduce(m->absmax + l + 1, m->absmax + l + 1, 1, ncclUint32, ncclMax, m->comm_x, m->stream));
             M_TRY(cast_grad(c, m->g, (size_t)T * D, m->absmax + l + 1, m->g_fast, m->ginv, sqrtf((float)D / ((float)E * X)), mc.sko,
                             m->fscale));
-            M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->moe_g));
+            const int xrows = m->ep ? ly.plan.x_rows : rows;
+            const int *x_token_of = m->ep ? ly.x_token_of : ly.token_of;
+            const float *x_weight_of = m->ep ? ly.x_weight_of : ly.weight_of;
+            if (m->ep) {
+                M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->own_g));
+                M_TRY(ep_exchange(m, ly, true, m->own_g, m->moe_g, D * fs, true));
+            } else {
+                M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->moe_g));
+            }
             Epilogue e3;
             e3.alpha = 1.f / (32.f * sqrtf((float)D));
             e3.out_kind = TS2_OUT_F16;
-            M_TRY(gemm_rows_grouped(m, ly, rows, X, D, m->moe_g, D, ly.WcT, D, m->drg, X, e3));
-            if (tune_layers) {
-                Epilogue e6;
-                e6.alpha = 1.f / m->s_act;
-                e6.dyn_scale = m->ginv;
-                e6.out_kind = TS2_OUT_F32_ADD;
-                M_TRY(gemm_k_grouped(m, ly, D, X, rows, m->moe_g, D, ly.rg, X, mc.grad, (int64_t)D * X, e6));
+            if (xrows) {
+                M_TRY(gemm_rows_grouped(m, ly, xrows, X, D, m->moe_g, D, ly.WcT, D, m->drg, X, e3));
+                if (tune_layers) {
+                    Epilogue e6;
+                    e6.alpha = 1.f / m->s_act;
+                    e6.dyn_scale = m->ginv;
+                    e6.out_kind = TS2_OUT_F32_ADD;
+                    M_TRY(gemm_k_grouped(m, ly, D, X, xrows, m->moe_g, D, ly.rg, X, mc.grad, (int64_t)D * X, e6));
+                }
+                M_TRY(moe_act_backward(c, m->drg, ly.cat16, ly.what, ly.wscale, x_token_of, x_weight_of, xrows, X, m->dcat, m->dmoe_part));
             }
-            M_TRY(moe_act_backward(c, m->drg, ly.cat16, ly.what, ly.wscale, ly.token_of, ly.weight_of, rows, X, m->dcat, m->dmoe_part));
-            M_TRY(moe_router_backward(c, m->dmoe_part, X / 128, ly.ids, ly.weights, ly.slot_of, T, K, E, m->epad, m->moe_dl));
+            const float *part_own = m->dmoe_part;
+            if (m->ep) {
+                M_TRY(ep_exchange(m, ly, false, m->own_part, m->dmoe_part, (size_t)(X / 128) * 4, false));
+                part_own = m->own_part;
+            }
+            M_TRY(moe_router_backward(c, part_own, X / 128, ly.ids, ly.weights, ly.slot_of, T, K, E, m->epad, m->moe_dl));
             // router: dn = dl . Sel * sqrt(1/D) (scale-free matrix), dW_sel = dl^T . n
             Epilogue er;
             er.alpha = sqrtf(1.0f / D) / 32.f;
@@ -1104,17 +1297,23 @@ int backward(ts2_model *m)
             Epilogue e4;
             e4.alpha = sqrtf(1.0f / D) / 32.f;
             e4.out_kind = TS2_OUT_F32;
-            M_TRY(gemm_rows_grouped(m, ly, rows, D, 2 * X, m->dcat, 2 * X, ly.WcatT, 2 * X, m->moe_y, D, e4));
-            M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, nullptr, m->dn));
-            if (tune_layers) {
+            if (xrows)
+                M_TRY(gemm_rows_grouped(m, ly, xrows, D, 2 * X, m->dcat, 2 * X, ly.WcatT, 2 * X, m->moe_y, D, e4));
+            const float *y_own = m->moe_y;
+            if (m->ep) {
+                M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 4, false));
+                y_own = m->own_y;
+            }
+            M_TRY(moe_combine(c, y_own, ly.slot_of, T, K, D, nullptr, m->dn));
+            if (tune_layers && xrows) {
                 Epilogue e5;
                 e5.alpha = 1.f / m->s_act;
                 e5.dyn_scale = m->fscale;
                 e5.out_kind = TS2_OUT_F32_ADD;
                 Epilogue e5e = e5;
                 e5e.row_scale = ly.bwd_row_e; // expand is followed by a normalisation: rows divided by its matrix scale
-                M_TRY(gemm_k_grouped(m, ly, X, D, rows, m->dcat, 2 * X, ly.n_rows, D, m->mats[ly.mat0].grad, (int64_t)X * D, e5e));
-                M_TRY(gemm_k_grouped(m, ly, X, D, rows, (const uint8_t *)m->dcat + (size_t)X * fs, 2 * X, ly.n_rows, D,
+                M_TRY(gemm_k_grouped(m, ly, X, D, xrows, m->dcat, 2 * X, ly.n_rows, D, m->mats[ly.mat0].grad, (int64_t)X * D, e5e));
+                M_TRY(gemm_k_grouped(m, ly, X, D, xrows, (const uint8_t *)m->dcat + (size_t)X * fs, 2 * X, ly.n_rows, D,
                                      m->mats[ly.mat0 + 1].grad, (int64_t)X * D, e5));
             }
             M_TRY(reduce_matrices(m, ly.mat0, l + 1 < L ? m->layers[l + 1].mat0 : (int)m->mats.size()));
@@ -1462,8 +1661,12 @@ void ts2_destroy(ts2_model *m)
         return;
     cudaSetDevice(m->device);
     cudaDeviceSynchronize();
+    if (m->comm_x)
+        ncclCommDestroy(m->comm_x);
     if (m->comm)
         ncclCommDestroy(m->comm);
+    if (m->h_cnt)
+        cudaFreeHost(m->h_cnt);
     for (void *p : m->allocs)
         cudaFree(p);
     if (m->pinned)
@@ -1781,6 +1984,11 @@ int ts2_debug_read(ts2_model *m, const char *name, int layer, void *dst, int64_t
                       : n == "ids" ? (const void *)ly.ids : n == "weights" ? (const void *)ly.weights
                       : n == "cat16" ? (const void *)ly.cat16 : n == "n_fast" ? ly.n_fast : n == "n_rows" ? ly.n_rows
                       : n == "logits" ? (const void *)ly.logits : n == "moe_g" ? m->moe_g : n == "drg" ? (const void *)m->drg
+                      : n == "weight_of" ? (const void *)ly.weight_of : n == "x_seg" ? (const void *)ly.x_seg
+                      : n == "x_valid" ? (const void *)ly.x_valid : n == "x_token_of" ? (const void *)ly.x_token_of
+                      : n == "x_weight_of" ? (const void *)ly.x_weight_of : n == "x_tile_group" ? (const void *)ly.x_tile_group
+                      : n == "own_rows" ? (const void *)m->own_rows : n == "own_y" ? (const void *)m->own_y
+                      : n == "moe_y" ? (const void *)m->moe_y
                       : n == "capture" && (size_t)bytes <= m->capture_bytes ? m->capture_buf : nullptr;
     if (!src)
         return fail(TS2_ERR_INVALID_ARG, "ts2_debug_read: unknown or absent buffer '%s'", name);
@@ -1967,6 +2175,101 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
     m->nseg_shard = (int)segs.size();
     m->d_segs_shard = nullptr;
     M_TRY(upload_segments(m, segs, &m->d_segs_shard));
+    return TS2_OK;
+}
+
+int ts2_set_expert_parallel(ts2_model *m, float capacity_factor)
+{
+    if (!m)
+        return TS2_ERR_INVALID_ARG;
+    if (!m->comm || m->world < 2)
+        return fail(TS2_ERR_INVALID_ARG, "expert parallel needs ts2_comm_init with more than one rank first");
+    if (m->ep)
+        return fail(TS2_ERR_INVALID_ARG, "expert parallel is already on");
+    if (m->E == 0 || m->moe_rows == 0)
+        return fail(TS2_ERR_INVALID_ARG, "the model has no mixture-of-experts layer");
+    if (m->E % m->world)
+        return fail(TS2_ERR_UNSUPPORTED, "%d experts do not divide over %d ranks", m->E, m->world);
+    if (!(capacity_factor >= 1.f) || capacity_factor > (float)m->world)
+        capacity_factor = std::min(2.f, (float)m->world);
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(sync_master(m));
+    TS2_CUDA(cudaDeviceSynchronize());
+    ncclResult_t r = ncclCommSplit(m->comm, 0, m->rank, &m->comm_x, nullptr);
+    if (r != ncclSuccess) {
+        m->comm_x = nullptr;
+        return mfail(m, fail(TS2_ERR_COMM, "ncclCommSplit failed: %s", ncclGetErrorString(r)));
+    }
+    // received layout: a rank's share of all (token, choice) rows times the factor, plus the padding of its experts
+    const size_t own = (size_t)m->K * m->max_nodes;
+    const size_t R = ((size_t)(capacity_factor * (double)own) + 127) / 128 * 128 + 128 * (size_t)(m->E / m->world);
+    m->x_cap = (int)R;
+    const size_t D = m->D, X = m->X, fs = fast_size(m), T = m->max_nodes;
+    for (Layer &ly : m->layers) {
+        if (ly.type != TS2_LAYER_MOE)
+            continue;
+        M_TRY(regrow(m, (uint8_t **)&ly.n_rows, R * D * fs));
+        M_TRY(regrow(m, &ly.cat16, R * 2 * X));
+        M_TRY(regrow(m, &ly.what, R * X));
+        M_TRY(regrow(m, &ly.wscale, R * (X / 128)));
+        M_TRY(regrow(m, (uint8_t **)&ly.rg, R * X * fs));
+        M_TRY(dalloc(m, &ly.x_token_of, R));
+        M_TRY(dalloc(m, &ly.x_weight_of, R));
+        M_TRY(dalloc(m, &ly.x_tile_group, R / 128));
+        M_TRY(dalloc(m, &ly.x_seg, (size_t)m->E + 1));
+        M_TRY(dalloc(m, &ly.x_valid, (size_t)m->E));
+    }
+    size_t max_wide = 0, max_cat = 0;
+    for (const Layer &ly : m->layers)
+        if (ly.type != TS2_LAYER_MOE) {
+            max_wide = std::max<size_t>(max_wide, ly.wide);
+            max_cat = std::max<size_t>(max_cat, (size_t)ly.ncat * ly.wide);
+        }
+    M_TRY(regrow(m, &m->moe_y, R * D));
+    M_TRY(regrow(m, (uint8_t **)&m->moe_g, R * D * fs));
+    M_TRY(regrow(m, &m->dmoe_part, R * (X / 128)));
+    M_TRY(regrow(m, &m->drg, std::max(T * max_wide, R * X)));
+    M_TRY(regrow(m, (uint8_t **)&m->dcat, std::max(T * max_cat, R * 2 * X) * fs));
+    const size_t own_rows = m->moe_rows;
+    M_TRY(dalloc(m, (uint8_t **)&m->own_rows, own_rows * D * fs));
+    M_TRY(dalloc(m, (uint8_t **)&m->own_g, own_rows * D * fs));
+    M_TRY(dalloc(m, &m->own_y, own_rows * D));
+    M_TRY(dalloc(m, &m->own_part, own_rows * (X / 128)));
+    M_TRY(dalloc(m, &m->cnt_own, (size_t)m->E));
+    M_TRY(dalloc(m, &m->cnt_all, (size_t)m->E * m->world));
+    TS2_CUDA(cudaMallocHost(&m->h_cnt, (size_t)m->E * m->world * 4));
+    m->ep = true;
+    return TS2_OK;
+}
+
+int ts2_moe_exchange_plan(int world_size, int rank, int expert_count, const int32_t *counts, int32_t *own_seg, int32_t *x_seg,
+                          int32_t *x_valid, int32_t *moves, int max_moves, int32_t *n_out, int32_t *n_in, int32_t *max_x_rows)
+{
+    if (world_size < 1 || rank < 0 || rank >= world_size || expert_count < 1 || expert_count % world_size || !counts || !own_seg || !x_seg ||
+        !x_valid || !moves || !n_out || !n_in || !max_x_rows)
+        return fail(TS2_ERR_INVALID_ARG, "ts2_moe_exchange_plan: bad arguments");
+    EpPlan p;
+    int mx = 0;
+    ep_plan(world_size, rank, expert_count, counts, &p, &mx);
+    if ((int)(p.out.size() + p.in.size()) > max_moves)
+        return fail(TS2_ERR_TOO_LARGE, "ts2_moe_exchange_plan: %zu moves, room for %d", p.out.size() + p.in.size(), max_moves);
+    own_seg[0] = 0;
+    for (int e = 0; e < expert_count; ++e)
+        own_seg[e + 1] = own_seg[e] + (counts[rank * expert_count + e] + 127) / 128 * 128;
+    memcpy(x_seg, p.x_seg.data(), (size_t)(expert_count + 1) * 4);
+    memcpy(x_valid, p.x_valid.data(), (size_t)expert_count * 4);
+    int k = 0;
+    for (const auto *list : {&p.out, &p.in})
+        for (const EpPlan::Move &mv : *list) {
+            moves[4 * k + 0] = mv.peer;
+            moves[4 * k + 1] = mv.own_row;
+            moves[4 * k + 2] = mv.x_row;
+            moves[4 * k + 3] = mv.rows;
+            ++k;
+        }
+    *n_out = (int)p.out.size();
+    *n_in = (int)p.in.size();
+    *max_x_rows = mx;
     return TS2_OK;
 }
 

@@ -110,6 +110,25 @@ def dp_layout(spec: ModelSpec):
     return mo, bo, be, bf
 
 
+def moe_exchange_plan(world: int, rank: int, counts: np.ndarray) -> dict:
+    """The expert-parallel exchange of one mixture-of-experts layer as rank `rank` plans it from all ranks' per-expert
+    row counts counts[world][experts] (ts2_moe_exchange_plan; host arithmetic of the CUDA library, no device needed).
+    out / recv: arrays of (peer, first row in the sender's own layout or -1, first row in the owner's layout, rows)."""
+    lib = capi.load_library()
+    counts = np.ascontiguousarray(counts, np.int32)
+    E = counts.shape[1]
+    own_seg, x_seg, x_valid = np.zeros(E + 1, np.int32), np.zeros(E + 1, np.int32), np.zeros(E, np.int32)
+    cap = E * (world + 1)
+    moves = np.zeros((cap, 4), np.int32)
+    n_out, n_in, max_x = C.c_int(), C.c_int(), C.c_int()
+    rc = lib.ts2_moe_exchange_plan(world, rank, E, counts.ctypes.data, own_seg.ctypes.data, x_seg.ctypes.data, x_valid.ctypes.data,
+                                   moves.ctypes.data, cap, C.byref(n_out), C.byref(n_in), C.byref(max_x))
+    if rc != capi.TS2_OK:
+        raise capi.Ts2Error(rc, lib.ts2_last_error(None).decode())
+    return dict(own_seg=own_seg, x_seg=x_seg, x_valid=x_valid, out=moves[:n_out.value].copy(),
+                recv=moves[n_out.value:n_out.value + n_in.value].copy(), max_x_rows=max_x.value)
+
+
 def init_weights(spec: ModelSpec, seed: int, std: float = 0.02, select_std: float = None) -> List[np.ndarray]:
     """fp32 master weights ~ N(0, std) from numpy's default_rng(seed)."""
     rng = np.random.default_rng(seed)

@@ -198,6 +198,11 @@ class Model:
         buf = (C.c_uint8 * capi.COMM_ID_BYTES).from_buffer_copy(id_bytes)
         self._check(self.lib.ts2_comm_init(self.h, rank, world, buf))
 
+    def set_expert_parallel(self, capacity_factor=0.0):
+        """After comm_init, on every rank: the experts of the mixture-of-experts layers are divided over the ranks and
+        the (token, choice) rows travel to the experts' owners and back (ts2_set_expert_parallel)."""
+        self._check(self.lib.ts2_set_expert_parallel(self.h, capacity_factor))
+
     def last_step_ms(self):
         v = C.c_float()
         self._check(self.lib.ts2_last_step_ms(self.h, C.byref(v)))
