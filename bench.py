@@ -381,6 +381,9 @@ def main():
     model.set_kernel_timing(True)
     model.get_kernel_timing(reset=True)
     model.launch_count(reset=True)
+    ep_on = "ep" in config["parallelism"]
+    if ep_on:
+        model.exchange_timing(True)
     sampler = ClockSampler(local_rank)
     sampler.start()
     model.timer_begin()
@@ -389,6 +392,11 @@ def main():
     ms = model.timer_end()
     launches = model.launch_count()
     barrier()
+    exchange = None
+    if ep_on:  # device time of the row exchanges (events on the compute stream), this rank
+        x_ms, x_bytes, x_n = model.exchange_timing(False)
+        exchange = {"ms_per_step": x_ms / args.steps, "gb_sent_per_step": x_bytes / args.steps / 1e9,
+                    "gbs_per_direction": x_bytes / 1e9 / max(x_ms / 1e3, 1e-9), "exchanges_per_step": x_n / args.steps}
     clocks = sampler.stop()
     # every step of the timed region is checked afterwards (no device read inside it): the per-step training error
     # from the engine's loss ring, and the per-layer-boundary flags the norm-backward kernel raises on a NaN / infinity
@@ -474,6 +482,8 @@ def main():
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_max / args.steps, "last_loss": loss,
                     "losses_checked": len(e2e_losses)},
             "gpu_launches": int(launches), "roofline": roofline}
+    if exchange:
+        line["expert_exchange"] = exchange
     if world == 1 and not args.no_cpu_baseline:
         cb, _, _ = run_cpu_reference(w, 1, 0)
         line["cpu_baseline"] = cb

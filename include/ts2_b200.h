@@ -273,6 +273,9 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
  * this exchange.  capacity_factor (1 .. world size; 0 = the default 2): a rank can receive up to that many times its own
  * number of rows; a step that needs more fails on every rank with TS2_ERR_TOO_LARGE. */
 int ts2_set_expert_parallel(ts2_model *m, float capacity_factor);
+/* Measurement hook: device time (events around every row exchange on the compute stream), bytes this rank sent to
+ * other ranks and number of exchanges since the last call; enable switches the recording on or off from now on. */
+int ts2_get_exchange_ms(ts2_model *m, int enable, float *ms, double *bytes_sent, int *exchanges);
 /* The plan of one layer's exchange, as every rank computes it from all ranks' per-expert row counts
  * counts[world_size][expert_count] (host arithmetic only; no device needed).  own_seg[E + 1]: this rank's own
  * expert-sorted layout (segments padded to 128 rows); x_seg[E + 1], x_valid[E]: the layout of the rows it receives for

@@ -1,12 +1,12 @@
 """Run by test_dp_gpu.py under torchrun, one process per GPU.  Expert parallel on top of data parallel
 (ts2_set_expert_parallel): every rank routes its own tokens, the (token, choice) rows travel to the experts' owners and
 the results back.  Checked:
-  * after one applied step the weights of every matrix equal those of ONE process that accumulates the ranks' batches
-    and applies once.  fp16 operands: the expert contractions sum the same products in another order, 1e-3 of the size
-    of the update (measured: forward states identical, state gradients 2e-10).  e4m3 operands: the rows of all ranks
-    meet in one contraction, so the ranks agree on one power-of-two gradient scale per layer where the single process
-    picks one per batch; values at the bottom of e4m3's range then round differently: 0.15 of the update (measured
-    up to 0.083, on 5 of 27 matrices above 0.02);
+  * after one applied step the update of every matrix (new weights - old weights, relative L2) equals that of ONE
+    process that accumulates the ranks' batches and applies once.  The results of the experts return as fp16 rows and
+    the expert contractions sum the same products in another order: fp16 operands 5e-3.  e4m3 operands: those
+    differences of 1e-4 flip e4m3 roundings downstream, and the ranks agree on one power-of-two gradient scale per layer
+    where the single process picks one per batch; the first step's update is normalised by the gradient's own
+    magnitude, so it shows every flip: 0.25 (the distance between two e4m3 runs that differ in rounding only);
   * the ranks stay bit-identical over further steps, and the loss stays finite;
   * a capacity too small for the rows a rank would receive is refused on every rank with TS2_ERR_TOO_LARGE."""
 import os
@@ -38,7 +38,7 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("gloo")
     problems = []
-    for precision, tol in ((capi.PREC_F16, 1e-3), (capi.PREC_FP8, 0.15)):
+    for precision, tol in ((capi.PREC_F16, 5e-3), (capi.PREC_FP8, 0.25)):
         spec = moe_spec(precision)
         mats = host.init_weights(spec, 5, select_std=1.0)
         batches = [host.synthetic_batch(spec, 6, 200, 300 + r) for r in range(world)]
@@ -57,12 +57,15 @@ def main():
                 single.set_batch(batches[r])
                 single.backprop(step0, apply=(r == world - 1))
                 print(f"single, batch {r}: loss {single.avg_train_err():.6f}", flush=True)
+            worst = 0.0
             for name, a, b, w0 in zip(spec.matrix_names(), w_ep, single.get_weights(), mats):
-                d = float(np.abs(a.astype(np.float64) - b).max())
-                upd = float(np.abs(b.astype(np.float64) - w0).max())
-                if not d <= tol * upd:
-                    problems.append(f"precision {precision}, {name}: expert-parallel step differs from the accumulated "
-                                    f"single-process step by {d:.3e} (update {upd:.3e})")
+                upd = np.linalg.norm(b.astype(np.float64) - w0)
+                d = np.linalg.norm(a.astype(np.float64) - b) / upd
+                worst = max(worst, d)
+                if not d <= tol:
+                    problems.append(f"precision {precision}, {name}: the update of the expert-parallel step differs from that of "
+                                    f"the accumulated single-process step by {d:.3e} (relative L2)")
+            print(f"precision {precision}: largest relative L2 difference of an update {worst:.3e}", flush=True)
             single.close()
         model.backprop(host.training_step(rate=0.01, iteration=1), apply=False)
         for i in range(3):

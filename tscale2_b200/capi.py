@@ -116,6 +116,7 @@ def _declare(lib):
         "ts2_comm_unique_id": (i32, [P(C.c_uint8)]),
         "ts2_comm_init": (i32, [vp, i32, i32, P(C.c_uint8)]),
         "ts2_set_expert_parallel": (i32, [vp, f32]),
+        "ts2_get_exchange_ms": (i32, [vp, i32, P(f32), P(C.c_double), P(i32)]),
         "ts2_moe_exchange_plan": (i32, [i32, i32, i32, vp, vp, vp, vp, vp, i32, P(i32), P(i32), P(i32)]),
         "ts2_launch_count": (i64, [vp, i32]),
         "ts2_last_step_ms": (i32, [vp, P(f32)]),

@@ -156,6 +156,10 @@ int moe_build_slots(const Ctx &c, const int *ids, const float *weights, int T, i
 // the rows with data valid[E]; zeroing of the padding rows of a received buffer
 int moe_ep_tables(const Ctx &c, const int *seg, const int *valid, int E, int max_rows, int *tile_group, int *token_of);
 int moe_zero_pad_rows(const Ctx &c, void *buf, int row_bytes, const int *seg, const int *valid, int E);
+// row blocks pulled from other ranks' buffers over peer memory (bases[peer], plain loads) into `local`:
+// moves[i] = {peer, row on the sender side, row on the owner side, rows}; to_owner: sender rows -> owner rows
+int moe_pull_rows(const Ctx &c, const int4 *moves, int n_moves, uint8_t *const *bases, void *local, int row_bytes, bool to_owner,
+                  long long total_bytes);
 int moe_gather_rows(const Ctx &c, const void *src, const int *token_of, int rows, int row_bytes, void *dst);
 int moe_act_forward(const Ctx &c, const __half *cat, const int *token_of, const float *weight_of, int rows, int X, __half *what,
                     float *wscale, void *rg);
@@ -163,6 +167,7 @@ int moe_act_backward(const Ctx &c, const __half *drg, const __half *cat, const _
                      const float *weight_of, int rows, int X, void *dcat, float *dmoe_part);
 // out[t] = (in ? in[t] : out[t]) + sum_j y[slot_of[t*k+j]]
 int moe_combine(const Ctx &c, const float *y, const int *slot_of, int T, int k, int D, const float *in, float *out);
+int moe_combine_half(const Ctx &c, const __half *y, const int *slot_of, int T, int k, int D, const float *in, float *out);
 int moe_router_backward(const Ctx &c, const float *dmoe_part, int tiles, const int *ids, const float *weights, const int *slot_of, int T,
                         int k, int E, int ld, void *dl);
 

@@ -221,6 +221,75 @@ int moe_zero_pad_rows(const Ctx &c, void *buf, int row_bytes, const int *seg, co
     return TS2_OK;
 }
 
+// Row exchange between ranks over peer memory (NVLink): each block of rows is pulled by the rank that needs it with
+// plain loads from the other rank's buffer (mapped through CUDA IPC; this rank's own buffer is in the same table, so
+// local blocks go the same way).  moves[i] = {peer, row in the sender-side layout, row in the owner-side layout, rows};
+// to_owner: source = bases[peer] + sender row, destination = local + owner row; otherwise the other way round.
+// A CTA takes chunks of 32 KB; V = bytes per access (16, or 4 for rows that are not multiples of 16 bytes).
+constexpr int PULL_CHUNK = 32768;
+constexpr int PULL_MAX_MOVES = 256;
+
+template <int V>
+__global__ void __launch_bounds__(256) moe_pull_rows_kernel(const int4 *__restrict__ moves, int n_moves, uint8_t *const *__restrict__ bases,
+                                                            uint8_t *__restrict__ local, int row_bytes, int to_owner)
+{
+    __shared__ int first_chunk[PULL_MAX_MOVES + 1];
+    using VT = typename std::conditional<V == 16, uint4, uint32_t>::type;
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < n_moves; ++i) {
+            first_chunk[i] = run;
+            run += (int)(((long long)moves[i].w * row_bytes + PULL_CHUNK - 1) / PULL_CHUNK);
+        }
+        first_chunk[n_moves] = run;
+    }
+    __syncthreads();
+    const int total = first_chunk[n_moves];
+    for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+        int lo = 0, hi = n_moves; // the move this chunk belongs to: last i with first_chunk[i] <= chunk
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (first_chunk[mid] <= chunk)
+                lo = mid;
+            else
+                hi = mid;
+        }
+        const int4 mv = moves[lo];
+        const long long bytes = (long long)mv.w * row_bytes, off = (long long)(chunk - first_chunk[lo]) * PULL_CHUNK;
+        const int n = (int)(min((long long)PULL_CHUNK, bytes - off) / V);
+        const long long src_row = to_owner ? mv.y : mv.z, dst_row = to_owner ? mv.z : mv.y;
+        const VT *src = (const VT *)(bases[mv.x] + src_row * row_bytes + off);
+        VT *dst = (VT *)(local + dst_row * row_bytes + off);
+        int i = threadIdx.x;
+        for (; i + 3 * 256 < n; i += 4 * 256) { // four loads in flight per thread
+            const VT a = src[i], b = src[i + 256], c = src[i + 512], d = src[i + 768];
+            dst[i] = a;
+            dst[i + 256] = b;
+            dst[i + 512] = c;
+            dst[i + 768] = d;
+        }
+        for (; i < n; i += 256)
+            dst[i] = src[i];
+    }
+}
+
+int moe_pull_rows(const Ctx &c, const int4 *moves, int n_moves, uint8_t *const *bases, void *local, int row_bytes, bool to_owner,
+                  long long total_bytes)
+{
+    if (n_moves <= 0)
+        return TS2_OK;
+    if (n_moves > PULL_MAX_MOVES || row_bytes % 4)
+        return fail(TS2_ERR_INVALID_ARG, "moe_pull_rows: %d moves (at most %d), rows of %d bytes", n_moves, PULL_MAX_MOVES, row_bytes);
+    const long long chunks = total_bytes / PULL_CHUNK + n_moves;
+    const int grid = (int)std::max<long long>(1, std::min<long long>(chunks, (long long)sm_count(c.device) * 8));
+    if (row_bytes % 16 == 0)
+        moe_pull_rows_kernel<16><<<grid, 256, 0, c.stream>>>(moves, n_moves, bases, (uint8_t *)local, row_bytes, to_owner ? 1 : 0);
+    else
+        moe_pull_rows_kernel<4><<<grid, 256, 0, c.stream>>>(moves, n_moves, bases, (uint8_t *)local, row_bytes, to_owner ? 1 : 0);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // dst[s] = src[token_of[s]] (zeros for unused slots); rows of row_bytes (multiple of 16)
 __global__ void moe_gather_rows_kernel(const uint8_t *__restrict__ src, const int *__restrict__ token_of, int rows, int row_bytes,
@@ -358,6 +427,31 @@ __global__ void moe_combine_kernel(const float *__restrict__ y, const int *__res
         }
         *(float4 *)(out + t * D + off) = acc;
     }
+}
+
+// the same sum over fp16 rows (expert parallel: results come back from the experts' owners as fp16)
+__global__ void moe_combine_half_kernel(const __half *__restrict__ y, const int *__restrict__ slot_of, int T, int k, int D,
+                                        const float *__restrict__ in, float *__restrict__ out)
+{
+    const int tiles = D / TILE;
+    WARP_ITEM_LOOP((long long)T * tiles)
+    {
+        const size_t t = item / tiles;
+        const int off = (item % tiles) * TILE + lane * 4;
+        float4 acc = *(const float4 *)((in ? in : out) + t * D + off);
+        for (int j = 0; j < k; ++j) {
+            const float4 v = load_half4(y + (size_t)slot_of[t * k + j] * D + off);
+            acc = make_float4(acc.x + v.x, acc.y + v.y, acc.z + v.z, acc.w + v.w);
+        }
+        *(float4 *)(out + t * D + off) = acc;
+    }
+}
+
+int moe_combine_half(const Ctx &c, const __half *y, const int *slot_of, int T, int k, int D, const float *in, float *out)
+{
+    moe_combine_half_kernel<<<grid_for(c, (long long)T * (D / TILE)), THREADS, 0, c.stream>>>(y, slot_of, T, k, D, in, out);
+    TS2_CHECK_LAUNCH();
+    return TS2_OK;
 }
 
 int moe_combine(const Ctx &c, const float *y, const int *slot_of, int T, int k, int D, const float *in, float *out)

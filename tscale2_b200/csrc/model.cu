@@ -83,6 +83,7 @@ struct Layer {
     // for the experts it owns) have tables of their own, and a plan of the exchange kept from the forward pass
     int *x_token_of = nullptr, *x_tile_group = nullptr, *x_seg = nullptr, *x_valid = nullptr;
     float *x_weight_of = nullptr;
+    int4 *d_moves = nullptr; // plan.out then plan.in as {peer, sender row, owner row, rows}
     EpPlan plan;
 };
 
@@ -188,6 +189,19 @@ struct ts2_model {
     int *cnt_own = nullptr, *cnt_all = nullptr;       // [E], [world][E] row counts per expert
     int *h_cnt = nullptr;                             // pinned copy of cnt_all
     ncclComm_t comm_x = nullptr;                      // communicator of the row exchanges (a split of comm)
+    // exchange over peer memory: the staging buffers of every rank mapped into this process (CUDA IPC); tables of the
+    // N base pointers per buffer on the device; a 4-byte all-reduce on comm_x is the barrier between "written" and "read"
+    enum { PB_OWN_ROWS, PB_OWN_G, PB_OWN_W, PB_MOE_Y, PB_PART, PB_COUNT };
+    bool x_peer = false;
+    std::vector<void *> ipc_opened;
+    uint8_t **d_peer = nullptr; // [PB_COUNT][world]
+    float *own_w = nullptr;     // routing weights of the own rows, staged for the owners
+    int *x_flag = nullptr;
+    // device time of the exchanges (events around each one, summed by ts2_get_exchange_ms); off unless asked for
+    bool x_timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> x_events;
+    size_t x_events_used = 0;
+    double x_bytes = 0; // bytes this rank sent to other ranks since the last read
     unsigned *absmax = nullptr; // [L+2]
     float *ginv = nullptr, *fscale = nullptr, *logp = nullptr;
     void *workspace = nullptr;
@@ -520,6 +534,10 @@ void ep_plan(int world, int rank, int E, const int *cnt, EpPlan *p, int *max_x_r
     const int per = E / world;
     auto pad = [](int n) { return (n + 127) / 128 * 128; };
     std::vector<int> own_seg(E + 1, 0), total(E, 0), before(E, 0), owner_seg(E, 0);
+    std::vector<int> seg_of((size_t)world * (E + 1), 0); // every rank's own expert-sorted layout
+    for (int s = 0; s < world; ++s)
+        for (int e = 0; e < E; ++e)
+            seg_of[(size_t)s * (E + 1) + e + 1] = seg_of[(size_t)s * (E + 1) + e] + pad(cnt[s * E + e]);
     for (int e = 0; e < E; ++e) {
         own_seg[e + 1] = own_seg[e] + pad(cnt[rank * E + e]);
         for (int s = 0; s < world; ++s) {
@@ -553,7 +571,7 @@ void ep_plan(int world, int rank, int E, const int *cnt, EpPlan *p, int *max_x_r
         for (int s = 0; s < world; ++s) {
             const int n = cnt[s * E + e];
             if (n)
-                p->in.push_back({s, s == rank ? own_seg[e] : -1, pos + off, n});
+                p->in.push_back({s, seg_of[(size_t)s * (E + 1) + e], pos + off, n});
             off += n;
         }
         p->x_valid[e] = off;
@@ -583,6 +601,56 @@ int ep_prepare(ts2_model *m, Layer &ly)
     TS2_CUDA(cudaMemcpyAsync(ly.x_valid, ly.plan.x_valid.data(), (size_t)E * 4, cudaMemcpyHostToDevice, m->stream));
     if (ly.plan.x_rows)
         M_TRY(moe_ep_tables(ctx_of(m), ly.x_seg, ly.x_valid, E, ly.plan.x_rows, ly.x_tile_group, ly.x_token_of));
+    if (m->x_peer) {
+        const size_t n = ly.plan.out.size() + ly.plan.in.size();
+        static_assert(sizeof(EpPlan::Move) == sizeof(int4), "moves are uploaded as they are");
+        if (!ly.plan.out.empty())
+            TS2_CUDA(cudaMemcpyAsync(ly.d_moves, ly.plan.out.data(), ly.plan.out.size() * sizeof(int4), cudaMemcpyHostToDevice, m->stream));
+        if (!ly.plan.in.empty())
+            TS2_CUDA(cudaMemcpyAsync(ly.d_moves + ly.plan.out.size(), ly.plan.in.data(), ly.plan.in.size() * sizeof(int4),
+                                     cudaMemcpyHostToDevice, m->stream));
+        (void)n;
+    }
+    return TS2_OK;
+}
+
+// The same exchange with this library's own copy kernel over peer memory: after a barrier (all ranks have written their
+// side) the rank that needs a block pulls it from the other rank's buffer.  which_remote: the table of the buffer the
+// blocks are read from (the senders' staging buffer on the way to the owners, the owners' result buffer on the way
+// back); the barrier of the next exchange also tells that every rank is done reading this one's sources.
+int ep_exchange_peer(ts2_model *m, const Layer &ly, bool to_owner, int which_remote, void *local, size_t row_bytes, bool zero_pads,
+                     bool barrier = true)
+{
+    const EpPlan &p = ly.plan;
+    cudaStream_t cs = m->stream;
+    std::pair<cudaEvent_t, cudaEvent_t> *ev = nullptr;
+    if (m->x_timing) {
+        if (m->x_events_used == m->x_events.size()) {
+            std::pair<cudaEvent_t, cudaEvent_t> e;
+            TS2_CUDA(cudaEventCreate(&e.first));
+            TS2_CUDA(cudaEventCreate(&e.second));
+            m->x_events.push_back(e);
+        }
+        ev = &m->x_events[m->x_events_used++];
+        TS2_CUDA(cudaEventRecord(ev->first, cs));
+    }
+    if (barrier)
+        M_NCCL(ncclAllReduce(m->x_flag, m->x_flag, 1, ncclInt32, ncclMax, m->comm_x, cs));
+    // on the way to the owners this rank pulls what it receives (plan.in); on the way back what it sent (plan.out)
+    const std::vector<EpPlan::Move> &list = to_owner ? p.in : p.out;
+    const int4 *moves = ly.d_moves + (to_owner ? p.out.size() : 0);
+    long long bytes = 0;
+    for (const EpPlan::Move &mv : list) {
+        bytes += (long long)mv.rows * (long long)row_bytes;
+        if (m->x_timing && mv.peer != m->rank)
+            m->x_bytes += (double)mv.rows * row_bytes; // received = sent, by symmetry of the roles
+    }
+    M_TRY(moe_pull_rows(ctx_of(m), moves, (int)list.size(), m->d_peer + (size_t)which_remote * m->world, local, (int)row_bytes, to_owner,
+                        bytes));
+    if (ev)
+        TS2_CUDA(cudaEventRecord(ev->second, cs));
+    if (to_owner && zero_pads && p.x_rows)
+        M_TRY(moe_zero_pad_rows(ctx_of(m), local, (int)row_bytes, ly.x_seg, ly.x_valid, m->E));
     return TS2_OK;
 }
 
@@ -594,6 +662,20 @@ int ep_exchange(ts2_model *m, const Layer &ly, bool to_owner, void *own, void *x
     const EpPlan &p = ly.plan;
     cudaStream_t cs = m->stream;
     uint8_t *o = (uint8_t *)own, *xx = (uint8_t *)x;
+    std::pair<cudaEvent_t, cudaEvent_t> *ev = nullptr;
+    if (m->x_timing) {
+        if (m->x_events_used == m->x_events.size()) {
+            std::pair<cudaEvent_t, cudaEvent_t> e;
+            TS2_CUDA(cudaEventCreate(&e.first));
+            TS2_CUDA(cudaEventCreate(&e.second));
+            m->x_events.push_back(e);
+        }
+        ev = &m->x_events[m->x_events_used++];
+        TS2_CUDA(cudaEventRecord(ev->first, cs));
+        for (const EpPlan::Move &mv : to_owner ? p.out : p.in)
+            if (mv.peer != m->rank)
+                m->x_bytes += (double)mv.rows * row_bytes;
+    }
     for (const EpPlan::Move &mv : p.in)
         if (mv.peer == m->rank) {
             uint8_t *a = o + (size_t)mv.own_row * row_bytes, *b = xx + (size_t)mv.x_row * row_bytes;
@@ -619,6 +701,8 @@ int ep_exchange(ts2_model *m, const Layer &ly, bool to_owner, void *own, void *x
             M_NCCL(ncclSend(b, (size_t)mv.rows * row_bytes, ncclUint8, mv.peer, m->comm_x, cs));
     }
     M_NCCL(ncclGroupEnd());
+    if (ev)
+        TS2_CUDA(cudaEventRecord(ev->second, cs));
     if (to_owner && zero_pads && p.x_rows)
         M_TRY(moe_zero_pad_rows(ctx_of(m), x, (int)row_bytes, ly.x_seg, ly.x_valid, m->E));
     return TS2_OK;
@@ -1019,8 +1103,14 @@ int forward(ts2_model *m)
                 xrows = ly.plan.x_rows;
                 x_token_of = ly.x_token_of;
                 x_weight_of = ly.x_weight_of;
-                M_TRY(ep_exchange(m, ly, true, m->own_rows, ly.n_rows, D * fs, true));
-                M_TRY(ep_exchange(m, ly, true, ly.weight_of, ly.x_weight_of, 4, false));
+                if (m->x_peer) {
+                    TS2_CUDA(cudaMemcpyAsync(m->own_w, ly.weight_of, (size_t)rows * 4, cudaMemcpyDeviceToDevice, m->stream));
+                    M_TRY(ep_exchange_peer(m, ly, true, ts2_model::PB_OWN_ROWS, ly.n_rows, D * fs, true));
+                    M_TRY(ep_exchange_peer(m, ly, true, ts2_model::PB_OWN_W, ly.x_weight_of, 4, false, false));
+                } else {
+                    M_TRY(ep_exchange(m, ly, true, m->own_rows, ly.n_rows, D * fs, true));
+                    M_TRY(ep_exchange(m, ly, true, ly.weight_of, ly.x_weight_of, 4, false));
+                }
             } else {
                 M_TRY(moe_gather_rows(c, ly.n_fast, ly.token_of, rows, (int)(D * fs), ly.n_rows));
             }
@@ -1031,18 +1121,21 @@ int forward(ts2_model *m)
             Epilogue e2;
             e2.alpha = sqrtf(1.0f / ((float)E * X)) / (m->s_act * 32.f);
             e2.dyn_scale = m->mats[ly.mat0 + 2].sko;
-            e2.out_kind = TS2_OUT_F32;
+            e2.out_kind = m->ep ? TS2_OUT_F16 : TS2_OUT_F32; // expert parallel: the results travel back as fp16
             if (xrows) {
                 M_TRY(gemm_rows_grouped(m, ly, xrows, 2 * X, D, ly.n_rows, D, ly.Wcat, D, ly.cat16, 2 * X, e1));
                 M_TRY(moe_act_forward(c, ly.cat16, x_token_of, x_weight_of, xrows, X, ly.what, ly.wscale, ly.rg));
                 M_TRY(gemm_rows_grouped(m, ly, xrows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
             }
-            const float *y_own = m->moe_y;
             if (m->ep) {
-                M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 4, false));
-                y_own = m->own_y;
+                if (m->x_peer)
+                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, (size_t)D * 2, false));
+                else
+                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 2, false));
+                M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+            } else {
+                M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
             }
-            M_TRY(moe_combine(c, y_own, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
             TRACE("state", l + 1, m->states[l + 1], (size_t)T * D * 4, TR_F32);
             continue;
         }
@@ -1258,7 +1351,10 @@ int backward(ts2_model *m)
             const float *x_weight_of = m->ep ? ly.x_weight_of : ly.weight_of;
             if (m->ep) {
                 M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->own_g));
-                M_TRY(ep_exchange(m, ly, true, m->own_g, m->moe_g, D * fs, true));
+                if (m->x_peer)
+                    M_TRY(ep_exchange_peer(m, ly, true, ts2_model::PB_OWN_G, m->moe_g, D * fs, true));
+                else
+                    M_TRY(ep_exchange(m, ly, true, m->own_g, m->moe_g, D * fs, true));
             } else {
                 M_TRY(moe_gather_rows(c, m->g_fast, ly.token_of, rows, (int)(D * fs), m->moe_g));
             }
@@ -1278,7 +1374,10 @@ int backward(ts2_model *m)
             }
             const float *part_own = m->dmoe_part;
             if (m->ep) {
-                M_TRY(ep_exchange(m, ly, false, m->own_part, m->dmoe_part, (size_t)(X / 128) * 4, false));
+                if (m->x_peer)
+                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_PART, m->own_part, (size_t)(X / 128) * 4, false));
+                else
+                    M_TRY(ep_exchange(m, ly, false, m->own_part, m->dmoe_part, (size_t)(X / 128) * 4, false));
                 part_own = m->own_part;
             }
             M_TRY(moe_router_backward(c, part_own, X / 128, ly.ids, ly.weights, ly.slot_of, T, K, E, m->epad, m->moe_dl));
@@ -1296,15 +1395,18 @@ int backward(ts2_model *m)
             }
             Epilogue e4;
             e4.alpha = sqrtf(1.0f / D) / 32.f;
-            e4.out_kind = TS2_OUT_F32;
+            e4.out_kind = m->ep ? TS2_OUT_F16 : TS2_OUT_F32;
             if (xrows)
                 M_TRY(gemm_rows_grouped(m, ly, xrows, D, 2 * X, m->dcat, 2 * X, ly.WcatT, 2 * X, m->moe_y, D, e4));
-            const float *y_own = m->moe_y;
             if (m->ep) {
-                M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 4, false));
-                y_own = m->own_y;
+                if (m->x_peer)
+                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, (size_t)D * 2, false));
+                else
+                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 2, false));
+                M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, nullptr, m->dn));
+            } else {
+                M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, nullptr, m->dn));
             }
-            M_TRY(moe_combine(c, y_own, ly.slot_of, T, K, D, nullptr, m->dn));
             if (tune_layers && xrows) {
                 Epilogue e5;
                 e5.alpha = 1.f / m->s_act;
@@ -1661,12 +1763,28 @@ void ts2_destroy(ts2_model *m)
         return;
     cudaSetDevice(m->device);
     cudaDeviceSynchronize();
+    if (m->x_peer && m->comm_x) {
+        // other ranks may still be reading this rank's exchange buffers: meet them once more before anything is freed
+        // (bounded: a rank that is gone must not keep this one here)
+        if (ncclAllReduce(m->x_flag, m->x_flag, 1, ncclInt32, ncclMax, m->comm_x, m->stream) == ncclSuccess) {
+            const auto t0 = std::chrono::steady_clock::now();
+            while (cudaStreamQuery(m->stream) == cudaErrorNotReady &&
+                   std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() < 10.0)
+                std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        }
+    }
+    for (void *p : m->ipc_opened)
+        cudaIpcCloseMemHandle(p);
     if (m->comm_x)
         ncclCommDestroy(m->comm_x);
     if (m->comm)
         ncclCommDestroy(m->comm);
     if (m->h_cnt)
         cudaFreeHost(m->h_cnt);
+    for (auto &e : m->x_events) {
+        cudaEventDestroy(e.first);
+        cudaEventDestroy(e.second);
+    }
     for (void *p : m->allocs)
         cudaFree(p);
     if (m->pinned)
@@ -2178,6 +2296,63 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
     return TS2_OK;
 }
 
+// Maps the exchange buffers of every other rank into this process (CUDA IPC handles travel through an all-gather) and
+// puts the base pointers, this rank's own among them, in a device table.  All ranks agree on the outcome: where any
+// rank cannot map a buffer, every rank keeps the ncclSend / ncclRecv exchange (TS2_EP_EXCHANGE=nccl asks for that).
+static int ep_map_peers(ts2_model *m)
+{
+    const int N = m->world, NB = ts2_model::PB_COUNT;
+    void *local[NB] = {m->own_rows, m->own_g, m->own_w, m->moe_y, m->dmoe_part};
+    const char *mode = getenv("TS2_EP_EXCHANGE");
+    int ok = !(mode && std::string(mode) == "nccl");
+    std::vector<cudaIpcMemHandle_t> all((size_t)N * NB);
+    cudaIpcMemHandle_t mine[NB];
+    memset(mine, 0, sizeof(mine));
+    for (int k = 0; k < NB && ok; ++k)
+        if (cudaIpcGetMemHandle(&mine[k], local[k]) != cudaSuccess) {
+            cudaGetLastError();
+            ok = 0;
+        }
+    uint8_t *d_h = nullptr;
+    const size_t hb = sizeof(mine);
+    M_TRY(dalloc(m, &d_h, hb * (N + 1) + 16));
+    TS2_CUDA(cudaMemcpy(d_h + hb * N, mine, hb, cudaMemcpyHostToDevice));
+    M_NCCL(ncclAllGather(d_h + hb * N, d_h, hb, ncclUint8, m->comm_x, m->stream));
+    int *d_ok = (int *)(d_h + hb * (N + 1));
+    TS2_CUDA(cudaMemcpyAsync(d_ok, &ok, 4, cudaMemcpyHostToDevice, m->stream));
+    M_NCCL(ncclAllReduce(d_ok, d_ok, 1, ncclInt32, ncclMin, m->comm_x, m->stream));
+    TS2_CUDA(cudaStreamSynchronize(m->stream));
+    TS2_CUDA(cudaMemcpy(all.data(), d_h, hb * N, cudaMemcpyDeviceToHost));
+    TS2_CUDA(cudaMemcpy(&ok, d_ok, 4, cudaMemcpyDeviceToHost));
+    std::vector<uint8_t *> table((size_t)NB * N, nullptr);
+    for (int r = 0; r < N && ok; ++r)
+        for (int k = 0; k < NB && ok; ++k) {
+            if (r == m->rank) {
+                table[(size_t)k * N + r] = (uint8_t *)local[k];
+                continue;
+            }
+            void *ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, all[(size_t)r * NB + k], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                ok = 0;
+                break;
+            }
+            m->ipc_opened.push_back(ptr);
+            table[(size_t)k * N + r] = (uint8_t *)ptr;
+        }
+    // every rank must have opened everything
+    TS2_CUDA(cudaMemcpyAsync(d_ok, &ok, 4, cudaMemcpyHostToDevice, m->stream));
+    M_NCCL(ncclAllReduce(d_ok, d_ok, 1, ncclInt32, ncclMin, m->comm_x, m->stream));
+    TS2_CUDA(cudaStreamSynchronize(m->stream));
+    TS2_CUDA(cudaMemcpy(&ok, d_ok, 4, cudaMemcpyDeviceToHost));
+    if (ok) {
+        M_TRY(dalloc(m, &m->d_peer, (size_t)NB * N));
+        TS2_CUDA(cudaMemcpy(m->d_peer, table.data(), table.size() * sizeof(uint8_t *), cudaMemcpyHostToDevice));
+    }
+    m->x_peer = ok != 0;
+    return TS2_OK;
+}
+
 int ts2_set_expert_parallel(ts2_model *m, float capacity_factor)
 {
     if (!m)
@@ -2238,7 +2413,38 @@ int ts2_set_expert_parallel(ts2_model *m, float capacity_factor)
     M_TRY(dalloc(m, &m->cnt_own, (size_t)m->E));
     M_TRY(dalloc(m, &m->cnt_all, (size_t)m->E * m->world));
     TS2_CUDA(cudaMallocHost(&m->h_cnt, (size_t)m->E * m->world * 4));
+    M_TRY(dalloc(m, &m->own_w, own_rows));
+    M_TRY(dalloc(m, &m->x_flag, 1));
+    TS2_CUDA(cudaMemset(m->x_flag, 0, 4));
+    for (Layer &ly : m->layers)
+        if (ly.type == TS2_LAYER_MOE)
+            M_TRY(dalloc(m, &ly.d_moves, (size_t)m->E * (m->world + 1)));
+    M_TRY(ep_map_peers(m));
     m->ep = true;
+    return TS2_OK;
+}
+
+int ts2_get_exchange_ms(ts2_model *m, int enable, float *ms, double *bytes_sent, int *exchanges)
+{
+    if (!m)
+        return TS2_ERR_INVALID_ARG;
+    TS2_CUDA(cudaSetDevice(m->device));
+    M_TRY(wait_stream(m));
+    float total = 0.f;
+    for (size_t i = 0; i < m->x_events_used; ++i) {
+        float t = 0.f;
+        TS2_CUDA(cudaEventElapsedTime(&t, m->x_events[i].first, m->x_events[i].second));
+        total += t;
+    }
+    if (ms)
+        *ms = total;
+    if (bytes_sent)
+        *bytes_sent = m->x_bytes;
+    if (exchanges)
+        *exchanges = (int)m->x_events_used;
+    m->x_events_used = 0;
+    m->x_bytes = 0;
+    m->x_timing = enable != 0;
     return TS2_OK;
 }
 

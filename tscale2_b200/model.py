@@ -203,6 +203,12 @@ class Model:
         the (token, choice) rows travel to the experts' owners and back (ts2_set_expert_parallel)."""
         self._check(self.lib.ts2_set_expert_parallel(self.h, capacity_factor))
 
+    def exchange_timing(self, enable=True):
+        """(ms, bytes sent to other ranks, exchanges) of the expert-parallel row exchanges since the last call."""
+        ms, nbytes, n = C.c_float(), C.c_double(), C.c_int()
+        self._check(self.lib.ts2_get_exchange_ms(self.h, int(enable), C.byref(ms), C.byref(nbytes), C.byref(n)))
+        return ms.value, nbytes.value, n.value
+
     def last_step_ms(self):
         v = C.c_float()
         self._check(self.lib.ts2_last_step_ms(self.h, C.byref(v)))
