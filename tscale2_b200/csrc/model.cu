@@ -632,10 +632,14 @@ int ep_exchange_peer(ts2_model *m, const Layer &ly, bool to_owner, int which_rem
             m->x_events.push_back(e);
         }
         ev = &m->x_events[m->x_events_used++];
-        TS2_CUDA(cudaEventRecord(ev->first, cs));
     }
+    static const bool copy_only = getenv("TS2_EP_TIME_COPY_ONLY") != nullptr; // leave the barrier out of the timed part
+    if (ev && !copy_only)
+        TS2_CUDA(cudaEventRecord(ev->first, cs));
     if (barrier)
         M_NCCL(ncclAllReduce(m->x_flag, m->x_flag, 1, ncclInt32, ncclMax, m->comm_x, cs));
+    if (ev && copy_only)
+        TS2_CUDA(cudaEventRecord(ev->first, cs));
     // on the way to the owners this rank pulls what it receives (plan.in); on the way back what it sent (plan.out)
     const std::vector<EpPlan::Move> &list = to_owner ? p.in : p.out;
     const int4 *moves = ly.d_moves + (to_owner ? p.out.size() : 0);
