@@ -97,6 +97,10 @@ struct Bucket {
     int mat0 = 0, mat1 = 0;    // matrices [mat0, mat1)
     int qsize = 1;             // bytes per quantized element
     uint8_t *qflat = nullptr;  // row-major quantized copies of the bucket's matrices, in flat order (elems * qsize bytes)
+    // one expert matrix of a mixture-of-experts layer ([E x rows][cols]: an expert is a row range, so the r-th of N parts
+    // of the bucket is exactly the experts of rank r)
+    bool expert_matrix = false;
+    bool owner_only = false; // expert parallel: the owner holds the complete gradient of its part, nothing is exchanged
 };
 
 struct BatchDev {
@@ -448,14 +452,28 @@ void layout_buckets(const ts2_model_descr *d, const std::vector<std::pair<int64_
                     std::vector<size_t> *mat_off, std::vector<int> *mat_bucket)
 {
     const int n_mats = (int)shapes.size();
+    // buckets: embedding, final layer, one per layer; a mixture-of-experts layer has one per matrix (expand, gate,
+    // contract, select)
     std::vector<int> first = {0, 1};
+    std::vector<bool> expert = {false, false};
     int mi = 2;
     for (int l = 0; l < d->layer_count; ++l) {
-        first.push_back(mi);
-        mi += layer_matrix_count(d->layers[l].layer_type);
+        const int n = layer_matrix_count(d->layers[l].layer_type);
+        if (d->layers[l].layer_type == TS2_LAYER_MOE) {
+            for (int j = 0; j < n; ++j) {
+                first.push_back(mi + j);
+                expert.push_back(j < 3);
+            }
+        } else {
+            first.push_back(mi);
+            expert.push_back(false);
+        }
+        mi += n;
     }
     first.push_back(n_mats);
     buckets->assign(first.size() - 1, Bucket());
+    for (size_t b = 0; b + 1 < first.size(); ++b)
+        (*buckets)[b].expert_matrix = expert[b];
     mat_off->assign(n_mats, 0);
     mat_bucket->assign(n_mats, 0);
     size_t off = 0;
@@ -723,8 +741,10 @@ int post_quantize(ts2_model *m)
     const float a = sqrtf(1.0f / D) / (m->s_act * 32.f);
     for (Layer &ly : m->layers) {
         const int W = ly.wide, n = ly.ncat;
-        const Bucket &bk = m->buckets[m->mat_bucket[ly.mat0]];
-        auto qsrc = [&](int mat) { return bk.qflat + (m->mats[mat].offset - bk.off) * fs; };
+        auto qsrc = [&](int mat) {
+            const Bucket &bk = m->buckets[m->mat_bucket[mat]];
+            return bk.qflat + (m->mats[mat].offset - bk.off) * fs;
+        };
         if (ly.type == TS2_LAYER_MOE) {
             // the flat order keeps each matrix whole ([E X][D] expand, gate; [E D][X] contract); the contractions want
             // the blocks of one expert together: Wcat [E][2X][D], WcatT [E][D][2X], Wc [E][D][X], WcT [E][X][D]
@@ -1243,16 +1263,21 @@ int tap_gradient(ts2_model *m, int boundary)
 // data-parallel sum of the gradient of the bucket that starts at matrix m0, on the communication stream, ordered
 // after what the main stream has queued so far; the backward pass goes on meanwhile.  Reduce-scatter: every rank
 // receives the sum for the 1 / world part of the bucket it will update (in place: the part sits where it was).
-static int reduce_matrices(ts2_model *m, int m0, int)
+// gradients of the matrices [m0, m1) (whole buckets) are complete: reduce-scatter their buckets
+static int reduce_matrices(ts2_model *m, int m0, int m1)
 {
     if (!m->reduce_in_backward)
         return TS2_OK;
-    const Bucket &bk = m->buckets[m->mat_bucket[m0]];
-    const size_t part = bk.elems / m->world;
     TS2_CUDA(cudaEventRecord(m->ev_grads, m->stream));
     TS2_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_grads, 0));
-    M_NCCL(ncclReduceScatter(m->grad_flat + bk.off, m->grad_flat + bk.off + part * m->rank, part, ncclFloat, ncclSum, m->comm,
-                             m->comm_stream));
+    for (int b = m->mat_bucket[m0]; b < (int)m->buckets.size() && m->buckets[b].mat0 < m1; ++b) {
+        const Bucket &bk = m->buckets[b];
+        if (bk.owner_only)
+            continue; // expert parallel: this rank's part is its own experts, whose gradient arose here in full
+        const size_t part = bk.elems / m->world;
+        M_NCCL(ncclReduceScatter(m->grad_flat + bk.off, m->grad_flat + bk.off + part * m->rank, part, ncclFloat, ncclSum, m->comm,
+                                 m->comm_stream));
+    }
     return TS2_OK;
 }
 
@@ -1532,6 +1557,8 @@ int apply(ts2_model *m, const ts2_training_step *step)
     if (dp) {
         M_NCCL(ncclGroupStart());
         for (const Bucket &bk : m->buckets) {
+            if (bk.owner_only)
+                continue; // a rank only reads the quantized weights of its own experts
             const size_t part = bk.elems / m->world * bk.qsize;
             ncclResult_t r = ncclAllGather(bk.qflat + part * m->rank, bk.qflat, part, ncclUint8, m->comm, m->stream);
             if (r != ncclSuccess) {
@@ -2424,6 +2451,15 @@ int ts2_set_expert_parallel(ts2_model *m, float capacity_factor)
         if (ly.type == TS2_LAYER_MOE)
             M_TRY(dalloc(m, &ly.d_moves, (size_t)m->E * (m->world + 1)));
     M_TRY(ep_map_peers(m));
+    // the expert matrices stop travelling: rank r's part of such a bucket is the rows of its experts (no padding, whole
+    // experts per part), their gradient arises there in full and only that rank reads their quantized weights
+    for (Bucket &bk : m->buckets) {
+        if (!bk.expert_matrix)
+            continue;
+        const Matrix &mt = m->mats[bk.mat0];
+        const size_t per_expert = (size_t)mt.x * mt.y / m->E;
+        bk.owner_only = bk.mat1 == bk.mat0 + 1 && bk.elems == (size_t)mt.x * mt.y && (bk.elems / m->world) % per_expert == 0;
+    }
     m->ep = true;
     return TS2_OK;
 }

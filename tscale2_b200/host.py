@@ -99,7 +99,7 @@ def dp_layout(spec: ModelSpec):
     lib = capi.load_library()
     descr, keep = spec.to_c()
     n = len(spec.matrix_shapes())
-    nb = 2 + len(spec.layers)
+    nb = 2 + sum(4 if l.layer_type == capi.LAYER_MOE else 1 for l in spec.layers)
     mo, bo, be = np.zeros(n, np.int64), np.zeros(nb, np.int64), np.zeros(nb, np.int64)
     bf = np.zeros(nb, np.int32)
     p64 = C.POINTER(C.c_int64)
