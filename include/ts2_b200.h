@@ -249,7 +249,8 @@ const char *ts2_debug_trace_name(ts2_model *m, int index);
  * (TS2_PARAM_GRADIENT) after an applied step holds the summed gradient in the rank's own parts and the rank's local
  * gradient elsewhere. */
 /* Layout of the data-parallel exchange, computable without a device.  The engine keeps weights, momentum and gradient
- * in flat fp32 buffers: the matrices in the order above, grouped into buckets (embedding; final layer; one per layer)
+ * in flat fp32 buffers: the matrices in the order above, grouped into buckets (embedding; final layer; one per layer,
+ * but one per matrix in a mixture-of-experts layer, so that a rank's part of an expert matrix is whole experts)
  * whose lengths are padded to a multiple of 1024 elements.  With world_size ranks, rank r owns elements
  * [bucket_offset[b] + r * bucket_elems[b] / world_size, + bucket_elems[b] / world_size) of every bucket b: a step
  * reduce-scatters each bucket's gradient onto those parts (as soon as the backward pass has written the bucket),
