@@ -360,7 +360,9 @@ def main():
         dist.broadcast_object_list(ids, src=0)
         model.comm_init(rank, world, ids[0])
         if "experts" in w and args.expert_parallel and w["experts"] % world == 0:
-            model.set_expert_parallel()
+            # capacity = the worst case (every row of every rank on one rank): the synthetic router (weights N(0, 1), no
+            # balancing term) sends up to ~3x a rank's share to the most popular experts
+            model.set_expert_parallel(float(world))
             config["parallelism"] = f"dp{world} x ep{world} (experts divided over the ranks, rows exchanged with ncclSend / ncclRecv)"
 
     def barrier():

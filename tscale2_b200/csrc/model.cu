@@ -1145,18 +1145,26 @@ int forward(ts2_model *m)
             Epilogue e2;
             e2.alpha = sqrtf(1.0f / ((float)E * X)) / (m->s_act * 32.f);
             e2.dyn_scale = m->mats[ly.mat0 + 2].sko;
-            e2.out_kind = m->ep ? TS2_OUT_F16 : TS2_OUT_F32; // expert parallel: the results travel back as fp16
+            // expert parallel, e4m3 pipeline: the results travel back as fp16 (half the bytes of the largest message).  The
+            // fp16 pipeline keeps fp32: a perturbation of 1e-4 of the states flips the expert choice of borderline tokens
+            // in the layers above, and that pipeline is the one held to the single-process result.
+            const bool y16 = m->ep && m->ft == 0;
+            e2.out_kind = y16 ? TS2_OUT_F16 : TS2_OUT_F32;
             if (xrows) {
                 M_TRY(gemm_rows_grouped(m, ly, xrows, 2 * X, D, ly.n_rows, D, ly.Wcat, D, ly.cat16, 2 * X, e1));
                 M_TRY(moe_act_forward(c, ly.cat16, x_token_of, x_weight_of, xrows, X, ly.what, ly.wscale, ly.rg));
                 M_TRY(gemm_rows_grouped(m, ly, xrows, D, X, ly.rg, X, ly.Wc, X, m->moe_y, D, e2));
             }
             if (m->ep) {
+                const size_t yb = (size_t)D * (y16 ? 2 : 4);
                 if (m->x_peer)
-                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, (size_t)D * 2, false));
+                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, yb, false));
                 else
-                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 2, false));
-                M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, yb, false));
+                if (y16)
+                    M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
+                else
+                    M_TRY(moe_combine(c, m->own_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
             } else {
                 M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, m->states[l], m->states[l + 1]));
             }
@@ -1424,15 +1432,20 @@ int backward(ts2_model *m)
             }
             Epilogue e4;
             e4.alpha = sqrtf(1.0f / D) / 32.f;
-            e4.out_kind = m->ep ? TS2_OUT_F16 : TS2_OUT_F32;
+            const bool y16 = m->ep && m->ft == 0;
+            e4.out_kind = y16 ? TS2_OUT_F16 : TS2_OUT_F32;
             if (xrows)
                 M_TRY(gemm_rows_grouped(m, ly, xrows, D, 2 * X, m->dcat, 2 * X, ly.WcatT, 2 * X, m->moe_y, D, e4));
             if (m->ep) {
+                const size_t yb = (size_t)D * (y16 ? 2 : 4);
                 if (m->x_peer)
-                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, (size_t)D * 2, false));
+                    M_TRY(ep_exchange_peer(m, ly, false, ts2_model::PB_MOE_Y, m->own_y, yb, false));
                 else
-                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, (size_t)D * 2, false));
-                M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, nullptr, m->dn));
+                    M_TRY(ep_exchange(m, ly, false, m->own_y, m->moe_y, yb, false));
+                if (y16)
+                    M_TRY(moe_combine_half(c, (const __half *)m->own_y, ly.slot_of, T, K, D, nullptr, m->dn));
+                else
+                    M_TRY(moe_combine(c, m->own_y, ly.slot_of, T, K, D, nullptr, m->dn));
             } else {
                 M_TRY(moe_combine(c, m->moe_y, ly.slot_of, T, K, D, nullptr, m->dn));
             }
