@@ -29,7 +29,7 @@ def build(reference="/root/reference"):
     """Compile the restatement, and the reference-linked variant where the reference tree exists."""
     subprocess.check_call(["make", "-s", "-C", _HERE])
     if os.path.isdir(os.path.join(reference, "src")):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "ckpt", f"REFERENCE={reference}"])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "ckpt", "opt", f"REFERENCE={reference}"])
 
 
 _fp = C.POINTER(C.c_float)
@@ -231,3 +231,28 @@ class Oracle:
 
 def have_reference_build():
     return os.path.exists(REF_PATH)
+
+
+OPT_REF_PATH = os.path.join(_HERE, "_ref", "libts2_opt_ref.so")
+
+
+def reference_add_delta(weights, avg_grad, grad, row_disp, sum_weight, sparsity, step):
+    """The reference's own host-side optimizer step, THostModelMatrix::AddDelta (src/gpt/matrix/host_matrix.cpp:123-157),
+    compiled from its sources (oracle/opt_ref.cpp).  The gradient goes in as fp32 and is put into the reference's delta
+    form (fp16 values times a power-of-two scale per row).  Returns (weights, avg_grad, row_disp, sum_weight, sum2,
+    grad_seen): grad_seen is the gradient as the reference then sees it - feed THAT to a restatement under test."""
+    lib = C.CDLL(OPT_REF_PATH)
+    w = np.ascontiguousarray(weights, np.float32).copy()
+    ag = np.ascontiguousarray(avg_grad, np.float32).copy()
+    g = np.ascontiguousarray(grad, np.float32)
+    rd = np.ascontiguousarray(row_disp, np.float32).copy()
+    seen = np.zeros_like(g)
+    sw, sum2 = C.c_float(sum_weight), C.c_float()
+    y, x = w.shape
+    lib.ts2ref_add_delta.argtypes = [_fp, _fp, _fp, C.c_longlong, C.c_longlong, _fp, C.c_longlong, _fp] + [C.c_float] * 7 + [_fp, _fp]
+    lib.ts2ref_add_delta.restype = C.c_int
+    rc = lib.ts2ref_add_delta(_f(w), _f(ag), _f(g), x, y, _f(rd), len(rd), C.cast(C.byref(sw), _fp), sparsity, step.rate, step.l2reg,
+                              step.beta1, step.weight0, step.weight1, step.disp_decay, _f(seen), C.cast(C.byref(sum2), _fp))
+    if rc != 0:
+        raise ValueError("ts2ref_add_delta: x must be a multiple of 8 and row_disp must divide the rows")
+    return w, ag, rd, sw.value, sum2.value, seen

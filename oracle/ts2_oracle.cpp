@@ -856,7 +856,8 @@ int ts2o_backprop(const ts2_model_descr *descr, const ts2_matrix_view *mats, int
     return TS2_OK;
 }
 
-// MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel, agpu_cuda.cu:32-134
+// MatrixRowSum2Kernel + UpdateGlobalRowDisp + AddGradientKernel, agpu_cuda.cu:32-134; the same step on the host:
+// THostModelMatrix::AddDelta, host_matrix.cpp:123-157, against which tests/test_optimizer_vs_reference.py checks this
 int ts2o_apply_gradient(float *weights, float *avg_grad, const float *grad, int64_t x_size, int64_t y_size, float *row_disp,
                         int64_t row_disp_size, float *sum_weight, float sparsity, const ts2_training_step *step)
 {
