@@ -215,3 +215,15 @@ void B200CommInit(IModel *model, yint rank, yint rankCount, const ui8 *id)
         abort();
     }
 }
+
+// mixture-of-experts models: after B200CommInit on every rank, divides the experts over the ranks (the counterpart of
+// TCudaMoELayer::GetExpertSpan over a device group, src/gpt/compute/layer_moe.cu:52-66); capacityFactor 0 = default
+void B200SetExpertParallel(IModel *model, float capacityFactor)
+{
+    TB200Model *m = dynamic_cast<TB200Model *>(model);
+    Y_VERIFY(m && "not a B200 model");
+    if (ts2_set_expert_parallel(m->GetHandle(), capacityFactor) != TS2_OK) {
+        DebugPrintf("ts2_b200: %s\n", ts2_last_error(m->GetHandle()));
+        abort();
+    }
+}
