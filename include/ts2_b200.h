@@ -272,7 +272,15 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
  * experts over the devices of a device group that all see the same tokens (GetExpertSpan / AllGatherMoe / ReduceMoe,
  * src/gpt/compute/layer_moe.cu:52-66,170,231); with one process per GPU and different tokens on every rank that becomes
  * this exchange.  capacity_factor (1 .. world size; 0 = the default 2): a rank can receive up to that many times its own
- * number of rows; a step that needs more fails on every rank with TS2_ERR_TOO_LARGE. */
+ * number of rows; a step that needs more fails on every rank with TS2_ERR_TOO_LARGE.
+ * The rows travel through the library's own copy kernel over peer memory: the staging buffers of all ranks are mapped
+ * into every process with CUDA IPC (one node), a 4-byte all-reduce is the barrier before each copy; where a buffer
+ * cannot be mapped, or with TS2_EP_EXCHANGE=nccl, all ranks use ncclSend / ncclRecv on the same blocks instead.
+ * In the e4m3 pipeline the experts' results return as fp16 rows, in the fp16 pipeline as fp32.
+ * The three expert matrices of a layer are buckets of their own (ts2_dp_layout) whose r-th part is rank r's experts:
+ * they are neither reduce-scattered nor all-gathered any more.
+ * After this call ts2_forward_score is a collective call like ts2_backprop (every forward pass exchanges rows), and
+ * ts2_destroy must be called by all ranks (it meets the others once more before the mapped buffers are freed). */
 int ts2_set_expert_parallel(ts2_model *m, float capacity_factor);
 /* Measurement hook: device time (events around every row exchange on the compute stream), bytes this rank sent to
  * other ranks and number of exchanges since the last call; enable switches the recording on or off from now on. */
