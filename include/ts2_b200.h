@@ -271,7 +271,7 @@ int ts2_comm_init(ts2_model *m, int rank, int world_size, const uint8_t id[TS2_C
  * arises complete on its owner.  The counts are read on the host once per layer and step.  The reference splits
  * experts over the devices of a device group that all see the same tokens (GetExpertSpan / AllGatherMoe / ReduceMoe,
  * src/gpt/compute/layer_moe.cu:52-66,170,231); with one process per GPU and different tokens on every rank that becomes
- * this exchange.  capacity_factor (1 .. world size; 0 = the default 2): a rank can receive up to that many times its own
+ * this exchange.  capacity_factor (1 .. world size; 0 = the default, min(world size, 4)): a rank can receive up to that many times its own
  * number of rows; a step that needs more fails on every rank with TS2_ERR_TOO_LARGE.
  * The rows travel through the library's own copy kernel over peer memory: the staging buffers of all ranks are mapped
  * into every process with CUDA IPC (one node), a 4-byte all-reduce is the barrier before each copy; where a buffer

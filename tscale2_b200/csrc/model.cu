@@ -2410,7 +2410,7 @@ int ts2_set_expert_parallel(ts2_model *m, float capacity_factor)
     if (m->E % m->world)
         return fail(TS2_ERR_UNSUPPORTED, "%d experts do not divide over %d ranks", m->E, m->world);
     if (!(capacity_factor >= 1.f) || capacity_factor > (float)m->world)
-        capacity_factor = std::min(2.f, (float)m->world);
+        capacity_factor = std::min(4.f, (float)m->world); // a router without a balancing term sent 2.9x to one of 4 ranks
     TS2_CUDA(cudaSetDevice(m->device));
     M_TRY(sync_master(m));
     TS2_CUDA(cudaDeviceSynchronize());
