@@ -229,3 +229,50 @@ def test_malformed_batches_are_reported_and_harmless(what, code):
     model.backprop(host.training_step(), apply=False)
     model.wait()
     assert np.isfinite(model.avg_train_err())
+
+
+def _tiny_batch(spec, T, n_targets, rng):
+    """One fragment of T nodes, one label per node, causal spans of width 32, targets on the first n_targets nodes."""
+    label_arr = rng.integers(1, spec.label_count, T).astype(np.uint32)
+    label_ptr = np.arange(T + 1, dtype=np.uint32)
+    t = np.arange(T)
+    start, finish = np.maximum(0, t - 32).astype(np.int32), (t - 1).astype(np.int32)
+    has = finish >= start
+    ptr = np.concatenate([[0], np.cumsum(has)]).astype(np.int32)
+    target_node = np.arange(n_targets, dtype=np.int32)
+    target_id = rng.integers(0, spec.vocab, n_targets).astype(np.int32)
+    return host.Batch.from_arrays(T, label_arr, label_ptr, target_node, target_id, [(start[has], finish[has], ptr)])
+
+
+@pytest.mark.parametrize("T,n_targets", [(1, 1), (2, 0), (5, 5), (129, 3), (257, 0)])
+def test_smallest_and_targetless_batches_match_the_oracle(oracle_port, T, n_targets):
+    """Edge cases of the batch: a single node (no span at all), sizes next to a tile border, no target anywhere (every
+    gradient is exactly zero and the training error is 0, not NaN)."""
+    spec = small_spec(vocab=512)
+    rng = np.random.default_rng(T * 10 + n_targets)
+    batch = _tiny_batch(spec, T, n_targets, rng)
+    mats = host.init_weights(spec, 4)
+    ref = oracle_port.backprop(spec, mats, batch, oracle.QUANT_HALF, want_states=True)
+    model = Model(spec, mats, max(T, 4))
+    model.set_debug_taps(True)
+    model.set_batch(batch)
+    model.backprop(host.training_step(), apply=False)
+    model.wait()
+    L = len(spec.layers)
+    assert np.linalg.norm(model.get_state_tap(L, False, T) - ref["states"][L]) <= 2e-3 * np.linalg.norm(ref["states"][L])
+    err = model.avg_train_err()
+    assert np.isfinite(err)
+    for name, g, r in zip(spec.matrix_names(), model.get_gradients(), ref["grads"]):
+        assert np.isfinite(g).all(), name
+        if n_targets == 0:
+            assert not g.any() and not r.any(), name
+        else:
+            assert np.linalg.norm(g.astype(np.float64) - r) <= 5e-3 * max(np.linalg.norm(r), 1e-30), name
+    if n_targets == 0:
+        assert err == 0.0
+    else:
+        assert abs(-err - ref["score"]) < 2e-3
+    # and an applied step on such a batch leaves finite weights
+    model.backprop(host.training_step(), apply=True)
+    model.wait()
+    assert all(np.isfinite(w).all() for w in model.get_weights())
