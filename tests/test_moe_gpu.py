@@ -113,3 +113,24 @@ def test_moe_step_applies_and_trains(oracle_port):
         model.backprop(host.training_step(rate=0.02, iteration=i), apply=True)
         errs.append(model.avg_train_err())
     assert errs[-1] < errs[0] - 0.05, errs
+
+
+def test_experts_without_rows(oracle_port):
+    """32 experts, 2 selected, 24 nodes: most experts receive no row at all (empty segments of the grouped
+    contractions, weight gradients that must stay exactly zero), a few receive one or two."""
+    s = host.ModelSpec(dim=128, head_count=1, ffn_tiles=2, vocab=256, attention_widths=[16], expert_dim=128,
+                       moe_expert_count=32, moe_selected=2, precision=capi.PREC_F16)
+    spec = s.add_blocks(1, moe=True)
+    mats = host.init_weights(spec, 11, select_std=1.0)
+    batch = host.synthetic_batch(spec, 2, 12, 12)
+    ref = oracle_port.backprop(spec, mats, batch, oracle.QUANT_HALF, want_states=True)
+    model = _moe_engine(spec, mats, batch)
+    names = spec.matrix_names()
+    grads = model.get_gradients()
+    for name, g, r in zip(names, grads, ref["grads"]):
+        assert rel_l2(g, r) < 5e-3, name
+    X, D, E = 128, 128, 32
+    expand = grads[names.index("L1.moe.expand")].reshape(E, X, D)
+    used = np.array([expand[e].any() for e in range(E)])
+    ref_used = np.array([ref["grads"][names.index("L1.moe.expand")].reshape(E, X, D)[e].any() for e in range(E)])
+    assert np.array_equal(used, ref_used) and 0 < used.sum() < E, "the same experts are touched, and some are not"
