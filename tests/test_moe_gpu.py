@@ -134,3 +134,26 @@ def test_experts_without_rows(oracle_port):
     used = np.array([expand[e].any() for e in range(E)])
     ref_used = np.array([ref["grads"][names.index("L1.moe.expand")].reshape(E, X, D)[e].any() for e in range(E)])
     assert np.array_equal(used, ref_used) and 0 < used.sum() < E, "the same experts are touched, and some are not"
+
+
+def test_expert_matrices_step_with_their_sparsity(oracle_port):
+    """The applied step of every matrix of a mixture-of-experts model against the restated optimizer on the engine's own
+    gradient: the expert matrices move by rate x sqrt(selected / experts) (TModelMatrix::Sparsity), the others by rate."""
+    spec = moe_spec(capi.PREC_F16)
+    mats = host.init_weights(spec, 5, select_std=1.0)
+    batch = host.synthetic_batch(spec, 3, 40, 6)
+    model = Model(spec, mats, batch.node_count)
+    model.set_batch(batch)
+    step = host.training_step(rate=0.01, l2reg=0.05, iteration=2)
+    model.backprop(step, apply=False)
+    g = model.get_gradients()
+    model.discard_gradient()
+    model.backprop(step, apply=True)
+    new_w, mom = model.get_weights(), model.get_momentum()
+    sparsity = spec.matrix_sparsity()
+    assert sorted(set(sparsity)) == [0.5, 1.0]
+    for i, (name, w0) in enumerate(zip(spec.matrix_names(), mats)):
+        n_disp = w0.shape[0] if i < 2 else 1
+        w_ref, ag_ref, _, _ = oracle_port.apply_gradient(w0, np.zeros_like(w0), g[i], np.zeros(n_disp, np.float32), 0.0, sparsity[i], step)
+        assert rel_l2(new_w[i] - w0, w_ref - w0) < 1e-4, name
+        assert rel_l2(mom[i], ag_ref) < 1e-4, name

@@ -160,9 +160,10 @@ def from_model(model, bias=None, **kw) -> ModelFile:
     """Snapshot of an engine (tscale2_b200.model.Model): weights, momentum, dispersion of every matrix (GetParams)."""
     w, g = model.get_weights(), model.get_momentum()
     mats = []
+    sparsity = model.spec.matrix_sparsity()
     for i, (a, b) in enumerate(zip(w, g)):
         rd, sw = model.get_row_disp(i)
-        mats.append(MatrixState(a, b, sw, rd, 1.0))
+        mats.append(MatrixState(a, b, sw, rd, sparsity[i]))
     vocab = model.spec.vocab
     return ModelFile(model.spec, mats, np.zeros(vocab, np.float32) if bias is None else np.asarray(bias, np.float32),
                      input_token_count=kw.pop("input_token_count", vocab), **kw)

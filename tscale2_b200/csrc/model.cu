@@ -893,6 +893,10 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
         if (ly.type == TS2_LAYER_MOE) {
             has_moe = true;
             const size_t E = m->E, X = m->X, R = m->moe_rows;
+            // an expert sees the fraction selected / experts of the tokens: the reference scales the step of the expert
+            // matrices by the square root of it (moeFraction, EnumLayerMatrices, model_dim.h:230,252-254; host_matrix.cpp:40)
+            for (int j = 0; j < 3; ++j)
+                m->mats[ly.mat0 + j].sparsity = (float)m->K / (float)m->E;
             M_TRY(dalloc(m, (uint8_t **)&ly.Wcat, E * 2 * X * D * fs));
             M_TRY(dalloc(m, (uint8_t **)&ly.WcatT, E * 2 * X * D * fs));
             M_TRY(dalloc(m, (uint8_t **)&ly.Wc, E * X * D * fs));

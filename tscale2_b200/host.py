@@ -78,6 +78,17 @@ class ModelSpec:
                 names += [f"L{i}.moe.{n}" for n in ("expand", "gate", "contract", "select")]
         return names
 
+    def matrix_sparsity(self) -> List[float]:
+        """Fraction of the tokens a matrix sees (TModelMatrix::Sparsity; EnumLayerMatrices, model_dim.h:230,252-254):
+        selected / experts for the expert matrices of a mixture-of-experts layer, 1 elsewhere."""
+        out = [1.0, 1.0]
+        for l in self.layers:
+            if l.layer_type == capi.LAYER_MOE:
+                out += [self.moe_selected / self.moe_expert_count] * 3 + [1.0]
+            else:
+                out += [1.0] * (5 if l.layer_type == capi.LAYER_ATT else 3)
+        return out
+
     def param_count(self) -> int:
         return sum(a * b for a, b in self.matrix_shapes())
 
