@@ -62,6 +62,13 @@ def test_description_is_validated_without_a_device(lib):
     d3, k3 = spec.to_c()
     d3.q_dim = 64  # head dim 64 is not what the reference computes with (Q_DIM = 128)
     assert lib.ts2_matrix_count(C.byref(d3)) == capi.TS2_ERR_UNSUPPORTED
+    for flag in (0x10, 0x10000, 0x20000):  # MPF_SAMPLE_EMBED_VECTORS, MPF_RNN, MPF_RNN_CROSS change the compute path
+        d4, k4 = spec.to_c()
+        d4.flags = flag
+        assert lib.ts2_matrix_count(C.byref(d4)) == capi.TS2_ERR_UNSUPPORTED
+    d5, k5 = spec.to_c()
+    d5.flags = 0x800 | 0x4  # MPF_DISABLE_NOISE_LABELS, MPF_USE_DOC_START_TOKEN: data preparation only
+    assert lib.ts2_matrix_count(C.byref(d5)) == 2 + 2 * 8
 
 
 def test_host_batch_matches_reference_span_rule():

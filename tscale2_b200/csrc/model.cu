@@ -388,6 +388,11 @@ int validate(const ts2_model_descr *d)
         return fail(TS2_ERR_INVALID_ARG, "bad head / ffn / layer counts");
     if (d->label_count <= 0 || d->output_token_count <= 0 || d->output_token_count % 32)
         return fail(TS2_ERR_INVALID_ARG, "label_count must be positive and output_token_count a positive multiple of 32");
+    // flags that change the compute path in ways this backend does not implement (model_dim.h:40,51-52): per-node
+    // sample vectors added to the embedding (MPF_SAMPLE_EMBED_VECTORS, cpu_transformer.cpp:93-99), the RNN variants
+    if (d->flags & (0x10ull | 0x10000ull | 0x20000ull))
+        return fail(TS2_ERR_UNSUPPORTED, "model flags 0x%llx: MPF_SAMPLE_EMBED_VECTORS / MPF_RNN / MPF_RNN_CROSS are not supported",
+                    (unsigned long long)d->flags);
     if (d->precision != TS2_PREC_FP8 && d->precision != TS2_PREC_F16 && d->precision != TS2_PREC_INT8)
         return fail(TS2_ERR_UNSUPPORTED, "precision must be TS2_PREC_FP8, TS2_PREC_F16 or TS2_PREC_INT8");
     for (int l = 0; l < d->layer_count; ++l) {
