@@ -1842,6 +1842,9 @@ void ts2_destroy(ts2_model *m)
         cudaFree(p);
     if (m->pinned)
         cudaFreeHost(m->pinned);
+    for (cudaEvent_t e : m->batch.slot_ev)
+        if (e)
+            cudaEventDestroy(e);
     if (m->ev_start)
         cudaEventDestroy(m->ev_start);
     if (m->ev_stop)
