@@ -10,7 +10,10 @@ the results back.  Checked:
     gradient's own magnitude, so it shows every flip: 0.25 (the distance between two e4m3 runs that differ in rounding
     only; measured 0.07 - 0.11);
   * the ranks stay bit-identical over further steps, and the loss stays finite;
-  * a capacity too small for the rows a rank would receive is refused on every rank with TS2_ERR_TOO_LARGE."""
+  * a capacity too small for the rows a rank would receive is refused on every rank with TS2_ERR_TOO_LARGE.
+Switches for a run by hand (any number of GPUs that divides the expert count): TS2_TEST_EP=0 leaves expert parallel off
+(the plain data-parallel step of the same model), TS2_TEST_QUICK=1 runs the fp16 pipeline only and skips the capacity
+case, TS2_TEST_EXPERTS=n changes the expert count (the capacity case needs at least 4 experts on rank 0)."""
 import os
 import sys
 
