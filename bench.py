@@ -454,9 +454,14 @@ def main():
     else:
         peak = peaks["bf16_tflops_sustained"]
         peak_note = f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_src})"
-    # DRAM traffic per launch is not measured in this run (it needs ncu): null; profiles/ holds small-case captures with
-    # dram__bytes next to the algorithmic bytes.  The algorithmic bytes here are counted by the library at launch time.
+    # DRAM traffic per launch needs ncu, so it is not measured in this run.  For the headline workload it comes from a
+    # small-case capture (profiles/gemm_dram_traffic_one_block_step.md): one block of the same model at the same number
+    # of nodes launches exactly the contractions of one layer pair and of the final layer; 12 x the layer launches + the
+    # final layer's = 97.7 GB over the step's 183 launches = 534.1 MB per launch, next to 544.8 MB of algorithmic bytes
+    # counted by the library (the last lines written are still in L2 when a kernel ends).  Other workloads: null.
     traffic = None
+    if args.workload == "c3_dense12_d768" and args.precision == "fp8" and gemm_n:
+        traffic = 0.980 * gemm_bytes / gemm_n
     by_class = {}
     for name, (c_ms, c_n, c_fl) in gemm_classes.items():
         if c_n:
@@ -470,6 +475,8 @@ def main():
         backward["frac_of_cublaslt_fp8_sustained"] = backward["tflops"] / vendor_fp8["sustained"]
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                "traffic_source": ("small-case ncu capture scaled by the units processed: 0.980 x algorithmic bytes "
+                                   "(profiles/gemm_dram_traffic_one_block_step.md)") if traffic else None,
                 "algorithmic_bytes_per_launch": gemm_bytes / gemm_n if gemm_n else None,
                 "hbm_gbs_algorithmic": gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else None,
                 "hbm_peak_gbs": peaks.get("hbm_gbs"), "kernel": "gemm_kernel (tcgen05)",
