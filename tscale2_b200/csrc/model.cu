@@ -962,7 +962,18 @@ int build_model(ts2_model *m, const ts2_matrix_view *mats, int n_mats, const flo
     M_TRY(dalloc(m, (uint8_t **)&m->nF_fast, (size_t)T * D * fs));
     M_TRY(dalloc(m, &m->nF16, (size_t)T * D));
     // the final layer is processed in chunks of nodes so that its logits stay a few hundred MB
-    m->chunk = std::min(T, std::max(128, (int)((size_t)(1u << 28) / (size_t)m->V) / 128 * 128));
+    {
+        // Memory bound: logits of a chunk <= 512 MB of fp16.  Within it the chunk is sized so that the dX contraction of the
+        // final layer ([chunk][D] from K = V, 128 x 256 tiles) is one full wave of the SMs: its time per wave is set by K,
+        // so a chunk of 41 tile rows x 3 (123 of 148 SMs at dim 768) cost as much as one of 49 x 3.
+        const int by_memory = std::max(128, (int)((size_t)(1u << 28) / (size_t)m->V) / 128 * 128);
+        const int n_tiles = (D + 255) / 256, sms = sm_count(m->device);
+        const int wave_rows = std::max(1, sms / n_tiles) * 128;
+        int chunk = wave_rows;
+        while (chunk + wave_rows <= by_memory * 5 / 4) // whole waves while the buffer stays within 25 % of the bound
+            chunk += wave_rows;
+        m->chunk = std::min(T, chunk);
+    }
     M_TRY(dalloc(m, &m->logits, (size_t)m->chunk * m->V));
     size_t drg_elems = (size_t)T * max_wide, dcat_elems = (size_t)T * max_cat;
     if (has_moe) {
