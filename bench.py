@@ -457,8 +457,8 @@ def main():
     # DRAM traffic per launch needs ncu, so it is not measured in this run.  For the headline workload it comes from a
     # small-case capture (profiles/gemm_dram_traffic_one_block_step.md): one block of the same model at the same number
     # of nodes launches exactly the contractions of one layer pair and of the final layer; 12 x the layer launches + the
-    # final layer's = 97.7 GB over the step's 183 launches = 534.1 MB per launch, next to 544.8 MB of algorithmic bytes
-    # counted by the library (the last lines written are still in L2 when a kernel ends).  Other workloads: null.
+    # final layer's moved 0.980 x the algorithmic bytes the library counted for the same launches (operands once, outputs
+    # once; the last lines written are still in L2 when a kernel ends).  Other workloads: null.
     traffic = None
     if args.workload == "c3_dense12_d768" and args.precision == "fp8" and gemm_n:
         traffic = 0.980 * gemm_bytes / gemm_n
